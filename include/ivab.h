@@ -1,0 +1,172 @@
+/*
+ * ivab.h -- C ABI of libivab.so: paged-KV append, gather and single-query decode
+ * attention for NVIDIA B200 (sm_100a).
+ *
+ * The reference project is pure Python; the operators this library replaces are Python
+ * functions, cited per entry point below (paths inside the reference project).  A binding
+ * needs only ctypes / cffi: every argument is a plain pointer, integer or float.
+ *
+ * Conventions
+ *   - All data pointers are CUDA device pointers owned by the caller.  The library
+ *     allocates no device memory; scratch space is passed in as `workspace`.
+ *   - Strides are in ELEMENTS of `dtype`.  The innermost (head_dim) axis is contiguous.
+ *   - `stream` is a cudaStream_t (NULL = legacy default stream).  Calls only enqueue work.
+ *   - Return value: IVAB_OK (0) or a negative IVAB_ERR_* code; ivab_last_error() then
+ *     returns a message for the calling thread.  Nothing throws or aborts.
+ *   - Index data (slot ids, page ids, context lengths) lives on the device, so it cannot
+ *     be validated before launch.  Kernels check every index, SKIP (or clamp) a bad access
+ *     instead of faulting, and OR a bit into an int32 status word the caller supplies
+ *     (`status`, may be NULL) or that lives in the decode workspace.
+ *   - Page pool layout: element (head h, page p, offset o, dim d) is at
+ *         pool + h*pool_stride_head + p*pool_stride_page + o*head_dim + d,
+ *     i.e. each (head, page) block of page_size*head_dim elements is contiguous.
+ *     The reference cache layout [1, H, num_pages*page_size, D]
+ *     (src/kernels_t/kv_ops_triton.py:105) has pool_stride_page = page_size*D and
+ *     pool_stride_head = num_pages*page_size*D.
+ */
+#ifndef IVAB_H_
+#define IVAB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with -fvisibility=hidden */
+#endif
+
+#define IVAB_OK 0
+#define IVAB_ERR_INVALID (-1)     /* bad argument (null pointer, misaligned, negative size ...) */
+#define IVAB_ERR_UNSUPPORTED (-2) /* shape / dtype combination not compiled in */
+#define IVAB_ERR_CUDA (-3)        /* a CUDA runtime call failed */
+#define IVAB_ERR_WORKSPACE (-4)   /* workspace too small */
+#define IVAB_ERR_DEVICE (-5)      /* device-side status word non-zero */
+
+#define IVAB_F32 0
+#define IVAB_F16 1
+#define IVAB_BF16 2
+
+/* bits of the device-side status word */
+#define IVAB_STATUS_WAIT_TIMEOUT 1       /* a bounded in-kernel wait expired; the CTA unwound */
+#define IVAB_STATUS_BAD_PAGE 2           /* block-table entry outside [0, num_pages) */
+#define IVAB_STATUS_BAD_CTX_LEN 4        /* context length < 0 or beyond the block table */
+#define IVAB_STATUS_BAD_SLOT 8           /* slot / index outside [0, num_slots) */
+#define IVAB_STATUS_WORKSPACE_OVERFLOW 16
+
+/* layouts of ivab_paged_gather's output */
+#define IVAB_OUT_TOKEN_MAJOR 0 /* [total_tokens, H, D]                                  */
+#define IVAB_OUT_HEAD_MAJOR 1  /* sequence s is [H, L_s, D] starting at out_offsets[s]*H*D */
+
+const char* ivab_last_error(void);
+int ivab_version(void);
+
+/*
+ * out[b,h,n,:] = cache[b,h,indices[n],:]
+ * Replaces kv_gather_kernel + KVOpsTriton.forward(operation="gather")
+ * (src/kernels_t/kv_ops_triton.py:18-40,111-123).  `indices` is int64[N], shared by all
+ * batch rows and heads.  out_dtype == dtype, or IVAB_F32 to reproduce the reference's
+ * always-fp32 output (kv_ops_triton.py:112).  head_dim*sizeof(dtype) must be a multiple
+ * of 16 bytes and all base pointers / strides 16-byte aligned.
+ */
+int ivab_kv_gather(const void* cache, const int64_t* indices, void* out, int dtype, int out_dtype,
+                   int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
+                   int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
+                   int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
+                   int32_t* status, void* stream);
+
+/*
+ * cache[b,h,indices[n],:] = values[b,h,n,:]   (IN PLACE)
+ * Replaces kv_scatter_kernel (src/kernels_t/kv_ops_triton.py:43-65).  The reference clones
+ * the whole cache first (kv_ops_triton.py:129); a caller that wants that behaviour clones
+ * before calling.  Duplicate indices race, as they do in the reference.
+ */
+int ivab_kv_scatter(void* cache, const int64_t* indices, const void* values, int dtype,
+                    int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
+                    int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
+                    int64_t values_stride_b, int64_t values_stride_h, int64_t values_stride_n,
+                    int32_t* status, void* stream);
+
+/*
+ * Block-table append: K and V of T new tokens written to their slots in one launch.
+ *   pool[h, slot_mapping[t]] = new[t, h, :]          slot = page*page_size + offset
+ * The slot mapping is the `indices` vector of the reference scatter
+ * (src/kernels_t/kv_ops_triton.py:58) read on the flattened slot axis; it also replaces the
+ * concat-append of AttentionTorch.forward (src/core/attention.py:61-63).
+ */
+int ivab_paged_append(const void* k_new, const void* v_new, int64_t new_stride_t, int64_t new_stride_h,
+                      const int64_t* slot_mapping, void* k_pool, void* v_pool,
+                      int64_t pool_stride_head, int64_t pool_stride_page, int dtype,
+                      int64_t n_tokens, int64_t heads, int64_t head_dim, int64_t page_size,
+                      int64_t num_pages, int32_t* status, void* stream);
+
+/*
+ * Paged gather of every sequence to contiguous storage, through the block table:
+ *   out[token out_offsets[s]+j, h, :] = pool[h, block_table[s][j/page_size], j%page_size, :]
+ * for j < ctx_len[s].  Same semantics as the reference gather
+ * (src/kernels_t/kv_ops_triton.py:33-40) called with each sequence's slot list.
+ * out_offsets is int64[B+1] (cumulative lengths, in tokens).
+ */
+int ivab_paged_gather(const void* pool, int64_t pool_stride_head, int64_t pool_stride_page,
+                      const int32_t* block_table, int64_t block_table_stride, const int32_t* ctx_len,
+                      const int64_t* out_offsets, void* out, int out_layout, int dtype,
+                      int64_t batch, int64_t heads, int64_t head_dim, int64_t page_size,
+                      int64_t num_pages, int64_t max_pages_per_seq, int32_t* status, void* stream);
+
+/*
+ * Bytes of scratch ivab_paged_decode_attn needs on the current device for up to `batch`
+ * sequences (plan, split-K partials, status word).
+ */
+int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                size_t* bytes_out);
+
+/*
+ * Single-query decode attention read through a block table:
+ *   out[s,hq,:] = softmax_j( q[s,hq,:] . K[s,kvh(hq),j,:] * scale ) . V[s,kvh(hq),j,:],  j < ctx_len[s]
+ *   lse[s,hq]   = log sum_j exp( q.K_j * scale )                       (natural log; may be NULL)
+ * The math is AttentionTorch.forward lines 77, 99, 102 (src/core/attention.py) for one query
+ * and no mask; it takes the place of the unusable attention_kernel
+ * (src/kernels_t/attention_triton.py:18-71).  kvh(hq) = hq / (q_heads/kv_heads); the group
+ * size must be 1, 2, 4 or 8, head_dim 64 or 128, page_size 16.
+ * Enqueues three kernels (plan, split-K attention, logsumexp merge).  ctx_len[s] == 0
+ * yields zeros and -inf.  `workspace` must be 256-byte aligned and hold
+ * ivab_decode_workspace_bytes(); concurrent calls need distinct workspaces.
+ */
+int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                           const void* k_pool, const void* v_pool,
+                           int64_t pool_stride_head, int64_t pool_stride_page,
+                           const int32_t* block_table, int64_t block_table_stride,
+                           const int32_t* ctx_len,
+                           void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                           int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                           int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Copies the status word of the last ivab_paged_decode_attn call on `workspace` to the host
+ * (synchronises `stream`).  *status_out is a mask of IVAB_STATUS_* bits; returns
+ * IVAB_ERR_DEVICE if it is non-zero.
+ */
+int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream);
+
+/*
+ * Number of kernels of this library launched by the calling process since load
+ * (for benchmark bookkeeping).
+ */
+int64_t ivab_launch_count(void);
+
+/*
+ * Failure-detection self test: one CTA waits on a barrier that nothing will ever complete,
+ * with the given limit; it must give up, set IVAB_STATUS_WAIT_TIMEOUT in *status (device
+ * int32) and return normally.  Demonstrates that an in-kernel wait cannot hang the GPU.
+ */
+int ivab_selftest_bounded_wait(int32_t* status, int64_t limit_ns, void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* IVAB_H_ */

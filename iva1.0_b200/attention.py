@@ -1,0 +1,300 @@
+"""Single-query decode attention through a block table, behind the reference's contracts.
+
+* ``paged_decode_attention`` -- the native operator: q ``[B,H_q,D]``, page pools, block table,
+  context lengths -> ``out [B,H_q,D]`` (+ per-head logsumexp).
+* ``attention(q, k, v, scale, dropout_prob, training)`` -- the signature of ``attention_triton``
+  (src/kernels_t/attention_triton.py:215-223) on ``[B,H,S,D]`` tensors.  The reference kernel
+  behind that signature cannot run; the math implemented here is the one the model really
+  uses, AttentionTorch.forward lines 77, 99, 102 (src/core/attention.py) without masks.
+* ``AttentionB200`` -- an ``nn.Module`` with AttentionTorch's parameters and forward signature
+  (src/core/attention.py:19-45), so ``load_state_dict`` round-trips with the reference module;
+  ``get_attention(config)`` mirrors the reference factory (attention.py:190-194).
+
+Inference only: no dropout, no autograd.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .kv_ops import _pool_strides
+
+__all__ = ["paged_decode_attention", "attention", "AttentionB200", "get_attention", "decode_workspace_bytes",
+           "decode_status"]
+
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def decode_workspace_bytes(batch: int, q_heads: int, kv_heads: int, head_dim: int) -> int:
+    """Scratch bytes one ``paged_decode_attention`` call needs on the current device."""
+    lib = _lib.load_library()
+    n = ctypes.c_size_t(0)
+    _lib.check(lib.ivab_decode_workspace_bytes(batch, q_heads, kv_heads, head_dim, ctypes.byref(n)))
+    return int(n.value)
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """One scratch buffer per (device, stream), grown on demand.  Calls on the same stream are
+    ordered, so they can share it; calls on different streams get different buffers."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def decode_status(workspace: torch.Tensor) -> int:
+    """Synchronise and return the device status bits of the last decode call on ``workspace``
+    (0 = fine)."""
+    lib = _lib.load_library()
+    v = ctypes.c_int32(0)
+    with torch.cuda.device(workspace.device):
+        rc = lib.ivab_decode_status(workspace.data_ptr(), ctypes.byref(v), _lib.stream_ptr(workspace.device))
+    if rc not in (_lib.OK, _lib.ERR_DEVICE):
+        _lib.check(rc)
+    return int(v.value)
+
+
+def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                           block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
+                           scale: Optional[float] = None, *, out: Optional[torch.Tensor] = None,
+                           lse: Optional[torch.Tensor] = None, return_lse: bool = False,
+                           workspace: Optional[torch.Tensor] = None, check: bool = False):
+    """``out[s,h] = softmax(q[s,h] . K_s^T * scale) . V_s`` over the ``ctx_len[s]`` cached tokens of
+    sequence ``s``, K/V read in place from the page pool through ``block_table``.
+
+    q ``[B,H_q,D]``; pools ``[1,H_kv,num_pages*page_size,D]`` (or ``[num_pages,H_kv,page_size,D]``);
+    ``block_table`` int32 ``[B,max_pages]``; ``ctx_len`` int32 ``[B]``.  ``H_q/H_kv`` in {1,2,4,8}.
+    Returns ``out`` (dtype of q) or ``(out, lse)`` with ``lse`` fp32 ``[B,H_q]`` (natural log).
+    ``check=True`` synchronises and raises if the kernels flagged a bad page id / length or a
+    timed-out wait.
+    """
+    _lib.require_cuda(q, k_pool, v_pool, block_table, ctx_len)
+    Hkv, num_pages, sh, sp = _pool_strides(k_pool, page_size)
+    if _pool_strides(v_pool, page_size) != (Hkv, num_pages, sh, sp) or v_pool.dtype != k_pool.dtype:
+        raise ValueError("k_pool and v_pool must have the same shape, strides and dtype")
+    if k_pool.dtype != q.dtype or k_pool.shape[-1] != q.shape[-1]:
+        raise ValueError("q and the pools must share dtype and head_dim")
+    return _decode(q, k_pool, v_pool, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
+                   out, lse, return_lse, workspace, check)
+
+
+def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
+            out, lse, return_lse, workspace, check):
+    """Argument checks and the library call; ``k_base`` / ``v_base`` only supply base pointers, the
+    pool geometry is given by ``Hkv, num_pages, sh, sp`` (element strides of head and page)."""
+    if q.requires_grad:
+        raise RuntimeError("paged_decode_attention is inference-only")
+    lib = _lib.load_library()
+    dev = q.device
+    if q.dim() != 3:
+        raise ValueError("q must be [batch, q_heads, head_dim]")
+    B, Hq, D = q.shape
+    if Hq % Hkv:
+        raise ValueError("q_heads must be a multiple of kv_heads")
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    if block_table.dtype != torch.int32 or block_table.dim() != 2 or block_table.stride(1) != 1:
+        block_table = block_table.to(torch.int32).reshape(B, -1).contiguous()
+    if ctx_len.dtype != torch.int32 or not ctx_len.is_contiguous():
+        ctx_len = ctx_len.to(torch.int32).contiguous()
+    if block_table.shape[0] != B or ctx_len.numel() != B:
+        raise ValueError("block_table / ctx_len batch size does not match q")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty(B, Hq, D, device=dev, dtype=q.dtype)
+    elif out.shape != (B, Hq, D) or out.dtype != q.dtype or out.stride(-1) != 1:
+        raise ValueError("out must be [B,H_q,D] in q's dtype with a contiguous last axis")
+    if lse is None and return_lse:
+        lse = torch.empty(B, Hq, device=dev, dtype=torch.float32)
+    if lse is not None and (lse.shape != (B, Hq) or lse.dtype != torch.float32 or not lse.is_contiguous()):
+        raise ValueError("lse must be a contiguous fp32 [B,H_q] tensor")
+    with torch.cuda.device(dev):
+        stream = _lib.stream_ptr(dev)
+        if workspace is None:
+            workspace = _workspace(dev, stream, decode_workspace_bytes(B, Hq, Hkv, D))
+        _lib.check(lib.ivab_paged_decode_attn(
+            q.data_ptr(), q.stride(0), q.stride(1), k_base.data_ptr(), v_base.data_ptr(), sh, sp,
+            block_table.data_ptr(), block_table.stride(0), ctx_len.data_ptr(),
+            out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr() if lse is not None else None,
+            _lib.dtype_code(q.dtype), B, Hq, Hkv, D, page_size, num_pages, block_table.shape[1],
+            float(scale), workspace.data_ptr(), workspace.numel(), stream))
+    if check:
+        st = decode_status(workspace)
+        if st:
+            raise _lib.IvabError(_lib.ERR_DEVICE, _lib.status_message(st))
+    return (out, lse) if (return_lse or lse is not None) else out
+
+
+_PAGE = 16
+
+
+def _dense_as_pool(k: torch.Tensor, v: torch.Tensor):
+    """View dense ``[B,H,L,D]`` K/V as a page pool plus a block table.
+
+    With ``L`` a multiple of 16, rows ``16p..16p+15`` of (batch b, head h) are already one
+    contiguous page; numbering pages ``b*H*L/16 + p`` with a head stride of ``L*D`` addresses
+    them without moving a byte.  Other lengths are zero-padded to the next multiple first."""
+    B, H, L, D = k.shape
+    Lp = (L + _PAGE - 1) // _PAGE * _PAGE
+    if Lp != L or not k.is_contiguous() or not v.is_contiguous():
+        kp = k.new_zeros(B, H, Lp, D)
+        vp = v.new_zeros(B, H, Lp, D)
+        kp[:, :, :L] = k
+        vp[:, :, :L] = v
+        k, v = kp, vp
+    pages_per_row = Lp // _PAGE
+    n_pages = B * H * pages_per_row
+    bt = (torch.arange(B, device=k.device, dtype=torch.int32).view(B, 1) * (H * pages_per_row)
+          + torch.arange(pages_per_row, device=k.device, dtype=torch.int32).view(1, -1))
+    # pool geometry: head stride Lp*D, page stride 16*D (elements)
+    return k, v, bt.contiguous(), n_pages, Lp * D, _PAGE * D
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, dropout_prob: float = 0.0,
+              training: bool = True, *, ctx_len: Optional[torch.Tensor] = None,
+              return_lse: bool = False):
+    """``softmax(q k^T * scale) v`` on ``[B,H,S,D]`` queries against ``[B,H,L,D]`` keys/values.
+
+    Signature of ``attention_triton`` (src/kernels_t/attention_triton.py:215-223).  Every query
+    row sees all ``L`` keys (the reference module's behaviour with ``causal=False``,
+    src/core/attention.py:77-102); pass ``ctx_len`` (int32 ``[B,S]`` or ``[B]``) to limit the keys
+    each query sees, e.g. ``prior + i + 1`` for causal prefill.  Dropout is not implemented:
+    a non-zero ``dropout_prob`` with ``training=True`` raises, as does ``requires_grad``.
+    """
+    _lib.require_cuda(q, k, v)
+    if q.dim() != 4 or k.dim() != 4 or k.shape != v.shape:
+        raise ValueError("q, k, v must be [batch, heads, seq, head_dim]")
+    if dropout_prob != 0.0 and training:
+        raise NotImplementedError("attention dropout is not implemented (inference-only backend)")
+    if q.requires_grad or k.requires_grad or v.requires_grad:
+        raise RuntimeError("attention is inference-only: call it under torch.no_grad() on detached tensors")
+    B, Hq, S, D = q.shape
+    Bk, Hkv, L, Dk = k.shape
+    if Bk != B or Dk != D or Hq % Hkv:
+        raise ValueError("q and k/v shapes do not match")
+    kd, vd, bt, n_pages, sh, sp = _dense_as_pool(k.to(q.dtype), v.to(q.dtype))
+    # one pseudo-sequence per (batch row, query position), all sharing the row's block table
+    q2 = q.permute(0, 2, 1, 3).reshape(B * S, Hq, D)
+    bt2 = bt.repeat_interleave(S, dim=0) if S > 1 else bt
+    if ctx_len is None:
+        cl = torch.full((B * S,), L, dtype=torch.int32, device=q.device)
+    else:
+        cl = ctx_len.to(device=q.device, dtype=torch.int32)
+        cl = (cl.view(B, 1).expand(B, S) if cl.numel() == B else cl.reshape(B, S)).reshape(-1).contiguous()
+    res = _decode(q2, kd, vd, Hkv, n_pages, sh, sp, bt2, cl, _PAGE, scale, None, None, return_lse, None, False)
+    o2, lse = res if return_lse else (res, None)
+    o = o2.view(B, S, Hq, D).permute(0, 2, 1, 3)
+    if return_lse:
+        return o, lse.view(B, S, Hq).permute(0, 2, 1)
+    return o
+
+
+class AttentionB200(nn.Module):
+    """Drop-in for the reference attention modules (src/core/attention.py:17-110,151-187).
+
+    Same parameters (bias-free ``q_proj/k_proj/v_proj/o_proj``, ``d_model -> d_model``), same
+    ``forward`` signature and return value ``(output [B,S,d_model], new_kv_cache)``.
+
+    * ``kv_cache`` is a ``PagedKVCache``: the new tokens' K/V are appended to its page pool in
+      place and attention reads the pool through the block table; the same cache object is
+      returned.
+    * ``kv_cache`` is any object with dense ``.k/.v [B,H,L,D]`` (the reference ``KVCache``): the
+      reference's concat semantics are kept (attention.py:61-73) and a new cache object of the
+      same type is returned.
+    * ``kv_cache`` is ``None``: attention over the ``S`` tokens of ``x`` only.
+
+    ``config.causal`` is honoured as "query ``i`` sees the cache and tokens ``0..i``".  (The
+    reference builds ``tril(ones(S, L+S))`` (attention.py:80), which with a cache hides all but
+    the first ``i+1`` *cached* keys; that is not reproduced.  With ``causal=False`` the results
+    equal the reference's.)  Masks, sliding windows, sink configs and RoPE state are not part of
+    the decode path and raise ``NotImplementedError`` when given.
+    """
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.d_model = config.d_model
+        self.n_heads = config.n_heads
+        self.head_dim = config.d_model // config.n_heads
+        self.dropout = getattr(config, "dropout", 0.0)
+        self.causal = getattr(config, "causal", True)
+        self.q_proj = nn.Linear(self.d_model, self.d_model, bias=False)
+        self.k_proj = nn.Linear(self.d_model, self.d_model, bias=False)
+        self.v_proj = nn.Linear(self.d_model, self.d_model, bias=False)
+        self.o_proj = nn.Linear(self.d_model, self.d_model, bias=False)
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                kv_cache: Optional[Any] = None, rope_state: Optional[torch.Tensor] = None,
+                sliding_window: Optional[int] = None, sink_cfg: Optional[Dict[str, Any]] = None
+                ) -> Tuple[torch.Tensor, Optional[Any]]:
+        if attention_mask is not None or sliding_window is not None or sink_cfg is not None:
+            raise NotImplementedError("AttentionB200 implements the unmasked decode path only")
+        if self.training and self.dropout:
+            raise NotImplementedError("AttentionB200 is inference-only: call .eval()")
+        from .paged_cache import PagedKVCache
+
+        B, S, dm = x.shape
+        H, D = self.n_heads, self.head_dim
+        q = self.q_proj(x).view(B, S, H, D)
+        k = self.k_proj(x).view(B, S, H, D)
+        v = self.v_proj(x).view(B, S, H, D)
+        # rope_state is accepted and ignored, like the reference's _apply_rope (attention.py:112-113)
+
+        if isinstance(kv_cache, PagedKVCache):
+            prior = kv_cache.append(k, v)                     # [B] lengths before the append (host list)
+            bt, cl = kv_cache.block_table_dev, kv_cache.ctx_len_dev
+            if S == 1:
+                o = paged_decode_attention(q.reshape(B, H, D), kv_cache.k_pool, kv_cache.v_pool, bt, cl,
+                                           kv_cache.page_size, self.scale)
+            else:
+                q2 = q.reshape(B * S, H, D)
+                bt2 = bt.repeat_interleave(S, dim=0)
+                if self.causal:
+                    base = torch.tensor(prior, dtype=torch.int32, device=x.device).view(B, 1)
+                    cl2 = (base + torch.arange(1, S + 1, dtype=torch.int32, device=x.device).view(1, S)).reshape(-1)
+                else:
+                    cl2 = cl.repeat_interleave(S)
+                o = paged_decode_attention(q2, kv_cache.k_pool, kv_cache.v_pool, bt2, cl2.contiguous(),
+                                           kv_cache.page_size, self.scale)
+            new_cache = kv_cache
+            o = o.reshape(B, S, dm)
+        else:
+            kh, vh = k.transpose(1, 2), v.transpose(1, 2)     # [B,H,S,D]
+            prior_len = 0
+            new_cache = None
+            if kv_cache is not None:
+                prior_len = kv_cache.k.size(2)
+                kh = torch.cat([kv_cache.k.to(kh.dtype), kh], dim=2)
+                vh = torch.cat([kv_cache.v.to(vh.dtype), vh], dim=2)
+                new_cache = type(kv_cache)(batch_size=kv_cache.batch_size, n_heads=kv_cache.n_heads,
+                                           head_dim=kv_cache.head_dim, seq_len=kv_cache.seq_len + S,
+                                           device=x.device)
+                new_cache.k, new_cache.v = kh, vh
+            cl = None
+            if self.causal and S > 1:
+                cl = (prior_len + torch.arange(1, S + 1, dtype=torch.int32, device=x.device)).view(1, S).expand(B, S)
+            o = attention(q.transpose(1, 2), kh, vh, self.scale, 0.0, False, ctx_len=cl)
+            o = o.transpose(1, 2).reshape(B, S, dm)
+        return self.o_proj(o), new_cache
+
+
+def get_attention(config) -> nn.Module:
+    """Factory with the reference's name (src/core/attention.py:190-194).  The reference admits
+    ``attn_impl in {"torch", "triton"}`` (src/core/transformer.py:71-72); this backend takes the
+    ``"triton"`` slot and also answers to ``"b200"``.  Any other value raises: this package ships
+    one CUDA implementation and no PyTorch fallback."""
+    impl = getattr(config, "attn_impl", "triton")
+    if impl in ("triton", "b200"):
+        return AttentionB200(config)
+    raise ValueError(f"attn_impl={impl!r}: iva_b200 provides the CUDA backend only ('triton' or 'b200')")

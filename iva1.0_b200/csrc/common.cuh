@@ -1,0 +1,164 @@
+// Shared device/host helpers for the sm_100a paged-KV kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ivab.h"
+
+namespace ivab {
+
+// Bits of the device-side status word (mirrored in include/ivab.h).
+constexpr int kStatusWaitTimeout = IVAB_STATUS_WAIT_TIMEOUT;
+constexpr int kStatusBadPage     = IVAB_STATUS_BAD_PAGE;
+constexpr int kStatusBadCtxLen   = IVAB_STATUS_BAD_CTX_LEN;
+constexpr int kStatusBadSlot     = IVAB_STATUS_BAD_SLOT;
+constexpr int kStatusOverflow    = IVAB_STATUS_WORKSPACE_OVERFLOW;
+
+// Host-side error plumbing (defined in abi.cu).
+int  set_error(int code, const char* fmt, ...);
+int  check_cuda(cudaError_t e, const char* what);
+int  sm_count();                      // SMs of the current device (cached per device)
+size_t dtype_size(int dtype);
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---- mbarrier -------------------------------------------------------------------------------
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_inval(uint32_t bar) {
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+    // Makes the initialised barriers visible to the async (TMA) proxy.
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Every wait in these kernels is bounded: after `limit_ns` without the phase completing the
+// waiter raises the CTA-wide abort flag and returns false; a waiter that sees the flag raised
+// by someone else also returns false.  The caller then unwinds instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint64_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (((++spins) & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// ---- TMA bulk copy (global -> shared, no multicast) --------------------------------------------
+
+__device__ __forceinline__ void tma_bulk_g2s(uint32_t dst_smem, const void* src_global, uint32_t bytes,
+                                             uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst_smem), "l"(src_global), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+// ---- small numeric helpers -------------------------------------------------------------------
+
+__device__ __forceinline__ float warp_max_f32(float v) {
+    // redux.sync on f32 exists on sm_100a; one instruction instead of five shuffles.
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+
+__device__ __forceinline__ float warp_sum_f32(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename T> struct Elt;
+template <> struct Elt<float> {
+    static constexpr int kPerVec = 4;
+    __device__ __forceinline__ static void unpack(const uint4& u, float* f) {
+        f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y);
+        f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+    }
+    __device__ __forceinline__ static float load(const float* p) { return *p; }
+    __device__ __forceinline__ static void store(float* p, float v) { *p = v; }
+};
+template <> struct Elt<__nv_bfloat16> {
+    static constexpr int kPerVec = 8;
+    __device__ __forceinline__ static void unpack(const uint4& u, float* f) {
+        // bf16 is the high half of an fp32: a shift or a mask per element.
+        f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+        f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+        f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+        f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+    }
+    __device__ __forceinline__ static float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    __device__ __forceinline__ static void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+template <> struct Elt<__half> {
+    static constexpr int kPerVec = 8;
+    __device__ __forceinline__ static void unpack(const uint4& u, float* f) {
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 t = __half22float2(h[i]);
+            f[2 * i] = t.x; f[2 * i + 1] = t.y;
+        }
+    }
+    __device__ __forceinline__ static float load(const __half* p) { return __half2float(*p); }
+    __device__ __forceinline__ static void store(__half* p, float v) { *p = __float2half_rn(v); }
+};
+
+#endif  // __CUDACC__
+
+}  // namespace ivab

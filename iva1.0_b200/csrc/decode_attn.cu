@@ -1,0 +1,787 @@
+// Single-query decode attention through a block table (flash-decoding, split-K).
+//
+// Three kernels per call, all on the caller's stream:
+//
+//   1. plan_kernel   (1 CTA)      reads ctx_len on the device, picks one chunk size (in pages) for
+//                                 the whole batch so that the work list has a few items per
+//                                 resident CTA, and writes the list of (sequence, page range)
+//                                 chunks.  No host synchronisation: ragged batches never stall
+//                                 the stream.
+//   2. decode_kernel (persistent) one CTA per resident slot.  Work items are (kv head, chunk)
+//                                 pairs taken from an atomic counter, kv-head-major so that CTAs
+//                                 running at the same time read the same head's slab of the pool.
+//                                 Warp 4 is the producer: it walks the block table and issues one
+//                                 TMA bulk copy per K page and V page (4 KB each for 16x128 bf16)
+//                                 into a ring of shared-memory stages guarded by mbarriers.  The
+//                                 ring runs across item boundaries, so the copy engine never
+//                                 drains between items.  Warps 0-3 consume pages round-robin;
+//                                 each keeps its own online-softmax state (running max, sum and
+//                                 fp32 accumulators) for all query heads of the kv head, so a
+//                                 page is read from HBM once per GQA group.  At the end of an
+//                                 item the four states are merged through shared memory and either
+//                                 written as the final output (one-chunk sequences) or as an
+//                                 fp32 partial (o, m, l).
+//   3. merge_kernel               one warp per (sequence, query head): logsumexp-merge of the
+//                                 partials of multi-chunk sequences.
+//
+// All waits are bounded (see mbar_wait_bounded); a wait that expires raises a CTA-wide abort
+// flag, the status word gets IVAB_STATUS_WAIT_TIMEOUT and every warp unwinds.  Intra-CTA
+// synchronisation uses mbarriers only (no bar.sync), so a warp that unwinds can never leave
+// another one stuck at a barrier.
+#include <atomic>
+
+#include "common.cuh"
+
+namespace ivab {
+
+extern std::atomic<long long> g_launches;
+
+namespace {
+
+constexpr int kPage = 16;            // tokens per page (compile-time for the inner loops)
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kItemRing = 4;
+constexpr int kMaxStages = 32;
+constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
+constexpr int kMinChunkPages = 8;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
+
+// header words at the start of the workspace
+enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrWords = 64 };
+
+struct ChunkDesc {
+    int seq, page_begin, n_pages, chunk_idx, n_chunks, pad0, pad1, pad2;
+};
+static_assert(sizeof(ChunkDesc) == 32, "ChunkDesc is two 16-byte vectors");
+
+struct Workspace {
+    int* header;
+    int* seq_prefix;      // [B+1] exclusive prefix of chunks per sequence
+    ChunkDesc* chunks;    // [cap]
+    float* part_ml;       // [cap*Hkv][G][2]   (running max in log2 units, sum)
+    float* part_o;        // [cap*Hkv][G][D]
+    int cap;
+    int target_chunks;
+};
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int resident_slots() { return sm_count() * 2; }
+
+int target_chunks_for(int64_t kv_heads) {
+    const int64_t items = (int64_t)resident_slots() * kItemsPerSlot;
+    int64_t t = (items + kv_heads - 1) / kv_heads;
+    return (int)(t < 1 ? 1 : t);
+}
+
+size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D, Workspace* ws) {
+    const int target = target_chunks_for(Hkv);
+    const int64_t cap = B + target;
+    size_t off = 0;
+    char* p = static_cast<char*>(base);
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return p ? p + o : nullptr; };
+    int* header = reinterpret_cast<int*>(take(kHdrWords * sizeof(int)));
+    int* prefix = reinterpret_cast<int*>(take((B + 1) * sizeof(int)));
+    ChunkDesc* chunks = reinterpret_cast<ChunkDesc*>(take(cap * sizeof(ChunkDesc)));
+    float* ml = reinterpret_cast<float*>(take((size_t)cap * Hq * 2 * sizeof(float)));
+    float* po = reinterpret_cast<float*>(take((size_t)cap * Hq * D * sizeof(float)));
+    if (ws) { ws->header = header; ws->seq_prefix = prefix; ws->chunks = chunks; ws->part_ml = ml; ws->part_o = po;
+              ws->cap = (int)cap; ws->target_chunks = target; }
+    return off;
+}
+
+// ------------------------------------------------------------------------------------------------
+// 1. plan
+// ------------------------------------------------------------------------------------------------
+
+constexpr int kPlanThreads = 1024;
+
+__device__ int block_inclusive_scan(int v, int* warp_sums, int* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, v, off);
+        if (lane >= off) v += t;
+    }
+    if (lane == 31) warp_sums[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_sums[lane];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            int t = __shfl_up_sync(0xffffffffu, w, off);
+            if (lane >= off) w += t;
+        }
+        warp_sums[lane] = w;
+    }
+    __syncthreads();
+    if (warp > 0) v += warp_sums[warp - 1];
+    *total = warp_sums[31];
+    __syncthreads();
+    return v;
+}
+
+__global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __restrict__ ctx_len, int B, int page_size,
+                                                            int max_pages, int target_chunks, int cap, int Hkv,
+                                                            Workspace ws) {
+    __shared__ int warp_sums[32];
+    __shared__ long long s_total_pages;
+    __shared__ int s_bad;
+    const int tid = threadIdx.x;
+    if (tid == 0) { s_total_pages = 0; s_bad = 0; }
+    __syncthreads();
+
+    // total pages of the batch
+    long long local = 0;
+    for (int s = tid; s < B; s += kPlanThreads) {
+        int L = ctx_len[s];
+        if (L < 0 || (long long)L > (long long)max_pages * page_size) { s_bad = 1; L = L < 0 ? 0 : max_pages * page_size; }
+        local += (L + page_size - 1) / page_size;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
+    if ((tid & 31) == 0 && local) atomicAdd(reinterpret_cast<unsigned long long*>(&s_total_pages), (unsigned long long)local);
+    __syncthreads();
+    const long long total_pages = s_total_pages;
+    long long c64 = (total_pages + target_chunks - 1) / target_chunks;
+    if (c64 < kMinChunkPages) c64 = kMinChunkPages;
+    const int chunk_pages = (int)(c64 > 0x3fffffff ? 0x3fffffff : c64);
+
+    // chunks per sequence and their exclusive prefix
+    int running = 0;
+    for (int base = 0; base < B; base += kPlanThreads) {
+        const int s = base + tid;
+        int n = 0;
+        if (s < B) {
+            int L = ctx_len[s];
+            L = L < 0 ? 0 : (((long long)L > (long long)max_pages * page_size) ? max_pages * page_size : L);
+            const int pages = (L + page_size - 1) / page_size;
+            n = (pages + chunk_pages - 1) / chunk_pages;
+            if (n < 1) n = 1;   // an empty sequence still gets one (empty) item, which writes zeros / -inf
+        }
+        int tile_total;
+        const int incl = block_inclusive_scan(n, warp_sums, &tile_total);
+        if (s < B) ws.seq_prefix[s] = running + incl - n;
+        running += tile_total;
+    }
+    int num_chunks = running;
+    int overflow = 0;
+    if (num_chunks > cap) { overflow = 1; num_chunks = 0; }   // cannot happen when cap = B + target_chunks
+    if (tid == 0) {
+        ws.seq_prefix[B] = running;
+        ws.header[kHdrNumChunks] = num_chunks;
+        ws.header[kHdrChunkPages] = chunk_pages;
+        ws.header[kHdrCounter] = 0;
+        ws.header[kHdrStatus] = (s_bad ? kStatusBadCtxLen : 0) | (overflow ? kStatusOverflow : 0);
+        ws.header[kHdrTotalItems] = num_chunks * Hkv;
+    }
+    __syncthreads();   // seq_prefix writes of this block are visible to this block
+
+    for (int ci = tid; ci < num_chunks; ci += kPlanThreads) {
+        int lo = 0, hi = B - 1;   // largest s with seq_prefix[s] <= ci
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (ws.seq_prefix[mid] <= ci) lo = mid; else hi = mid - 1;
+        }
+        const int s = lo;
+        const int first = ws.seq_prefix[s];
+        const int n = ws.seq_prefix[s + 1] - first;
+        const int j = ci - first;
+        int L = ctx_len[s];
+        L = L < 0 ? 0 : (((long long)L > (long long)max_pages * page_size) ? max_pages * page_size : L);
+        const int pages = (L + page_size - 1) / page_size;
+        const int per = pages / n, rem = pages % n;   // even split: first `rem` chunks get one more page
+        ChunkDesc d;
+        d.seq = s;
+        d.page_begin = j * per + (j < rem ? j : rem);
+        d.n_pages = per + (j < rem ? 1 : 0);
+        d.chunk_idx = j;
+        d.n_chunks = n;
+        d.pad0 = L;
+        d.pad1 = d.pad2 = 0;
+        ws.chunks[ci] = d;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 2. persistent split-K attention
+// ------------------------------------------------------------------------------------------------
+
+struct DecodeParams {
+    const void* q; int64_t q_sb, q_sh;
+    const char* k_pool; const char* v_pool; int64_t pool_sh_bytes, pool_sp_bytes;
+    const int32_t* block_table; int64_t bt_stride;
+    void* out; int64_t out_sb, out_sh; float* lse;
+    int Hq, num_pages;
+    float scale_log2;          // scale * log2(e): scores are kept in base-2 units
+    int stages;
+    uint64_t wait_limit_ns;
+    Workspace ws;
+};
+
+// item ring entry (ints): what the producer tells the consumers about the next work item
+enum { kItSeq = 0, kItHead = 1, kItPages = 2, kItPageBegin = 3, kItChunks = 4, kItIndex = 5, kItPageBase = 6, kItLen = 7 };
+
+template <typename T, int D, int G>
+struct Cfg {
+    static constexpr int EPL = 16 / (int)sizeof(T);   // elements per lane per 16-byte vector
+    static constexpr int LPR = D / EPL;               // lanes covering one row
+    static constexpr int RPI = 32 / LPR;              // rows (tokens) per warp-wide load
+    static constexpr int NV = kPage / RPI;            // warp-wide loads per page
+    static constexpr int DUP = LPR / NV;              // lanes holding the same score after the reduce
+    static constexpr int PAGE_BYTES = kPage * D * (int)sizeof(T);
+    static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+    static_assert(LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0, "row must map onto a power-of-two lane group");
+    static_assert(NV >= 1 && NV <= LPR, "page too large for the transposing reduce");
+    // shared memory carve-up (bytes)
+    static constexpr int OFF_BARS = 0;                                  // 2*kMaxStages + 2*kItemRing + 2 barriers
+    static constexpr int OFF_ABORT = 1024 - 16;
+    static constexpr int OFF_ITEMS = 1024;                              // kItemRing * 8 ints
+    static constexpr int OFF_P = OFF_ITEMS + kItemRing * 32;            // [W][G][kPage] floats
+    static constexpr int OFF_MRG_ML = OFF_P + kConsumerWarps * G * kPage * 4;       // [2][W][G][2]
+    static constexpr int OFF_MRG_O = OFF_MRG_ML + 2 * kConsumerWarps * G * 2 * 4;   // [2][W][G][D]
+    static constexpr int OFF_STAGES = (OFF_MRG_O + 2 * kConsumerWarps * G * D * 4 + 127) / 128 * 128;
+    static constexpr int CTAS_PER_SM = (G >= 8) ? 1 : 2;
+};
+
+// Sum NV per-lane values across the LPR lanes of a row group.  While more than one value is
+// left, each step trades half of them with the partner lane (so the number of shuffles halves
+// every step); the remaining steps are plain butterflies.  Returns the fully reduced value this
+// lane ends up owning; which one that is is given by owned_index().
+template <int NV, int OFF>
+__device__ __forceinline__ float transpose_reduce(float (&v)[NV], int lane) {
+    if constexpr (OFF == 0) {
+        return v[0];
+    } else if constexpr (NV > 1) {
+        float h[NV / 2];
+        const bool upper = (lane & OFF) != 0;
+#pragma unroll
+        for (int i = 0; i < NV / 2; ++i) {
+            const float send = upper ? v[i] : v[i + NV / 2];
+            const float keep = upper ? v[i + NV / 2] : v[i];
+            h[i] = keep + __shfl_xor_sync(0xffffffffu, send, OFF);
+        }
+        return transpose_reduce<NV / 2, OFF / 2>(h, lane);
+    } else {
+        float h[1];
+        h[0] = v[0] + __shfl_xor_sync(0xffffffffu, v[0], OFF);
+        return transpose_reduce<1, OFF / 2>(h, lane);
+    }
+}
+
+template <int NV, int LPR>
+__device__ __forceinline__ int owned_index(int lane) {
+    int idx = 0, nv = NV;
+#pragma unroll
+    for (int off = LPR / 2; off >= 1; off >>= 1) {
+        if (nv > 1) { nv >>= 1; if (lane & off) idx += nv; }
+    }
+    return idx;
+}
+
+template <typename T, int D, int G>
+__global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_kernel(const DecodeParams p) {
+    using C = Cfg<T, D, G>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stages = p.stages;
+
+    const uint32_t bars = smem_u32(smem + C::OFF_BARS);
+    auto bar_full = [&](int s) { return bars + 8u * s; };
+    auto bar_empty = [&](int s) { return bars + 8u * (kMaxStages + s); };
+    auto bar_item_full = [&](int s) { return bars + 8u * (2 * kMaxStages + s); };
+    auto bar_item_empty = [&](int s) { return bars + 8u * (2 * kMaxStages + kItemRing + s); };
+    auto bar_merge = [&](int s) { return bars + 8u * (2 * kMaxStages + 2 * kItemRing + s); };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT);
+    volatile int* items = reinterpret_cast<volatile int*>(smem + C::OFF_ITEMS);
+    unsigned char* stage_base = smem + C::OFF_STAGES;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < stages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int s = 0; s < kItemRing; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), kConsumerWarps); }
+        mbar_init(bar_merge(0), kConsumerWarps);
+        mbar_init(bar_merge(1), kConsumerWarps);
+        fence_mbar_init();
+    }
+    __syncthreads();   // the only CTA-wide barrier: before any warp can have unwound
+
+    const int num_chunks = p.ws.header[kHdrNumChunks];
+    const int total_items = p.ws.header[kHdrTotalItems];
+    int* counter = p.ws.header + kHdrCounter;
+    int* status = p.ws.header + kHdrStatus;
+    const uint64_t limit = p.wait_limit_ns;
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------ producer warp ------------------------------------------
+        int n = 0;          // pages issued by this CTA so far (ring position)
+        int published = 0;  // items published so far
+        bool aborted = false;
+        int item = 0;
+        if (lane == 0) item = atomicAdd(counter, 1);
+        item = __shfl_sync(0xffffffffu, item, 0);
+        for (;;) {
+            const bool done = item >= total_items;
+            int h = 0;
+            ChunkDesc d{};
+            int next_item = 0;
+            if (!done) {
+                h = item / num_chunks;
+                const int ci = item - h * num_chunks;
+                const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + ci);
+                const int4 a = __ldg(src), b = __ldg(src + 1);
+                d.seq = a.x; d.page_begin = a.y; d.n_pages = a.z; d.chunk_idx = a.w; d.n_chunks = b.x; d.pad0 = b.y;
+                if (lane == 0) next_item = atomicAdd(counter, 1);   // fetched early, used after this item
+            }
+            const int slot = published % kItemRing;
+            if (!mbar_wait_bounded(bar_item_empty(slot), ((published / kItemRing) & 1) ^ 1, abort_flag, limit)) {
+                aborted = true; break;
+            }
+            if (lane == 0) {
+                volatile int* it = items + slot * 8;
+                it[kItSeq] = d.seq; it[kItHead] = h; it[kItPages] = done ? -1 : d.n_pages;
+                it[kItPageBegin] = d.page_begin; it[kItChunks] = d.n_chunks; it[kItIndex] = item;
+                it[kItPageBase] = n; it[kItLen] = d.pad0;
+                mbar_arrive(bar_item_full(slot));
+            }
+            ++published;
+            if (done) break;
+
+            const int32_t* bt = p.block_table + (int64_t)d.seq * p.bt_stride + d.page_begin;
+            const char* kbase = p.k_pool + (int64_t)h * p.pool_sh_bytes;
+            const char* vbase = p.v_pool + (int64_t)h * p.pool_sh_bytes;
+            for (int p0 = 0; p0 < d.n_pages && !aborted; p0 += 32) {
+                int mine = 0;
+                if (p0 + lane < d.n_pages) {
+                    mine = __ldg(bt + p0 + lane);
+                    if (mine < 0 || mine >= p.num_pages) { atomicOr(status, kStatusBadPage); mine = 0; }
+                }
+                const int cnt = min(32, d.n_pages - p0);
+                for (int j = 0; j < cnt; ++j) {
+                    const int pid = __shfl_sync(0xffffffffu, mine, j);
+                    const int stage = n % stages;
+                    if (!mbar_wait_bounded(bar_empty(stage), ((n / stages) & 1) ^ 1, abort_flag, limit)) {
+                        aborted = true; break;
+                    }
+                    if (lane == 0) {
+                        const uint32_t dst = smem_u32(stage_base + (size_t)stage * C::STAGE_BYTES);
+                        mbar_arrive_expect_tx(bar_full(stage), C::STAGE_BYTES);
+                        tma_bulk_g2s(dst, kbase + (int64_t)pid * p.pool_sp_bytes, C::PAGE_BYTES, bar_full(stage));
+                        tma_bulk_g2s(dst + C::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes, C::PAGE_BYTES,
+                                     bar_full(stage));
+                    }
+                    ++n;
+                }
+            }
+            if (aborted) break;
+            item = __shfl_sync(0xffffffffu, next_item, 0);
+        }
+        if (aborted) {
+            if (lane == 0) atomicOr(status, kStatusWaitTimeout);
+            // Copies already issued still target this CTA's shared memory: give each of the
+            // most recent `stages` copies a bounded chance to land before the CTA retires.
+            volatile int no_abort = 0;
+            const int first = n > stages ? n - stages : 0;
+            for (int m = first; m < n; ++m)
+                mbar_wait_bounded(bar_full(m % stages), (m / stages) & 1, &no_abort, limit);
+        }
+        return;
+    }
+
+    // ---------------------------------- consumer warps --------------------------------------------
+    const int r = lane / C::LPR;             // which of the RPI rows of a warp-wide load this lane reads
+    const int c = lane % C::LPR;             // which 16-byte vector of the row
+    const int own_iter = owned_index<C::NV, C::LPR>(c);
+    const int own_tok = own_iter * C::RPI + r;                 // token (within a page) whose score this lane owns
+    const bool owner = (c & (C::DUP - 1)) == 0;                // one lane of each duplicate group
+    float* p_smem = reinterpret_cast<float*>(smem + C::OFF_P) + warp * (G * kPage);
+    float* mrg_ml = reinterpret_cast<float*>(smem + C::OFF_MRG_ML);
+    float* mrg_o = reinterpret_cast<float*>(smem + C::OFF_MRG_O);
+    const T* qg = static_cast<const T*>(p.q);
+    T* outg = static_cast<T*>(p.out);
+
+    int consumed = 0;   // items consumed
+    for (;;) {
+        const int slot = consumed % kItemRing;
+        if (!mbar_wait_bounded(bar_item_full(slot), (consumed / kItemRing) & 1, abort_flag, limit)) break;
+        volatile int* it = items + slot * 8;
+        const int seq = it[kItSeq], h = it[kItHead], n_pages = it[kItPages], page_begin = it[kItPageBegin];
+        const int n_chunks = it[kItChunks], item = it[kItIndex], page_base = it[kItPageBase], L = it[kItLen];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_item_empty(slot));
+        if (n_pages < 0) break;   // sentinel: the work list is exhausted
+
+        // query heads of this kv head, pre-scaled, as fp32 in registers
+        float qf[G][C::EPL];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const T* qp = qg + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh + c * C::EPL;
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(qp));
+            Elt<T>::unpack(u, qf[g]);
+#pragma unroll
+            for (int e = 0; e < C::EPL; ++e) qf[g][e] *= p.scale_log2;
+        }
+        float m_run[G], l_run[G], acc[G][C::EPL];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            m_run[g] = -INFINITY; l_run[g] = 0.f;
+#pragma unroll
+            for (int e = 0; e < C::EPL; ++e) acc[g][e] = 0.f;
+        }
+
+        bool ok = true;
+        const int k0 = (warp - (page_base % kConsumerWarps) + kConsumerWarps) % kConsumerWarps;
+        for (int k = k0; k < n_pages; k += kConsumerWarps) {
+            const int n = page_base + k;
+            const int stage = n % stages;
+            if (!mbar_wait_bounded(bar_full(stage), (n / stages) & 1, abort_flag, limit)) { ok = false; break; }
+            const uint4* kp = reinterpret_cast<const uint4*>(stage_base + (size_t)stage * C::STAGE_BYTES) + lane;
+            const uint4* vp = kp + C::PAGE_BYTES / 16;
+            const int n_valid = min(kPage, L - (page_begin + k) * kPage);
+
+            // ---- scores: q . k for the page's 16 tokens, all G heads
+            float sc[G][C::NV];
+#pragma unroll
+            for (int i = 0; i < C::NV; ++i) {
+                const uint4 u = kp[i * 32];
+                float kf[C::EPL];
+                Elt<T>::unpack(u, kf);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int e = 0; e < C::EPL; ++e) a = fmaf(qf[g][e], kf[e], a);
+                    sc[g][i] = a;
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float s = transpose_reduce<C::NV, C::LPR / 2>(sc[g], c);
+                if (own_tok >= n_valid) s = -INFINITY;       // select, not arithmetic: stale slots may hold NaN
+                const float m_page = warp_max_f32(s);
+                if (m_page > m_run[g]) {                     // warp-uniform
+                    const float alpha = fast_exp2(m_run[g] - m_page);
+                    l_run[g] *= alpha;
+#pragma unroll
+                    for (int e = 0; e < C::EPL; ++e) acc[g][e] *= alpha;
+                    m_run[g] = m_page;
+                }
+                const float pr = fast_exp2(s - m_run[g]);
+                if (owner) { l_run[g] += pr; p_smem[g * kPage + own_tok] = pr; }
+            }
+            __syncwarp();
+
+            // ---- weighted sum of V
+            if (n_valid == kPage) {
+#pragma unroll
+                for (int i = 0; i < C::NV; ++i) {
+                    const uint4 u = vp[i * 32];
+                    float vf[C::EPL];
+                    Elt<T>::unpack(u, vf);
+                    const int tok = i * C::RPI + r;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float pg = p_smem[g * kPage + tok];
+#pragma unroll
+                        for (int e = 0; e < C::EPL; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
+                    }
+                }
+            } else {
+                // last page of the sequence: rows past ctx_len are skipped, never multiplied
+#pragma unroll
+                for (int i = 0; i < C::NV; ++i) {
+                    const int tok = i * C::RPI + r;
+                    if (tok < n_valid) {
+                        const uint4 u = vp[i * 32];
+                        float vf[C::EPL];
+                        Elt<T>::unpack(u, vf);
+#pragma unroll
+                        for (int g = 0; g < G; ++g) {
+                            const float pg = p_smem[g * kPage + tok];
+#pragma unroll
+                            for (int e = 0; e < C::EPL; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty(stage));
+        }
+        if (!ok) break;
+
+        // ---- fold the row groups of this warp, then publish the warp's state
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int off = C::LPR; off < 32; off <<= 1) {
+#pragma unroll
+                for (int e = 0; e < C::EPL; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+            }
+            l_run[g] = warp_sum_f32(l_run[g]);
+        }
+        const int mb = consumed & 1;
+        float* my_ml = mrg_ml + ((mb * kConsumerWarps + warp) * G) * 2;
+        float* my_o = mrg_o + ((size_t)(mb * kConsumerWarps + warp) * G) * D;
+        if (r == 0) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+#pragma unroll
+                for (int e = 0; e < C::EPL; ++e) my_o[g * D + c * C::EPL + e] = acc[g][e];
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) { my_ml[g * 2] = m_run[g]; my_ml[g * 2 + 1] = l_run[g]; }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_merge(mb));
+        if (!mbar_wait_bounded(bar_merge(mb), (consumed >> 1) & 1, abort_flag, limit)) break;
+
+        // ---- merge the four warp states; the G*D outputs are spread over the consumer threads
+        const float* all_ml = mrg_ml + (mb * kConsumerWarps * G) * 2;
+        const float* all_o = mrg_o + (size_t)(mb * kConsumerWarps * G) * D;
+        for (int idx = threadIdx.x; idx < G * D; idx += kConsumerWarps * 32) {
+            const int g = idx / D, dd = idx % D;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, all_ml[(w * G + g) * 2]);
+            float Lsum = 0.f, O = 0.f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                const float mw = all_ml[(w * G + g) * 2];
+                const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+                Lsum = fmaf(all_ml[(w * G + g) * 2 + 1], f, Lsum);
+                O = fmaf(all_o[(size_t)(w * G + g) * D + dd], f, O);
+            }
+            const int hq = h * G + g;
+            if (n_chunks == 1) {
+                const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+                Elt<T>::store(outg + (int64_t)seq * p.out_sb + (int64_t)hq * p.out_sh + dd, O * inv);
+                if (dd == 0 && p.lse != nullptr)
+                    p.lse[(int64_t)seq * p.Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * 0.6931471805599453f : -INFINITY;
+            } else {
+                p.ws.part_o[((size_t)item * G + g) * D + dd] = O;
+                if (dd == 0) {
+                    p.ws.part_ml[((size_t)item * G + g) * 2] = M;
+                    p.ws.part_ml[((size_t)item * G + g) * 2 + 1] = Lsum;
+                }
+            }
+        }
+        ++consumed;
+    }
+    if (*abort_flag && threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
+}
+
+// ------------------------------------------------------------------------------------------------
+// 3. logsumexp merge of split-K partials
+// ------------------------------------------------------------------------------------------------
+
+template <typename T>
+__global__ void __launch_bounds__(128) merge_kernel(int B, int Hq, int G, int D, Workspace ws, T* out, int64_t out_sb,
+                                                    int64_t out_sh, float* lse) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= B * Hq) return;
+    const int s = warp / Hq, hq = warp % Hq;
+    const int first = ws.seq_prefix[s];
+    const int n = ws.seq_prefix[s + 1] - first;
+    if (n <= 1) return;   // single-chunk sequences were written by the attention kernel
+    const int num_chunks = ws.header[kHdrNumChunks];
+    if (num_chunks == 0) return;
+    const int h = hq / G, g = hq % G;
+    const size_t item0 = (size_t)h * num_chunks + first;
+
+    float M = -INFINITY;
+    for (int j = lane; j < n; j += 32) M = fmaxf(M, ws.part_ml[((item0 + j) * G + g) * 2]);
+    M = warp_max_f32(M);
+
+    float Lsum = 0.f;
+    float O[8];   // D <= 256
+#pragma unroll
+    for (int i = 0; i < 8; ++i) O[i] = 0.f;
+    for (int j = 0; j < n; ++j) {
+        const float mj = ws.part_ml[((item0 + j) * G + g) * 2];
+        const float lj = ws.part_ml[((item0 + j) * G + g) * 2 + 1];
+        const float f = (mj == -INFINITY) ? 0.f : fast_exp2(mj - M);
+        Lsum = fmaf(lj, f, Lsum);
+        const float* po = ws.part_o + ((item0 + j) * G + g) * D;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int dd = lane + 32 * i;
+            if (dd < D) O[i] = fmaf(po[dd], f, O[i]);
+        }
+    }
+    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int dd = lane + 32 * i;
+        if (dd < D) Elt<T>::store(out + (int64_t)s * out_sb + (int64_t)hq * out_sh + dd, O[i] * inv);
+    }
+    if (lane == 0 && lse != nullptr)
+        lse[(int64_t)s * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * 0.6931471805599453f : -INFINITY;
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+
+template <typename T, int D, int G>
+int launch_decode(const DecodeParams& p0, int B, cudaStream_t st) {
+    using C = Cfg<T, D, G>;
+    DecodeParams p = p0;
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    int max_optin = 0;
+    if (int rc = check_cuda(cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev),
+                            "cudaDeviceGetAttribute")) return rc;
+    int per_sm = 0;
+    if (int rc = check_cuda(cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev),
+                            "cudaDeviceGetAttribute")) return rc;
+    // each resident CTA also pays 1 KB of system-reserved shared memory
+    int budget = per_sm / C::CTAS_PER_SM - 1024;
+    if (budget > max_optin) budget = max_optin;
+    int stages = (budget - C::OFF_STAGES) / C::STAGE_BYTES;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for two stages");
+    p.stages = stages;
+    const size_t smem = (size_t)C::OFF_STAGES + (size_t)stages * C::STAGE_BYTES;
+    auto kern = decode_kernel<T, D, G>;
+    static bool configured[64] = {false};
+    if (dev < 64 && !configured[dev]) {
+        if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin),
+                                "cudaFuncSetAttribute")) return rc;
+        configured[dev] = true;
+    }
+    const int grid = sm_count() * C::CTAS_PER_SM;
+    kern<<<grid, kThreads, smem, st>>>(p);
+    g_launches++;
+    if (int rc = check_cuda(cudaGetLastError(), "decode_kernel launch")) return rc;
+
+    const int warps = B * p.Hq;
+    merge_kernel<T><<<(warps + 3) / 4, 128, 0, st>>>(B, p.Hq, G, D, p.ws, static_cast<T*>(p.out), p.out_sb, p.out_sh, p.lse);
+    g_launches++;
+    return check_cuda(cudaGetLastError(), "merge_kernel launch");
+}
+
+template <typename T, int D>
+int dispatch_group(int G, const DecodeParams& p, int B, cudaStream_t st) {
+    switch (G) {
+        case 1: return launch_decode<T, D, 1>(p, B, st);
+        case 2: return launch_decode<T, D, 2>(p, B, st);
+        case 4: return launch_decode<T, D, 4>(p, B, st);
+        case 8: return launch_decode<T, D, 8>(p, B, st);
+        default: return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: q_heads/kv_heads = %d (supported: 1, 2, 4, 8)", G);
+    }
+}
+
+template <typename T>
+int dispatch_dim(int D, int G, const DecodeParams& p, int B, cudaStream_t st) {
+    switch (D) {
+        case 64: return dispatch_group<T, 64>(G, p, B, st);
+        case 128: return dispatch_group<T, 128>(G, p, B, st);
+        default: return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: head_dim %d (supported: 64, 128)", D);
+    }
+}
+
+__global__ void bounded_wait_selftest_kernel(int* status, uint64_t limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    // Nothing ever arrives on `bar`: the wait must give up after limit_ns.
+    const bool ok = mbar_wait_bounded(smem_u32(&bar), 0, &abort_flag, limit_ns);
+    if (!ok && threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
+}
+
+}  // namespace
+}  // namespace ivab
+
+using namespace ivab;
+
+extern "C" int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                           size_t* bytes_out) {
+    if (!bytes_out) return set_error(IVAB_ERR_INVALID, "ivab_decode_workspace_bytes: null bytes_out");
+    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || q_heads % kv_heads)
+        return set_error(IVAB_ERR_INVALID, "ivab_decode_workspace_bytes: bad sizes");
+    *bytes_out = carve_workspace(nullptr, batch, q_heads, kv_heads, head_dim, nullptr);
+    return IVAB_OK;
+}
+
+extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                      const void* k_pool, const void* v_pool,
+                                      int64_t pool_stride_head, int64_t pool_stride_page,
+                                      const int32_t* block_table, int64_t block_table_stride,
+                                      const int32_t* ctx_len,
+                                      void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                                      int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                      int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
+    const char* fn = "ivab_paged_decode_attn";
+    const size_t esz = dtype_size(dtype);
+    if (esz == 0) return set_error(IVAB_ERR_INVALID, "%s: unknown dtype %d", fn, dtype);
+    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || num_pages < 0 || max_pages_per_seq < 0)
+        return set_error(IVAB_ERR_INVALID, "%s: bad sizes", fn);
+    if (batch == 0) return IVAB_OK;
+    if (page_size != kPage) return set_error(IVAB_ERR_UNSUPPORTED, "%s: page_size %lld (supported: 16)", fn, (long long)page_size);
+    if (!q || !k_pool || !v_pool || !block_table || !ctx_len || !out || !workspace)
+        return set_error(IVAB_ERR_INVALID, "%s: null pointer", fn);
+    auto mis = [](const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) != 0; };
+    if (mis(q, 16) || mis(k_pool, 16) || mis(v_pool, 16) || mis(workspace, 256) || (q_stride_b * esz) % 16 ||
+        (q_stride_h * esz) % 16 || (pool_stride_head * esz) % 16 || (pool_stride_page * esz) % 16)
+        return set_error(IVAB_ERR_INVALID, "%s: q / pools must be 16-byte aligned (workspace 256) with 16-byte strides", fn);
+    if (batch >= (1LL << 30) || max_pages_per_seq * page_size >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: batch or context too large", fn);
+
+    Workspace ws;
+    const size_t need = carve_workspace(workspace, batch, q_heads, kv_heads, head_dim, &ws);
+    if (workspace_bytes < need)
+        return set_error(IVAB_ERR_WORKSPACE, "%s: workspace of %zu bytes, need %zu", fn, workspace_bytes, need);
+    if ((int64_t)ws.cap * kv_heads >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "%s: too many work items", fn);
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, (int)batch, (int)page_size, (int)max_pages_per_seq,
+                                            ws.target_chunks, ws.cap, (int)kv_heads, ws);
+    g_launches++;
+    if (int rc = check_cuda(cudaGetLastError(), "plan_kernel launch")) return rc;
+
+    DecodeParams p{};
+    p.q = q; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
+    p.k_pool = static_cast<const char*>(k_pool); p.v_pool = static_cast<const char*>(v_pool);
+    p.pool_sh_bytes = pool_stride_head * (int64_t)esz; p.pool_sp_bytes = pool_stride_page * (int64_t)esz;
+    p.block_table = block_table; p.bt_stride = block_table_stride;
+    p.out = out; p.out_sb = out_stride_b; p.out_sh = out_stride_h; p.lse = lse;
+    p.Hq = (int)q_heads; p.num_pages = (int)num_pages;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.wait_limit_ns = kWaitLimitNs;
+    p.ws = ws;
+    const int G = (int)(q_heads / kv_heads);
+    switch (dtype) {
+        case IVAB_F32: return dispatch_dim<float>((int)head_dim, G, p, (int)batch, st);
+        case IVAB_F16: return dispatch_dim<__half>((int)head_dim, G, p, (int)batch, st);
+        default: return dispatch_dim<__nv_bfloat16>((int)head_dim, G, p, (int)batch, st);
+    }
+}
+
+extern "C" int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream) {
+    if (!workspace || !status_out) return set_error(IVAB_ERR_INVALID, "ivab_decode_status: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t v = 0;
+    if (int rc = check_cuda(cudaMemcpyAsync(&v, static_cast<const int*>(workspace) + kHdrStatus, sizeof(int),
+                                            cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)")) return rc;
+    if (int rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return rc;
+    *status_out = v;
+    if (v != 0) return set_error(IVAB_ERR_DEVICE, "device status 0x%x", v);
+    return IVAB_OK;
+}
+
+extern "C" int ivab_selftest_bounded_wait(int32_t* status, int64_t limit_ns, void* stream) {
+    if (!status || limit_ns <= 0 || limit_ns > 1000000000ll)
+        return set_error(IVAB_ERR_INVALID, "ivab_selftest_bounded_wait: need status and 0 < limit_ns <= 1e9");
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, (uint64_t)limit_ns);
+    g_launches++;
+    return check_cuda(cudaGetLastError(), "bounded_wait_selftest_kernel launch");
+}

@@ -1,0 +1,336 @@
+// KV append (scatter) and gather: pure vectorised copy kernels.
+//
+// The unit of work is one row of head_dim elements -- 128..512 bytes -- addressed on one side
+// through an index (a slot id / a block-table entry) and on the other side densely.  Every
+// thread moves 16-byte vectors; a CTA issues four independent loads per thread before the
+// first store so that enough bytes are in flight to cover HBM latency.  Consecutive threads
+// touch consecutive 16-byte vectors of the dense side, so dense traffic is fully coalesced and
+// indexed traffic is coalesced per row (and per 4 KB page where slots are consecutive).
+#include <atomic>
+
+#include "common.cuh"
+
+namespace ivab {
+
+extern std::atomic<long long> g_launches;
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+constexpr uint32_t kTile = kThreads * kUnroll;
+
+struct RowCopyParams {
+    const char* src[2];
+    char* dst[2];
+    const int64_t* idx;
+    // indexed side: offset(b,h,id) = b*ix_b + h*ix_h + (id / page_size)*ix_page + (id % page_size)*ix_slot
+    int64_t ix_b, ix_h, ix_page, ix_slot;
+    // dense side: offset(b,h,n) = b*dn_b + h*dn_h + n*dn_n
+    int64_t dn_b, dn_h, dn_n;
+    int64_t id_bound;       // valid ids are [0, id_bound)
+    uint32_t N, H;
+    uint32_t vec_per_row;   // 16-byte vectors per source row
+    uint32_t total;         // N * H * vec_per_row
+    uint32_t page_size;
+    int h_fastest;          // row order on the dense side: 1 = (n, h), 0 = (h, n)
+    int* status;
+};
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void st_stream(void* p, const uint4& v) {
+    __stcs(reinterpret_cast<uint4*>(p), v);
+}
+
+// GATHER: indexed side is the source.  SCATTER: indexed side is the destination.
+// CVT: 0 = raw copy, 1 = fp16 -> fp32, 2 = bf16 -> fp32 (gather only; the reference's gather
+// always returns fp32, src/kernels_t/kv_ops_triton.py:112).
+template <bool GATHER, int CVT>
+__global__ void __launch_bounds__(kThreads) row_copy_kernel(const RowCopyParams p) {
+    const char* __restrict__ src = p.src[blockIdx.z];
+    char* __restrict__ dst = p.dst[blockIdx.z];
+    const int64_t b = blockIdx.y;
+    const uint32_t n_tiles = (p.total + kTile - 1) / kTile;
+
+    for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const uint32_t base = tile * kTile + threadIdx.x;
+        uint4 v[kUnroll];
+        int64_t doff[kUnroll];
+        bool ok[kUnroll];
+#pragma unroll
+        for (int k = 0; k < kUnroll; ++k) {
+            const uint32_t i = base + k * kThreads;
+            ok[k] = i < p.total;
+            doff[k] = 0;
+            v[k] = make_uint4(0, 0, 0, 0);
+            if (ok[k]) {
+                const uint32_t vec = i % p.vec_per_row;
+                const uint32_t r = i / p.vec_per_row;
+                uint32_t h, n;
+                if (p.h_fastest) { h = r % p.H; n = r / p.H; } else { n = r % p.N; h = r / p.N; }
+                const int64_t id = __ldg(p.idx + n);
+                if (id < 0 || id >= p.id_bound) {
+                    // Out-of-range index: record it and skip the row instead of faulting.
+                    if (p.status != nullptr && vec == 0) atomicOr(p.status, kStatusBadSlot);
+                    ok[k] = false;
+                } else {
+                    const uint32_t uid = static_cast<uint32_t>(id);
+                    const int64_t ix = b * p.ix_b + h * p.ix_h + (int64_t)(uid / p.page_size) * p.ix_page +
+                                       (int64_t)(uid % p.page_size) * p.ix_slot;
+                    const int64_t dn = b * p.dn_b + h * p.dn_h + (int64_t)n * p.dn_n;
+                    const int64_t soff = (GATHER ? ix : dn) + (int64_t)vec * 16;
+                    doff[k] = (GATHER ? dn : ix) + (int64_t)vec * (CVT ? 32 : 16);
+                    v[k] = ld_stream(src + soff);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kUnroll; ++k) {
+            if (!ok[k]) continue;
+            if (CVT == 0) {
+                st_stream(dst + doff[k], v[k]);
+            } else {
+                float f[8];
+                if (CVT == 1) Elt<__half>::unpack(v[k], f); else Elt<__nv_bfloat16>::unpack(v[k], f);
+                st_stream(dst + doff[k], *reinterpret_cast<uint4*>(&f[0]));
+                st_stream(dst + doff[k] + 16, *reinterpret_cast<uint4*>(&f[4]));
+            }
+        }
+    }
+}
+
+struct PagedGatherParams {
+    const char* pool;
+    char* out;
+    const int32_t* block_table;
+    const int32_t* ctx_len;
+    const int64_t* out_offsets;
+    int64_t bt_stride;
+    int64_t pool_sh, pool_sp;   // bytes
+    uint32_t H, vec_per_row, page_size;
+    int32_t num_pages, max_pages;
+    int head_major;
+    int* status;
+};
+
+// One CTA per (page index, sequence): copies that page of every head.  Within a head the page
+// is one contiguous block of the pool, so reads are up to 4 KB sequential.
+__global__ void __launch_bounds__(kThreads) paged_gather_kernel(const PagedGatherParams p) {
+    const int s = blockIdx.y;
+    int L = p.ctx_len[s];
+    const int64_t cap = (int64_t)p.max_pages * p.page_size;
+    if (L < 0 || L > cap) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && p.status) atomicOr(p.status, kStatusBadCtxLen);
+        L = L < 0 ? 0 : (int)cap;
+    }
+    const uint32_t n_pages = (L + p.page_size - 1) / p.page_size;
+    const int64_t row_bytes = (int64_t)p.vec_per_row * 16;
+    const int64_t off = p.out_offsets[s];
+
+    for (uint32_t pg = blockIdx.x; pg < n_pages; pg += gridDim.x) {
+        int pid = p.block_table[(int64_t)s * p.bt_stride + pg];
+        if (pid < 0 || pid >= p.num_pages) {
+            if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusBadPage);
+            continue;   // skip the page instead of reading outside the pool
+        }
+        const uint32_t first = pg * p.page_size;
+        const uint32_t n_valid = min(p.page_size, (uint32_t)L - first);
+        const uint32_t per_head = n_valid * p.vec_per_row;
+        const uint32_t total = per_head * p.H;
+        const char* __restrict__ src0 = p.pool + (int64_t)pid * p.pool_sp;
+        for (uint32_t base = threadIdx.x; base < total; base += kTile) {
+            uint4 v[kUnroll];
+            int64_t doff[kUnroll];
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                const uint32_t j = base + k * kThreads;
+                if (j < total) {
+                    const uint32_t h = j / per_head;
+                    const uint32_t rem = j - h * per_head;
+                    v[k] = ld_stream(src0 + (int64_t)h * p.pool_sh + (int64_t)rem * 16);
+                    if (p.head_major) {
+                        doff[k] = (off * p.H + (int64_t)h * L + first) * row_bytes + (int64_t)rem * 16;
+                    } else {
+                        const uint32_t tok = rem / p.vec_per_row;
+                        const uint32_t vec = rem - tok * p.vec_per_row;
+                        doff[k] = ((off + first + tok) * p.H + h) * row_bytes + (int64_t)vec * 16;
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                const uint32_t j = base + k * kThreads;
+                if (j < total) st_stream(p.out + doff[k], v[k]);
+            }
+        }
+    }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int launch_row_copy(bool gather, int cvt, const RowCopyParams& p, int64_t batch, int n_tensors, cudaStream_t st) {
+    if (p.total == 0 || batch == 0) return IVAB_OK;
+    const uint32_t n_tiles = (p.total + kTile - 1) / kTile;
+    const uint32_t max_x = (uint32_t)sm_count() * 16u;
+    dim3 grid(n_tiles < max_x ? n_tiles : max_x, (unsigned)batch, (unsigned)n_tensors);
+    if (gather) {
+        if (cvt == 0) row_copy_kernel<true, 0><<<grid, kThreads, 0, st>>>(p);
+        else if (cvt == 1) row_copy_kernel<true, 1><<<grid, kThreads, 0, st>>>(p);
+        else row_copy_kernel<true, 2><<<grid, kThreads, 0, st>>>(p);
+    } else {
+        row_copy_kernel<false, 0><<<grid, kThreads, 0, st>>>(p);
+    }
+    g_launches++;
+    return check_cuda(cudaGetLastError(), "row_copy_kernel launch");
+}
+
+int common_checks(const char* fn, int dtype, int64_t head_dim, size_t* esz) {
+    *esz = dtype_size(dtype);
+    if (*esz == 0) return set_error(IVAB_ERR_INVALID, "%s: unknown dtype %d", fn, dtype);
+    if (head_dim <= 0 || (head_dim * (int64_t)*esz) % 16 != 0)
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: head_dim*sizeof(dtype) = %lld bytes is not a multiple of 16",
+                         fn, (long long)(head_dim * (int64_t)*esz));
+    return IVAB_OK;
+}
+
+}  // namespace
+}  // namespace ivab
+
+using namespace ivab;
+
+extern "C" int ivab_kv_gather(const void* cache, const int64_t* indices, void* out, int dtype, int out_dtype,
+                              int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
+                              int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
+                              int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
+                              int32_t* status, void* stream) {
+    size_t esz;
+    if (int rc = common_checks("ivab_kv_gather", dtype, head_dim, &esz)) return rc;
+    if (batch < 0 || heads < 0 || seq_len < 0 || n_indices < 0)
+        return set_error(IVAB_ERR_INVALID, "ivab_kv_gather: negative size");
+    if (batch == 0 || heads == 0 || n_indices == 0) return IVAB_OK;
+    if (!cache || !indices || !out) return set_error(IVAB_ERR_INVALID, "ivab_kv_gather: null pointer");
+    int cvt = 0;
+    size_t osz = esz;
+    if (out_dtype != dtype) {
+        if (out_dtype != IVAB_F32 || dtype == IVAB_F32)
+            return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_gather: out_dtype must equal dtype or be fp32");
+        cvt = dtype == IVAB_F16 ? 1 : 2;
+        osz = 4;
+    }
+    if (!aligned16(cache) || !aligned16(out) || (cache_stride_b * esz) % 16 || (cache_stride_h * esz) % 16 ||
+        (cache_stride_s * esz) % 16 || (out_stride_b * osz) % 16 || (out_stride_h * osz) % 16 ||
+        (out_stride_n * osz) % 16)
+        return set_error(IVAB_ERR_INVALID, "ivab_kv_gather: pointers and strides must be 16-byte aligned");
+    if (batch > 65535) return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_gather: batch > 65535");
+    const int64_t vpr = head_dim * (int64_t)esz / 16;
+    const int64_t total = n_indices * heads * vpr;
+    if (total >= (1LL << 32) - 4096 || seq_len >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_gather: more than 2^32 vectors per batch row; split the call");
+    RowCopyParams p{};
+    p.src[0] = static_cast<const char*>(cache);
+    p.dst[0] = static_cast<char*>(out);
+    p.idx = indices;
+    p.ix_b = cache_stride_b * esz; p.ix_h = cache_stride_h * esz; p.ix_page = cache_stride_s * esz; p.ix_slot = 0;
+    p.dn_b = out_stride_b * osz; p.dn_h = out_stride_h * osz; p.dn_n = out_stride_n * osz;
+    p.id_bound = seq_len; p.N = (uint32_t)n_indices; p.H = (uint32_t)heads; p.vec_per_row = (uint32_t)vpr;
+    p.total = (uint32_t)total; p.page_size = 1; p.h_fastest = out_stride_h < out_stride_n; p.status = status;
+    return launch_row_copy(true, cvt, p, batch, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ivab_kv_scatter(void* cache, const int64_t* indices, const void* values, int dtype,
+                               int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
+                               int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
+                               int64_t values_stride_b, int64_t values_stride_h, int64_t values_stride_n,
+                               int32_t* status, void* stream) {
+    size_t esz;
+    if (int rc = common_checks("ivab_kv_scatter", dtype, head_dim, &esz)) return rc;
+    if (batch < 0 || heads < 0 || seq_len < 0 || n_indices < 0)
+        return set_error(IVAB_ERR_INVALID, "ivab_kv_scatter: negative size");
+    if (batch == 0 || heads == 0 || n_indices == 0) return IVAB_OK;
+    if (!cache || !indices || !values) return set_error(IVAB_ERR_INVALID, "ivab_kv_scatter: null pointer");
+    if (!aligned16(cache) || !aligned16(values) || (cache_stride_b * esz) % 16 || (cache_stride_h * esz) % 16 ||
+        (cache_stride_s * esz) % 16 || (values_stride_b * esz) % 16 || (values_stride_h * esz) % 16 ||
+        (values_stride_n * esz) % 16)
+        return set_error(IVAB_ERR_INVALID, "ivab_kv_scatter: pointers and strides must be 16-byte aligned");
+    if (batch > 65535) return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_scatter: batch > 65535");
+    const int64_t vpr = head_dim * (int64_t)esz / 16;
+    const int64_t total = n_indices * heads * vpr;
+    if (total >= (1LL << 32) - 4096 || seq_len >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_scatter: more than 2^32 vectors per batch row; split the call");
+    RowCopyParams p{};
+    p.src[0] = static_cast<const char*>(values);
+    p.dst[0] = static_cast<char*>(cache);
+    p.idx = indices;
+    p.ix_b = cache_stride_b * esz; p.ix_h = cache_stride_h * esz; p.ix_page = cache_stride_s * esz; p.ix_slot = 0;
+    p.dn_b = values_stride_b * esz; p.dn_h = values_stride_h * esz; p.dn_n = values_stride_n * esz;
+    p.id_bound = seq_len; p.N = (uint32_t)n_indices; p.H = (uint32_t)heads; p.vec_per_row = (uint32_t)vpr;
+    p.total = (uint32_t)total; p.page_size = 1; p.h_fastest = values_stride_h < values_stride_n; p.status = status;
+    return launch_row_copy(false, 0, p, batch, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ivab_paged_append(const void* k_new, const void* v_new, int64_t new_stride_t, int64_t new_stride_h,
+                                 const int64_t* slot_mapping, void* k_pool, void* v_pool,
+                                 int64_t pool_stride_head, int64_t pool_stride_page, int dtype,
+                                 int64_t n_tokens, int64_t heads, int64_t head_dim, int64_t page_size,
+                                 int64_t num_pages, int32_t* status, void* stream) {
+    size_t esz;
+    if (int rc = common_checks("ivab_paged_append", dtype, head_dim, &esz)) return rc;
+    if (n_tokens < 0 || heads < 0 || page_size <= 0 || num_pages < 0)
+        return set_error(IVAB_ERR_INVALID, "ivab_paged_append: bad size");
+    if (n_tokens == 0 || heads == 0) return IVAB_OK;
+    if (!k_new || !v_new || !slot_mapping || !k_pool || !v_pool)
+        return set_error(IVAB_ERR_INVALID, "ivab_paged_append: null pointer");
+    if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_pool) || !aligned16(v_pool) ||
+        (new_stride_t * esz) % 16 || (new_stride_h * esz) % 16 || (pool_stride_head * esz) % 16 ||
+        (pool_stride_page * esz) % 16)
+        return set_error(IVAB_ERR_INVALID, "ivab_paged_append: pointers and strides must be 16-byte aligned");
+    const int64_t vpr = head_dim * (int64_t)esz / 16;
+    const int64_t total = n_tokens * heads * vpr;
+    if (total >= (1LL << 32) - 4096 || num_pages * page_size >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_paged_append: more than 2^32 vectors; split the call");
+    RowCopyParams p{};
+    p.src[0] = static_cast<const char*>(k_new); p.src[1] = static_cast<const char*>(v_new);
+    p.dst[0] = static_cast<char*>(k_pool); p.dst[1] = static_cast<char*>(v_pool);
+    p.idx = slot_mapping;
+    p.ix_b = 0; p.ix_h = pool_stride_head * esz; p.ix_page = pool_stride_page * esz; p.ix_slot = head_dim * esz;
+    p.dn_b = 0; p.dn_h = new_stride_h * esz; p.dn_n = new_stride_t * esz;
+    p.id_bound = num_pages * page_size; p.N = (uint32_t)n_tokens; p.H = (uint32_t)heads;
+    p.vec_per_row = (uint32_t)vpr; p.total = (uint32_t)total; p.page_size = (uint32_t)page_size;
+    p.h_fastest = new_stride_h < new_stride_t; p.status = status;
+    return launch_row_copy(false, 0, p, 1, 2, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ivab_paged_gather(const void* pool, int64_t pool_stride_head, int64_t pool_stride_page,
+                                 const int32_t* block_table, int64_t block_table_stride, const int32_t* ctx_len,
+                                 const int64_t* out_offsets, void* out, int out_layout, int dtype,
+                                 int64_t batch, int64_t heads, int64_t head_dim, int64_t page_size,
+                                 int64_t num_pages, int64_t max_pages_per_seq, int32_t* status, void* stream) {
+    size_t esz;
+    if (int rc = common_checks("ivab_paged_gather", dtype, head_dim, &esz)) return rc;
+    if (batch < 0 || heads < 0 || page_size <= 0 || num_pages < 0 || max_pages_per_seq < 0)
+        return set_error(IVAB_ERR_INVALID, "ivab_paged_gather: bad size");
+    if (batch == 0 || heads == 0 || max_pages_per_seq == 0) return IVAB_OK;
+    if (!pool || !block_table || !ctx_len || !out_offsets || !out)
+        return set_error(IVAB_ERR_INVALID, "ivab_paged_gather: null pointer");
+    if (out_layout != IVAB_OUT_TOKEN_MAJOR && out_layout != IVAB_OUT_HEAD_MAJOR)
+        return set_error(IVAB_ERR_INVALID, "ivab_paged_gather: unknown out_layout %d", out_layout);
+    if (!aligned16(pool) || !aligned16(out) || (pool_stride_head * esz) % 16 || (pool_stride_page * esz) % 16)
+        return set_error(IVAB_ERR_INVALID, "ivab_paged_gather: pointers and strides must be 16-byte aligned");
+    if (batch > 65535) return set_error(IVAB_ERR_UNSUPPORTED, "ivab_paged_gather: batch > 65535; split the call");
+    if (page_size * heads * head_dim * (int64_t)esz / 16 >= (1LL << 31) || max_pages_per_seq * page_size >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_paged_gather: page too large");
+    PagedGatherParams p{};
+    p.pool = static_cast<const char*>(pool); p.out = static_cast<char*>(out);
+    p.block_table = block_table; p.ctx_len = ctx_len; p.out_offsets = out_offsets;
+    p.bt_stride = block_table_stride; p.pool_sh = pool_stride_head * esz; p.pool_sp = pool_stride_page * esz;
+    p.H = (uint32_t)heads; p.vec_per_row = (uint32_t)(head_dim * esz / 16); p.page_size = (uint32_t)page_size;
+    p.num_pages = (int32_t)num_pages; p.max_pages = (int32_t)max_pages_per_seq;
+    p.head_major = out_layout == IVAB_OUT_HEAD_MAJOR; p.status = status;
+    const int64_t gx = max_pages_per_seq < 65535 * 32 ? max_pages_per_seq : 65535 * 32;
+    dim3 grid((unsigned)gx, (unsigned)batch, 1);
+    paged_gather_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    g_launches++;
+    return check_cuda(cudaGetLastError(), "paged_gather_kernel launch");
+}

@@ -1,0 +1,219 @@
+"""A paged KV cache that duck-types the reference's dense ``KVCache``.
+
+The reference cache (src/core/rope_kv.py:71-137) is two dense ``[B,H,S,D]`` tensors that are
+re-concatenated on every decode step (src/core/attention.py:61-63) and re-allocated on every
+``resize``.  ``PagedKVCache`` keeps the same constructor keywords, attributes and methods, but
+stores K and V in a pool of fixed-size pages addressed through a per-sequence block table, so
+appending a token writes one row and nothing is ever copied.
+
+Host side (Python): the free list, the block table and the per-sequence lengths -- the same
+bookkeeping a serving engine keeps on the CPU.  Device side: the two pools, an int32 copy of the
+block table and of the lengths, and the kernels of ``libivab.so`` for append / gather / decode
+attention.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .kv_ops import paged_append, paged_gather
+
+__all__ = ["PagedKVCache", "PoolExhausted"]
+
+
+class PoolExhausted(RuntimeError):
+    """No free page left in the pool."""
+
+
+class PagedKVCache:
+    """Page pool + block table for ``batch_size`` sequences of one attention layer.
+
+    Constructor keywords follow ``KVCache(batch_size, n_heads, head_dim, seq_len, device, dtype)``
+    (rope_kv.py:73-81; default dtype fp16 as at rope_kv.py:80).  ``seq_len`` is the number of tokens
+    considered already present (their K/V are zero, as in the reference, which zero-fills).
+    Extra keywords: ``page_size`` (16), ``num_pages`` (pool capacity; default enough for
+    ``max_seq_len`` tokens per sequence), ``shuffle_seed`` (hand out pages in a seeded random order
+    instead of ascending, to exercise non-contiguous block tables).
+    """
+
+    def __init__(self, batch_size: int, n_heads: int, head_dim: int, seq_len: int = 0,
+                 device="cuda", dtype: torch.dtype = torch.float16, *, page_size: int = 16,
+                 num_pages: Optional[int] = None, max_seq_len: int = 4096,
+                 shuffle_seed: Optional[int] = None):
+        self.batch_size = batch_size
+        self.n_heads = n_heads
+        self.head_dim = head_dim
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.page_size = page_size
+        max_seq_len = max(max_seq_len, seq_len, 1)
+        self.max_pages_per_seq = (max_seq_len + page_size - 1) // page_size
+        if num_pages is None:
+            num_pages = batch_size * self.max_pages_per_seq
+        self.num_pages = num_pages
+        S = num_pages * page_size
+        self.k_pool = torch.zeros(1, n_heads, S, head_dim, device=self.device, dtype=dtype)
+        self.v_pool = torch.zeros(1, n_heads, S, head_dim, device=self.device, dtype=dtype)
+        if shuffle_seed is None:
+            order = list(range(num_pages))
+        else:
+            order = torch.randperm(num_pages, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
+        self._free: List[int] = order[::-1]          # pop() hands out order[0] first
+        self._lens: List[int] = [0] * batch_size
+        self._tables: List[List[int]] = [[] for _ in range(batch_size)]
+        self._bt_host = torch.full((batch_size, self.max_pages_per_seq), -1, dtype=torch.int32)
+        self._len_host = torch.zeros(batch_size, dtype=torch.int32)
+        self.block_table_dev = torch.full((batch_size, self.max_pages_per_seq), -1, dtype=torch.int32,
+                                          device=self.device)
+        self.ctx_len_dev = torch.zeros(batch_size, dtype=torch.int32, device=self.device)
+        self._bt_dirty = False
+        if seq_len:
+            self._reserve([seq_len] * batch_size)
+            self._sync_device()
+
+    # ---- bookkeeping ------------------------------------------------------------------------
+
+    @property
+    def seq_len(self) -> int:
+        """Longest sequence length (the reference cache has one length for the whole batch)."""
+        return max(self._lens) if self._lens else 0
+
+    @property
+    def lengths(self) -> List[int]:
+        return list(self._lens)
+
+    @property
+    def free_pages(self) -> int:
+        return len(self._free)
+
+    def _reserve(self, new_lens: Sequence[int]) -> None:
+        """Grow block tables so that sequence ``s`` can hold ``new_lens[s]`` tokens."""
+        need_total = 0
+        for s, L in enumerate(new_lens):
+            need = (L + self.page_size - 1) // self.page_size
+            if need > self.max_pages_per_seq:
+                raise PoolExhausted(f"sequence {s} needs {need} pages, block table holds {self.max_pages_per_seq}")
+            need_total += max(0, need - len(self._tables[s]))
+        if need_total > len(self._free):
+            raise PoolExhausted(f"need {need_total} pages, {len(self._free)} free")
+        for s, L in enumerate(new_lens):
+            need = (L + self.page_size - 1) // self.page_size
+            while len(self._tables[s]) < need:
+                page = self._free.pop()
+                self._bt_host[s, len(self._tables[s])] = page
+                self._tables[s].append(page)
+                self._bt_dirty = True
+            self._lens[s] = L
+            self._len_host[s] = L
+
+    def _staged(self, t: torch.Tensor) -> torch.Tensor:
+        """A private pinned snapshot of a host table: the asynchronous upload reads host memory
+        when the copy executes, so it must not alias a buffer the next step will overwrite."""
+        return t.clone().pin_memory() if self.device.type == "cuda" else t.clone()
+
+    def _sync_device(self) -> None:
+        if self._bt_dirty:
+            self.block_table_dev.copy_(self._staged(self._bt_host), non_blocking=True)
+            self._bt_dirty = False
+        self.ctx_len_dev.copy_(self._staged(self._len_host), non_blocking=True)
+
+    def slots(self, seq: int, start: int, stop: int) -> List[int]:
+        ps, tab = self.page_size, self._tables[seq]
+        return [tab[p // ps] * ps + p % ps for p in range(start, stop)]
+
+    # ---- the hot path -----------------------------------------------------------------------
+
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> List[int]:
+        """Append ``S`` tokens to every sequence.  ``k_new`` / ``v_new`` are ``[B,S,H,D]`` (projection
+        output order), ``[B,H,D]`` for one token, or the reference's ``[B,H,S,D]`` when passed through
+        ``update``.  Returns the lengths before the append."""
+        if k_new.dim() == 3:
+            k_new, v_new = k_new.unsqueeze(1), v_new.unsqueeze(1)
+        B, S, H, D = k_new.shape
+        if B != self.batch_size or H != self.n_heads or D != self.head_dim:
+            raise ValueError(f"expected [{self.batch_size},S,{self.n_heads},{self.head_dim}], got {list(k_new.shape)}")
+        prior = list(self._lens)
+        self._reserve([L + S for L in prior])
+        slots: List[int] = []
+        for s in range(B):
+            slots.extend(self.slots(s, prior[s], prior[s] + S))
+        slot_t = torch.tensor(slots, dtype=torch.int64)
+        if self.device.type == "cuda":
+            slot_t = slot_t.pin_memory()
+        slot_dev = slot_t.to(self.device, non_blocking=True)
+        self._sync_device()
+        paged_append(self.k_pool, self.v_pool, slot_dev, k_new.reshape(B * S, H, D), v_new.reshape(B * S, H, D),
+                     self.page_size)
+        return prior
+
+    def gather(self, layout: str = "head_major"):
+        """Contiguous K and V of every sequence (lists of ``[1,H,L_s,D]`` for ``head_major``, packed
+        ``[sum L,H,D]`` for ``token_major``)."""
+        k = paged_gather(self.k_pool, self.block_table_dev, self.ctx_len_dev, self.page_size, layout=layout)
+        v = paged_gather(self.v_pool, self.block_table_dev, self.ctx_len_dev, self.page_size, layout=layout)
+        return k, v
+
+    # ---- KVCache duck type (rope_kv.py:83-137) ----------------------------------------------------
+
+    def _dense(self, pool: torch.Tensor) -> torch.Tensor:
+        seqs = paged_gather(pool, self.block_table_dev, self.ctx_len_dev, self.page_size, layout="head_major")
+        L = self.seq_len
+        out = torch.zeros(self.batch_size, self.n_heads, L, self.head_dim, device=self.device, dtype=self.dtype)
+        for s, t in enumerate(seqs):
+            out[s, :, :t.shape[2]] = t[0]
+        return out
+
+    @property
+    def k(self) -> torch.Tensor:
+        """Dense ``[B,H,seq_len,D]`` view of the keys, gathered on demand (shorter sequences are
+        zero-padded at the end)."""
+        return self._dense(self.k_pool)
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self._dense(self.v_pool)
+
+    def update(self, new_k: torch.Tensor, new_v: torch.Tensor, start_pos: int) -> None:
+        """Write ``[B,H,S,D]`` tokens at positions ``start_pos..start_pos+S-1`` of every sequence
+        (rope_kv.py:98-110), growing the block tables as needed."""
+        B, H, S, D = new_k.shape
+        end = start_pos + S
+        self._reserve([max(L, end) for L in self._lens])
+        slots: List[int] = []
+        for s in range(B):
+            slots.extend(self.slots(s, start_pos, end))
+        slot_dev = torch.tensor(slots, dtype=torch.int64).to(self.device)
+        self._sync_device()
+        paged_append(self.k_pool, self.v_pool, slot_dev,
+                     new_k.permute(0, 2, 1, 3).reshape(B * S, H, D).contiguous(),
+                     new_v.permute(0, 2, 1, 3).reshape(B * S, H, D).contiguous(), self.page_size)
+
+    def resize(self, new_seq_len: int) -> None:
+        """Make room for ``new_seq_len`` tokens per sequence (rope_kv.py:112-130).  Pages are taken
+        from the free list; nothing is copied.  New positions read as zero only if their pages were
+        never used, so callers should write them before reading."""
+        self._reserve([max(L, new_seq_len) for L in self._lens])
+        self._sync_device()
+
+    def clear(self) -> None:
+        """Zero the pools (rope_kv.py:132-134); lengths and block tables are kept, as the reference
+        keeps ``seq_len``."""
+        self.k_pool.zero_()
+        self.v_pool.zero_()
+
+    def get_slice(self, start: int, end: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Dense ``[B,H,end-start,D]`` K and V (rope_kv.py:136-137)."""
+        return self.k[:, :, start:end], self.v[:, :, start:end]
+
+    def reset(self, seq: Optional[int] = None) -> None:
+        """Return the pages of one sequence (or of all) to the free list."""
+        for s in (range(self.batch_size) if seq is None else [seq]):
+            self._free.extend(reversed(self._tables[s]))
+            self._tables[s] = []
+            self._lens[s] = 0
+            self._len_host[s] = 0
+            self._bt_host[s].fill_(-1)
+        self._bt_dirty = True
+        self._sync_device()

@@ -1,0 +1,104 @@
+"""Multi-GPU forms of the decode path: one process per GPU.
+
+* Request sharding -- sequences (with their page pools and block tables) are partitioned across
+  ranks at admission; every rank runs append / gather / attention on its own pool and NOTHING is
+  exchanged on the hot path.  ``shard_requests`` and ``balance_by_pages`` are the partitioners.
+* Head-parallel decode of one very long sequence -- KV heads (and the query heads attached to
+  them) are sliced across ranks; the pool layout ``[1,H_kv,S,D]`` makes each rank's slab
+  self-contained and the block table is replicated.  After the local attention one all-gather
+  (NCCL over NVLink on GPUs) reassembles ``out [B,H_q,D]`` and ``lse [B,H_q]``.  No K/V ever
+  crosses a link.
+
+The reference has no parallel decode path (its distributed wrappers,
+src/utils/distributed.py:106-150, have no caller); its backend choice -- NCCL through
+``torch.distributed`` (src/utils/distributed.py:29-34) -- is kept.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+__all__ = ["shard_requests", "balance_by_pages", "head_slice", "HeadParallelDecoder"]
+
+
+def shard_requests(n_seq: int, world: int, rank: int) -> range:
+    """Contiguous, balanced share of ``n_seq`` sequences for ``rank`` (the first ``n_seq % world``
+    ranks get one more)."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    per, rem = divmod(n_seq, world)
+    lo = rank * per + min(rank, rem)
+    return range(lo, lo + per + (1 if rank < rem else 0))
+
+
+def balance_by_pages(ctx_lens: Sequence[int], world: int, page_size: int = 16) -> List[List[int]]:
+    """Partition sequences so that every rank reads about the same number of pages per step
+    (longest-processing-time greedy).  Returns the sequence ids of each rank."""
+    order = sorted(range(len(ctx_lens)), key=lambda s: -int(ctx_lens[s]))
+    load = [0] * world
+    parts: List[List[int]] = [[] for _ in range(world)]
+    for s in order:
+        r = min(range(world), key=lambda i: (load[i], i))
+        parts[r].append(s)
+        load[r] += (int(ctx_lens[s]) + page_size - 1) // page_size
+    for p in parts:
+        p.sort()
+    return parts
+
+
+def head_slice(n_q_heads: int, n_kv_heads: int, world: int, rank: int) -> Tuple[slice, slice]:
+    """(query-head slice, kv-head slice) owned by ``rank``; query heads follow their KV head."""
+    if n_kv_heads % world:
+        raise ValueError(f"{n_kv_heads} KV heads do not split over {world} ranks")
+    group = n_q_heads // n_kv_heads
+    per = n_kv_heads // world
+    return slice(rank * per * group, (rank + 1) * per * group), slice(rank * per, (rank + 1) * per)
+
+
+class HeadParallelDecoder:
+    """Decode attention for a batch whose KV heads are sliced across the ranks of ``group``.
+
+    ``attn_fn(q_local, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale,
+    return_lse=True) -> (out, lse)`` defaults to the CUDA operator; tests on CPU ranks inject a
+    checker in its place to exercise the slicing and the all-gather.
+    """
+
+    def __init__(self, n_q_heads: int, n_kv_heads: int, group: Optional[dist.ProcessGroup] = None,
+                 attn_fn: Optional[Callable] = None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.n_q_heads, self.n_kv_heads = n_q_heads, n_kv_heads
+        self.q_slice, self.kv_slice = head_slice(n_q_heads, n_kv_heads, self.world, self.rank)
+        if attn_fn is None:
+            from .attention import paged_decode_attention as attn_fn
+        self.attn_fn = attn_fn
+
+    def local_pools(self, k_pool: torch.Tensor, v_pool: torch.Tensor):
+        """This rank's slab of full ``[1,H_kv,S,D]`` pools (a view, no copy)."""
+        return k_pool[:, self.kv_slice], v_pool[:, self.kv_slice]
+
+    def decode(self, q: torch.Tensor, k_pool_local: torch.Tensor, v_pool_local: torch.Tensor,
+               block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
+               scale: Optional[float] = None):
+        """``q`` is the full ``[B,H_q,D]`` query (replicated) or already this rank's slice.  Returns the
+        full ``out [B,H_q,D]`` and ``lse [B,H_q]`` on every rank."""
+        B = q.shape[0]
+        if q.shape[1] == self.n_q_heads and self.world > 1:
+            q = q[:, self.q_slice]
+        out_l, lse_l = self.attn_fn(q.contiguous(), k_pool_local, v_pool_local, block_table, ctx_len, page_size,
+                                    scale, return_lse=True)
+        if self.world == 1:
+            return out_l, lse_l
+        Hl, D = out_l.shape[1], out_l.shape[2]
+        # rank r's block lands in rows r*B..(r+1)*B-1 of the gathered tensor
+        out_all = torch.empty(self.world * B, Hl, D, dtype=out_l.dtype, device=out_l.device)
+        lse_all = torch.empty(self.world * B, Hl, dtype=lse_l.dtype, device=lse_l.device)
+        dist.all_gather_into_tensor(out_all, out_l.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(lse_all, lse_l.contiguous(), group=self.group)
+        out = out_all.view(self.world, B, Hl, D).permute(1, 0, 2, 3).reshape(B, self.world * Hl, D)
+        lse = lse_all.view(self.world, B, Hl).permute(1, 0, 2).reshape(B, self.world * Hl)
+        return out, lse

@@ -1,0 +1,240 @@
+"""GPU parity: single-query decode attention through the block table, called through the C ABI,
+against the CPU checker, the reference's golden outputs, and itself under re-paging."""
+
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import iva_b200
+from iva_b200 import workloads
+from iva_b200.attention import decode_status, decode_workspace_bytes
+from oracle import paged_ref as ref
+from util import assert_attn_close, assert_lse_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def run_step(wl, check=True):
+    """append one token per sequence, then attention over ctx_len+1 keys -- all on the GPU."""
+    d = wl.to(DEV)
+    iva_b200.paged_append(d.k_pool, d.v_pool, d.slot_mapping, d.k_new, d.v_new, wl.page_size, check=check)
+    lens = (d.ctx_len + 1).contiguous()
+    out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, lens, wl.page_size,
+                                               wl.scale, return_lse=True, check=check)
+    return d, out, lse
+
+
+def test_c1_against_reference_golden(golden, golden_inputs):
+    """Config C1 exactly as the reference module computed it (fp32)."""
+    wl = golden_inputs.c1_module_workload()
+    _, out, lse = run_step(wl)
+    assert (out.cpu() - torch.from_numpy(golden["c1_out"])).abs().max().item() <= 2e-5
+    assert (lse.cpu() - torch.from_numpy(golden["c1_lse"])).abs().max().item() <= 1e-4
+
+
+def test_c1_against_oracle_bit_exact_pools():
+    wl = workloads.config_c1()
+    kp, vp, out_ref, lse_ref = ref.decode_step_ref(wl)
+    d, out, lse = run_step(wl)
+    assert torch.equal(d.k_pool.cpu(), kp) and torch.equal(d.v_pool.cpu(), vp)
+    assert_attn_close(out, out_ref, torch.float32)
+    assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("group", [1, 2, 4, 8])
+def test_page_boundary_contexts(dtype, D, group):
+    """Contexts around every page boundary, plus an empty sequence; stale slots hold NaN."""
+    ctx = torch.tensor([0, 1, 14, 15, 16, 17, 31, 32, 33, 47, 48, 127, 128, 129, 255, 300])
+    wl = workloads.make_decode_workload("edge", ctx, n_q_heads=2 * group, n_kv_heads=2, head_dim=D, dtype=dtype,
+                                        seed=group * 10 + D, free_frac=0.2, poison_unused=True)
+    _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
+    _, out, lse = run_step(wl)
+    assert_attn_close(out, out_ref, dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_empty_sequence_gives_zeros_and_minus_inf():
+    wl = workloads.make_decode_workload("z", torch.tensor([5, 0, 9]), n_q_heads=4, n_kv_heads=4, head_dim=128, seed=1)
+    d = wl.to(DEV)
+    out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16,
+                                               return_lse=True, check=True)
+    assert not out[1].any() and torch.isinf(lse[1]).all() and (lse[1] < 0).all()
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16)
+    assert_attn_close(out, out_ref, wl.dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("dtype,Hq,Hkv", [(torch.bfloat16, 32, 32), (torch.bfloat16, 32, 8), (torch.float16, 16, 4)])
+def test_long_contexts_take_the_split_path(dtype, Hq, Hkv):
+    """Few long sequences: each is cut into several chunks and merged by logsumexp."""
+    ctx = torch.tensor([5000, 9000, 4097, 70])
+    wl = workloads.make_decode_workload("long", ctx, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=128, dtype=dtype, seed=4)
+    _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
+    d, out, lse = run_step(wl)
+    assert_attn_close(out, out_ref, dtype, strict=True)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_ragged_gqa_batch_scaled_c3():
+    wl = workloads.config_c3(batch=24, median=700, hi=6000, seed=3)
+    _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
+    _, out, lse = run_step(wl)
+    assert_attn_close(out, out_ref, wl.dtype, strict=True)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_mha_uniform_batch_scaled_c2():
+    wl = workloads.config_c2(batch=8, context=1024)
+    _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
+    _, out, lse = run_step(wl)
+    assert_attn_close(out, out_ref, wl.dtype, strict=True)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_result_is_independent_of_page_placement():
+    """Moving every page somewhere else in the pool (and updating the block table) must not change
+    a single bit: the work list, the chunking and the arithmetic do not depend on page ids."""
+    wl = workloads.make_decode_workload("perm", torch.tensor([333, 2000, 16]), n_q_heads=8, n_kv_heads=2,
+                                        head_dim=128, seed=6, free_frac=0.5)
+    d = wl.to(DEV)
+    lens = d.ctx_len.contiguous()
+    a = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, lens, 16, check=True)
+    P = wl.num_pages
+    perm = torch.randperm(P, generator=torch.Generator().manual_seed(1)).to(DEV)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(P, device=DEV)
+    move = lambda pool: pool.view(1, 2, P, 16, 128)[:, :, inv].reshape(1, 2, P * 16, 128).contiguous()
+    bt = d.block_table.clone()
+    valid = bt >= 0
+    bt[valid] = perm[bt[valid].long()].to(torch.int32)
+    b = iva_b200.paged_decode_attention(d.q, move(d.k_pool), move(d.v_pool), bt, lens, 16, check=True)
+    assert torch.equal(a, b)
+
+
+def test_page_major_pool_layout():
+    wl = workloads.make_decode_workload("pm", torch.tensor([100, 33]), n_q_heads=8, n_kv_heads=4, head_dim=128, seed=8)
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16)
+    P = wl.num_pages
+    to_pm = lambda t: t.view(4, P, 16, 128).permute(1, 0, 2, 3).contiguous().to(DEV)
+    d = wl.to(DEV)
+    out, lse = iva_b200.paged_decode_attention(d.q, to_pm(wl.k_pool[0]), to_pm(wl.v_pool[0]), d.block_table,
+                                               d.ctx_len, 16, return_lse=True, check=True)
+    assert_attn_close(out, out_ref, wl.dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_bad_page_id_and_length_are_flagged_not_dereferenced():
+    wl = workloads.make_decode_workload("bad", torch.tensor([40, 40]), n_q_heads=2, n_kv_heads=2, head_dim=128, seed=2)
+    d = wl.to(DEV)
+    ws = torch.empty(decode_workspace_bytes(2, 2, 2, 128), dtype=torch.uint8, device=DEV)
+    bt = d.block_table.clone()
+    bt[1, 1] = 1 << 20
+    iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, bt, d.ctx_len, 16, workspace=ws)
+    assert decode_status(ws) & 2
+    with pytest.raises(iva_b200.IvabError):
+        iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table,
+                                        torch.tensor([40, 10 ** 6], dtype=torch.int32, device=DEV), 16,
+                                        workspace=ws, check=True)
+    iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16, workspace=ws, check=True)
+
+
+def test_argument_errors():
+    wl = workloads.make_decode_workload("e", torch.tensor([20]), n_q_heads=6, n_kv_heads=2, head_dim=128, seed=2).to(DEV)
+    with pytest.raises(ValueError, match="supported: 1, 2, 4, 8"):
+        iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16)
+    wl = workloads.make_decode_workload("e", torch.tensor([20]), n_q_heads=2, n_kv_heads=2, head_dim=128, seed=2).to(DEV)
+    with pytest.raises(ValueError):
+        iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16,
+                                        workspace=torch.empty(256, dtype=torch.uint8, device=DEV)[3:])
+    with pytest.raises(iva_b200.IvabError, match="workspace"):
+        iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16,
+                                        workspace=torch.empty(512, dtype=torch.uint8, device=DEV))
+    with pytest.raises(RuntimeError, match="inference-only"):
+        iva_b200.paged_decode_attention(wl.q.float().requires_grad_(), wl.k_pool.float(), wl.v_pool.float(),
+                                        wl.block_table, wl.ctx_len, 16)
+
+
+def test_bounded_wait_gives_up_instead_of_hanging():
+    """Failure detection without a fault: a wait on a barrier nothing completes returns after its
+    limit, reports IVAB_STATUS_WAIT_TIMEOUT, and the context stays usable."""
+    lib = iva_b200.load_library()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rc = lib.ivab_selftest_bounded_wait(status.data_ptr(), 50_000_000, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1
+    assert float(torch.ones(4, device=DEV).sum()) == 4.0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("L", [1, 16, 50, 256])
+def test_attention_operator_on_dense_tensors(dtype, L):
+    """attention(q,k,v,scale) with the reference operator's [B,H,S,D] signature, one query row."""
+    g = torch.Generator().manual_seed(L)
+    B, H, D = 3, 4, 64
+    q = torch.randn(B, H, 1, D, generator=g).to(dtype)
+    k = torch.randn(B, H, L, D, generator=g).to(dtype)
+    v = torch.randn(B, H, L, D, generator=g).to(dtype)
+    scale = 1 / math.sqrt(D)
+    want, lse_want = ref.attention_math_ref(q, k, v, scale)
+    got, lse = iva_b200.attention(q.to(DEV), k.to(DEV), v.to(DEV), scale, 0.0, False, return_lse=True)
+    assert got.shape == (B, H, 1, D) and got.dtype == dtype
+    assert_attn_close(got, want, dtype, strict=False)
+    assert_lse_close(lse, lse_want)
+
+
+def test_attention_operator_multi_query_and_errors():
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(2, 4, 5, 64, generator=g)
+    k = torch.randn(2, 4, 37, 64, generator=g)
+    v = torch.randn(2, 4, 37, 64, generator=g)
+    want, _ = ref.attention_math_ref(q, k, v, 0.125)
+    got = iva_b200.attention(q.to(DEV), k.to(DEV), v.to(DEV), 0.125, 0.0, False)
+    assert_attn_close(got, want, torch.float32)
+    with pytest.raises(NotImplementedError):
+        iva_b200.attention(q.to(DEV), k.to(DEV), v.to(DEV), 0.125, 0.1, True)
+    with pytest.raises(RuntimeError, match="inference-only"):
+        iva_b200.attention(q.to(DEV).requires_grad_(), k.to(DEV), v.to(DEV), 0.125)
+
+
+def test_module_matches_attention_torch_golden(golden, golden_inputs):
+    """AttentionB200 with the reference module's weights and a dense reference-style cache."""
+    B, H, hd, L, w, x, ck, cv = golden_inputs.module_inputs()
+    cfg = SimpleNamespace(d_model=H * hd, n_heads=H, dropout=0.0, causal=False, attn_impl="triton")
+    mod = iva_b200.get_attention(cfg).to(DEV).eval()
+    mod.load_state_dict({"q_proj.weight": w[0], "k_proj.weight": w[1], "v_proj.weight": w[2], "o_proj.weight": w[3]})
+    cache = ref.KVCacheRef(B, H, hd, L, DEV, torch.float32)
+    cache.k, cache.v = ck.to(DEV), cv.to(DEV)
+    y, new_cache = mod(x.to(DEV), kv_cache=cache)
+    assert isinstance(new_cache, ref.KVCacheRef) and new_cache.seq_len == L + 1
+    assert torch.allclose(new_cache.k.cpu(), torch.from_numpy(golden["module_new_k"]), atol=1e-5)
+    assert (y.cpu() - torch.from_numpy(golden["module_out"])).abs().max().item() <= 5e-5
+
+
+def test_module_with_paged_cache_decodes_like_the_dense_reference():
+    """Prefill 19 tokens, then 20 single-token steps through a PagedKVCache with a shuffled pool;
+    every step must equal the reference module's math on the dense concatenated cache."""
+    torch.manual_seed(0)
+    B, H, hd = 3, 4, 64
+    dm = H * hd
+    cfg = SimpleNamespace(d_model=dm, n_heads=H, dropout=0.0, causal=False, attn_impl="b200")
+    mod = iva_b200.AttentionB200(cfg).to(DEV).eval()
+    w = [p.detach().cpu() for p in (mod.q_proj.weight, mod.k_proj.weight, mod.v_proj.weight, mod.o_proj.weight)]
+    cache = iva_b200.PagedKVCache(batch_size=B, n_heads=H, head_dim=hd, seq_len=0, device=DEV, dtype=torch.float32,
+                                  max_seq_len=64, shuffle_seed=3)
+    dense_k = dense_v = None
+    xs = [torch.randn(B, 19, dm)] + [torch.randn(B, 1, dm) for _ in range(20)]
+    for x in xs:
+        y, cache2 = mod(x.to(DEV), kv_cache=cache)
+        assert cache2 is cache
+        y_ref, dense_k, dense_v = ref.attention_module_ref(x, *w, H, dense_k, dense_v)
+        assert (y.cpu() - y_ref).abs().max().item() <= 1e-4
+    assert cache.seq_len == 39 and cache.lengths == [39] * B
+    assert torch.allclose(cache.k.cpu(), dense_k, atol=1e-5) and torch.allclose(cache.v.cpu(), dense_v, atol=1e-5)
+    k2, v2 = cache.get_slice(5, 9)
+    assert torch.allclose(k2.cpu(), dense_k[:, :, 5:9], atol=1e-5)

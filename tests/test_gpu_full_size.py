@@ -1,0 +1,83 @@
+"""GPU checks at the benchmark's full sizes, through size-independent properties plus a sampled
+comparison against the CPU checker (a few sequences/heads finish in seconds on the host)."""
+
+import pytest
+import torch
+
+import iva_b200
+from iva_b200 import workloads
+from oracle import paged_ref as ref
+from util import assert_attn_close, assert_lse_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _sampled_oracle(wl_gpu, lens, seqs, out, lse):
+    """Oracle on a few sequences: copy only their pages' worth of pool to the host."""
+    kp, vp = wl_gpu.k_pool.cpu(), wl_gpu.v_pool.cpu()
+    out_ref, lse_ref = ref.paged_decode_ref(wl_gpu.q.cpu(), kp, vp, wl_gpu.block_table.cpu(), lens.cpu(),
+                                            wl_gpu.page_size, wl_gpu.scale, seqs=seqs)
+    assert_attn_close(out[seqs], out_ref[seqs], wl_gpu.dtype, strict=True)
+    assert_lse_close(lse[seqs], lse_ref[seqs])
+
+
+def test_c2_full_size_step():
+    """64 x 32 heads x 4096 context, bf16: append then attention; sampled oracle + invariances."""
+    wl = workloads.config_c2(device=DEV)
+    pos_before = wl.k_pool[0, :, wl.slot_mapping].clone()
+    iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, 16, check=True)
+    assert torch.equal(wl.k_pool[0, :, wl.slot_mapping], wl.k_new.permute(1, 0, 2))     # append landed, bit-exact
+    assert not torch.equal(pos_before, wl.k_new.permute(1, 0, 2))
+    lens = (wl.ctx_len + 1).contiguous()
+    out, lse = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                               return_lse=True, check=True)
+    _sampled_oracle(wl, lens, [0, 37, 63], out, lse)
+    # linearity in V: doubling V doubles the output exactly (power of two), lse unchanged
+    wl.v_pool.mul_(2)
+    out2, lse2 = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                                 return_lse=True, check=True)
+    assert torch.equal(out2.float(), out.float() * 2) and torch.equal(lse2, lse)
+    # run-to-run determinism
+    out3 = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16)
+    assert torch.equal(out3, out2)
+
+
+def test_c3_full_size_ragged_gqa():
+    wl = workloads.config_c3(device=DEV)
+    iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, 16, check=True)
+    lens = (wl.ctx_len + 1).contiguous()
+    out, lse = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                               return_lse=True, check=True)
+    order = torch.argsort(wl.ctx_len.cpu())
+    seqs = [int(order[0]), int(order[len(order) // 2]), int(order[-1])]          # shortest, median, longest
+    _sampled_oracle(wl, lens, seqs, out, lse)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+
+
+def test_c4_full_size_append_gather_roundtrip():
+    """256 sequences x 512-token fp16 chunks after priors U[0,8192]: append, then gather every
+    sequence; the chunk must come back bit-exact and the priors must be untouched."""
+    wl = workloads.config_c4(device=DEV)
+    T, chunk = wl.k_new.shape[0], wl.new_tokens_per_seq
+    lens = (wl.ctx_len + chunk).contiguous()
+    offs = torch.zeros(wl.batch + 1, dtype=torch.int64, device=DEV)
+    offs[1:] = torch.cumsum(lens.long(), 0)
+    total = int(offs[-1])
+    before = iva_b200.paged_gather(wl.k_pool, wl.block_table, wl.ctx_len, 16, layout="token_major", check=True)
+    iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, 16, check=True)
+    for pool, new in ((wl.k_pool, wl.k_new), (wl.v_pool, wl.v_new)):
+        got = iva_b200.paged_gather(pool, wl.block_table, lens, 16, layout="token_major", out_offsets=offs,
+                                    total_tokens=total, check=True)
+        pos = torch.arange(total, device=DEV)
+        seq_of = torch.bucketize(pos, offs[1:], right=True)
+        within = pos - offs[seq_of]
+        is_new = within >= wl.ctx_len.long()[seq_of]
+        assert int(is_new.sum()) == T
+        assert torch.equal(got[is_new], new)                                   # round trip of the chunk
+        if pool is wl.k_pool:
+            assert torch.equal(got[~is_new], before)                            # priors untouched
+        del got
+    # the reference-signature operator on the same pool: gather the chunk's slots back
+    back = iva_b200.kv_ops(wl.v_pool, wl.slot_mapping[:4096], None, "gather", compat=False, check=True)
+    assert torch.equal(back[0].permute(1, 0, 2), wl.v_new[:4096])

@@ -1,0 +1,34 @@
+"""Helpers shared by the GPU parity tests."""
+
+import torch
+
+# Tolerances of the decode-attention parity bar: max-abs 2e-3 (bf16), 1e-3 (fp16), and 1e-3 on the
+# per-head logsumexp.  fp32 inputs are held to 2e-5.
+OUT_TOL = {torch.bfloat16: 2e-3, torch.float16: 1e-3, torch.float32: 2e-5}
+LSE_TOL = 1e-3
+# One unit in the last place of the storage dtype, relative: the kernel's fp32 result is rounded
+# once to the output dtype, which for |out| of order 1 (contexts of a few tokens) is itself larger
+# than the absolute bar.  Tests on such short contexts allow abs + one rounding step.
+ULP = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 0.0}
+
+
+def assert_attn_close(got, ref32, dtype, strict=True, what="out"):
+    got32 = got.float().cpu()
+    ref32 = ref32.float().cpu()
+    assert torch.isfinite(got32).all(), f"{what}: non-finite values"
+    err = (got32 - ref32).abs()
+    if strict:
+        assert err.max().item() <= OUT_TOL[dtype], f"{what}: max-abs {err.max().item():.3e} > {OUT_TOL[dtype]}"
+    else:
+        bound = OUT_TOL[dtype] + ULP[dtype] * ref32.abs()
+        bad = err > bound
+        assert not bad.any(), f"{what}: max-abs {err.max().item():.3e} beyond abs+1ulp bound"
+
+
+def assert_lse_close(got, ref):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    inf = torch.isinf(ref)
+    assert torch.equal(torch.isinf(got), inf)
+    err = (got[~inf] - ref[~inf]).abs()
+    if err.numel():
+        assert err.max().item() <= LSE_TOL, f"lse: max-abs {err.max().item():.3e} > {LSE_TOL}"
