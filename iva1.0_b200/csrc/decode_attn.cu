@@ -677,9 +677,15 @@ int dispatch_group(int G, const DecodeParams& p, int B, cudaStream_t st) {
 template <typename T>
 int dispatch_dim(int D, int G, const DecodeParams& p, int B, cudaStream_t st) {
     switch (D) {
+        case 32: return dispatch_group<T, 32>(G, p, B, st);
         case 64: return dispatch_group<T, 64>(G, p, B, st);
         case 128: return dispatch_group<T, 128>(G, p, B, st);
-        default: return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: head_dim %d (supported: 64, 128)", D);
+        case 256:
+            if constexpr (sizeof(T) == 2) return dispatch_group<T, 256>(G, p, B, st);
+            [[fallthrough]];
+        default:
+            return set_error(IVAB_ERR_UNSUPPORTED,
+                             "decode attention: head_dim %d (supported: 32, 64, 128; 256 for 16-bit types)", D);
     }
 }
 
