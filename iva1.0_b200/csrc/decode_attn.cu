@@ -43,6 +43,7 @@ constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kItemRing = 4;
 constexpr int kMaxStages = 32;
+static_assert(kMaxStages % kConsumerWarps == 0, "stage ring must divide among the consumer warps");
 constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
 constexpr int kMinChunkPages = 8;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
@@ -239,9 +240,9 @@ struct Cfg {
     static constexpr int OFF_ABORT = 1024 - 16;
     static constexpr int OFF_ITEMS = 1024;                              // kItemRing * 8 ints
     static constexpr int OFF_P = OFF_ITEMS + kItemRing * 32;            // [W][G][kPage] floats
-    static constexpr int OFF_MRG_ML = OFF_P + kConsumerWarps * G * kPage * 4;       // [2][W][G][2]
-    static constexpr int OFF_MRG_O = OFF_MRG_ML + 2 * kConsumerWarps * G * 2 * 4;   // [2][W][G][D]
-    static constexpr int OFF_STAGES = (OFF_MRG_O + 2 * kConsumerWarps * G * D * 4 + 127) / 128 * 128;
+    static constexpr int OFF_MRG_ML = OFF_P + kConsumerWarps * G * kPage * 4;       // [W][G][2]
+    static constexpr int OFF_MRG_O = OFF_MRG_ML + kConsumerWarps * G * 2 * 4;       // [W][G][D]
+    static constexpr int OFF_STAGES = (OFF_MRG_O + kConsumerWarps * G * D * 4 + 127) / 128 * 128;
     static constexpr int CTAS_PER_SM = (G >= 8) ? 1 : 2;
 };
 
@@ -301,8 +302,8 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
         *abort_flag = 0;
         for (int s = 0; s < stages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
         for (int s = 0; s < kItemRing; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), kConsumerWarps); }
-        mbar_init(bar_merge(0), kConsumerWarps);
-        mbar_init(bar_merge(1), kConsumerWarps);
+        mbar_init(bar_merge(0), kConsumerWarps);   // all warp states published
+        mbar_init(bar_merge(1), kConsumerWarps);   // all warps done reading them
         fence_mbar_init();
     }
     __syncthreads();   // the only CTA-wide barrier: before any warp can have unwound
@@ -520,9 +521,12 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
             }
             l_run[g] = warp_sum_f32(l_run[g]);
         }
-        const int mb = consumed & 1;
-        float* my_ml = mrg_ml + ((mb * kConsumerWarps + warp) * G) * 2;
-        float* my_o = mrg_o + ((size_t)(mb * kConsumerWarps + warp) * G) * D;
+        // The merge scratch is shared by consecutive items: wait until every warp has finished
+        // reading the previous item's states before overwriting them.
+        if (consumed > 0 &&
+            !mbar_wait_bounded(bar_merge(1), (consumed - 1) & 1, abort_flag, limit)) break;
+        float* my_ml = mrg_ml + (warp * G) * 2;
+        float* my_o = mrg_o + (size_t)(warp * G) * D;
         if (r == 0) {
 #pragma unroll
             for (int g = 0; g < G; ++g) {
@@ -535,12 +539,12 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
             for (int g = 0; g < G; ++g) { my_ml[g * 2] = m_run[g]; my_ml[g * 2 + 1] = l_run[g]; }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_merge(mb));
-        if (!mbar_wait_bounded(bar_merge(mb), (consumed >> 1) & 1, abort_flag, limit)) break;
+        if (lane == 0) mbar_arrive(bar_merge(0));
+        if (!mbar_wait_bounded(bar_merge(0), consumed & 1, abort_flag, limit)) break;
 
         // ---- merge the four warp states; the G*D outputs are spread over the consumer threads
-        const float* all_ml = mrg_ml + (mb * kConsumerWarps * G) * 2;
-        const float* all_o = mrg_o + (size_t)(mb * kConsumerWarps * G) * D;
+        const float* all_ml = mrg_ml;
+        const float* all_o = mrg_o;
         for (int idx = threadIdx.x; idx < G * D; idx += kConsumerWarps * 32) {
             const int g = idx / D, dd = idx % D;
             float M = -INFINITY;
@@ -568,6 +572,8 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
                 }
             }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_merge(1));
         ++consumed;
     }
     if (*abort_flag && threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
@@ -642,7 +648,11 @@ int launch_decode(const DecodeParams& p0, int B, cudaStream_t st) {
     if (budget > max_optin) budget = max_optin;
     int stages = (budget - C::OFF_STAGES) / C::STAGE_BYTES;
     if (stages > kMaxStages) stages = kMaxStages;
-    if (stages < 2) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for two stages");
+    // Pages go to consumer warps round-robin.  With a stage count that is a multiple of the warp
+    // count, a stage is always consumed by the same warp, so a warp waiting for the next phase of a
+    // stage has itself consumed the previous one -- the precondition of a parity wait.
+    stages -= stages % kConsumerWarps;
+    if (stages < kConsumerWarps) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for the stage ring");
     p.stages = stages;
     const size_t smem = (size_t)C::OFF_STAGES + (size_t)stages * C::STAGE_BYTES;
     auto kern = decode_kernel<T, D, G>;
