@@ -256,16 +256,19 @@ def run_gpu(args):
 
     # ---- device-resident timing (the headline `value`) ----
     launches0 = lib.ivab_launch_count()
-    with ClockSampler(local) as clocks:
-        barrier()
-        per_step = time_region(step, args.steps, flush)
-        barrier()
-        launches = lib.ivab_launch_count() - launches0
-        total_ms = sum(per_step)
-        # per-kernel legs, same stream, same conditions
-        attn_ms = time_region(attend, args.steps, flush) if name != "c4" else None
-        app_ms = time_region(append, args.steps, flush)
-        gat_ms = time_region(gather, max(2, args.steps // 4)) if name == "c4" else None
+    # clocks are sampled from here to the end of the end-to-end leg (a K-step region alone can be
+    # shorter than one nvidia-smi sampling period)
+    clocks = ClockSampler(local)
+    clocks.__enter__()
+    barrier()
+    per_step = time_region(step, args.steps, flush)
+    barrier()
+    launches = lib.ivab_launch_count() - launches0
+    total_ms = sum(per_step)
+    # per-kernel legs, same stream, same conditions
+    attn_ms = time_region(attend, args.steps, flush) if name != "c4" else None
+    app_ms = time_region(append, args.steps, flush)
+    gat_ms = time_region(gather, max(2, args.steps // 4)) if name == "c4" else None
     if dist is not None:
         t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -312,6 +315,7 @@ def run_gpu(args):
                "d2h_bytes_per_step": out_host.numel() * out_host.element_size(),
                "ms_per_step": e2e_ms / args.steps, "wall_ms_per_step": wall_ms / args.steps}
 
+    clocks.__exit__(None, None, None)
     if rank != 0:
         if dist is not None:
             dist.barrier()

@@ -222,7 +222,7 @@ struct DecodeParams {
 };
 
 // item ring entry (ints): what the producer tells the consumers about the next work item
-enum { kItSeq = 0, kItHead = 1, kItPages = 2, kItPageBegin = 3, kItChunks = 4, kItIndex = 5, kItPageBase = 6, kItLen = 7 };
+enum { kItSeq = 0, kItHead = 1, kItPages = 2, kItPageBegin = 3, kItChunks = 4, kItIndex = 5, kItStart = 6, kItLen = 7 };
 
 template <typename T, int D, int G>
 struct Cfg {
@@ -316,7 +316,14 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
 
     if (warp == kConsumerWarps) {
         // ------------------------------ producer warp ------------------------------------------
-        int n = 0;          // pages issued by this CTA so far (ring position)
+        // The stage ring is split into one sub-ring per consumer warp (stage = slot*W + warp).
+        // Page k of an item goes to warp (start + k) % W with start = (seq + chunk) % W, so which
+        // warp sums which pages -- and therefore every fp32 rounding -- depends only on the
+        // inputs, never on which CTA happened to pick the item up: results are bit-reproducible.
+        int cnt[kConsumerWarps];   // pages issued to each warp so far
+#pragma unroll
+        for (int i = 0; i < kConsumerWarps; ++i) cnt[i] = 0;
+        const int spw = stages / kConsumerWarps;   // stages per warp
         int published = 0;  // items published so far
         bool aborted = false;
         int item = 0;
@@ -343,7 +350,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
                 volatile int* it = items + slot * 8;
                 it[kItSeq] = d.seq; it[kItHead] = h; it[kItPages] = done ? -1 : d.n_pages;
                 it[kItPageBegin] = d.page_begin; it[kItChunks] = d.n_chunks; it[kItIndex] = item;
-                it[kItPageBase] = n; it[kItLen] = d.pad0;
+                it[kItStart] = (d.seq + d.chunk_idx) % kConsumerWarps; it[kItLen] = d.pad0;
                 mbar_arrive(bar_item_full(slot));
             }
             ++published;
@@ -352,17 +359,22 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
             const int32_t* bt = p.block_table + (int64_t)d.seq * p.bt_stride + d.page_begin;
             const char* kbase = p.k_pool + (int64_t)h * p.pool_sh_bytes;
             const char* vbase = p.v_pool + (int64_t)h * p.pool_sh_bytes;
+            const int start = (d.seq + d.chunk_idx) % kConsumerWarps;
             for (int p0 = 0; p0 < d.n_pages && !aborted; p0 += 32) {
                 int mine = 0;
                 if (p0 + lane < d.n_pages) {
                     mine = __ldg(bt + p0 + lane);
                     if (mine < 0 || mine >= p.num_pages) { atomicOr(status, kStatusBadPage); mine = 0; }
                 }
-                const int cnt = min(32, d.n_pages - p0);
-                for (int j = 0; j < cnt; ++j) {
+                const int in_batch = min(32, d.n_pages - p0);
+                for (int j = 0; j < in_batch; ++j) {
                     const int pid = __shfl_sync(0xffffffffu, mine, j);
-                    const int stage = n % stages;
-                    if (!mbar_wait_bounded(bar_empty(stage), ((n / stages) & 1) ^ 1, abort_flag, limit)) {
+                    const int w = (start + p0 + j) % kConsumerWarps;
+                    int c = 0;
+#pragma unroll
+                    for (int i = 0; i < kConsumerWarps; ++i) if (i == w) { c = cnt[i]; cnt[i] = c + 1; }
+                    const int stage = (c % spw) * kConsumerWarps + w;
+                    if (!mbar_wait_bounded(bar_empty(stage), ((c / spw) & 1) ^ 1, abort_flag, limit)) {
                         aborted = true; break;
                     }
                     if (lane == 0) {
@@ -372,7 +384,6 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
                         tma_bulk_g2s(dst + C::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes, C::PAGE_BYTES,
                                      bar_full(stage));
                     }
-                    ++n;
                 }
             }
             if (aborted) break;
@@ -383,9 +394,13 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
             // Copies already issued still target this CTA's shared memory: give each of the
             // most recent `stages` copies a bounded chance to land before the CTA retires.
             volatile int no_abort = 0;
-            const int first = n > stages ? n - stages : 0;
-            for (int m = first; m < n; ++m)
-                mbar_wait_bounded(bar_full(m % stages), (m / stages) & 1, &no_abort, limit);
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                // the copy whose empty-wait just failed was counted but never issued
+                for (int m = cnt[w] > spw ? cnt[w] - spw : 0; m < cnt[w]; ++m)
+                    mbar_wait_bounded(bar_full((m % spw) * kConsumerWarps + w), (m / spw) & 1, &no_abort,
+                                      limit < 100000000ull ? limit : 100000000ull);
+            }
         }
         return;
     }
@@ -402,13 +417,15 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
     const T* qg = static_cast<const T*>(p.q);
     T* outg = static_cast<T*>(p.out);
 
+    const int spw = stages / kConsumerWarps;   // stages of this warp's sub-ring
+    int taken = 0;      // pages this warp has consumed so far (position in its sub-ring)
     int consumed = 0;   // items consumed
     for (;;) {
         const int slot = consumed % kItemRing;
         if (!mbar_wait_bounded(bar_item_full(slot), (consumed / kItemRing) & 1, abort_flag, limit)) break;
         volatile int* it = items + slot * 8;
         const int seq = it[kItSeq], h = it[kItHead], n_pages = it[kItPages], page_begin = it[kItPageBegin];
-        const int n_chunks = it[kItChunks], item = it[kItIndex], page_base = it[kItPageBase], L = it[kItLen];
+        const int n_chunks = it[kItChunks], item = it[kItIndex], start = it[kItStart], L = it[kItLen];
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_item_empty(slot));
         if (n_pages < 0) break;   // sentinel: the work list is exhausted
@@ -432,11 +449,10 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
         }
 
         bool ok = true;
-        const int k0 = (warp - (page_base % kConsumerWarps) + kConsumerWarps) % kConsumerWarps;
-        for (int k = k0; k < n_pages; k += kConsumerWarps) {
-            const int n = page_base + k;
-            const int stage = n % stages;
-            if (!mbar_wait_bounded(bar_full(stage), (n / stages) & 1, abort_flag, limit)) { ok = false; break; }
+        const int k0 = (warp - start + kConsumerWarps) % kConsumerWarps;
+        for (int k = k0; k < n_pages; k += kConsumerWarps, ++taken) {
+            const int stage = (taken % spw) * kConsumerWarps + warp;
+            if (!mbar_wait_bounded(bar_full(stage), (taken / spw) & 1, abort_flag, limit)) { ok = false; break; }
             const uint4* kp = reinterpret_cast<const uint4*>(stage_base + (size_t)stage * C::STAGE_BYTES) + lane;
             const uint4* vp = kp + C::PAGE_BYTES / 16;
             const int n_valid = min(kPage, L - (page_begin + k) * kPage);
