@@ -218,7 +218,8 @@ def paged_gather(pool: torch.Tensor, block_table: torch.Tensor, ctx_len: torch.T
         total_tokens = int(lens_host.sum())
     else:
         offs = out_offsets.to(device=dev, dtype=torch.int64).contiguous()
-    out = torch.empty(total_tokens, H, D, device=dev, dtype=pool.dtype)
+    # (an empty result still needs a real base pointer for the library's argument check)
+    out = torch.empty(max(total_tokens, 1), H, D, device=dev, dtype=pool.dtype)[:total_tokens]
     status = _status_word(dev)
     with torch.cuda.device(dev):
         _lib.check(lib.ivab_paged_gather(
