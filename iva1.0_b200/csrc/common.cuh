@@ -102,6 +102,71 @@ __device__ __forceinline__ void tma_bulk_g2s(uint32_t dst_smem, const void* src_
         : "memory");
 }
 
+// Tiled TMA copy (4-D tensor map, no multicast): one box lands in shared memory with the swizzle
+// recorded in the map.  The innermost coordinate times the element size must be a multiple of 16.
+__device__ __forceinline__ void tma_tile4d_g2s(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
+                                               int c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst_smem), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- warp-level matrix helpers (16-bit operands, fp32 accumulate) ---------------------------------
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// D(16x8) += A(16x16) * B(16x8) where rows 8..15 of A are zero: only the two accumulators of
+// rows 0..7 (c0, c1) are live; the other two stay zero and are discarded.
+template <typename T>
+__device__ __forceinline__ void mma_m16n8k16_top(float (&c)[2], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1);
+
+template <>
+__device__ __forceinline__ void mma_m16n8k16_top<__nv_bfloat16>(float (&c)[2], uint32_t a0, uint32_t a2, uint32_t b0,
+                                                                uint32_t b1) {
+    float d2, d3;   // rows 8..15 of the tile: always zero, discarded
+    (void)d2; (void)d3;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %10, %10};"
+        : "+f"(c[0]), "+f"(c[1]), "=f"(d2), "=f"(d3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+template <>
+__device__ __forceinline__ void mma_m16n8k16_top<__half>(float (&c)[2], uint32_t a0, uint32_t a2, uint32_t b0,
+                                                         uint32_t b1) {
+    float d2, d3;   // rows 8..15 of the tile: always zero, discarded
+    (void)d2; (void)d3;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %10, %10};"
+        : "+f"(c[0]), "+f"(c[1]), "=f"(d2), "=f"(d3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
 // ---- small numeric helpers -------------------------------------------------------------------
 
 __device__ __forceinline__ float warp_max_f32(float v) {

@@ -28,7 +28,11 @@
 // flag, the status word gets IVAB_STATUS_WAIT_TIMEOUT and every warp unwinds.  Intra-CTA
 // synchronisation uses mbarriers only (no bar.sync), so a warp that unwinds can never leave
 // another one stuck at a barrier.
+#include <cuda.h>
+
 #include <atomic>
+#include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -242,7 +246,7 @@ struct Cfg {
     static constexpr int OFF_P = OFF_ITEMS + kItemRing * 32;            // [W][G][kPage] floats
     static constexpr int OFF_MRG_ML = OFF_P + kConsumerWarps * G * kPage * 4;       // [W][G][2]
     static constexpr int OFF_MRG_O = OFF_MRG_ML + kConsumerWarps * G * 2 * 4;       // [W][G][D]
-    static constexpr int OFF_STAGES = (OFF_MRG_O + kConsumerWarps * G * D * 4 + 127) / 128 * 128;
+    static constexpr int OFF_STAGES = (OFF_MRG_O + kConsumerWarps * G * D * 4 + 1023) / 1024 * 1024;  // swizzled tiles need 1 KB alignment
     static constexpr int CTAS_PER_SM = (G >= 8) ? 1 : 2;
 };
 
@@ -281,10 +285,296 @@ __device__ __forceinline__ int owned_index(int lane) {
     return idx;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Page engines: what a consumer warp does with one staged K/V page.
+//
+//   SimtEngine  CUDA cores.  Lanes own 16-byte vectors of a row; scores come from a transposing
+//               shuffle reduction.  Pages are staged by one untiled TMA bulk copy each (row-major).
+//               Used for fp32 and for multi-head attention (one query head per KV head), where
+//               the kernel is HBM-bound at ~1/3 issue utilisation.
+//   MmaEngine   Tensor cores for grouped-query attention with 16-bit K/V.  With G >= 2 query heads
+//               per KV head the CUDA-core path becomes issue-bound (4 flop/byte, ~52 % issue
+//               utilisation at 46 % DRAM in ncu), so the G heads form the M side of
+//               mma.sync.m16n8k16 tiles: S^T[head, token] = Q K^T, then O[head, dim] += P^T V.
+//               Pages are staged by tiled TMA copies (64-element column tiles, 128-byte swizzle)
+//               so that ldmatrix / ldmatrix.trans read them without bank conflicts.  Putting heads
+//               on M makes the S^T accumulator fragment identical to the A fragment of the second
+//               product: P never moves between lanes.
+//
+// Both engines leave the same per-warp state in shared memory (m in log2 units, l, o[G][D]) so
+// the merge / epilogue code of the kernel is shared.
+// ------------------------------------------------------------------------------------------------
+
 template <typename T, int D, int G>
-__global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_kernel(const DecodeParams p) {
+struct SimtEngine {
     using C = Cfg<T, D, G>;
-    extern __shared__ __align__(128) unsigned char smem[];
+    static constexpr bool kTiled = false;
+    static constexpr int PAGE_BYTES = C::PAGE_BYTES;
+    static constexpr int STAGE_BYTES = C::STAGE_BYTES;
+
+    float qf[G][C::EPL];
+    float m_run[G], l_run[G], acc[G][C::EPL];
+    int r, c, own_tok;
+    bool owner;
+
+    __device__ __forceinline__ void setup(int lane) {
+        r = lane / C::LPR;             // which of the RPI rows of a warp-wide load this lane reads
+        c = lane % C::LPR;             // which 16-byte vector of the row
+        own_tok = owned_index<C::NV, C::LPR>(c) * C::RPI + r;   // token whose score this lane ends up owning
+        owner = (c & (C::DUP - 1)) == 0;                        // one lane of each duplicate group
+    }
+
+    __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
+        const T* qg = static_cast<const T*>(p.q);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const T* qp = qg + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh + c * C::EPL;
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(qp));
+            Elt<T>::unpack(u, qf[g]);
+#pragma unroll
+            for (int e = 0; e < C::EPL; ++e) qf[g][e] *= p.scale_log2;   // scores in base-2 units
+            m_run[g] = -INFINITY; l_run[g] = 0.f;
+#pragma unroll
+            for (int e = 0; e < C::EPL; ++e) acc[g][e] = 0.f;
+        }
+    }
+
+    __device__ __forceinline__ void page(const DecodeParams&, const unsigned char* stage, int n_valid, int lane,
+                                         float* p_smem) {
+        const uint4* kp = reinterpret_cast<const uint4*>(stage) + lane;
+        const uint4* vp = kp + C::PAGE_BYTES / 16;
+        // ---- scores: q . k for the page's 16 tokens, all G heads
+        float sc[G][C::NV];
+#pragma unroll
+        for (int i = 0; i < C::NV; ++i) {
+            const uint4 u = kp[i * 32];
+            float kf[C::EPL];
+            Elt<T>::unpack(u, kf);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float a = 0.f;
+#pragma unroll
+                for (int e = 0; e < C::EPL; ++e) a = fmaf(qf[g][e], kf[e], a);
+                sc[g][i] = a;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float s = transpose_reduce<C::NV, C::LPR / 2>(sc[g], c);
+            if (own_tok >= n_valid) s = -INFINITY;       // select, not arithmetic: stale slots may hold NaN
+            const float m_page = warp_max_f32(s);
+            if (m_page > m_run[g]) {                     // warp-uniform
+                const float alpha = fast_exp2(m_run[g] - m_page);
+                l_run[g] *= alpha;
+#pragma unroll
+                for (int e = 0; e < C::EPL; ++e) acc[g][e] *= alpha;
+                m_run[g] = m_page;
+            }
+            const float pr = fast_exp2(s - m_run[g]);
+            if (owner) { l_run[g] += pr; p_smem[g * kPage + own_tok] = pr; }
+        }
+        __syncwarp();
+        // ---- weighted sum of V
+        if (n_valid == kPage) {
+#pragma unroll
+            for (int i = 0; i < C::NV; ++i) {
+                const uint4 u = vp[i * 32];
+                float vf[C::EPL];
+                Elt<T>::unpack(u, vf);
+                const int tok = i * C::RPI + r;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pg = p_smem[g * kPage + tok];
+#pragma unroll
+                    for (int e = 0; e < C::EPL; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
+                }
+            }
+        } else {
+            // last page of the sequence: rows past ctx_len are skipped, never multiplied
+#pragma unroll
+            for (int i = 0; i < C::NV; ++i) {
+                const int tok = i * C::RPI + r;
+                if (tok < n_valid) {
+                    const uint4 u = vp[i * 32];
+                    float vf[C::EPL];
+                    Elt<T>::unpack(u, vf);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float pg = p_smem[g * kPage + tok];
+#pragma unroll
+                        for (int e = 0; e < C::EPL; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // fold the row groups of this warp and publish (m, l, o) of every head
+    __device__ __forceinline__ void publish(const DecodeParams&, float* my_ml, float* my_o, int lane) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int off = C::LPR; off < 32; off <<= 1) {
+#pragma unroll
+                for (int e = 0; e < C::EPL; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+            }
+            l_run[g] = warp_sum_f32(l_run[g]);
+        }
+        if (r == 0) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+#pragma unroll
+                for (int e = 0; e < C::EPL; ++e) my_o[g * D + c * C::EPL + e] = acc[g][e];
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) { my_ml[g * 2] = m_run[g]; my_ml[g * 2 + 1] = l_run[g]; }
+        }
+    }
+};
+
+template <typename T, int D, int G>
+struct MmaEngine {
+    static_assert(sizeof(T) == 2 && D % 64 == 0 && G >= 1 && G <= 8, "tensor-core engine: 16-bit K/V, D % 64 == 0, G <= 8");
+    static constexpr bool kTiled = true;
+    static constexpr int TILES = D / 64;               // 64-element (128-byte) column tiles per row
+    static constexpr int TILE_BYTES = kPage * 128;     // 16 rows x 128 B, swizzled in 16-byte units
+    static constexpr int PAGE_BYTES = TILES * TILE_BYTES;
+    static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+    static constexpr int KSTEPS = D / 16;              // k-steps of Q K^T
+    static constexpr int NBLK = D / 8;                 // 8-wide output blocks of P^T V
+
+    uint32_t qa[KSTEPS][2];    // A fragments of Q: head lane/4; rows 8..15 of the tile are zero
+    float o[NBLK][2];          // head lane/4, dims 8j + 2*(lane%4) + {0,1}
+    float m_run, l_run;        // running max (raw score units) and this lane's share of the sum
+
+    __device__ __forceinline__ void setup(int) {}
+
+    __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
+        const int g = lane >> 2, c = lane & 3;
+        if (g < G) {
+            const T* qrow = static_cast<const T*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh;
+#pragma unroll
+            for (int s = 0; s < KSTEPS; ++s) {
+                qa[s][0] = __ldg(reinterpret_cast<const uint32_t*>(qrow + 16 * s + 2 * c));
+                qa[s][1] = __ldg(reinterpret_cast<const uint32_t*>(qrow + 16 * s + 2 * c + 8));
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < KSTEPS; ++s) qa[s][0] = qa[s][1] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < NBLK; ++j) o[j][0] = o[j][1] = 0.f;
+        m_run = -INFINITY;
+        l_run = 0.f;
+    }
+
+    // byte offset of 16-byte chunk `q` (0 .. D/8-1) of row `token` inside a swizzled page
+    __device__ __forceinline__ static uint32_t chunk_off(int token, int q) {
+        return (uint32_t)((q >> 3) * TILE_BYTES + token * 128 + (((q & 7) ^ (token & 7)) << 4));
+    }
+
+    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int lane, float*) {
+        const uint32_t kbase = smem_u32(stage);
+        const uint32_t vbase = kbase + PAGE_BYTES;
+        const int c = lane & 3;
+        const int mi = lane >> 3, rr = lane & 7;   // ldmatrix: this lane addresses row rr of matrix mi
+
+        if (n_valid < kPage) {
+            // Last page of the sequence: rows past ctx_len may hold stale bits (NaN included).  Their
+            // weights are exactly zero, but 0 * NaN is NaN inside the MMA, so clear those V rows.
+            const int n_vec = (kPage - n_valid) * 8;                       // 16-byte chunks per tile
+            for (int t = 0; t < TILES; ++t)
+                for (int i = lane; i < n_vec; i += 32)
+                    *reinterpret_cast<uint4*>(stage + PAGE_BYTES + t * TILE_BYTES + n_valid * 128 + i * 16) =
+                        make_uint4(0, 0, 0, 0);
+            __syncwarp();
+        }
+
+        // ---- S^T[head, token] = Q K^T : two 8-token column blocks, KSTEPS k-steps each
+        float s[2][2];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+            s[nb][0] = s[nb][1] = 0.f;
+            const int token = nb * 8 + rr;
+#pragma unroll
+            for (int sp = 0; sp < KSTEPS / 2; ++sp) {
+                uint32_t b[4];
+                ldmatrix_x4(kbase + chunk_off(token, 4 * sp + mi), b);     // k-steps 2sp (b0,b1) and 2sp+1 (b2,b3)
+                mma_m16n8k16_top<T>(s[nb], qa[2 * sp][0], qa[2 * sp][1], b[0], b[1]);
+                mma_m16n8k16_top<T>(s[nb], qa[2 * sp + 1][0], qa[2 * sp + 1][1], b[2], b[3]);
+            }
+        }
+        // this lane: head lane/4, tokens 2c, 2c+1 (block 0) and 8+2c, 9+2c (block 1)
+        if (n_valid < kPage) {
+            if (2 * c >= n_valid) s[0][0] = -INFINITY;
+            if (2 * c + 1 >= n_valid) s[0][1] = -INFINITY;
+            if (8 + 2 * c >= n_valid) s[1][0] = -INFINITY;
+            if (9 + 2 * c >= n_valid) s[1][1] = -INFINITY;
+        }
+        float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float sl2 = p.scale_log2;
+        if (__any_sync(0xffffffffu, m_new > m_run)) {
+            const float alpha = fast_exp2((m_run - m_new) * sl2);          // exp2(-inf) = 0 on the first page
+            l_run *= alpha;
+#pragma unroll
+            for (int j = 0; j < NBLK; ++j) { o[j][0] *= alpha; o[j][1] *= alpha; }
+            m_run = m_new;
+        }
+        const float msl = m_run * sl2;
+        const float p0 = fast_exp2(fmaf(s[0][0], sl2, -msl)), p1 = fast_exp2(fmaf(s[0][1], sl2, -msl));
+        const float p2 = fast_exp2(fmaf(s[1][0], sl2, -msl)), p3 = fast_exp2(fmaf(s[1][1], sl2, -msl));
+        l_run += (p0 + p1) + (p2 + p3);
+        // The S^T accumulator layout (row = head, cols = tokens 2c, 2c+1) is the A-fragment layout of
+        // the next product: a0a1 = tokens 2c,2c+1, a4a5 = tokens 8+2c, 9+2c.
+        const uint32_t pa0 = pack2<T>(p0, p1), pa2 = pack2<T>(p2, p3);
+
+        // ---- O[head, dim] += P^T V : NBLK 8-wide blocks, one k-step of 16 tokens
+        const int vtok = (mi & 1) * 8 + rr;
+#pragma unroll
+        for (int jp = 0; jp < NBLK / 2; ++jp) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(vbase + chunk_off(vtok, 2 * jp + (mi >> 1)), b);   // blocks 2jp (b0,b1), 2jp+1 (b2,b3)
+            mma_m16n8k16_top<T>(o[2 * jp], pa0, pa2, b[0], b[1]);
+            mma_m16n8k16_top<T>(o[2 * jp + 1], pa0, pa2, b[2], b[3]);
+        }
+        if (n_valid < kPage) fence_proxy_async_smem();   // order the row clearing before the next TMA write
+        __syncwarp();
+    }
+
+    __device__ __forceinline__ void publish(const DecodeParams& p, float* my_ml, float* my_o, int lane) {
+        const int g = lane >> 2, c = lane & 3;
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        if (g < G) {
+#pragma unroll
+            for (int j = 0; j < NBLK; ++j)
+                *reinterpret_cast<float2*>(my_o + g * D + 8 * j + 2 * c) = make_float2(o[j][0], o[j][1]);
+            if (c == 0) {
+                my_ml[g * 2] = (m_run == -INFINITY) ? -INFINITY : m_run * p.scale_log2;
+                my_ml[g * 2 + 1] = l_run;
+            }
+        }
+    }
+};
+
+struct alignas(64) TensorMaps {
+    CUtensorMap k, v;   // 4-D maps of the K and V pools: (dim, token in page, page, head)
+};
+
+template <typename T, int D, int G, bool TC>
+__global__ void __launch_bounds__(kThreads, TC ? 2 : Cfg<T, D, G>::CTAS_PER_SM)
+decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ TensorMaps tm) {
+    using C = Cfg<T, D, G>;
+    using Eng = std::conditional_t<TC, MmaEngine<T, D, G>, SimtEngine<T, D, G>>;
+    extern __shared__ unsigned char smem_raw[];
+    // the carve-up assumes a 1 KB-aligned base; the launch reserves 1 KB of slack for this
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
 
@@ -378,11 +668,20 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
                         aborted = true; break;
                     }
                     if (lane == 0) {
-                        const uint32_t dst = smem_u32(stage_base + (size_t)stage * C::STAGE_BYTES);
-                        mbar_arrive_expect_tx(bar_full(stage), C::STAGE_BYTES);
-                        tma_bulk_g2s(dst, kbase + (int64_t)pid * p.pool_sp_bytes, C::PAGE_BYTES, bar_full(stage));
-                        tma_bulk_g2s(dst + C::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes, C::PAGE_BYTES,
-                                     bar_full(stage));
+                        const uint32_t dst = smem_u32(stage_base + (size_t)stage * Eng::STAGE_BYTES);
+                        mbar_arrive_expect_tx(bar_full(stage), Eng::STAGE_BYTES);
+                        if constexpr (Eng::kTiled) {
+#pragma unroll
+                            for (int t = 0; t < Eng::TILES; ++t) {
+                                tma_tile4d_g2s(dst + t * Eng::TILE_BYTES, &tm.k, t * 64, 0, pid, h, bar_full(stage));
+                                tma_tile4d_g2s(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * 64, 0, pid, h,
+                                               bar_full(stage));
+                            }
+                        } else {
+                            tma_bulk_g2s(dst, kbase + (int64_t)pid * p.pool_sp_bytes, Eng::PAGE_BYTES, bar_full(stage));
+                            tma_bulk_g2s(dst + Eng::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes,
+                                         Eng::PAGE_BYTES, bar_full(stage));
+                        }
                     }
                 }
             }
@@ -406,16 +705,12 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
     }
 
     // ---------------------------------- consumer warps --------------------------------------------
-    const int r = lane / C::LPR;             // which of the RPI rows of a warp-wide load this lane reads
-    const int c = lane % C::LPR;             // which 16-byte vector of the row
-    const int own_iter = owned_index<C::NV, C::LPR>(c);
-    const int own_tok = own_iter * C::RPI + r;                 // token (within a page) whose score this lane owns
-    const bool owner = (c & (C::DUP - 1)) == 0;                // one lane of each duplicate group
     float* p_smem = reinterpret_cast<float*>(smem + C::OFF_P) + warp * (G * kPage);
     float* mrg_ml = reinterpret_cast<float*>(smem + C::OFF_MRG_ML);
     float* mrg_o = reinterpret_cast<float*>(smem + C::OFF_MRG_O);
-    const T* qg = static_cast<const T*>(p.q);
     T* outg = static_cast<T*>(p.out);
+    Eng eng;
+    eng.setup(lane);
 
     const int spw = stages / kConsumerWarps;   // stages of this warp's sub-ring
     int taken = 0;      // pages this warp has consumed so far (position in its sub-ring)
@@ -430,130 +725,24 @@ __global__ void __launch_bounds__(kThreads, Cfg<T, D, G>::CTAS_PER_SM) decode_ke
         if (lane == 0) mbar_arrive(bar_item_empty(slot));
         if (n_pages < 0) break;   // sentinel: the work list is exhausted
 
-        // query heads of this kv head, pre-scaled, as fp32 in registers
-        float qf[G][C::EPL];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const T* qp = qg + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh + c * C::EPL;
-            const uint4 u = __ldg(reinterpret_cast<const uint4*>(qp));
-            Elt<T>::unpack(u, qf[g]);
-#pragma unroll
-            for (int e = 0; e < C::EPL; ++e) qf[g][e] *= p.scale_log2;
-        }
-        float m_run[G], l_run[G], acc[G][C::EPL];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            m_run[g] = -INFINITY; l_run[g] = 0.f;
-#pragma unroll
-            for (int e = 0; e < C::EPL; ++e) acc[g][e] = 0.f;
-        }
+        eng.begin_item(p, seq, h, lane);   // query heads of this kv head into registers, state reset
 
         bool ok = true;
         const int k0 = (warp - start + kConsumerWarps) % kConsumerWarps;
         for (int k = k0; k < n_pages; k += kConsumerWarps, ++taken) {
             const int stage = (taken % spw) * kConsumerWarps + warp;
             if (!mbar_wait_bounded(bar_full(stage), (taken / spw) & 1, abort_flag, limit)) { ok = false; break; }
-            const uint4* kp = reinterpret_cast<const uint4*>(stage_base + (size_t)stage * C::STAGE_BYTES) + lane;
-            const uint4* vp = kp + C::PAGE_BYTES / 16;
             const int n_valid = min(kPage, L - (page_begin + k) * kPage);
-
-            // ---- scores: q . k for the page's 16 tokens, all G heads
-            float sc[G][C::NV];
-#pragma unroll
-            for (int i = 0; i < C::NV; ++i) {
-                const uint4 u = kp[i * 32];
-                float kf[C::EPL];
-                Elt<T>::unpack(u, kf);
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    float a = 0.f;
-#pragma unroll
-                    for (int e = 0; e < C::EPL; ++e) a = fmaf(qf[g][e], kf[e], a);
-                    sc[g][i] = a;
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float s = transpose_reduce<C::NV, C::LPR / 2>(sc[g], c);
-                if (own_tok >= n_valid) s = -INFINITY;       // select, not arithmetic: stale slots may hold NaN
-                const float m_page = warp_max_f32(s);
-                if (m_page > m_run[g]) {                     // warp-uniform
-                    const float alpha = fast_exp2(m_run[g] - m_page);
-                    l_run[g] *= alpha;
-#pragma unroll
-                    for (int e = 0; e < C::EPL; ++e) acc[g][e] *= alpha;
-                    m_run[g] = m_page;
-                }
-                const float pr = fast_exp2(s - m_run[g]);
-                if (owner) { l_run[g] += pr; p_smem[g * kPage + own_tok] = pr; }
-            }
-            __syncwarp();
-
-            // ---- weighted sum of V
-            if (n_valid == kPage) {
-#pragma unroll
-                for (int i = 0; i < C::NV; ++i) {
-                    const uint4 u = vp[i * 32];
-                    float vf[C::EPL];
-                    Elt<T>::unpack(u, vf);
-                    const int tok = i * C::RPI + r;
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        const float pg = p_smem[g * kPage + tok];
-#pragma unroll
-                        for (int e = 0; e < C::EPL; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
-                    }
-                }
-            } else {
-                // last page of the sequence: rows past ctx_len are skipped, never multiplied
-#pragma unroll
-                for (int i = 0; i < C::NV; ++i) {
-                    const int tok = i * C::RPI + r;
-                    if (tok < n_valid) {
-                        const uint4 u = vp[i * 32];
-                        float vf[C::EPL];
-                        Elt<T>::unpack(u, vf);
-#pragma unroll
-                        for (int g = 0; g < G; ++g) {
-                            const float pg = p_smem[g * kPage + tok];
-#pragma unroll
-                            for (int e = 0; e < C::EPL; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
-                        }
-                    }
-                }
-            }
-            __syncwarp();
+            eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, lane, p_smem);
             if (lane == 0) mbar_arrive(bar_empty(stage));
         }
         if (!ok) break;
 
-        // ---- fold the row groups of this warp, then publish the warp's state
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-#pragma unroll
-            for (int off = C::LPR; off < 32; off <<= 1) {
-#pragma unroll
-                for (int e = 0; e < C::EPL; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], off);
-            }
-            l_run[g] = warp_sum_f32(l_run[g]);
-        }
         // The merge scratch is shared by consecutive items: wait until every warp has finished
         // reading the previous item's states before overwriting them.
         if (consumed > 0 &&
             !mbar_wait_bounded(bar_merge(1), (consumed - 1) & 1, abort_flag, limit)) break;
-        float* my_ml = mrg_ml + (warp * G) * 2;
-        float* my_o = mrg_o + (size_t)(warp * G) * D;
-        if (r == 0) {
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-#pragma unroll
-                for (int e = 0; e < C::EPL; ++e) my_o[g * D + c * C::EPL + e] = acc[g][e];
-            }
-        }
-        if (lane == 0) {
-#pragma unroll
-            for (int g = 0; g < G; ++g) { my_ml[g * 2] = m_run[g]; my_ml[g * 2 + 1] = l_run[g]; }
-        }
+        eng.publish(p, mrg_ml + (warp * G) * 2, mrg_o + (size_t)(warp * G) * D, lane);
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_merge(0));
         if (!mbar_wait_bounded(bar_merge(0), consumed & 1, abort_flag, limit)) break;
@@ -647,9 +836,59 @@ __global__ void __launch_bounds__(128) merge_kernel(int B, int Hq, int G, int D,
 // host side
 // ------------------------------------------------------------------------------------------------
 
-template <typename T, int D, int G>
-int launch_decode(const DecodeParams& p0, int B, cudaStream_t st) {
+// cuTensorMapEncodeTiled is a driver entry point; it is looked up through the runtime so that the
+// library does not link against libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// 4-D map of a page pool: (head_dim, token in page, page, kv head); box = one 64-element column tile
+// of one page (16 rows x 128 bytes), 128-byte swizzle.  Returns false if the driver rejects the
+// geometry (the caller then uses the CUDA-core engine).
+bool encode_pool_map(CUtensorMap* tm, const void* pool, bool bf16, int64_t D, int64_t num_pages, int64_t Hkv,
+                     int64_t sp_bytes, int64_t sh_bytes) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[4] = {(cuuint64_t)D, (cuuint64_t)kPage, (cuuint64_t)num_pages, (cuuint64_t)Hkv};
+    const cuuint64_t gstride[3] = {(cuuint64_t)(D * 2), (cuuint64_t)sp_bytes, (cuuint64_t)sh_bytes};
+    const cuuint32_t box[4] = {64, (cuuint32_t)kPage, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                          const_cast<void*>(pool), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Smallest q_heads/kv_heads ratio that takes the tensor-core engine (16-bit K/V only).  Multi-head
+// attention (ratio 1) stays on CUDA cores, where it is HBM-bound; IVAB_TC_MIN_GROUP overrides the
+// threshold for experiments (1 = always, 99 = never).
+int tc_min_group() {
+    static int v = [] {
+        const char* e = std::getenv("IVAB_TC_MIN_GROUP");
+        const int n = e ? std::atoi(e) : 2;
+        return n < 1 ? 1 : n;
+    }();
+    return v;
+}
+
+template <typename T, int D, int G, bool TC>
+int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStream_t st) {
     using C = Cfg<T, D, G>;
+    using Eng = std::conditional_t<TC, MmaEngine<T, D, G>, SimtEngine<T, D, G>>;
+    constexpr int kCtas = TC ? 2 : C::CTAS_PER_SM;
     DecodeParams p = p0;
     int dev = 0;
     if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
@@ -659,10 +898,10 @@ int launch_decode(const DecodeParams& p0, int B, cudaStream_t st) {
     int per_sm = 0;
     if (int rc = check_cuda(cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev),
                             "cudaDeviceGetAttribute")) return rc;
-    // each resident CTA also pays 1 KB of system-reserved shared memory
-    int budget = per_sm / C::CTAS_PER_SM - 1024;
+    // each resident CTA also pays 1 KB of system-reserved shared memory; 1 KB more is alignment slack
+    int budget = per_sm / kCtas - 1024;
     if (budget > max_optin) budget = max_optin;
-    int stages = (budget - C::OFF_STAGES) / C::STAGE_BYTES;
+    int stages = (budget - C::OFF_STAGES - 1024) / Eng::STAGE_BYTES;
     if (stages > kMaxStages) stages = kMaxStages;
     // Pages go to consumer warps round-robin.  With a stage count that is a multiple of the warp
     // count, a stage is always consumed by the same warp, so a warp waiting for the next phase of a
@@ -670,16 +909,16 @@ int launch_decode(const DecodeParams& p0, int B, cudaStream_t st) {
     stages -= stages % kConsumerWarps;
     if (stages < kConsumerWarps) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for the stage ring");
     p.stages = stages;
-    const size_t smem = (size_t)C::OFF_STAGES + (size_t)stages * C::STAGE_BYTES;
-    auto kern = decode_kernel<T, D, G>;
+    const size_t smem = (size_t)C::OFF_STAGES + 1024 + (size_t)stages * Eng::STAGE_BYTES;
+    auto kern = decode_kernel<T, D, G, TC>;
     static bool configured[64] = {false};
     if (dev < 64 && !configured[dev]) {
         if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin),
                                 "cudaFuncSetAttribute")) return rc;
         configured[dev] = true;
     }
-    const int grid = sm_count() * C::CTAS_PER_SM;
-    kern<<<grid, kThreads, smem, st>>>(p);
+    const int grid = sm_count() * kCtas;
+    kern<<<grid, kThreads, smem, st>>>(p, tm);
     g_launches++;
     if (int rc = check_cuda(cudaGetLastError(), "decode_kernel launch")) return rc;
 
@@ -689,25 +928,39 @@ int launch_decode(const DecodeParams& p0, int B, cudaStream_t st) {
     return check_cuda(cudaGetLastError(), "merge_kernel launch");
 }
 
+template <typename T, int D, int G>
+int choose_engine(const DecodeParams& p, int B, int Hkv, cudaStream_t st) {
+    TensorMaps tm{};
+    if constexpr (sizeof(T) == 2 && D % 64 == 0) {
+        if (G >= tc_min_group() && p.scale_log2 > 0.f &&
+            encode_pool_map(&tm.k, p.k_pool, std::is_same<T, __nv_bfloat16>::value, D, p.num_pages, Hkv,
+                            p.pool_sp_bytes, p.pool_sh_bytes) &&
+            encode_pool_map(&tm.v, p.v_pool, std::is_same<T, __nv_bfloat16>::value, D, p.num_pages, Hkv,
+                            p.pool_sp_bytes, p.pool_sh_bytes))
+            return launch_decode<T, D, G, true>(p, tm, B, st);
+    }
+    return launch_decode<T, D, G, false>(p, tm, B, st);
+}
+
 template <typename T, int D>
-int dispatch_group(int G, const DecodeParams& p, int B, cudaStream_t st) {
+int dispatch_group(int G, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
     switch (G) {
-        case 1: return launch_decode<T, D, 1>(p, B, st);
-        case 2: return launch_decode<T, D, 2>(p, B, st);
-        case 4: return launch_decode<T, D, 4>(p, B, st);
-        case 8: return launch_decode<T, D, 8>(p, B, st);
+        case 1: return choose_engine<T, D, 1>(p, B, Hkv, st);
+        case 2: return choose_engine<T, D, 2>(p, B, Hkv, st);
+        case 4: return choose_engine<T, D, 4>(p, B, Hkv, st);
+        case 8: return choose_engine<T, D, 8>(p, B, Hkv, st);
         default: return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: q_heads/kv_heads = %d (supported: 1, 2, 4, 8)", G);
     }
 }
 
 template <typename T>
-int dispatch_dim(int D, int G, const DecodeParams& p, int B, cudaStream_t st) {
+int dispatch_dim(int D, int G, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
     switch (D) {
-        case 32: return dispatch_group<T, 32>(G, p, B, st);
-        case 64: return dispatch_group<T, 64>(G, p, B, st);
-        case 128: return dispatch_group<T, 128>(G, p, B, st);
+        case 32: return dispatch_group<T, 32>(G, Hkv, p, B, st);
+        case 64: return dispatch_group<T, 64>(G, Hkv, p, B, st);
+        case 128: return dispatch_group<T, 128>(G, Hkv, p, B, st);
         case 256:
-            if constexpr (sizeof(T) == 2) return dispatch_group<T, 256>(G, p, B, st);
+            if constexpr (sizeof(T) == 2) return dispatch_group<T, 256>(G, Hkv, p, B, st);
             [[fallthrough]];
         default:
             return set_error(IVAB_ERR_UNSUPPORTED,
@@ -792,9 +1045,9 @@ extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t
     p.ws = ws;
     const int G = (int)(q_heads / kv_heads);
     switch (dtype) {
-        case IVAB_F32: return dispatch_dim<float>((int)head_dim, G, p, (int)batch, st);
-        case IVAB_F16: return dispatch_dim<__half>((int)head_dim, G, p, (int)batch, st);
-        default: return dispatch_dim<__nv_bfloat16>((int)head_dim, G, p, (int)batch, st);
+        case IVAB_F32: return dispatch_dim<float>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
+        case IVAB_F16: return dispatch_dim<__half>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
+        default: return dispatch_dim<__nv_bfloat16>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
     }
 }
 

@@ -1,0 +1,43 @@
+"""Both page engines of the decode kernel on the same inputs.  The engine is chosen per call from
+the head-group size; IVAB_TC_MIN_GROUP (read once per process) moves the threshold, so each
+setting runs in a child process."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CHILD = r"""
+import sys, torch
+sys.path.insert(0, {root!r}); sys.path.insert(0, {root!r} + "/tests")
+import iva_b200
+from iva_b200 import workloads
+from oracle import paged_ref as ref
+from util import assert_attn_close, assert_lse_close
+for dtype in (torch.bfloat16, torch.float16):
+    for hq, hkv, D in ((4, 4, 128), (8, 2, 128), (16, 2, 64), (8, 4, 256)):
+        ctx = torch.tensor([0, 1, 15, 16, 17, 100, 333, 2500])
+        wl = workloads.make_decode_workload("eng", ctx, n_q_heads=hq, n_kv_heads=hkv, head_dim=D, dtype=dtype,
+                                            seed=hq + D, free_frac=0.3, poison_unused=True)
+        _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
+        d = wl.to("cuda")
+        iva_b200.paged_append(d.k_pool, d.v_pool, d.slot_mapping, d.k_new, d.v_new, 16, check=True)
+        out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, (d.ctx_len + 1).contiguous(),
+                                                   16, return_lse=True, check=True)
+        assert_attn_close(out, out_ref, dtype, strict=False)
+        assert_lse_close(lse, lse_ref)
+print("engines ok")
+"""
+
+
+@pytest.mark.parametrize("min_group", ["1", "2", "99"])
+def test_engine_threshold(min_group):
+    """1: tensor-core engine even for multi-head attention; 2: the default split; 99: CUDA cores only."""
+    env = dict(os.environ, IVAB_TC_MIN_GROUP=min_group)
+    res = subprocess.run([sys.executable, "-c", CHILD.format(root=ROOT)], env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert res.returncode == 0 and "engines ok" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
