@@ -167,6 +167,14 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t u);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+
 // ---- small numeric helpers -------------------------------------------------------------------
 
 __device__ __forceinline__ float warp_max_f32(float v) {

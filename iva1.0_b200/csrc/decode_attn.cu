@@ -532,7 +532,12 @@ struct MmaEngine {
         l_run += (p0 + p1) + (p2 + p3);
         // The S^T accumulator layout (row = head, cols = tokens 2c, 2c+1) is the A-fragment layout of
         // the next product: a0a1 = tokens 2c,2c+1, a4a5 = tokens 8+2c, 9+2c.
+        // The weights are carried as a 16-bit value plus a 16-bit correction (p = hi + lo), two MMAs
+        // per block, so that P^T V is accurate to ~2^-17 instead of the 2^-9 of a single bf16 rounding
+        // (which alone would exceed the 2e-3 output tolerance on contexts of a few tokens).
         const uint32_t pa0 = pack2<T>(p0, p1), pa2 = pack2<T>(p2, p3);
+        const float2 h01 = unpack2<T>(pa0), h23 = unpack2<T>(pa2);
+        const uint32_t pb0 = pack2<T>(p0 - h01.x, p1 - h01.y), pb2 = pack2<T>(p2 - h23.x, p3 - h23.y);
 
         // ---- O[head, dim] += P^T V : NBLK 8-wide blocks, one k-step of 16 tokens
         const int vtok = (mi & 1) * 8 + rr;
@@ -542,6 +547,8 @@ struct MmaEngine {
             ldmatrix_x4_trans(vbase + chunk_off(vtok, 2 * jp + (mi >> 1)), b);   // blocks 2jp (b0,b1), 2jp+1 (b2,b3)
             mma_m16n8k16_top<T>(o[2 * jp], pa0, pa2, b[0], b[1]);
             mma_m16n8k16_top<T>(o[2 * jp + 1], pa0, pa2, b[2], b[3]);
+            mma_m16n8k16_top<T>(o[2 * jp], pb0, pb2, b[0], b[1]);
+            mma_m16n8k16_top<T>(o[2 * jp + 1], pb0, pb2, b[2], b[3]);
         }
         if (n_valid < kPage) fence_proxy_async_smem();   // order the row clearing before the next TMA write
         __syncwarp();
