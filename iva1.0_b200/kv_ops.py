@@ -219,12 +219,13 @@ def paged_gather(pool: torch.Tensor, block_table: torch.Tensor, ctx_len: torch.T
     else:
         offs = out_offsets.to(device=dev, dtype=torch.int64).contiguous()
     # (an empty result still needs a real base pointer for the library's argument check)
-    out = torch.empty(max(total_tokens, 1), H, D, device=dev, dtype=pool.dtype)[:total_tokens]
+    buf = torch.empty(max(total_tokens, 1), H, D, device=dev, dtype=pool.dtype)
+    out = buf[:total_tokens]
     status = _status_word(dev)
     with torch.cuda.device(dev):
         _lib.check(lib.ivab_paged_gather(
             pool.data_ptr(), sh, sp, bt.data_ptr(), bt.stride(0), cl.data_ptr(), offs.data_ptr(),
-            out.data_ptr(), _lib.OUT_HEAD_MAJOR if layout == "head_major" else _lib.OUT_TOKEN_MAJOR,
+            buf.data_ptr(), _lib.OUT_HEAD_MAJOR if layout == "head_major" else _lib.OUT_TOKEN_MAJOR,
             _lib.dtype_code(pool.dtype), B, H, D, page_size, num_pages, bt.shape[1],
             status.data_ptr(), _lib.stream_ptr(dev)))
     _check_status(dev, check)
