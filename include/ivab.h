@@ -151,6 +151,38 @@ int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h
 int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream);
 
 /*
+ * ivab_paged_decode_attn without a workspace argument and without any allocation.
+ * (No counterpart in the reference: it exists for callers of this library that cannot allocate.)
+ *
+ * Some callers have no way to obtain device scratch at the point where they decode: a serving
+ * loop that handed out every byte of its memory budget at start-up, a plugin running inside a
+ * host that owns the allocator and does not expose it, or a latency-critical path that may not
+ * call cudaMalloc because it synchronises the whole device.  For them the split-K scratch is a
+ * fixed 8 MiB array inside the library image; every GPU that loads the library holds those
+ * 8 MiB until the process exits, whether or not this entry point is ever called.
+ *
+ * Arguments as ivab_paged_decode_attn; `status` (device int32, may be NULL) receives the
+ * IVAB_STATUS_* bits of this call on `stream`.  Limits and rules:
+ *   - the problem must fit: ivab_decode_workspace_bytes(batch, ...) <= 8 MiB, else
+ *     IVAB_ERR_WORKSPACE (e.g. 128 sequences x 32 query / 8 KV heads x head_dim 128 needs 6.9 MiB);
+ *   - calls no cudaMalloc / cudaFree or other allocating routine;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture;
+ *   - all calls on a device share the one array, which keeps the previous call's contents (the
+ *     kernels re-initialise what they read): two calls that overlap on the GPU -- different
+ *     streams, or different host threads -- race.  Serialise them.
+ */
+int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                   const void* k_pool, const void* v_pool,
+                                   int64_t pool_stride_head, int64_t pool_stride_page,
+                                   const int32_t* block_table, int64_t block_table_stride,
+                                   const int32_t* ctx_len,
+                                   void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                                   int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                   int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
+                                   int32_t* status, void* stream);
+
+/*
  * Number of kernels of this library launched by the calling process since load
  * (for benchmark bookkeeping).
  */

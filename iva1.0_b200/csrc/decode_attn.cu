@@ -1077,3 +1077,66 @@ extern "C" int ivab_selftest_bounded_wait(int32_t* status, int64_t limit_ns, voi
     g_launches++;
     return check_cuda(cudaGetLastError(), "bounded_wait_selftest_kernel launch");
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant: the scratch lives in the library image.
+// ------------------------------------------------------------------------------------------------
+
+// 8 MiB of device memory per GPU that loads this library, held until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the address
+// a kernel can use has to be asked for, once per device, with that device current.
+int static_scratch_ptr(unsigned char** out) {
+    static unsigned char* ptrs[64] = {nullptr};
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= 64) return set_error(IVAB_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        if (int rc = check_cuda(cudaGetSymbolAddress(&p, g_static_scratch), "cudaGetSymbolAddress(static scratch)"))
+            return rc;
+        if (p == nullptr) return set_error(IVAB_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        ptrs[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = ptrs[dev];
+    return IVAB_OK;
+}
+
+}  // namespace
+
+extern "C" int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                              const void* k_pool, const void* v_pool,
+                                              int64_t pool_stride_head, int64_t pool_stride_page,
+                                              const int32_t* block_table, int64_t block_table_stride,
+                                              const int32_t* ctx_len,
+                                              void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                                              int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                                              int64_t head_dim, int64_t page_size, int64_t num_pages,
+                                              int64_t max_pages_per_seq, float scale, int32_t* status, void* stream) {
+    const char* fn = "ivab_paged_decode_attn_noalloc";
+    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || q_heads % kv_heads)
+        return set_error(IVAB_ERR_INVALID, "%s: bad sizes", fn);
+    const size_t need = carve_workspace(nullptr, batch, q_heads, kv_heads, head_dim, nullptr);
+    if (need > kStaticScratchBytes)
+        return set_error(IVAB_ERR_WORKSPACE,
+                         "%s: this problem needs %zu bytes of scratch, the built-in buffer holds %zu; use "
+                         "ivab_paged_decode_attn with a caller-provided workspace", fn, need, kStaticScratchBytes);
+    unsigned char* scratch = nullptr;
+    if (int rc = static_scratch_ptr(&scratch)) return rc;
+    // Nothing in the scratch has to start at zero: the plan kernel rewrites the header (work counter,
+    // status word, chunk count) and every partial that is read was written by this call.
+    if (int rc = ivab_paged_decode_attn(q, q_stride_b, q_stride_h, k_pool, v_pool, pool_stride_head, pool_stride_page,
+                                        block_table, block_table_stride, ctx_len, out, out_stride_b, out_stride_h, lse,
+                                        dtype, batch, q_heads, kv_heads, head_dim, page_size, num_pages,
+                                        max_pages_per_seq, scale, scratch, kStaticScratchBytes, stream))
+        return rc;
+    if (status != nullptr && batch > 0)
+        return check_cuda(cudaMemcpyAsync(status, reinterpret_cast<int*>(scratch) + kHdrStatus, sizeof(int),
+                                          cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)),
+                          "cudaMemcpyAsync(status)");
+    return IVAB_OK;
+}
