@@ -74,8 +74,20 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 int resident_slots() { return sm_count() * 2; }
 
+// Work items per resident CTA the planner aims for.  More items = finer chunks = a shorter tail
+// when the last CTAs finish, at the price of more split-K partials.  IVAB_ITEMS_PER_SLOT overrides
+// the default for experiments (read once per process).
+int items_per_slot() {
+    static int v = [] {
+        const char* e = std::getenv("IVAB_ITEMS_PER_SLOT");
+        const int n = e ? std::atoi(e) : kItemsPerSlot;
+        return n < 1 ? 1 : (n > 64 ? 64 : n);
+    }();
+    return v;
+}
+
 int target_chunks_for(int64_t kv_heads) {
-    const int64_t items = (int64_t)resident_slots() * kItemsPerSlot;
+    const int64_t items = (int64_t)resident_slots() * items_per_slot();
     int64_t t = (items + kv_heads - 1) / kv_heads;
     return (int)(t < 1 ? 1 : t);
 }
@@ -795,48 +807,70 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
 // 3. logsumexp merge of split-K partials
 // ------------------------------------------------------------------------------------------------
 
-template <typename T>
-__global__ void __launch_bounds__(128) merge_kernel(int B, int Hq, int G, int D, Workspace ws, T* out, int64_t out_sb,
-                                                    int64_t out_sh, float* lse) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= B * Hq) return;
-    const int s = warp / Hq, hq = warp % Hq;
+constexpr int kMergeWarps = 8;
+
+// One CTA per (sequence, query head) that was split into several chunks.  Warp w folds chunks
+// w, w+8, ... (independent loads, unrolled), each lane owning D/32 consecutive dims; the eight warp
+// sums are then added in a fixed order, so the result does not depend on scheduling.
+template <typename T, int D>
+__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int Hq, int G, Workspace ws, T* out, int64_t out_sb,
+                                                                 int64_t out_sh, float* lse) {
+    constexpr int VPL = D / 32;   // dims per lane
+    const int s = blockIdx.x / Hq, hq = blockIdx.x % Hq;
     const int first = ws.seq_prefix[s];
     const int n = ws.seq_prefix[s + 1] - first;
     if (n <= 1) return;   // single-chunk sequences were written by the attention kernel
     const int num_chunks = ws.header[kHdrNumChunks];
     if (num_chunks == 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = hq / G, g = hq % G;
     const size_t item0 = (size_t)h * num_chunks + first;
+    const float* ml = ws.part_ml + (item0 * G + g) * 2;          // chunk j at ml + j*G*2
+    const float* po = ws.part_o + (item0 * G + g) * D + lane * VPL;   // chunk j at po + j*G*D
+
+    __shared__ float sh_m[kMergeWarps];
+    __shared__ float sh_l[kMergeWarps];
+    __shared__ float sh_o[kMergeWarps][D];
 
     float M = -INFINITY;
-    for (int j = lane; j < n; j += 32) M = fmaxf(M, ws.part_ml[((item0 + j) * G + g) * 2]);
+    for (int j = threadIdx.x; j < n; j += kMergeWarps * 32) M = fmaxf(M, ml[(size_t)j * G * 2]);
     M = warp_max_f32(M);
+    if (lane == 0) sh_m[warp] = M;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < kMergeWarps; ++w) M = fmaxf(M, sh_m[w]);
 
     float Lsum = 0.f;
-    float O[8];   // D <= 256
+    float acc[VPL];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) O[i] = 0.f;
-    for (int j = 0; j < n; ++j) {
-        const float mj = ws.part_ml[((item0 + j) * G + g) * 2];
-        const float lj = ws.part_ml[((item0 + j) * G + g) * 2 + 1];
+    for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+#pragma unroll 4
+    for (int j = warp; j < n; j += kMergeWarps) {
+        const float mj = ml[(size_t)j * G * 2];
+        const float lj = ml[(size_t)j * G * 2 + 1];
         const float f = (mj == -INFINITY) ? 0.f : fast_exp2(mj - M);
         Lsum = fmaf(lj, f, Lsum);
-        const float* po = ws.part_o + ((item0 + j) * G + g) * D;
+        const float* row = po + (size_t)j * G * D;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int dd = lane + 32 * i;
-            if (dd < D) O[i] = fmaf(po[dd], f, O[i]);
-        }
+        for (int i = 0; i < VPL; ++i) acc[i] = fmaf(row[i], f, acc[i]);
     }
-    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int dd = lane + 32 * i;
-        if (dd < D) Elt<T>::store(out + (int64_t)s * out_sb + (int64_t)hq * out_sh + dd, O[i] * inv);
+    for (int i = 0; i < VPL; ++i) sh_o[warp][lane * VPL + i] = acc[i];
+    if (lane == 0) sh_l[warp] = Lsum;
+    __syncthreads();
+
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMergeWarps; ++w) L += sh_l[w];
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int dd = threadIdx.x; dd < D; dd += kMergeWarps * 32) {
+        float O = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMergeWarps; ++w) O += sh_o[w][dd];
+        Elt<T>::store(out + (int64_t)s * out_sb + (int64_t)hq * out_sh + dd, O * inv);
     }
-    if (lane == 0 && lse != nullptr)
-        lse[(int64_t)s * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * 0.6931471805599453f : -INFINITY;
+    if (threadIdx.x == 0 && lse != nullptr)
+        lse[(int64_t)s * Hq + hq] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -929,8 +963,8 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     g_launches++;
     if (int rc = check_cuda(cudaGetLastError(), "decode_kernel launch")) return rc;
 
-    const int warps = B * p.Hq;
-    merge_kernel<T><<<(warps + 3) / 4, 128, 0, st>>>(B, p.Hq, G, D, p.ws, static_cast<T*>(p.out), p.out_sb, p.out_sh, p.lse);
+    merge_kernel<T, D><<<B * p.Hq, kMergeWarps * 32, 0, st>>>(p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb, p.out_sh,
+                                                              p.lse);
     g_launches++;
     return check_cuda(cudaGetLastError(), "merge_kernel launch");
 }
