@@ -85,7 +85,7 @@ class ClockSampler:
     """Samples nvidia-smi while the timed region runs (reads only; never changes a setting)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw,clocks.mem")
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
@@ -121,8 +121,16 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": statistics.median(int(r[0]) for r in self.rows), "sm_max_mhz": int(self.rows[0][1]),
-                "reasons": reasons, "samples": len(self.rows)}
+        def num(x):
+            try:
+                return float(x)
+            except ValueError:
+                return None
+        power = [num(r[6]) for r in self.rows if len(r) > 6 and num(r[6]) is not None]
+        mem = [num(r[7]) for r in self.rows if len(r) > 7 and num(r[7]) is not None]
+        return {"sm_mhz": statistics.median(int(r[0]) for r in self.rows), "sm_min_mhz": min(int(r[0]) for r in self.rows),
+                "sm_max_mhz": int(self.rows[0][1]), "reasons": reasons, "samples": len(self.rows),
+                "power_w_max": max(power) if power else None, "mem_mhz": statistics.median(mem) if mem else None}
 
 
 # ---- workloads ---------------------------------------------------------------------------------------
@@ -159,6 +167,27 @@ def describe(name, wl, world):
     }
 
 
+def live_copy_bandwidth(dev):
+    """STREAM-style copy on THIS GPU, the way the recorded peak was taken (b.copy_(a) over 1 Gi bf16
+    elements, read+write bytes, best of 10): B200s of one pool differ by a few per cent, so the
+    live figure is reported next to the recorded one."""
+    n = 1 << 30
+    a = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    b = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    a.fill_(1)
+    best = float("inf")
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        b.copy_(a)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    del a, b
+    torch.cuda.empty_cache()
+    return 2 * n * 2 / (best * 1e-3) / 1e9
+
+
 # ---- the GPU arm --------------------------------------------------------------------------------------
 
 def time_region(fn, steps, flush=None):
@@ -191,6 +220,7 @@ def run_gpu(args):
 
     lib = iva_b200.load_library()
     name = args.workload
+    copy_gbs = live_copy_bandwidth(dev)
     wl = build_workload(name, dev, rank, world, args)
     B = wl.batch
     lens = (wl.ctx_len + wl.new_tokens_per_seq).contiguous()
@@ -341,6 +371,7 @@ def run_gpu(args):
         "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                      "algorithmic_bytes": dom_bytes, "ms": dom_ms,
+                     "live_copy_GBs_this_gpu": copy_gbs, "frac_of_live_copy": achieved / copy_gbs,
                      "traffic": None if ratio is None else int(dom_bytes * ratio)},
         "kernels": {"append_ms": statistics.mean(app_ms), "append_GBs": append_bytes(wl) / (statistics.mean(app_ms) * 1e-3) / 1e9,
                     "attention_ms": None if attn_ms is None else statistics.mean(attn_ms),

@@ -136,25 +136,46 @@ __device__ __forceinline__ void mma_m16n8k16_top(float (&c)[2], uint32_t a0, uin
 template <>
 __device__ __forceinline__ void mma_m16n8k16_top<__nv_bfloat16>(float (&c)[2], uint32_t a0, uint32_t a2, uint32_t b0,
                                                                 uint32_t b1) {
-    float d2, d3;   // rows 8..15 of the tile: always zero, discarded
-    (void)d2; (void)d3;
+    float z2 = 0.f, z3 = 0.f;   // rows 8..15 of the tile: zero in, zero out
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-        "{%0, %1, %10, %10};"
-        : "+f"(c[0]), "+f"(c[1]), "=f"(d2), "=f"(d3)
-        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(z2), "+f"(z3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
 template <>
 __device__ __forceinline__ void mma_m16n8k16_top<__half>(float (&c)[2], uint32_t a0, uint32_t a2, uint32_t b0,
                                                          uint32_t b1) {
-    float d2, d3;   // rows 8..15 of the tile: always zero, discarded
-    (void)d2; (void)d3;
+    float z2 = 0.f, z3 = 0.f;   // rows 8..15 of the tile: zero in, zero out
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-        "{%0, %1, %10, %10};"
-        : "+f"(c[0]), "+f"(c[1]), "=f"(d2), "=f"(d3)
-        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(z2), "+f"(z3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+// Full tile: rows 0..7 take a0/a2, rows 8..15 take a1/a3; all four accumulators are live.
+template <typename T>
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_m16n8k16<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                            uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_m16n8k16<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                     uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);

@@ -459,7 +459,9 @@ struct MmaEngine {
     static constexpr int NBLK = D / 8;                 // 8-wide output blocks of P^T V
 
     uint32_t qa[KSTEPS][2];    // A fragments of Q: head lane/4; rows 8..15 of the tile are zero
-    float o[NBLK][2];          // head lane/4, dims 8j + 2*(lane%4) + {0,1}
+    // Accumulators of P^T V for head lane/4, dims 8j + 2*(lane%4) + {0,1}: [0],[1] collect the 16-bit
+    // weights (rows 0..7 of the A tile), [2],[3] the 16-bit corrections (rows 8..15); their sum is O.
+    float o[NBLK][4];
     float m_run, l_run;        // running max (raw score units) and this lane's share of the sum
 
     __device__ __forceinline__ void setup(int) {}
@@ -478,7 +480,7 @@ struct MmaEngine {
             for (int s = 0; s < KSTEPS; ++s) qa[s][0] = qa[s][1] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < NBLK; ++j) o[j][0] = o[j][1] = 0.f;
+        for (int j = 0; j < NBLK; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
         m_run = -INFINITY;
         l_run = 0.f;
     }
@@ -535,7 +537,7 @@ struct MmaEngine {
             const float alpha = fast_exp2((m_run - m_new) * sl2);          // exp2(-inf) = 0 on the first page
             l_run *= alpha;
 #pragma unroll
-            for (int j = 0; j < NBLK; ++j) { o[j][0] *= alpha; o[j][1] *= alpha; }
+            for (int j = 0; j < NBLK; ++j) { o[j][0] *= alpha; o[j][1] *= alpha; o[j][2] *= alpha; o[j][3] *= alpha; }
             m_run = m_new;
         }
         const float msl = m_run * sl2;
@@ -544,9 +546,10 @@ struct MmaEngine {
         l_run += (p0 + p1) + (p2 + p3);
         // The S^T accumulator layout (row = head, cols = tokens 2c, 2c+1) is the A-fragment layout of
         // the next product: a0a1 = tokens 2c,2c+1, a4a5 = tokens 8+2c, 9+2c.
-        // The weights are carried as a 16-bit value plus a 16-bit correction (p = hi + lo), two MMAs
-        // per block, so that P^T V is accurate to ~2^-17 instead of the 2^-9 of a single bf16 rounding
-        // (which alone would exceed the 2e-3 output tolerance on contexts of a few tokens).
+        // The weights are carried as a 16-bit value plus a 16-bit correction (p = hi + lo) so that P^T V
+        // is accurate to ~2^-17 instead of the 2^-9 of a single bf16 rounding (which alone would exceed
+        // the 2e-3 output tolerance on contexts of a few tokens).  The G <= 8 heads fill only rows 0..7
+        // of the 16-row A tile, so the corrections ride in rows 8..15 of the same MMA at no extra cost.
         const uint32_t pa0 = pack2<T>(p0, p1), pa2 = pack2<T>(p2, p3);
         const float2 h01 = unpack2<T>(pa0), h23 = unpack2<T>(pa2);
         const uint32_t pb0 = pack2<T>(p0 - h01.x, p1 - h01.y), pb2 = pack2<T>(p2 - h23.x, p3 - h23.y);
@@ -557,10 +560,8 @@ struct MmaEngine {
         for (int jp = 0; jp < NBLK / 2; ++jp) {
             uint32_t b[4];
             ldmatrix_x4_trans(vbase + chunk_off(vtok, 2 * jp + (mi >> 1)), b);   // blocks 2jp (b0,b1), 2jp+1 (b2,b3)
-            mma_m16n8k16_top<T>(o[2 * jp], pa0, pa2, b[0], b[1]);
-            mma_m16n8k16_top<T>(o[2 * jp + 1], pa0, pa2, b[2], b[3]);
-            mma_m16n8k16_top<T>(o[2 * jp], pb0, pb2, b[0], b[1]);
-            mma_m16n8k16_top<T>(o[2 * jp + 1], pb0, pb2, b[2], b[3]);
+            mma_m16n8k16<T>(o[2 * jp], pa0, pb0, pa2, pb2, b[0], b[1]);
+            mma_m16n8k16<T>(o[2 * jp + 1], pa0, pb0, pa2, pb2, b[2], b[3]);
         }
         if (n_valid < kPage) fence_proxy_async_smem();   // order the row clearing before the next TMA write
         __syncwarp();
@@ -573,7 +574,8 @@ struct MmaEngine {
         if (g < G) {
 #pragma unroll
             for (int j = 0; j < NBLK; ++j)
-                *reinterpret_cast<float2*>(my_o + g * D + 8 * j + 2 * c) = make_float2(o[j][0], o[j][1]);
+                *reinterpret_cast<float2*>(my_o + g * D + 8 * j + 2 * c) =
+                    make_float2(o[j][0] + o[j][2], o[j][1] + o[j][3]);
             if (c == 0) {
                 my_ml[g * 2] = (m_run == -INFINITY) ? -INFINITY : m_run * p.scale_log2;
                 my_ml[g * 2 + 1] = l_run;
