@@ -240,7 +240,7 @@ def run_gpu(args):
             k_loc, v_loc = hp.local_pools(wl.k_pool, wl.v_pool)
             k_loc, v_loc = k_loc.contiguous(), v_loc.contiguous()      # each rank keeps only its slab
             k_new_loc, v_new_loc = wl.k_new[:, hp.kv_slice].contiguous(), wl.v_new[:, hp.kv_slice].contiguous()
-            del wl.k_pool, wl.v_pool
+            wl.k_pool, wl.v_pool = k_loc, v_loc                        # drop the full pools
             torch.cuda.empty_cache()
 
     def append():
