@@ -1,0 +1,103 @@
+"""One decode step as a single CUDA-graph replay.
+
+A decode step of one attention layer is four small host->device copies, four kernel launches
+(append, plan, attention, merge) and one device->host copy.  Issued one by one from Python they
+cost more CPU time than the 64-token append takes on the GPU, so the step is captured once in a
+CUDA graph and replayed: one driver call per step.
+
+The caller owns the page pools and the block table (``PagedKVCache`` or its own allocator) and
+writes each step's inputs straight into the pinned staging tensors of this object
+(``q_host``, ``k_new_host``, ``v_new_host``, ``slot_mapping_host``, ``ctx_len_host``); ``run()``
+replays the graph, ``result()`` waits for it and returns the pinned output.  The reference has
+no counterpart: its decode loop re-runs the whole sequence every step
+(src/core/transformer.py:284-290).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .attention import decode_workspace_bytes, paged_decode_attention
+from .kv_ops import _pool_strides, paged_append
+
+__all__ = ["GraphedDecodeStep"]
+
+
+class GraphedDecodeStep:
+    """``append(k_new, v_new) -> attention(q)`` over a page pool, from and to pinned host memory.
+
+    ``block_table`` (int32 ``[B,max_pages]``, on the device) is read in place: update it between
+    steps when a sequence gets a new page.  ``ctx_len_host`` holds the lengths INCLUDING the token
+    appended in this step; ``slot_mapping_host`` its destination slots.
+    """
+
+    def __init__(self, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, n_q_heads: int,
+                 page_size: int = 16, scale: Optional[float] = None, return_lse: bool = False,
+                 use_graph: bool = True):
+        if not k_pool.is_cuda:
+            raise RuntimeError("GraphedDecodeStep needs CUDA tensors; there is no CPU implementation")
+        self.k_pool, self.v_pool, self.block_table = k_pool, v_pool, block_table
+        self.page_size = page_size
+        dev, dtype = k_pool.device, k_pool.dtype
+        Hkv, _, _, _ = _pool_strides(k_pool, page_size)
+        D = k_pool.shape[-1]
+        B = block_table.shape[0]
+        self.scale = scale if scale is not None else 1.0 / math.sqrt(D)
+
+        def pinned(*shape, dtype):
+            return torch.zeros(*shape, dtype=dtype).pin_memory()
+
+        self.q_host = pinned(B, n_q_heads, D, dtype=dtype)
+        self.k_new_host = pinned(B, Hkv, D, dtype=dtype)
+        self.v_new_host = pinned(B, Hkv, D, dtype=dtype)
+        self.slot_mapping_host = pinned(B, dtype=torch.int64)
+        self.ctx_len_host = pinned(B, dtype=torch.int32)
+        self.out_host = pinned(B, n_q_heads, D, dtype=dtype)
+        self.lse_host = pinned(B, n_q_heads, dtype=torch.float32) if return_lse else None
+        self._hosts = (self.q_host, self.k_new_host, self.v_new_host, self.slot_mapping_host, self.ctx_len_host)
+        self._devs = tuple(torch.empty_like(t, device=dev) for t in self._hosts)
+        self._out = torch.empty(B, n_q_heads, D, device=dev, dtype=dtype)
+        self._lse = torch.empty(B, n_q_heads, device=dev, dtype=torch.float32) if return_lse else None
+        self._ws = torch.empty(decode_workspace_bytes(B, n_q_heads, Hkv, D), dtype=torch.uint8, device=dev)
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in self._hosts)
+        self.d2h_bytes = self.out_host.numel() * self.out_host.element_size() + (
+            self.lse_host.numel() * 4 if return_lse else 0)
+        self.stream = torch.cuda.Stream(device=dev)
+        self.use_graph = use_graph
+        self.graph = None
+        self._steps = 0
+
+    def _enqueue(self) -> None:
+        for d, h in zip(self._devs, self._hosts):
+            d.copy_(h, non_blocking=True)
+        q, k_new, v_new, slots, lens = self._devs
+        paged_append(self.k_pool, self.v_pool, slots, k_new, v_new, self.page_size)
+        paged_decode_attention(q, self.k_pool, self.v_pool, self.block_table, lens, self.page_size, self.scale,
+                               out=self._out, lse=self._lse, workspace=self._ws)
+        self.out_host.copy_(self._out, non_blocking=True)
+        if self._lse is not None:
+            self.lse_host.copy_(self._lse, non_blocking=True)
+
+    def run(self) -> None:
+        """Enqueue one step (asynchronous).  The first step runs eagerly, which performs every
+        one-time set-up (kernel attributes, status words) outside a capture; the second call
+        records the graph; from then on a step is one graph launch."""
+        with torch.cuda.stream(self.stream):
+            if not self.use_graph or self._steps == 0:
+                self._enqueue()
+            else:
+                if self.graph is None:
+                    self.stream.synchronize()
+                    self.graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(self.graph, stream=self.stream):
+                        self._enqueue()
+                self.graph.replay()
+        self._steps += 1
+
+    def result(self) -> torch.Tensor:
+        """Wait for the last step and return the pinned output ``[B,H_q,D]``."""
+        self.stream.synchronize()
+        return self.out_host

@@ -94,11 +94,14 @@ class HeadParallelDecoder:
         if self.world == 1:
             return out_l, lse_l
         Hl, D = out_l.shape[1], out_l.shape[2]
-        # rank r's block lands in rows r*B..(r+1)*B-1 of the gathered tensor
-        out_all = torch.empty(self.world * B, Hl, D, dtype=out_l.dtype, device=out_l.device)
-        lse_all = torch.empty(self.world * B, Hl, dtype=lse_l.dtype, device=lse_l.device)
-        dist.all_gather_into_tensor(out_all, out_l.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(lse_all, lse_l.contiguous(), group=self.group)
-        out = out_all.view(self.world, B, Hl, D).permute(1, 0, 2, 3).reshape(B, self.world * Hl, D)
-        lse = lse_all.view(self.world, B, Hl).permute(1, 0, 2).reshape(B, self.world * Hl)
+        # One collective: the logsumexp travels as D+1-th fp32 column of the output rows
+        # (rank r's block lands in rows r*B..(r+1)*B-1 of the gathered tensor).
+        packed = torch.empty(B, Hl, D + 1, dtype=torch.float32, device=out_l.device)
+        packed[:, :, :D] = out_l
+        packed[:, :, D] = lse_l
+        gathered = torch.empty(self.world * B, Hl, D + 1, dtype=torch.float32, device=out_l.device)
+        dist.all_gather_into_tensor(gathered, packed, group=self.group)
+        gathered = gathered.view(self.world, B, Hl, D + 1).permute(1, 0, 2, 3).reshape(B, self.world * Hl, D + 1)
+        out = gathered[:, :, :D].to(out_l.dtype)
+        lse = gathered[:, :, D].contiguous()
         return out, lse

@@ -1,0 +1,101 @@
+"""The graphed decode step (public end-to-end call) and the multi-GPU forms on real GPUs."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import iva_b200
+from iva_b200 import workloads
+from oracle import paged_ref as ref
+from util import assert_attn_close, assert_lse_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_graphed_decode_steps_follow_the_dense_reference(use_graph):
+    """Six consecutive decode steps from pinned host buffers; every step is checked against the
+    CPU checker on the pool it should have produced."""
+    cache = iva_b200.PagedKVCache(batch_size=3, n_heads=2, head_dim=128, device=DEV, dtype=torch.bfloat16,
+                                  max_seq_len=96, shuffle_seed=5)
+    g = torch.Generator().manual_seed(3)
+    prompt_k = torch.randn(3, 40, 2, 128, generator=g).to(torch.bfloat16)
+    prompt_v = torch.randn(3, 40, 2, 128, generator=g).to(torch.bfloat16)
+    cache.append(prompt_k.to(DEV), prompt_v.to(DEV))
+    step = iva_b200.GraphedDecodeStep(cache.k_pool, cache.v_pool, cache.block_table_dev, n_q_heads=8,
+                                      return_lse=True, use_graph=use_graph)
+    k_ref, v_ref = cache.k_pool.cpu(), cache.v_pool.cpu()
+    for t in range(6):
+        L = 40 + t
+        cache._reserve([L + 1] * 3)                        # host bookkeeping: room for one more token
+        cache._sync_device()
+        q = torch.randn(3, 8, 128, generator=g).to(torch.bfloat16)
+        kn = torch.randn(3, 2, 128, generator=g).to(torch.bfloat16)
+        vn = torch.randn(3, 2, 128, generator=g).to(torch.bfloat16)
+        slots = torch.tensor([cache.slots(s, L, L + 1)[0] for s in range(3)])
+        step.q_host.copy_(q); step.k_new_host.copy_(kn); step.v_new_host.copy_(vn)
+        step.slot_mapping_host.copy_(slots); step.ctx_len_host.fill_(L + 1)
+        step.run()
+        out = step.result().clone()
+        lse = step.lse_host.clone()
+        k_ref = ref.paged_append_ref(k_ref, slots, kn)
+        v_ref = ref.paged_append_ref(v_ref, slots, vn)
+        out_ref, lse_ref = ref.paged_decode_ref(q, k_ref, v_ref, cache._bt_host, torch.full((3,), L + 1), 16)
+        assert_attn_close(out, out_ref, torch.bfloat16, strict=False)
+        assert_lse_close(lse, lse_ref)
+    assert torch.equal(cache.k_pool.cpu(), k_ref) and torch.equal(cache.v_pool.cpu(), v_ref)
+    assert (step.graph is not None) == use_graph
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _nccl_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from iva_b200.sharding import HeadParallelDecoder, shard_requests
+
+        dev = torch.device("cuda", rank)
+        # head-parallel: every rank holds the same inputs, keeps its KV-head slab, all-gathers outputs
+        wl = workloads.make_decode_workload("hp", torch.tensor([5000, 77]), n_q_heads=16, n_kv_heads=4, head_dim=128,
+                                            dtype=torch.bfloat16, seed=11)
+        out_ref, lse_ref = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16)
+        d = wl.to(dev)
+        dec = HeadParallelDecoder(16, 4)
+        kl, vl = dec.local_pools(d.k_pool, d.v_pool)
+        out, lse = dec.decode(d.q, kl.contiguous(), vl.contiguous(), d.block_table, d.ctx_len, 16, wl.scale)
+        single = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16)
+        ok = torch.equal(out, single)                                   # same bits as one GPU
+        err = (out.float().cpu() - out_ref).abs().max().item()
+        lerr = (lse.cpu() - lse_ref).abs().max().item()
+        # request sharding: each rank decodes its share on its own pool, nothing is exchanged
+        mine = shard_requests(6, world, rank)
+        wl2 = workloads.config_c5a(n_seq=6, context=300, rank=rank, world=world)
+        _, _, o2_ref, _ = ref.decode_step_ref(wl2)
+        d2 = wl2.to(dev)
+        iva_b200.paged_append(d2.k_pool, d2.v_pool, d2.slot_mapping, d2.k_new, d2.v_new, 16)
+        o2 = iva_b200.paged_decode_attention(d2.q, d2.k_pool, d2.v_pool, d2.block_table, (d2.ctx_len + 1).contiguous(), 16)
+        err2 = (o2.float().cpu() - o2_ref).abs().max().item()
+        ret[rank] = (bool(ok), err, lerr, err2, len(mine) == wl2.batch)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_head_parallel_and_request_sharding():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_nccl_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    for r in range(2):
+        ok, err, lerr, err2, covered = ret[r]
+        assert ok and covered and err <= 2e-3 + 2 ** -8 * 4 and lerr <= 1e-3 and err2 <= 2e-3, ret[r]
