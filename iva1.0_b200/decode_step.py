@@ -47,22 +47,32 @@ class GraphedDecodeStep:
         B = block_table.shape[0]
         self.scale = scale if scale is not None else 1.0 / math.sqrt(D)
 
-        def pinned(*shape, dtype):
-            return torch.zeros(*shape, dtype=dtype).pin_memory()
+        # All inputs of a step live in ONE pinned block (and one device block), carved into typed
+        # views, so that a step uploads them with a single host->device copy.
+        esz = k_pool.element_size()
+        sizes = [B * n_q_heads * D * esz, B * Hkv * D * esz, B * Hkv * D * esz, B * 8, B * 4]
+        offs, total = [], 0
+        for n in sizes:
+            offs.append(total)
+            total += (n + 255) // 256 * 256
+        self._stage_host = torch.zeros(total, dtype=torch.uint8).pin_memory()
+        self._stage_dev = torch.empty(total, dtype=torch.uint8, device=dev)
 
-        self.q_host = pinned(B, n_q_heads, D, dtype=dtype)
-        self.k_new_host = pinned(B, Hkv, D, dtype=dtype)
-        self.v_new_host = pinned(B, Hkv, D, dtype=dtype)
-        self.slot_mapping_host = pinned(B, dtype=torch.int64)
-        self.ctx_len_host = pinned(B, dtype=torch.int32)
-        self.out_host = pinned(B, n_q_heads, D, dtype=dtype)
-        self.lse_host = pinned(B, n_q_heads, dtype=torch.float32) if return_lse else None
-        self._hosts = (self.q_host, self.k_new_host, self.v_new_host, self.slot_mapping_host, self.ctx_len_host)
-        self._devs = tuple(torch.empty_like(t, device=dev) for t in self._hosts)
+        def views(block):
+            def v(i, dt, *shape):
+                return block[offs[i]:offs[i] + sizes[i]].view(dt).view(*shape)
+            return (v(0, dtype, B, n_q_heads, D), v(1, dtype, B, Hkv, D), v(2, dtype, B, Hkv, D),
+                    v(3, torch.int64, B), v(4, torch.int32, B))
+
+        self._hosts = views(self._stage_host)
+        self._devs = views(self._stage_dev)
+        self.q_host, self.k_new_host, self.v_new_host, self.slot_mapping_host, self.ctx_len_host = self._hosts
+        self.out_host = torch.zeros(B, n_q_heads, D, dtype=dtype).pin_memory()
+        self.lse_host = torch.zeros(B, n_q_heads, dtype=torch.float32).pin_memory() if return_lse else None
         self._out = torch.empty(B, n_q_heads, D, device=dev, dtype=dtype)
         self._lse = torch.empty(B, n_q_heads, device=dev, dtype=torch.float32) if return_lse else None
         self._ws = torch.empty(decode_workspace_bytes(B, n_q_heads, Hkv, D), dtype=torch.uint8, device=dev)
-        self.h2d_bytes = sum(t.numel() * t.element_size() for t in self._hosts)
+        self.h2d_bytes = total
         self.d2h_bytes = self.out_host.numel() * self.out_host.element_size() + (
             self.lse_host.numel() * 4 if return_lse else 0)
         self.stream = torch.cuda.Stream(device=dev)
@@ -71,8 +81,7 @@ class GraphedDecodeStep:
         self._steps = 0
 
     def _enqueue(self) -> None:
-        for d, h in zip(self._devs, self._hosts):
-            d.copy_(h, non_blocking=True)
+        self._stage_dev.copy_(self._stage_host, non_blocking=True)
         q, k_new, v_new, slots, lens = self._devs
         paged_append(self.k_pool, self.v_pool, slots, k_new, v_new, self.page_size)
         paged_decode_attention(q, self.k_pool, self.v_pool, self.block_table, lens, self.page_size, self.scale,
