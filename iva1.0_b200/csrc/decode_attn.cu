@@ -62,7 +62,10 @@ static_assert(sizeof(ChunkDesc) == 32, "ChunkDesc is two 16-byte vectors");
 
 struct Workspace {
     int* header;
-    int* seq_prefix;      // [B+1] exclusive prefix of chunks per sequence
+    int* pos_prefix;      // [B+1] exclusive prefix of chunks over sequences in processing order
+    int* order;           // [B]   sequence id at each position of the processing order
+    int* seq_first;       // [B]   first chunk index of each sequence
+    int* seq_count;       // [B]   number of chunks of each sequence
     ChunkDesc* chunks;    // [cap]
     float* part_ml;       // [cap*Hkv][G][2]   (running max in log2 units, sum)
     float* part_o;        // [cap*Hkv][G][D]
@@ -100,10 +103,14 @@ size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return p ? p + o : nullptr; };
     int* header = reinterpret_cast<int*>(take(kHdrWords * sizeof(int)));
     int* prefix = reinterpret_cast<int*>(take((B + 1) * sizeof(int)));
+    int* order = reinterpret_cast<int*>(take(B * sizeof(int)));
+    int* seq_first = reinterpret_cast<int*>(take(B * sizeof(int)));
+    int* seq_count = reinterpret_cast<int*>(take(B * sizeof(int)));
     ChunkDesc* chunks = reinterpret_cast<ChunkDesc*>(take(cap * sizeof(ChunkDesc)));
     float* ml = reinterpret_cast<float*>(take((size_t)cap * Hq * 2 * sizeof(float)));
     float* po = reinterpret_cast<float*>(take((size_t)cap * Hq * D * sizeof(float)));
-    if (ws) { ws->header = header; ws->seq_prefix = prefix; ws->chunks = chunks; ws->part_ml = ml; ws->part_o = po;
+    if (ws) { ws->header = header; ws->pos_prefix = prefix; ws->order = order; ws->seq_first = seq_first; ws->seq_count = seq_count;
+              ws->chunks = chunks; ws->part_ml = ml; ws->part_o = po;
               ws->cap = (int)cap; ws->target_chunks = target; }
     return off;
 }
@@ -113,6 +120,7 @@ size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D
 // ------------------------------------------------------------------------------------------------
 
 constexpr int kPlanThreads = 1024;
+constexpr int kSortMax = 1024;   // largest batch whose sequences are ordered longest-first (rank sort, O(B) per thread)
 
 __device__ int block_inclusive_scan(int v, int* warp_sums, int* total) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -145,6 +153,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     __shared__ int warp_sums[32];
     __shared__ long long s_total_pages;
     __shared__ int s_bad;
+    __shared__ int s_pages[kSortMax];
     const int tid = threadIdx.x;
     if (tid == 0) { s_total_pages = 0; s_bad = 0; }
     __syncthreads();
@@ -165,45 +174,74 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     if (c64 < kMinChunkPages) c64 = kMinChunkPages;
     const int chunk_pages = (int)(c64 > 0x3fffffff ? 0x3fffffff : c64);
 
-    // chunks per sequence and their exclusive prefix
+    // Processing order: longest sequence first (ties by index).  Work items are handed out in this
+    // order, so the CTAs that finish last are working on the shortest items and the tail of the
+    // kernel is short even for ragged batches.  Batches beyond kSortMax keep their natural order.
+    auto clamped_pages = [&](int s) {
+        int L = ctx_len[s];
+        L = L < 0 ? 0 : (((long long)L > (long long)max_pages * page_size) ? max_pages * page_size : L);
+        return (L + page_size - 1) / page_size;
+    };
+    const bool sorted = B <= kSortMax;
+    if (sorted) {
+        for (int s = tid; s < B; s += kPlanThreads) s_pages[s] = clamped_pages(s);
+        __syncthreads();
+        for (int s = tid; s < B; s += kPlanThreads) {
+            const int mine = s_pages[s];
+            int rank = 0;
+            for (int t = 0; t < B; ++t) {
+                const int other = s_pages[t];
+                rank += (other > mine) || (other == mine && t < s);
+            }
+            ws.order[rank] = s;
+        }
+    } else {
+        for (int s = tid; s < B; s += kPlanThreads) ws.order[s] = s;
+    }
+    __syncthreads();   // order[] written by this block is visible to this block
+
+    // chunks per position and their exclusive prefix
     int running = 0;
     for (int base = 0; base < B; base += kPlanThreads) {
-        const int s = base + tid;
-        int n = 0;
-        if (s < B) {
-            int L = ctx_len[s];
-            L = L < 0 ? 0 : (((long long)L > (long long)max_pages * page_size) ? max_pages * page_size : L);
-            const int pages = (L + page_size - 1) / page_size;
+        const int pos = base + tid;
+        int n = 0, s = 0;
+        if (pos < B) {
+            s = ws.order[pos];
+            const int pages = sorted ? s_pages[s] : clamped_pages(s);
             n = (pages + chunk_pages - 1) / chunk_pages;
             if (n < 1) n = 1;   // an empty sequence still gets one (empty) item, which writes zeros / -inf
         }
         int tile_total;
         const int incl = block_inclusive_scan(n, warp_sums, &tile_total);
-        if (s < B) ws.seq_prefix[s] = running + incl - n;
+        if (pos < B) {
+            ws.pos_prefix[pos] = running + incl - n;
+            ws.seq_first[s] = running + incl - n;
+            ws.seq_count[s] = n;
+        }
         running += tile_total;
     }
     int num_chunks = running;
     int overflow = 0;
     if (num_chunks > cap) { overflow = 1; num_chunks = 0; }   // cannot happen when cap = B + target_chunks
     if (tid == 0) {
-        ws.seq_prefix[B] = running;
+        ws.pos_prefix[B] = running;
         ws.header[kHdrNumChunks] = num_chunks;
         ws.header[kHdrChunkPages] = chunk_pages;
         ws.header[kHdrCounter] = 0;
         ws.header[kHdrStatus] = (s_bad ? kStatusBadCtxLen : 0) | (overflow ? kStatusOverflow : 0);
         ws.header[kHdrTotalItems] = num_chunks * Hkv;
     }
-    __syncthreads();   // seq_prefix writes of this block are visible to this block
+    __syncthreads();   // pos_prefix writes of this block are visible to this block
 
     for (int ci = tid; ci < num_chunks; ci += kPlanThreads) {
-        int lo = 0, hi = B - 1;   // largest s with seq_prefix[s] <= ci
+        int lo = 0, hi = B - 1;   // largest position with pos_prefix[pos] <= ci
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if (ws.seq_prefix[mid] <= ci) lo = mid; else hi = mid - 1;
+            if (ws.pos_prefix[mid] <= ci) lo = mid; else hi = mid - 1;
         }
-        const int s = lo;
-        const int first = ws.seq_prefix[s];
-        const int n = ws.seq_prefix[s + 1] - first;
+        const int s = ws.order[lo];
+        const int first = ws.pos_prefix[lo];
+        const int n = ws.pos_prefix[lo + 1] - first;
         const int j = ci - first;
         int L = ctx_len[s];
         L = L < 0 ? 0 : (((long long)L > (long long)max_pages * page_size) ? max_pages * page_size : L);
@@ -819,8 +857,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int Hq, int G, 
                                                                  int64_t out_sh, float* lse) {
     constexpr int VPL = D / 32;   // dims per lane
     const int s = blockIdx.x / Hq, hq = blockIdx.x % Hq;
-    const int first = ws.seq_prefix[s];
-    const int n = ws.seq_prefix[s + 1] - first;
+    const int first = ws.seq_first[s];
+    const int n = ws.seq_count[s];
     if (n <= 1) return;   // single-chunk sequences were written by the attention kernel
     const int num_chunks = ws.header[kHdrNumChunks];
     if (num_chunks == 0) return;
