@@ -52,6 +52,18 @@ constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
 constexpr int kMinChunkPages = 8;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 
+// Optional phase timing (debug builds only, -DIVAB_PROFILE): lane 0 of every warp accumulates
+// clock64() deltas per phase and adds them to 64-bit counters in header words 16..47.
+#ifdef IVAB_PROFILE
+#define PROF_DECL long long prof_t0 = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define PROF_MARK(i) { const long long prof_t1 = clock64(); prof_acc[i] += prof_t1 - prof_t0; prof_t0 = prof_t1; }
+#define PROF_FLUSH(base) if (lane == 0) { for (int i = 0; i < 8; ++i) atomicAdd(reinterpret_cast<unsigned long long*>(p.ws.header + 16) + (base) + i, (unsigned long long)prof_acc[i]); }
+#else
+#define PROF_DECL
+#define PROF_MARK(i)
+#define PROF_FLUSH(base)
+#endif
+
 // header words at the start of the workspace
 enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrWords = 64 };
 
@@ -230,6 +242,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         ws.header[kHdrCounter] = 0;
         ws.header[kHdrStatus] = (s_bad ? kStatusBadCtxLen : 0) | (overflow ? kStatusOverflow : 0);
         ws.header[kHdrTotalItems] = num_chunks * Hkv;
+#ifdef IVAB_PROFILE
+        for (int i = 16; i < 48; ++i) ws.header[i] = 0;
+#endif
     }
     __syncthreads();   // pos_prefix writes of this block are visible to this block
 
@@ -644,6 +659,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     auto bar_item_empty = [&](int s) { return bars + 8u * (2 * kMaxStages + kItemRing + s); };
     auto bar_merge = [&](int s) { return bars + 8u * (2 * kMaxStages + 2 * kItemRing + s); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT);
+    int* merge_cnt = reinterpret_cast<int*>(smem + C::OFF_ABORT + 4);   // warps that have published the current item
     volatile int* items = reinterpret_cast<volatile int*>(smem + C::OFF_ITEMS);
     unsigned char* stage_base = smem + C::OFF_STAGES;
 
@@ -651,8 +667,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         *abort_flag = 0;
         for (int s = 0; s < stages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
         for (int s = 0; s < kItemRing; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), kConsumerWarps); }
-        mbar_init(bar_merge(0), kConsumerWarps);   // all warp states published
-        mbar_init(bar_merge(1), kConsumerWarps);   // all warps done reading them
+        mbar_init(bar_merge(0), 1);                // unused
+        mbar_init(bar_merge(1), 1);                // completes when an item's states have been combined
+        *merge_cnt = 0;
         fence_mbar_init();
     }
     __syncthreads();   // the only CTA-wide barrier: before any warp can have unwound
@@ -675,26 +692,60 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         const int spw = stages / kConsumerWarps;   // stages per warp
         int published = 0;  // items published so far
         bool aborted = false;
-        int item = 0;
-        if (lane == 0) item = atomicAdd(counter, 1);
-        item = __shfl_sync(0xffffffffu, item, 0);
-        for (;;) {
-            const bool done = item >= total_items;
-            int h = 0;
+        // The fetch of an item is three dependent global accesses (work counter -> chunk descriptor ->
+        // block-table entries), about a microsecond each under load.  They are software-pipelined
+        // across items: while the pages of item i are being issued, the block-table entries of item
+        // i+1, the descriptor of item i+2 and the id of item i+3 are in flight, so the TMA issue
+        // stream does not pause at item boundaries.
+        auto fetch_id_async = [&]() {   // lane 0 holds the result; broadcast it only when it is needed
+            int v = 0;
+            if (lane == 0) v = atomicAdd(counter, 1);
+            return v;
+        };
+        auto fetch_id = [&]() { return __shfl_sync(0xffffffffu, fetch_id_async(), 0); };
+        auto load_desc = [&](int id, int* h_out) {
             ChunkDesc d{};
-            int next_item = 0;
-            if (!done) {
-                h = item / num_chunks;
-                const int ci = item - h * num_chunks;
-                const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + ci);
+            *h_out = 0;
+            if (id < total_items) {
+                const int h = id / num_chunks;
+                const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + (id - h * num_chunks));
                 const int4 a = __ldg(src), b = __ldg(src + 1);
                 d.seq = a.x; d.page_begin = a.y; d.n_pages = a.z; d.chunk_idx = a.w; d.n_chunks = b.x; d.pad0 = b.y;
-                if (lane == 0) next_item = atomicAdd(counter, 1);   // fetched early, used after this item
+                *h_out = h;
             }
+            return d;
+        };
+        auto load_pages = [&](const ChunkDesc& d, int p0) {   // this lane's entry of a 32-page batch
+            // (the value is validated where it is used, so that this load stays a prefetch)
+            int mine = 0;
+            if (p0 + lane < d.n_pages)
+                mine = __ldg(p.block_table + (int64_t)d.seq * p.bt_stride + d.page_begin + p0 + lane);
+            return mine;
+        };
+        PROF_DECL
+        int id0 = fetch_id(), id1 = fetch_id(), id2 = fetch_id();
+        int h0, h1;
+        ChunkDesc d0 = load_desc(id0, &h0);
+        ChunkDesc d1 = load_desc(id1, &h1);
+        int bt0 = id0 < total_items ? load_pages(d0, 0) : 0;
+        for (;;) {
+            const int item = id0, h = h0;
+            const ChunkDesc d = d0;
+            const bool done = item >= total_items;
+            // prefetch for the following items (ids past the end of the list load nothing)
+            int bt1 = 0, h2 = 0, id3_raw = 0;
+            ChunkDesc d2{};
+            if (!done) {
+                if (id1 < total_items) bt1 = load_pages(d1, 0);
+                d2 = load_desc(id2, &h2);
+                id3_raw = fetch_id_async();
+            }
+            PROF_MARK(0)   // fetch / prefetch issue
             const int slot = published % kItemRing;
             if (!mbar_wait_bounded(bar_item_empty(slot), ((published / kItemRing) & 1) ^ 1, abort_flag, limit)) {
                 aborted = true; break;
             }
+            PROF_MARK(1)   // wait for a free item slot
             if (lane == 0) {
                 volatile int* it = items + slot * 8;
                 it[kItSeq] = d.seq; it[kItHead] = h; it[kItPages] = done ? -1 : d.n_pages;
@@ -705,48 +756,70 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             ++published;
             if (done) break;
 
-            const int32_t* bt = p.block_table + (int64_t)d.seq * p.bt_stride + d.page_begin;
             const char* kbase = p.k_pool + (int64_t)h * p.pool_sh_bytes;
             const char* vbase = p.v_pool + (int64_t)h * p.pool_sh_bytes;
             const int start = (d.seq + d.chunk_idx) % kConsumerWarps;
             for (int p0 = 0; p0 < d.n_pages && !aborted; p0 += 32) {
-                int mine = 0;
-                if (p0 + lane < d.n_pages) {
-                    mine = __ldg(bt + p0 + lane);
-                    if (mine < 0 || mine >= p.num_pages) { atomicOr(status, kStatusBadPage); mine = 0; }
-                }
+                const int mine = p0 == 0 ? bt0 : load_pages(d, p0);
                 const int in_batch = min(32, d.n_pages - p0);
-                for (int j = 0; j < in_batch; ++j) {
-                    const int pid = __shfl_sync(0xffffffffu, mine, j);
-                    const int w = (start + p0 + j) % kConsumerWarps;
-                    int c = 0;
-#pragma unroll
-                    for (int i = 0; i < kConsumerWarps; ++i) if (i == w) { c = cnt[i]; cnt[i] = c + 1; }
-                    const int stage = (c % spw) * kConsumerWarps + w;
-                    if (!mbar_wait_bounded(bar_empty(stage), ((c / spw) & 1) ^ 1, abort_flag, limit)) {
-                        aborted = true; break;
+                PROF_MARK(2)   // block-table entries available
+                // Pages are issued a ring's worth at a time, ONE LANE PER PAGE: every lane waits for
+                // its own stage and issues its own copies, so the issue cost of up to `stages` pages
+                // overlaps.  A sub-batch never exceeds the ring (spw pages per consumer warp): a lane
+                // must not wait two phases ahead of a stage's barrier.
+                for (int q0 = 0; q0 < in_batch && !aborted; q0 += stages) {
+                    const int nb = min(stages, in_batch - q0);
+                    int pid = __shfl_sync(0xffffffffu, mine, (q0 + lane) & 31);
+                    if (lane < nb && (pid < 0 || pid >= p.num_pages)) {
+                        atomicOr(status, kStatusBadPage);   // flagged, and page 0 is read instead of faulting
+                        pid = 0;
                     }
-                    if (lane == 0) {
-                        const uint32_t dst = smem_u32(stage_base + (size_t)stage * Eng::STAGE_BYTES);
-                        mbar_arrive_expect_tx(bar_full(stage), Eng::STAGE_BYTES);
-                        if constexpr (Eng::kTiled) {
+                    const int b0 = (start + p0 + q0) & (kConsumerWarps - 1);
+                    const int w = (b0 + lane) & (kConsumerWarps - 1);          // consumer warp of this lane's page
+                    const int nth = lane >> 2;                                  // its rank among that warp's pages here
+                    int base_c = 0;
 #pragma unroll
-                            for (int t = 0; t < Eng::TILES; ++t) {
-                                tma_tile4d_g2s(dst + t * Eng::TILE_BYTES, &tm.k, t * 64, 0, pid, h, bar_full(stage));
-                                tma_tile4d_g2s(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * 64, 0, pid, h,
-                                               bar_full(stage));
-                            }
+                    for (int i = 0; i < kConsumerWarps; ++i) if (i == w) base_c = cnt[i];
+                    const int c = base_c + nth;
+                    bool fail = false;
+                    if (lane < nb) {
+                        const int stage = (c % spw) * kConsumerWarps + w;
+                        if (!mbar_wait_bounded(bar_empty(stage), ((c / spw) & 1) ^ 1, abort_flag, limit)) {
+                            fail = true;
                         } else {
-                            tma_bulk_g2s(dst, kbase + (int64_t)pid * p.pool_sp_bytes, Eng::PAGE_BYTES, bar_full(stage));
-                            tma_bulk_g2s(dst + Eng::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes,
-                                         Eng::PAGE_BYTES, bar_full(stage));
+                            const uint32_t dst = smem_u32(stage_base + (size_t)stage * Eng::STAGE_BYTES);
+                            mbar_arrive_expect_tx(bar_full(stage), Eng::STAGE_BYTES);
+                            if constexpr (Eng::kTiled) {
+#pragma unroll
+                                for (int t = 0; t < Eng::TILES; ++t) {
+                                    tma_tile4d_g2s(dst + t * Eng::TILE_BYTES, &tm.k, t * 64, 0, pid, h, bar_full(stage));
+                                    tma_tile4d_g2s(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * 64, 0, pid, h,
+                                                   bar_full(stage));
+                                }
+                            } else {
+                                tma_bulk_g2s(dst, kbase + (int64_t)pid * p.pool_sp_bytes, Eng::PAGE_BYTES, bar_full(stage));
+                                tma_bulk_g2s(dst + Eng::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes,
+                                             Eng::PAGE_BYTES, bar_full(stage));
+                            }
                         }
                     }
+                    if (__any_sync(0xffffffffu, fail)) aborted = true;
+                    // pages handed to consumer warp i in this sub-batch: lanes r_i, r_i+4, ... below nb
+#pragma unroll
+                    for (int i = 0; i < kConsumerWarps; ++i) {
+                        const int r_i = (i - b0) & (kConsumerWarps - 1);
+                        cnt[i] += nb > r_i ? (nb - r_i + kConsumerWarps - 1) / kConsumerWarps : 0;
+                    }
+                    PROF_MARK(3)   // stage wait + TMA issue of a sub-batch
                 }
             }
+            PROF_MARK(4)   // TMA issue
             if (aborted) break;
-            item = __shfl_sync(0xffffffffu, next_item, 0);
+            id0 = id1; h0 = h1; d0 = d1; bt0 = bt1;
+            id1 = id2; h1 = h2; d1 = d2;
+            id2 = __shfl_sync(0xffffffffu, id3_raw, 0);
         }
+        PROF_FLUSH(0)
         if (aborted) {
             if (lane == 0) atomicOr(status, kStatusWaitTimeout);
             // Copies already issued still target this CTA's shared memory: give each of the
@@ -774,9 +847,11 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     const int spw = stages / kConsumerWarps;   // stages of this warp's sub-ring
     int taken = 0;      // pages this warp has consumed so far (position in its sub-ring)
     int consumed = 0;   // items consumed
+    PROF_DECL
     for (;;) {
         const int slot = consumed % kItemRing;
         if (!mbar_wait_bounded(bar_item_full(slot), (consumed / kItemRing) & 1, abort_flag, limit)) break;
+        PROF_MARK(0)   // wait for the next item
         volatile int* it = items + slot * 8;
         const int seq = it[kItSeq], h = it[kItHead], n_pages = it[kItPages], page_begin = it[kItPageBegin];
         const int n_chunks = it[kItChunks], item = it[kItIndex], start = it[kItStart], L = it[kItLen];
@@ -785,61 +860,73 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         if (n_pages < 0) break;   // sentinel: the work list is exhausted
 
         eng.begin_item(p, seq, h, lane);   // query heads of this kv head into registers, state reset
+        PROF_MARK(1)   // q load issue
 
         bool ok = true;
         const int k0 = (warp - start + kConsumerWarps) % kConsumerWarps;
         for (int k = k0; k < n_pages; k += kConsumerWarps, ++taken) {
             const int stage = (taken % spw) * kConsumerWarps + warp;
             if (!mbar_wait_bounded(bar_full(stage), (taken / spw) & 1, abort_flag, limit)) { ok = false; break; }
+            PROF_MARK(2)   // wait for page data
             const int n_valid = min(kPage, L - (page_begin + k) * kPage);
             eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, lane, p_smem);
             if (lane == 0) mbar_arrive(bar_empty(stage));
+            PROF_MARK(3)   // page math
         }
         if (!ok) break;
 
-        // The merge scratch is shared by consecutive items: wait until every warp has finished
-        // reading the previous item's states before overwriting them.
-        if (consumed > 0 &&
-            !mbar_wait_bounded(bar_merge(1), (consumed - 1) & 1, abort_flag, limit)) break;
+        // ---- end of item: no CTA-wide barrier.  Every warp publishes its state and moves on to the
+        // next item at once; the warp that arrives LAST combines the four states (always in warp
+        // order 0..3, so the sum does not depend on who arrived when) and writes the result.  A
+        // stalled ring costs bandwidth directly, so three of four sub-rings keep draining while
+        // one warp does the combine.  The scratch is reused by the next item: a warp may overwrite
+        // its state only after the previous item's combine has finished.
+        if (consumed > 0 && !mbar_wait_bounded(bar_merge(1), (consumed - 1) & 1, abort_flag, limit)) break;
+        PROF_MARK(4)   // wait for the previous combine
         eng.publish(p, mrg_ml + (warp * G) * 2, mrg_o + (size_t)(warp * G) * D, lane);
+        __threadfence_block();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_merge(0));
-        if (!mbar_wait_bounded(bar_merge(0), consumed & 1, abort_flag, limit)) break;
-
-        // ---- merge the four warp states; the G*D outputs are spread over the consumer threads
-        const float* all_ml = mrg_ml;
-        const float* all_o = mrg_o;
-        for (int idx = threadIdx.x; idx < G * D; idx += kConsumerWarps * 32) {
-            const int g = idx / D, dd = idx % D;
-            float M = -INFINITY;
+        int arrival = 0;
+        if (lane == 0) arrival = atomicAdd(merge_cnt, 1);
+        arrival = __shfl_sync(0xffffffffu, arrival, 0);
+        if (arrival == kConsumerWarps - 1) {
+            __threadfence_block();
+            const volatile float* all_ml = mrg_ml;
+            const volatile float* all_o = mrg_o;
+            for (int idx = lane; idx < G * D; idx += 32) {
+                const int g = idx / D, dd = idx % D;
+                float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, all_ml[(w * G + g) * 2]);
-            float Lsum = 0.f, O = 0.f;
+                for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, all_ml[(w * G + g) * 2]);
+                float Lsum = 0.f, O = 0.f;
 #pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) {
-                const float mw = all_ml[(w * G + g) * 2];
-                const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-                Lsum = fmaf(all_ml[(w * G + g) * 2 + 1], f, Lsum);
-                O = fmaf(all_o[(size_t)(w * G + g) * D + dd], f, O);
-            }
-            const int hq = h * G + g;
-            if (n_chunks == 1) {
-                const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
-                Elt<T>::store(outg + (int64_t)seq * p.out_sb + (int64_t)hq * p.out_sh + dd, O * inv);
-                if (dd == 0 && p.lse != nullptr)
-                    p.lse[(int64_t)seq * p.Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * 0.6931471805599453f : -INFINITY;
-            } else {
-                p.ws.part_o[((size_t)item * G + g) * D + dd] = O;
-                if (dd == 0) {
-                    p.ws.part_ml[((size_t)item * G + g) * 2] = M;
-                    p.ws.part_ml[((size_t)item * G + g) * 2 + 1] = Lsum;
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    const float mw = all_ml[(w * G + g) * 2];
+                    const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+                    Lsum = fmaf(all_ml[(w * G + g) * 2 + 1], f, Lsum);
+                    O = fmaf(all_o[(size_t)(w * G + g) * D + dd], f, O);
+                }
+                const int hq = h * G + g;
+                if (n_chunks == 1) {
+                    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+                    Elt<T>::store(outg + (int64_t)seq * p.out_sb + (int64_t)hq * p.out_sh + dd, O * inv);
+                    if (dd == 0 && p.lse != nullptr)
+                        p.lse[(int64_t)seq * p.Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * 0.6931471805599453f : -INFINITY;
+                } else {
+                    p.ws.part_o[((size_t)item * G + g) * D + dd] = O;
+                    if (dd == 0) {
+                        p.ws.part_ml[((size_t)item * G + g) * 2] = M;
+                        p.ws.part_ml[((size_t)item * G + g) * 2 + 1] = Lsum;
+                    }
                 }
             }
+            __syncwarp();
+            if (lane == 0) { *merge_cnt = 0; mbar_arrive(bar_merge(1)); }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_merge(1));
+        PROF_MARK(5)   // publish (+ combine if last)
         ++consumed;
     }
+    PROF_FLUSH(8)
     if (*abort_flag && threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
 }
 
