@@ -65,7 +65,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 #endif
 
 // header words at the start of the workspace
-enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrWords = 64 };
+enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrNumSplit = 5,
+       kHdrWords = 64 };
 
 struct ChunkDesc {
     int seq, page_begin, n_pages, chunk_idx, n_chunks, pad0, pad1, pad2;
@@ -78,6 +79,7 @@ struct Workspace {
     int* order;           // [B]   sequence id at each position of the processing order
     int* seq_first;       // [B]   first chunk index of each sequence
     int* seq_count;       // [B]   number of chunks of each sequence
+    int* split_list;      // [B]   ids of the sequences that were cut into more than one chunk
     ChunkDesc* chunks;    // [cap]
     float* part_ml;       // [cap*Hkv][G][2]   (running max in log2 units, sum)
     float* part_o;        // [cap*Hkv][G][D]
@@ -118,10 +120,12 @@ size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D
     int* order = reinterpret_cast<int*>(take(B * sizeof(int)));
     int* seq_first = reinterpret_cast<int*>(take(B * sizeof(int)));
     int* seq_count = reinterpret_cast<int*>(take(B * sizeof(int)));
+    int* split_list = reinterpret_cast<int*>(take(B * sizeof(int)));
     ChunkDesc* chunks = reinterpret_cast<ChunkDesc*>(take(cap * sizeof(ChunkDesc)));
     float* ml = reinterpret_cast<float*>(take((size_t)cap * Hq * 2 * sizeof(float)));
     float* po = reinterpret_cast<float*>(take((size_t)cap * Hq * D * sizeof(float)));
     if (ws) { ws->header = header; ws->pos_prefix = prefix; ws->order = order; ws->seq_first = seq_first; ws->seq_count = seq_count;
+              ws->split_list = split_list;
               ws->chunks = chunks; ws->part_ml = ml; ws->part_o = po;
               ws->cap = (int)cap; ws->target_chunks = target; }
     return off;
@@ -166,8 +170,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     __shared__ long long s_total_pages;
     __shared__ int s_bad;
     __shared__ int s_pages[kSortMax];
+    __shared__ int s_ragged, s_split;
     const int tid = threadIdx.x;
-    if (tid == 0) { s_total_pages = 0; s_bad = 0; }
+    if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; }
     __syncthreads();
 
     // total pages of the batch
@@ -196,9 +201,15 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     };
     const bool sorted = B <= kSortMax;
     if (sorted) {
-        for (int s = tid; s < B; s += kPlanThreads) s_pages[s] = clamped_pages(s);
-        __syncthreads();
         for (int s = tid; s < B; s += kPlanThreads) {
+            const int pg = clamped_pages(s);
+            s_pages[s] = pg;
+            if (pg != clamped_pages(0)) s_ragged = 1;
+        }
+        __syncthreads();
+        const bool ragged = s_ragged != 0;   // a uniform batch needs no ordering
+        for (int s = tid; s < B; s += kPlanThreads) {
+            if (!ragged) { ws.order[s] = s; continue; }
             const int mine = s_pages[s];
             int rank = 0;
             for (int t = 0; t < B; ++t) {
@@ -229,6 +240,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
             ws.pos_prefix[pos] = running + incl - n;
             ws.seq_first[s] = running + incl - n;
             ws.seq_count[s] = n;
+            if (n > 1) ws.split_list[atomicAdd(&s_split, 1)] = s;   // order is irrelevant: one CTA per entry
         }
         running += tile_total;
     }
@@ -242,6 +254,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         ws.header[kHdrCounter] = 0;
         ws.header[kHdrStatus] = (s_bad ? kStatusBadCtxLen : 0) | (overflow ? kStatusOverflow : 0);
         ws.header[kHdrTotalItems] = num_chunks * Hkv;
+        ws.header[kHdrNumSplit] = overflow ? 0 : s_split;
 #ifdef IVAB_PROFILE
         for (int i = 16; i < 48; ++i) ws.header[i] = 0;
 #endif
@@ -943,21 +956,20 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int Hq, int G, Workspace ws, T* out, int64_t out_sb,
                                                                  int64_t out_sh, float* lse) {
     constexpr int VPL = D / 32;   // dims per lane
-    const int s = blockIdx.x / Hq, hq = blockIdx.x % Hq;
+    const int num_chunks = ws.header[kHdrNumChunks];
+    const int n_split = ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float sh_m[kMergeWarps];
+    __shared__ float sh_l[kMergeWarps];
+    __shared__ float sh_o[kMergeWarps][D];
+    for (int unit = blockIdx.x; unit < n_split * Hq; unit += gridDim.x) {
+    const int s = ws.split_list[unit / Hq], hq = unit % Hq;
     const int first = ws.seq_first[s];
     const int n = ws.seq_count[s];
-    if (n <= 1) return;   // single-chunk sequences were written by the attention kernel
-    const int num_chunks = ws.header[kHdrNumChunks];
-    if (num_chunks == 0) return;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = hq / G, g = hq % G;
     const size_t item0 = (size_t)h * num_chunks + first;
     const float* ml = ws.part_ml + (item0 * G + g) * 2;          // chunk j at ml + j*G*2
     const float* po = ws.part_o + (item0 * G + g) * D + lane * VPL;   // chunk j at po + j*G*D
-
-    __shared__ float sh_m[kMergeWarps];
-    __shared__ float sh_l[kMergeWarps];
-    __shared__ float sh_o[kMergeWarps][D];
 
     float M = -INFINITY;
     for (int j = threadIdx.x; j < n; j += kMergeWarps * 32) M = fmaxf(M, ml[(size_t)j * G * 2]);
@@ -998,6 +1010,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int Hq, int G, 
     }
     if (threadIdx.x == 0 && lse != nullptr)
         lse[(int64_t)s * Hq + hq] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+    __syncthreads();   // the shared scratch is reused by the next unit
+    }
+    (void)num_chunks;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1090,7 +1105,10 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     g_launches++;
     if (int rc = check_cuda(cudaGetLastError(), "decode_kernel launch")) return rc;
 
-    merge_kernel<T, D><<<B * p.Hq, kMergeWarps * 32, 0, st>>>(p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb, p.out_sh,
+    // a fixed, small grid walks the list of split (sequence, head) pairs the plan kernel left behind
+    const long long units = (long long)B * p.Hq;
+    const int merge_grid = (int)(units < (long long)sm_count() * 8 ? units : (long long)sm_count() * 8);
+    merge_kernel<T, D><<<merge_grid, kMergeWarps * 32, 0, st>>>(p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb, p.out_sh,
                                                               p.lse);
     g_launches++;
     return check_cuda(cudaGetLastError(), "merge_kernel launch");
