@@ -1107,7 +1107,7 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
 
     // a fixed, small grid walks the list of split (sequence, head) pairs the plan kernel left behind
     const long long units = (long long)B * p.Hq;
-    const int merge_grid = (int)(units < (long long)sm_count() * 8 ? units : (long long)sm_count() * 8);
+    const int merge_grid = (int)(units < (long long)sm_count() * 32 ? units : (long long)sm_count() * 32);
     merge_kernel<T, D><<<merge_grid, kMergeWarps * 32, 0, st>>>(p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb, p.out_sh,
                                                               p.lse);
     g_launches++;
