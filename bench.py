@@ -252,7 +252,13 @@ def run_gpu(args):
         else:
             iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, wl.page_size)
 
+    hp_graph = None
+    if hp is not None and not args.no_graph:
+        hp_graph, _, _ = hp.capture(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
+
     def attend():
+        if hp_graph is not None:
+            return hp_graph.replay()
         if hp is not None:
             return hp.decode(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
         return iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, wl.page_size,
@@ -458,6 +464,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (small ncu captures)")
     ap.add_argument("--context", type=int, default=0, help="override the context length")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--no-graph", action="store_true", help="head-parallel mode: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -105,3 +105,22 @@ class HeadParallelDecoder:
         out = gathered[:, :, :D].to(out_l.dtype)
         lse = gathered[:, :, D].contiguous()
         return out, lse
+
+    def capture(self, q: torch.Tensor, k_pool_local: torch.Tensor, v_pool_local: torch.Tensor,
+                block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
+                scale: Optional[float] = None):
+        """Record ``decode`` on these tensors in a CUDA graph (local attention kernels, packing and the
+        NCCL all-gather as one launch).  At 131072 tokens over 8 GPUs each rank reads 67 MB per step --
+        about 10 microseconds of HBM time -- so the step is bound by launch latency, which a graph
+        replay removes.  Returns ``(graph, out, lse)``: refill the input tensors in place, call
+        ``graph.replay()`` and read ``out`` / ``lse``.  Every rank must capture and replay in step."""
+        stream = torch.cuda.Stream(device=q.device)
+        stream.wait_stream(torch.cuda.current_stream(q.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):   # communicator channels and kernel attributes are set up outside the capture
+                self.decode(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out, lse = self.decode(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale)
+        return graph, out, lse
