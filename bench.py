@@ -252,13 +252,13 @@ def run_gpu(args):
         else:
             iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, wl.page_size)
 
-    hp_graph = None
+    hp_step = None
     if hp is not None and not args.no_graph:
-        hp_graph, _, _ = hp.capture(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
+        hp_step = hp.capture_local(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
 
     def attend():
-        if hp_graph is not None:
-            return hp_graph.replay()
+        if hp_step is not None:
+            return hp_step()
         if hp is not None:
             return hp.decode(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
         return iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, wl.page_size,

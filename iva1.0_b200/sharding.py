@@ -106,21 +106,51 @@ class HeadParallelDecoder:
         lse = gathered[:, :, D].contiguous()
         return out, lse
 
-    def capture(self, q: torch.Tensor, k_pool_local: torch.Tensor, v_pool_local: torch.Tensor,
-                block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
-                scale: Optional[float] = None):
-        """Record ``decode`` on these tensors in a CUDA graph (local attention kernels, packing and the
-        NCCL all-gather as one launch).  At 131072 tokens over 8 GPUs each rank reads 67 MB per step --
-        about 10 microseconds of HBM time -- so the step is bound by launch latency, which a graph
-        replay removes.  Returns ``(graph, out, lse)``: refill the input tensors in place, call
-        ``graph.replay()`` and read ``out`` / ``lse``.  Every rank must capture and replay in step."""
-        stream = torch.cuda.Stream(device=q.device)
-        stream.wait_stream(torch.cuda.current_stream(q.device))
-        with torch.cuda.stream(stream):
-            for _ in range(2):   # communicator channels and kernel attributes are set up outside the capture
-                self.decode(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale)
-        stream.synchronize()
+    def capture_local(self, q: torch.Tensor, k_pool_local: torch.Tensor, v_pool_local: torch.Tensor,
+                      block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
+                      scale: Optional[float] = None):
+        """Record this rank's share of a step -- the attention kernels and the packing of ``out`` and
+        ``lse`` into one fp32 buffer -- in a CUDA graph, and return ``step()``.
+
+        At 131072 tokens over 8 GPUs each rank reads 67 MB per step (about 10 microseconds of HBM
+        time), so the step is bound by launch latency.  ``step()`` replays the graph and then issues
+        ONE eager ``all_gather_into_tensor``; it returns fp32 views ``(out [B,H_q,D], lse [B,H_q])``
+        of the gathered buffer (no further kernels when ``B == 1``).  The collective is deliberately
+        kept outside the capture: recording an NCCL collective of ``torch.distributed`` inside a
+        CUDA-graph capture hung on the CUDA 12.9 / NCCL 2.28 stack this was developed on.
+        """
+        dev = q.device
+        B = q.shape[0]
+        if q.shape[1] == self.n_q_heads and self.world > 1:
+            q = q[:, self.q_slice]
+        q = q.contiguous()
+        Hl, D = q.shape[1], q.shape[2]
+        packed = torch.empty(B, Hl, D + 1, dtype=torch.float32, device=dev)
+        gathered = torch.empty(self.world * B, Hl, D + 1, dtype=torch.float32, device=dev)
+
+        def local():
+            out_l, lse_l = self.attn_fn(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale,
+                                        return_lse=True)
+            packed[:, :, :D] = out_l
+            packed[:, :, D] = lse_l
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            local()                      # one-time set-up of the kernels happens outside the capture
+        side.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            out, lse = self.decode(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale)
-        return graph, out, lse
+        with torch.cuda.graph(graph, stream=side):
+            local()
+        full = gathered.view(self.world, B, Hl, D + 1).permute(1, 0, 2, 3)
+
+        def step():
+            graph.replay()
+            if self.world > 1:
+                dist.all_gather_into_tensor(gathered, packed, group=self.group)
+                both = full.reshape(B, self.world * Hl, D + 1)
+            else:
+                both = packed
+            return both[:, :, :D], both[:, :, D]
+
+        return step
