@@ -177,29 +177,16 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
 
     // total pages of the batch
     long long local = 0;
-    int pages0;
-    {
-        int L0 = ctx_len[0];
-        L0 = L0 < 0 ? 0 : (((long long)L0 > (long long)max_pages * page_size) ? max_pages * page_size : L0);
-        pages0 = (L0 + page_size - 1) / page_size;
-    }
     for (int s = tid; s < B; s += kPlanThreads) {
         int L = ctx_len[s];
         if (L < 0 || (long long)L > (long long)max_pages * page_size) { s_bad = 1; L = L < 0 ? 0 : max_pages * page_size; }
-        const int pg = (L + page_size - 1) / page_size;
-        if (pg != pages0) s_ragged = 1;
-        local += pg;
+        local += (L + page_size - 1) / page_size;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
     if ((tid & 31) == 0 && local) atomicAdd(reinterpret_cast<unsigned long long*>(&s_total_pages), (unsigned long long)local);
     __syncthreads();
     const long long total_pages = s_total_pages;
-    // A ragged batch is cut finely (about kItemsPerSlot items per resident CTA) so that dynamic
-    // scheduling can even out the load.  When every sequence has the same number of pages there is
-    // nothing to even out, and fewer, larger items mean fewer item transitions and partials.
-    const bool ragged = s_ragged != 0;
-    if (!ragged) target_chunks = max(1, target_chunks * 3 / kItemsPerSlot);
     long long c64 = (total_pages + target_chunks - 1) / target_chunks;
     if (c64 < kMinChunkPages) c64 = kMinChunkPages;
     const int chunk_pages = (int)(c64 > 0x3fffffff ? 0x3fffffff : c64);
@@ -214,8 +201,13 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     };
     const bool sorted = B <= kSortMax;
     if (sorted) {
-        for (int s = tid; s < B; s += kPlanThreads) s_pages[s] = clamped_pages(s);
+        for (int s = tid; s < B; s += kPlanThreads) {
+            const int pg = clamped_pages(s);
+            s_pages[s] = pg;
+            if (pg != clamped_pages(0)) s_ragged = 1;
+        }
         __syncthreads();
+        const bool ragged = s_ragged != 0;   // a uniform batch needs no ordering
         for (int s = tid; s < B; s += kPlanThreads) {
             if (!ragged) { ws.order[s] = s; continue; }
             const int mine = s_pages[s];
