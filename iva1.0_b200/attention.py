@@ -66,7 +66,8 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
                            block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
                            scale: Optional[float] = None, *, out: Optional[torch.Tensor] = None,
                            lse: Optional[torch.Tensor] = None, return_lse: bool = False,
-                           workspace: Optional[torch.Tensor] = None, check: bool = False):
+                           workspace: Optional[torch.Tensor] = None, check: bool = False,
+                           ctx_begin: Optional[torch.Tensor] = None):
     """``out[s,h] = softmax(q[s,h] . K_s^T * scale) . V_s`` over the ``ctx_len[s]`` cached tokens of
     sequence ``s``, K/V read in place from the page pool through ``block_table``.
 
@@ -74,7 +75,8 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     ``block_table`` int32 ``[B,max_pages]``; ``ctx_len`` int32 ``[B]``.  ``H_q/H_kv`` in {1,2,4,8}.
     Returns ``out`` (dtype of q) or ``(out, lse)`` with ``lse`` fp32 ``[B,H_q]`` (natural log).
     ``check=True`` synchronises and raises if the kernels flagged a bad page id / length or a
-    timed-out wait.
+    timed-out wait.  ``ctx_begin`` (int32 ``[B]``, optional) restricts sequence ``s`` to the keys
+    ``ctx_begin[s] <= j < ctx_len[s]`` -- a sliding window; pages wholly before it are not read.
     """
     _lib.require_cuda(q, k_pool, v_pool, block_table, ctx_len)
     Hkv, num_pages, sh, sp = _pool_strides(k_pool, page_size)
@@ -83,11 +85,11 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     if k_pool.dtype != q.dtype or k_pool.shape[-1] != q.shape[-1]:
         raise ValueError("q and the pools must share dtype and head_dim")
     return _decode(q, k_pool, v_pool, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
-                   out, lse, return_lse, workspace, check)
+                   out, lse, return_lse, workspace, check, ctx_begin)
 
 
 def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
-            out, lse, return_lse, workspace, check):
+            out, lse, return_lse, workspace, check, ctx_begin=None):
     """Argument checks and the library call; ``k_base`` / ``v_base`` only supply base pointers, the
     pool geometry is given by ``Hkv, num_pages, sh, sp`` (element strides of head and page)."""
     if q.requires_grad:
@@ -107,6 +109,12 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
         ctx_len = ctx_len.to(torch.int32).contiguous()
     if block_table.shape[0] != B or ctx_len.numel() != B:
         raise ValueError("block_table / ctx_len batch size does not match q")
+    if ctx_begin is not None:
+        _lib.require_cuda(ctx_begin)
+        if ctx_begin.dtype != torch.int32 or not ctx_begin.is_contiguous():
+            ctx_begin = ctx_begin.to(torch.int32).contiguous()
+        if ctx_begin.numel() != B:
+            raise ValueError("ctx_begin batch size does not match q")
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     if out is None:
@@ -124,6 +132,7 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
         _lib.check(lib.ivab_paged_decode_attn(
             q.data_ptr(), q.stride(0), q.stride(1), k_base.data_ptr(), v_base.data_ptr(), sh, sp,
             block_table.data_ptr(), block_table.stride(0), ctx_len.data_ptr(),
+            ctx_begin.data_ptr() if ctx_begin is not None else None,
             out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr() if lse is not None else None,
             _lib.dtype_code(q.dtype), B, Hq, Hkv, D, page_size, num_pages, block_table.shape[1],
             float(scale), workspace.data_ptr(), workspace.numel(), stream))
@@ -161,13 +170,14 @@ def _dense_as_pool(k: torch.Tensor, v: torch.Tensor):
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, dropout_prob: float = 0.0,
               training: bool = True, *, ctx_len: Optional[torch.Tensor] = None,
-              return_lse: bool = False):
+              ctx_begin: Optional[torch.Tensor] = None, return_lse: bool = False):
     """``softmax(q k^T * scale) v`` on ``[B,H,S,D]`` queries against ``[B,H,L,D]`` keys/values.
 
     Signature of ``attention_triton`` (src/kernels_t/attention_triton.py:215-223).  Every query
     row sees all ``L`` keys (the reference module's behaviour with ``causal=False``,
     src/core/attention.py:77-102); pass ``ctx_len`` (int32 ``[B,S]`` or ``[B]``) to limit the keys
-    each query sees, e.g. ``prior + i + 1`` for causal prefill.  Dropout is not implemented:
+    each query sees, e.g. ``prior + i + 1`` for causal prefill, and ``ctx_begin`` (same shapes) for
+    the first key it sees (sliding window).  Dropout is not implemented:
     a non-zero ``dropout_prob`` with ``training=True`` raises, as does ``requires_grad``.
     """
     _lib.require_cuda(q, k, v)
@@ -190,7 +200,11 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, d
     else:
         cl = ctx_len.to(device=q.device, dtype=torch.int32)
         cl = (cl.view(B, 1).expand(B, S) if cl.numel() == B else cl.reshape(B, S)).reshape(-1).contiguous()
-    res = _decode(q2, kd, vd, Hkv, n_pages, sh, sp, bt2, cl, _PAGE, scale, None, None, return_lse, None, False)
+    cb = None
+    if ctx_begin is not None:
+        cb = ctx_begin.to(device=q.device, dtype=torch.int32)
+        cb = (cb.view(B, 1).expand(B, S) if cb.numel() == B else cb.reshape(B, S)).reshape(-1).contiguous()
+    res = _decode(q2, kd, vd, Hkv, n_pages, sh, sp, bt2, cl, _PAGE, scale, None, None, return_lse, None, False, cb)
     o2, lse = res if return_lse else (res, None)
     o = o2.view(B, S, Hq, D).permute(0, 2, 1, 3)
     if return_lse:
@@ -215,8 +229,13 @@ class AttentionB200(nn.Module):
     ``config.causal`` is honoured as "query ``i`` sees the cache and tokens ``0..i``".  (The
     reference builds ``tril(ones(S, L+S))`` (attention.py:80), which with a cache hides all but
     the first ``i+1`` *cached* keys; that is not reproduced.  With ``causal=False`` the results
-    equal the reference's.)  Masks, sliding windows, sink configs and RoPE state are not part of
-    the decode path and raise ``NotImplementedError`` when given.
+    equal the reference's.)  ``sliding_window=w`` limits query ``i`` (absolute position) to the keys
+    ``i-w+1 .. i``, which is the reference's window mask (attention.py:115-129) for a call without a
+    cache; with a cache the reference's mask indexes queries from 0 and hides everything but the
+    oldest keys, so there the documented meaning is implemented instead.  Keys outside the window
+    are not masked but skipped: their pages are never read and a ``PagedKVCache`` can hand them back
+    (``evict_before``).  Padding masks and sink configs raise ``NotImplementedError``; RoPE state is
+    ignored, as in the reference.
     """
 
     def __init__(self, config):
@@ -238,8 +257,8 @@ class AttentionB200(nn.Module):
                 kv_cache: Optional[Any] = None, rope_state: Optional[torch.Tensor] = None,
                 sliding_window: Optional[int] = None, sink_cfg: Optional[Dict[str, Any]] = None
                 ) -> Tuple[torch.Tensor, Optional[Any]]:
-        if attention_mask is not None or sliding_window is not None or sink_cfg is not None:
-            raise NotImplementedError("AttentionB200 implements the unmasked decode path only")
+        if attention_mask is not None or sink_cfg is not None:
+            raise NotImplementedError("AttentionB200 implements the decode path: no padding mask, no sink config")
         if self.training and self.dropout:
             raise NotImplementedError("AttentionB200 is inference-only: call .eval()")
         from .paged_cache import PagedKVCache
@@ -255,8 +274,9 @@ class AttentionB200(nn.Module):
             prior = kv_cache.append(k, v)                     # [B] lengths before the append (host list)
             bt, cl = kv_cache.block_table_dev, kv_cache.ctx_len_dev
             if S == 1:
+                cb = None if sliding_window is None else (cl - int(sliding_window)).clamp_(min=0)
                 o = paged_decode_attention(q.reshape(B, H, D), kv_cache.k_pool, kv_cache.v_pool, bt, cl,
-                                           kv_cache.page_size, self.scale)
+                                           kv_cache.page_size, self.scale, ctx_begin=cb)
             else:
                 q2 = q.reshape(B * S, H, D)
                 bt2 = bt.repeat_interleave(S, dim=0)
@@ -265,8 +285,14 @@ class AttentionB200(nn.Module):
                     cl2 = (base + torch.arange(1, S + 1, dtype=torch.int32, device=x.device).view(1, S)).reshape(-1)
                 else:
                     cl2 = cl.repeat_interleave(S)
+                cb2 = None
+                if sliding_window is not None:   # query i of the chunk sits at absolute position prior + i
+                    base = torch.tensor(prior, dtype=torch.int32, device=x.device).view(B, 1)
+                    pos = base + torch.arange(S, dtype=torch.int32, device=x.device).view(1, S)
+                    cb2 = (pos + 1 - int(sliding_window)).clamp_(min=0).reshape(-1).contiguous()
+                    cl2 = torch.minimum(cl2.view(B, S), pos + 1).reshape(-1) if not self.causal else cl2
                 o = paged_decode_attention(q2, kv_cache.k_pool, kv_cache.v_pool, bt2, cl2.contiguous(),
-                                           kv_cache.page_size, self.scale)
+                                           kv_cache.page_size, self.scale, ctx_begin=cb2)
             new_cache = kv_cache
             o = o.reshape(B, S, dm)
         else:
@@ -281,10 +307,13 @@ class AttentionB200(nn.Module):
                                            head_dim=kv_cache.head_dim, seq_len=kv_cache.seq_len + S,
                                            device=x.device)
                 new_cache.k, new_cache.v = kh, vh
-            cl = None
-            if self.causal and S > 1:
-                cl = (prior_len + torch.arange(1, S + 1, dtype=torch.int32, device=x.device)).view(1, S).expand(B, S)
-            o = attention(q.transpose(1, 2), kh, vh, self.scale, 0.0, False, ctx_len=cl)
+            cl = cb = None
+            pos1 = (prior_len + torch.arange(1, S + 1, dtype=torch.int32, device=x.device)).view(1, S).expand(B, S)
+            if (self.causal and S > 1) or sliding_window is not None:
+                cl = pos1                       # the window mask also hides the keys after the query
+            if sliding_window is not None:
+                cb = (pos1 - int(sliding_window)).clamp(min=0)
+            o = attention(q.transpose(1, 2), kh, vh, self.scale, 0.0, False, ctx_len=cl, ctx_begin=cb)
             o = o.transpose(1, 2).reshape(B, S, dm)
         return self.o_proj(o), new_cache
 

@@ -163,7 +163,8 @@ __device__ int block_inclusive_scan(int v, int* warp_sums, int* total) {
     return v;
 }
 
-__global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __restrict__ ctx_len, int B, int page_size,
+__global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __restrict__ ctx_len,
+                                                            const int32_t* __restrict__ ctx_begin, int B, int page_size,
                                                             int max_pages, int target_chunks, int cap, int Hkv,
                                                             Workspace ws) {
     __shared__ int warp_sums[32];
@@ -175,12 +176,26 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; }
     __syncthreads();
 
+    // Sequence s attends the keys [begin, L): L is ctx_len clamped to the block table, begin is
+    // ctx_begin (0 without one) clamped to [0, L].  Only the pages that hold such keys are read.
+    auto seq_range = [&](int s, int* L_out, int* begin_out) {
+        int L = ctx_len[s];
+        const long long cap_len = (long long)max_pages * page_size;
+        L = L < 0 ? 0 : ((long long)L > cap_len ? (int)cap_len : L);
+        int b = ctx_begin != nullptr ? ctx_begin[s] : 0;
+        b = b < 0 ? 0 : (b > L ? L : b);
+        *L_out = L; *begin_out = b;
+        return b >= L ? 0 : (L + page_size - 1) / page_size - b / page_size;   // pages to read
+    };
+
     // total pages of the batch
     long long local = 0;
     for (int s = tid; s < B; s += kPlanThreads) {
-        int L = ctx_len[s];
-        if (L < 0 || (long long)L > (long long)max_pages * page_size) { s_bad = 1; L = L < 0 ? 0 : max_pages * page_size; }
-        local += (L + page_size - 1) / page_size;
+        const int L_raw = ctx_len[s];
+        if (L_raw < 0 || (long long)L_raw > (long long)max_pages * page_size) s_bad = 1;
+        if (ctx_begin != nullptr && (ctx_begin[s] < 0 || ctx_begin[s] > L_raw)) s_bad = 1;
+        int L, b;
+        local += seq_range(s, &L, &b);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
@@ -195,9 +210,8 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     // order, so the CTAs that finish last are working on the shortest items and the tail of the
     // kernel is short even for ragged batches.  Batches beyond kSortMax keep their natural order.
     auto clamped_pages = [&](int s) {
-        int L = ctx_len[s];
-        L = L < 0 ? 0 : (((long long)L > (long long)max_pages * page_size) ? max_pages * page_size : L);
-        return (L + page_size - 1) / page_size;
+        int L, b;
+        return seq_range(s, &L, &b);
     };
     const bool sorted = B <= kSortMax;
     if (sorted) {
@@ -271,18 +285,18 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         const int first = ws.pos_prefix[lo];
         const int n = ws.pos_prefix[lo + 1] - first;
         const int j = ci - first;
-        int L = ctx_len[s];
-        L = L < 0 ? 0 : (((long long)L > (long long)max_pages * page_size) ? max_pages * page_size : L);
-        const int pages = (L + page_size - 1) / page_size;
+        int L, begin;
+        const int pages = seq_range(s, &L, &begin);
         const int per = pages / n, rem = pages % n;   // even split: first `rem` chunks get one more page
         ChunkDesc d;
         d.seq = s;
-        d.page_begin = j * per + (j < rem ? j : rem);
+        d.page_begin = begin / page_size + j * per + (j < rem ? j : rem);
         d.n_pages = per + (j < rem ? 1 : 0);
         d.chunk_idx = j;
         d.n_chunks = n;
         d.pad0 = L;
-        d.pad1 = d.pad2 = 0;
+        d.pad1 = begin;
+        d.pad2 = 0;
         ws.chunks[ci] = d;
     }
 }
@@ -304,7 +318,8 @@ struct DecodeParams {
 };
 
 // item ring entry (ints): what the producer tells the consumers about the next work item
-enum { kItSeq = 0, kItHead = 1, kItPages = 2, kItPageBegin = 3, kItChunks = 4, kItIndex = 5, kItStart = 6, kItLen = 7 };
+enum { kItSeq = 0, kItHead = 1, kItPages = 2, kItPageBegin = 3, kItChunks = 4, kItIndex = 5, kItStart = 6, kItLen = 7,
+       kItBegin = 8, kItWords = 16 };
 
 template <typename T, int D, int G>
 struct Cfg {
@@ -320,8 +335,8 @@ struct Cfg {
     // shared memory carve-up (bytes)
     static constexpr int OFF_BARS = 0;                                  // 2*kMaxStages + 2*kItemRing + 2 barriers
     static constexpr int OFF_ABORT = 1024 - 16;
-    static constexpr int OFF_ITEMS = 1024;                              // kItemRing * 8 ints
-    static constexpr int OFF_P = OFF_ITEMS + kItemRing * 32;            // [W][G][kPage] floats
+    static constexpr int OFF_ITEMS = 1024;                              // kItemRing * kItWords ints
+    static constexpr int OFF_P = OFF_ITEMS + kItemRing * kItWords * 4;  // [W][G][kPage] floats
     static constexpr int OFF_MRG_ML = OFF_P + kConsumerWarps * G * kPage * 4;       // [W][G][2]
     static constexpr int OFF_MRG_O = OFF_MRG_ML + kConsumerWarps * G * 2 * 4;       // [W][G][D]
     static constexpr int OFF_STAGES = (OFF_MRG_O + kConsumerWarps * G * D * 4 + 1023) / 1024 * 1024;  // swizzled tiles need 1 KB alignment
@@ -417,8 +432,8 @@ struct SimtEngine {
         }
     }
 
-    __device__ __forceinline__ void page(const DecodeParams&, const unsigned char* stage, int n_valid, int lane,
-                                         float* p_smem) {
+    __device__ __forceinline__ void page(const DecodeParams&, const unsigned char* stage, int n_valid, int n_skip,
+                                         int lane, float* p_smem) {
         const uint4* kp = reinterpret_cast<const uint4*>(stage) + lane;
         const uint4* vp = kp + C::PAGE_BYTES / 16;
         // ---- scores: q . k for the page's 16 tokens, all G heads
@@ -439,7 +454,7 @@ struct SimtEngine {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             float s = transpose_reduce<C::NV, C::LPR / 2>(sc[g], c);
-            if (own_tok >= n_valid) s = -INFINITY;       // select, not arithmetic: stale slots may hold NaN
+            if (own_tok >= n_valid || own_tok < n_skip) s = -INFINITY;   // select, not arithmetic: stale slots may hold NaN
             const float m_page = warp_max_f32(s);
             if (m_page > m_run[g]) {                     // warp-uniform
                 const float alpha = fast_exp2(m_run[g] - m_page);
@@ -453,7 +468,7 @@ struct SimtEngine {
         }
         __syncwarp();
         // ---- weighted sum of V
-        if (n_valid == kPage) {
+        if (n_valid == kPage && n_skip == 0) {
 #pragma unroll
             for (int i = 0; i < C::NV; ++i) {
                 const uint4 u = vp[i * 32];
@@ -468,11 +483,11 @@ struct SimtEngine {
                 }
             }
         } else {
-            // last page of the sequence: rows past ctx_len are skipped, never multiplied
+            // first / last page of the window: rows outside [n_skip, n_valid) are skipped, never multiplied
 #pragma unroll
             for (int i = 0; i < C::NV; ++i) {
                 const int tok = i * C::RPI + r;
-                if (tok < n_valid) {
+                if (tok < n_valid && tok >= n_skip) {
                     const uint4 u = vp[i * 32];
                     float vf[C::EPL];
                     Elt<T>::unpack(u, vf);
@@ -556,20 +571,25 @@ struct MmaEngine {
         return (uint32_t)((q >> 3) * TILE_BYTES + token * 128 + (((q & 7) ^ (token & 7)) << 4));
     }
 
-    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int lane, float*) {
+    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int n_skip, int lane,
+                                         float*) {
         const uint32_t kbase = smem_u32(stage);
         const uint32_t vbase = kbase + PAGE_BYTES;
         const int c = lane & 3;
         const int mi = lane >> 3, rr = lane & 7;   // ldmatrix: this lane addresses row rr of matrix mi
 
-        if (n_valid < kPage) {
-            // Last page of the sequence: rows past ctx_len may hold stale bits (NaN included).  Their
-            // weights are exactly zero, but 0 * NaN is NaN inside the MMA, so clear those V rows.
-            const int n_vec = (kPage - n_valid) * 8;                       // 16-byte chunks per tile
-            for (int t = 0; t < TILES; ++t)
-                for (int i = lane; i < n_vec; i += 32)
-                    *reinterpret_cast<uint4*>(stage + PAGE_BYTES + t * TILE_BYTES + n_valid * 128 + i * 16) =
-                        make_uint4(0, 0, 0, 0);
+        const bool partial = n_valid < kPage || n_skip > 0;
+        if (partial) {
+            // First / last page of the window: rows outside [n_skip, n_valid) may hold stale bits (NaN
+            // included).  Their weights are exactly zero, but 0 * NaN is NaN inside the MMA, so clear
+            // those V rows.  (Rows are 128 bytes in every tile; the swizzle only permutes within a row.)
+            for (int t = 0; t < TILES; ++t) {
+                unsigned char* tile = stage + PAGE_BYTES + t * TILE_BYTES;
+                for (int i = lane; i < (kPage - n_valid) * 8; i += 32)
+                    *reinterpret_cast<uint4*>(tile + n_valid * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+                for (int i = lane; i < n_skip * 8; i += 32)
+                    *reinterpret_cast<uint4*>(tile + i * 16) = make_uint4(0, 0, 0, 0);
+            }
             __syncwarp();
         }
 
@@ -588,11 +608,12 @@ struct MmaEngine {
             }
         }
         // this lane: head lane/4, tokens 2c, 2c+1 (block 0) and 8+2c, 9+2c (block 1)
-        if (n_valid < kPage) {
-            if (2 * c >= n_valid) s[0][0] = -INFINITY;
-            if (2 * c + 1 >= n_valid) s[0][1] = -INFINITY;
-            if (8 + 2 * c >= n_valid) s[1][0] = -INFINITY;
-            if (9 + 2 * c >= n_valid) s[1][1] = -INFINITY;
+        if (partial) {
+            auto masked = [&](int tok) { return tok >= n_valid || tok < n_skip; };
+            if (masked(2 * c)) s[0][0] = -INFINITY;
+            if (masked(2 * c + 1)) s[0][1] = -INFINITY;
+            if (masked(8 + 2 * c)) s[1][0] = -INFINITY;
+            if (masked(9 + 2 * c)) s[1][1] = -INFINITY;
         }
         float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -629,7 +650,7 @@ struct MmaEngine {
             mma_m16n8k16<T>(o[2 * jp], pa0, pb0, pa2, pb2, b[0], b[1]);
             mma_m16n8k16<T>(o[2 * jp + 1], pa0, pb0, pa2, pb2, b[2], b[3]);
         }
-        if (n_valid < kPage) fence_proxy_async_smem();   // order the row clearing before the next TMA write
+        if (partial) fence_proxy_async_smem();   // order the row clearing before the next TMA write
         __syncwarp();
     }
 
@@ -724,6 +745,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                 const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + (id - h * num_chunks));
                 const int4 a = __ldg(src), b = __ldg(src + 1);
                 d.seq = a.x; d.page_begin = a.y; d.n_pages = a.z; d.chunk_idx = a.w; d.n_chunks = b.x; d.pad0 = b.y;
+                d.pad1 = b.z;
                 *h_out = h;
             }
             return d;
@@ -760,10 +782,10 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             }
             PROF_MARK(1)   // wait for a free item slot
             if (lane == 0) {
-                volatile int* it = items + slot * 8;
+                volatile int* it = items + slot * kItWords;
                 it[kItSeq] = d.seq; it[kItHead] = h; it[kItPages] = done ? -1 : d.n_pages;
                 it[kItPageBegin] = d.page_begin; it[kItChunks] = d.n_chunks; it[kItIndex] = item;
-                it[kItStart] = (d.seq + d.chunk_idx) % kConsumerWarps; it[kItLen] = d.pad0;
+                it[kItStart] = (d.seq + d.chunk_idx) % kConsumerWarps; it[kItLen] = d.pad0; it[kItBegin] = d.pad1;
                 mbar_arrive(bar_item_full(slot));
             }
             ++published;
@@ -865,9 +887,10 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         const int slot = consumed % kItemRing;
         if (!mbar_wait_bounded(bar_item_full(slot), (consumed / kItemRing) & 1, abort_flag, limit)) break;
         PROF_MARK(0)   // wait for the next item
-        volatile int* it = items + slot * 8;
+        volatile int* it = items + slot * kItWords;
         const int seq = it[kItSeq], h = it[kItHead], n_pages = it[kItPages], page_begin = it[kItPageBegin];
         const int n_chunks = it[kItChunks], item = it[kItIndex], start = it[kItStart], L = it[kItLen];
+        const int begin = it[kItBegin];
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_item_empty(slot));
         if (n_pages < 0) break;   // sentinel: the work list is exhausted
@@ -881,8 +904,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             const int stage = (taken % spw) * kConsumerWarps + warp;
             if (!mbar_wait_bounded(bar_full(stage), (taken / spw) & 1, abort_flag, limit)) { ok = false; break; }
             PROF_MARK(2)   // wait for page data
-            const int n_valid = min(kPage, L - (page_begin + k) * kPage);
-            eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, lane, p_smem);
+            const int n_valid = min(kPage, L - (page_begin + k) * kPage);      // tokens [n_skip, n_valid) of the page count
+            const int n_skip = max(0, begin - (page_begin + k) * kPage);        // (non-zero only on the window's first page)
+            eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, n_skip, lane, p_smem);
             if (lane == 0) mbar_arrive(bar_empty(stage));
             PROF_MARK(3)   // page math
         }
@@ -1186,7 +1210,7 @@ extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t
                                       const void* k_pool, const void* v_pool,
                                       int64_t pool_stride_head, int64_t pool_stride_page,
                                       const int32_t* block_table, int64_t block_table_stride,
-                                      const int32_t* ctx_len,
+                                      const int32_t* ctx_len, const int32_t* ctx_begin,
                                       void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
                                       int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                                       int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
@@ -1214,7 +1238,7 @@ extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t
     if ((int64_t)ws.cap * kv_heads >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "%s: too many work items", fn);
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, (int)batch, (int)page_size, (int)max_pages_per_seq,
+    plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, ctx_begin, (int)batch, (int)page_size, (int)max_pages_per_seq,
                                             ws.target_chunks, ws.cap, (int)kv_heads, ws);
     g_launches++;
     if (int rc = check_cuda(cudaGetLastError(), "plan_kernel launch")) return rc;
@@ -1291,7 +1315,7 @@ extern "C" int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b,
                                               const void* k_pool, const void* v_pool,
                                               int64_t pool_stride_head, int64_t pool_stride_page,
                                               const int32_t* block_table, int64_t block_table_stride,
-                                              const int32_t* ctx_len,
+                                              const int32_t* ctx_len, const int32_t* ctx_begin,
                                               void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
                                               int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
                                               int64_t head_dim, int64_t page_size, int64_t num_pages,
@@ -1309,7 +1333,8 @@ extern "C" int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b,
     // Nothing in the scratch has to start at zero: the plan kernel rewrites the header (work counter,
     // status word, chunk count) and every partial that is read was written by this call.
     if (int rc = ivab_paged_decode_attn(q, q_stride_b, q_stride_h, k_pool, v_pool, pool_stride_head, pool_stride_page,
-                                        block_table, block_table_stride, ctx_len, out, out_stride_b, out_stride_h, lse,
+                                        block_table, block_table_stride, ctx_len, ctx_begin, out, out_stride_b, out_stride_h,
+                                        lse,
                                         dtype, batch, q_heads, kv_heads, head_dim, page_size, num_pages,
                                         max_pages_per_seq, scale, scratch, kStaticScratchBytes, stream))
         return rc;

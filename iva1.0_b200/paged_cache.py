@@ -217,3 +217,25 @@ class PagedKVCache:
             self._bt_host[s].fill_(-1)
         self._bt_dirty = True
         self._sync_device()
+
+
+    def evict_before(self, begin: Sequence[int]) -> int:
+        """Return to the pool every page that lies wholly before position ``begin[s]`` of sequence
+        ``s`` (the keys a sliding window no longer needs).  The block-table entries of those pages
+        become ``-1``; decode attention called with ``ctx_begin >= begin`` never reads them.  Dense
+        views (``.k``, ``gather``) of an evicted range are no longer available.  Returns the number
+        of pages freed."""
+        freed = 0
+        for s, b in enumerate(begin):
+            first_kept = min(int(b), self._lens[s]) // self.page_size
+            tab = self._tables[s]
+            for p in range(first_kept):
+                if tab[p] >= 0:
+                    self._free.append(tab[p])
+                    tab[p] = -1
+                    self._bt_host[s, p] = -1
+                    self._bt_dirty = True
+                    freed += 1
+        if freed:
+            self._sync_device()
+        return freed

@@ -135,7 +135,8 @@ def attention_math_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 def paged_decode_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                      block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int,
                      scale: Optional[float] = None,
-                     seqs: Optional[List[int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                     seqs: Optional[List[int]] = None,
+                     ctx_begin: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Single-query attention read through the block table.
 
     ``q`` is ``[B,H_q,D]``; pools are ``[1,H_kv,S,D]``.  Per sequence: gather its slots
@@ -144,8 +145,12 @@ def paged_decode_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     for its ``H_q/H_kv`` query heads; the reference itself is multi-head only
     (attention.py:28-31), so this is the same math applied per group.
 
+    ``ctx_begin`` (optional) limits sequence ``s`` to the keys ``ctx_begin[s] <= j < ctx_len[s]``:
+    the keys a sliding-window mask leaves visible to the newest query (attention.py:115-129 keeps
+    ``[i-w+1, i]`` for query ``i``); the hidden keys are not gathered at all.
+
     Returns ``out [B,H_q,D]`` fp32 and ``lse [B,H_q]`` fp32.  A sequence of length 0
-    yields zeros and ``-inf``.  ``seqs`` restricts the computation to some sequences
+    (or an empty window) yields zeros and ``-inf``.  ``seqs`` restricts the computation to some sequences
     (rows of the others are left zero).
     """
     B, Hq, D = q.shape
@@ -157,10 +162,11 @@ def paged_decode_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     lse = torch.full((B, Hq), float("-inf"), dtype=torch.float32)
     for s in (range(B) if seqs is None else seqs):
         L = int(ctx_len[s])
-        if L == 0:
+        b = 0 if ctx_begin is None else min(max(int(ctx_begin[s]), 0), L)
+        if L == 0 or b >= L:
             continue
-        slots = slots_for_sequence(block_table[s], L, page_size)
-        k = kv_gather_ref(k_pool, slots)            # [1,Hkv,L,D] fp32
+        slots = slots_for_sequence(block_table[s], L, page_size, start=b)
+        k = kv_gather_ref(k_pool, slots)            # [1,Hkv,L-b,D] fp32
         v = kv_gather_ref(v_pool, slots)
         if group > 1:
             k = k.repeat_interleave(group, dim=1)
@@ -220,10 +226,11 @@ class KVCacheRef:
         return self.k[:, :, start:end], self.v[:, :, start:end]
 
 
-def attention_module_ref(x, wq, wk, wv, wo, n_heads, cache_k=None, cache_v=None):
-    """AttentionTorch.forward (src/core/attention.py:46-110) with ``causal=False``, no
-    masks, eval mode: projections (:49-55), cache concat (:61-63), attention (:77,99,102),
-    output projection (:104-108).  Returns ``(output, k_all, v_all)``."""
+def attention_module_ref(x, wq, wk, wv, wo, n_heads, cache_k=None, cache_v=None, sliding_window=None):
+    """AttentionTorch.forward (src/core/attention.py:46-110) with ``causal=False``, eval mode:
+    projections (:49-55), cache concat (:61-63), attention (:77,99,102), optional sliding-window
+    mask (:83-87,115-129; query ``i`` keeps keys ``max(0,i-w+1)..i``), output projection
+    (:104-108).  Returns ``(output, k_all, v_all)``."""
     B, S, dm = x.shape
     hd = dm // n_heads
     q = F.linear(x, wq).view(B, S, n_heads, hd).transpose(1, 2)
@@ -233,6 +240,11 @@ def attention_module_ref(x, wq, wk, wv, wo, n_heads, cache_k=None, cache_v=None)
         k = torch.cat([cache_k, k], dim=2)
         v = torch.cat([cache_v, v], dim=2)
     scores = torch.matmul(q, k.transpose(-2, -1)) * (1.0 / math.sqrt(hd))
+    if sliding_window is not None:
+        mask = torch.zeros(S, k.size(2))
+        for i in range(S):
+            mask[i, max(0, i - sliding_window + 1):min(k.size(2), i + 1)] = 1
+        scores = scores.masked_fill(mask == 0, float("-inf"))
     w = F.softmax(scores, dim=-1)
     o = torch.matmul(w, v).transpose(1, 2).contiguous().view(B, S, dm)
     return F.linear(o, wo), k, v

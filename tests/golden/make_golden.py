@@ -79,6 +79,11 @@ def module_inputs(seed=13):
     return B, H, hd, L, w, x, ck, cv
 
 
+def window_inputs(seed=14):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(2, 12, 4 * 32, generator=g)
+
+
 def c1_module_workload():
     """Config C1 with the new token's K and V equal to q: with identity projections the
     reference module appends ``k = v = x`` (attention.py:50-51,62-63)."""
@@ -145,6 +150,13 @@ def main(ref_root):
     out["module_new_k"] = new_cache.k.numpy()
     out["module_new_v"] = new_cache.v.numpy()
     assert new_cache.seq_len == L + 1
+
+    # the same module without a cache on a 12-token input, sliding window of 5 (attention.py:83-87)
+    xw = window_inputs()
+    with torch.no_grad():
+        yw, none_cache = mod(xw, sliding_window=5)
+    assert none_cache is None
+    out["module_window_out"] = yw.numpy()
 
     wl = c1_module_workload()
     Hh, D = wl.n_q_heads, wl.head_dim

@@ -238,3 +238,59 @@ def test_module_with_paged_cache_decodes_like_the_dense_reference():
     assert torch.allclose(cache.k.cpu(), dense_k, atol=1e-5) and torch.allclose(cache.v.cpu(), dense_v, atol=1e-5)
     k2, v2 = cache.get_slice(5, 9)
     assert torch.allclose(k2.cpu(), dense_k[:, :, 5:9], atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype,Hq,Hkv,D", [(torch.bfloat16, 8, 8, 128), (torch.bfloat16, 16, 4, 128),
+                                            (torch.float16, 8, 2, 64), (torch.float32, 4, 2, 64)])
+def test_sliding_window_begin(dtype, Hq, Hkv, D):
+    """ctx_begin: windows starting on and inside pages, a full context, a one-key window and an empty
+    one; stale slots (and everything a window hides on its first page) must not leak in."""
+    ctx = torch.tensor([300, 300, 300, 47, 47, 16, 5000, 33])
+    begin = torch.tensor([0, 256, 261, 46, 47, 15, 4096 - 7, 1])
+    wl = workloads.make_decode_workload("win", ctx, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, dtype=dtype,
+                                        seed=Hq + D, free_frac=0.2, poison_unused=True)
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16, wl.scale,
+                                            ctx_begin=begin)
+    d = wl.to(DEV)
+    out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16, wl.scale,
+                                               return_lse=True, check=True, ctx_begin=begin.to(DEV))
+    assert_attn_close(out, out_ref, dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
+    assert not out[4].any() and torch.isinf(lse[4]).all()
+
+
+def test_window_never_reads_evicted_pages():
+    """After evict_before() the dropped pages are back in the pool (and get overwritten with NaN
+    here); a windowed decode must give the same bits as before the eviction."""
+    torch.manual_seed(1)
+    B, H, D = 2, 4, 128
+    cache = iva_b200.PagedKVCache(batch_size=B, n_heads=H, head_dim=D, device=DEV, dtype=torch.bfloat16,
+                                  max_seq_len=400, num_pages=60, shuffle_seed=2)
+    cache.append(torch.randn(B, 333, H, D).to(torch.bfloat16).to(DEV), torch.randn(B, 333, H, D).to(torch.bfloat16).to(DEV))
+    q = torch.randn(B, 8, D).to(torch.bfloat16).to(DEV)
+    window = 100
+    begin = (cache.ctx_len_dev - window).clamp(min=0)
+    before = iva_b200.paged_decode_attention(q, cache.k_pool, cache.v_pool, cache.block_table_dev, cache.ctx_len_dev,
+                                             16, ctx_begin=begin, check=True)
+    free0 = cache.free_pages
+    dropped = [cache._tables[s][:(333 - window) // 16] for s in range(B)]
+    freed = cache.evict_before([333 - window] * B)
+    assert freed == B * ((333 - window) // 16) and cache.free_pages == free0 + freed
+    for pages in dropped:                               # whoever gets those pages next may write anything
+        for p in pages:
+            cache.k_pool[:, :, p * 16:(p + 1) * 16] = float("nan")
+            cache.v_pool[:, :, p * 16:(p + 1) * 16] = float("nan")
+    after = iva_b200.paged_decode_attention(q, cache.k_pool, cache.v_pool, cache.block_table_dev, cache.ctx_len_dev,
+                                            16, ctx_begin=begin, check=True)
+    assert torch.equal(before, after)
+
+
+def test_module_sliding_window_matches_attention_torch_golden(golden, golden_inputs):
+    """AttentionB200 without a cache, 12 tokens, sliding window 5 -- the reference's own mask."""
+    B, H, hd, L, w, x, ck, cv = golden_inputs.module_inputs()
+    cfg = SimpleNamespace(d_model=H * hd, n_heads=H, dropout=0.0, causal=False, attn_impl="triton")
+    mod = iva_b200.get_attention(cfg).to(DEV).eval()
+    mod.load_state_dict({"q_proj.weight": w[0], "k_proj.weight": w[1], "v_proj.weight": w[2], "o_proj.weight": w[3]})
+    y, cache = mod(golden_inputs.window_inputs().to(DEV), sliding_window=5)
+    assert cache is None
+    assert (y.cpu() - torch.from_numpy(golden["module_window_out"])).abs().max().item() <= 5e-5

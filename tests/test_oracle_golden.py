@@ -65,6 +65,29 @@ def test_module_restatement_matches_attention_torch(golden, golden_inputs):
     assert torch.equal(v_all, _t(golden["module_new_v"]))
 
 
+def test_module_window_restatement_matches_attention_torch(golden, golden_inputs):
+    """No cache, 12 tokens, sliding window 5: the reference's own window mask (attention.py:115-129)."""
+    B, H, hd, L, w, x, ck, cv = golden_inputs.module_inputs()
+    y, _, _ = ref.attention_module_ref(golden_inputs.window_inputs(), w[0], w[1], w[2], w[3], H, sliding_window=5)
+    assert torch.allclose(y, _t(golden["module_window_out"]), atol=1e-6, rtol=1e-6)
+
+
+def test_window_is_a_slice_of_the_keys():
+    """ctx_begin in the checker = attention over the keys [begin, L) only."""
+    from iva_b200 import workloads
+
+    wl = workloads.make_decode_workload("w", torch.tensor([50, 20]), n_q_heads=4, n_kv_heads=4, head_dim=64,
+                                        dtype=torch.float32, seed=9)
+    begin = torch.tensor([37, 20])
+    out, lse = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16, ctx_begin=begin)
+    slots = ref.slots_for_sequence(wl.block_table[0], 50, 16)[37:]
+    k = ref.kv_gather_ref(wl.k_pool, slots)
+    v = ref.kv_gather_ref(wl.v_pool, slots)
+    o0, l0 = ref.attention_math_ref(wl.q[0].view(1, 4, 1, 64), k, v, wl.scale)
+    assert torch.equal(out[0], o0.view(4, 64)) and torch.equal(lse[0], l0.view(4))
+    assert not out[1].any() and torch.isinf(lse[1]).all()          # empty window
+
+
 def test_composed_decode_matches_attention_torch_on_c1(golden, golden_inputs):
     """Config C1 through append -> paged gather -> attention, against AttentionTorch run on the
     reference-gathered cache (identity projections, causal=False)."""
