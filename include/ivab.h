@@ -123,12 +123,15 @@ int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t kv_heads
 
 /*
  * Single-query decode attention read through a block table:
- *   out[s,hq,:] = softmax_j( q[s,hq,:] . K[s,kvh(hq),j,:] * scale ) . V[s,kvh(hq),j,:],  ctx_begin[s] <= j < ctx_len[s]
+ *   out[s,hq,:] = softmax_j( q[s,hq,:] . K[s,kvh(hq),j,:] * scale ) . V[s,kvh(hq),j,:]
+ *                 over the keys j < ctx_len[s] with j < sink_tokens or j >= ctx_begin[s]
  *   lse[s,hq]   = log sum_j exp( q.K_j * scale )                       (natural log; may be NULL)
  * ctx_begin may be NULL (= 0 for every sequence).  With a sliding window it is ctx_len - window:
  * pages that lie wholly before it are never read, so their block-table entries may be stale and the
  * pages themselves may already be back in the pool (the keys a sliding-window mask would hide,
- * src/core/attention.py:83-87,115-129, are dropped instead of masked).
+ * src/core/attention.py:83-87,115-129, are dropped instead of masked).  sink_tokens > 0 keeps the
+ * first sink_tokens keys of every sequence visible in front of its window (attention sinks,
+ * sink_cfg["sink_tokens"] of src/core/attention.py:131-148); their pages must stay allocated.
  * The math is AttentionTorch.forward lines 77, 99, 102 (src/core/attention.py) for one query
  * and no mask; it takes the place of the unusable attention_kernel
  * (src/kernels_t/attention_triton.py:18-71).  kvh(hq) = hq / (q_heads/kv_heads); the group
@@ -142,7 +145,7 @@ int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h
                            const void* k_pool, const void* v_pool,
                            int64_t pool_stride_head, int64_t pool_stride_page,
                            const int32_t* block_table, int64_t block_table_stride,
-                           const int32_t* ctx_len, const int32_t* ctx_begin,
+                           const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
                            void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
                            int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                            int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
@@ -181,7 +184,7 @@ int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b, int64_t q_
                                    const void* k_pool, const void* v_pool,
                                    int64_t pool_stride_head, int64_t pool_stride_page,
                                    const int32_t* block_table, int64_t block_table_stride,
-                                   const int32_t* ctx_len, const int32_t* ctx_begin,
+                                   const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
                                    void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
                                    int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                                    int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,

@@ -67,7 +67,7 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
                            scale: Optional[float] = None, *, out: Optional[torch.Tensor] = None,
                            lse: Optional[torch.Tensor] = None, return_lse: bool = False,
                            workspace: Optional[torch.Tensor] = None, check: bool = False,
-                           ctx_begin: Optional[torch.Tensor] = None):
+                           ctx_begin: Optional[torch.Tensor] = None, sink_tokens: int = 0):
     """``out[s,h] = softmax(q[s,h] . K_s^T * scale) . V_s`` over the ``ctx_len[s]`` cached tokens of
     sequence ``s``, K/V read in place from the page pool through ``block_table``.
 
@@ -77,6 +77,7 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     ``check=True`` synchronises and raises if the kernels flagged a bad page id / length or a
     timed-out wait.  ``ctx_begin`` (int32 ``[B]``, optional) restricts sequence ``s`` to the keys
     ``ctx_begin[s] <= j < ctx_len[s]`` -- a sliding window; pages wholly before it are not read.
+    ``sink_tokens`` keeps the first keys of every sequence visible in front of the window.
     """
     _lib.require_cuda(q, k_pool, v_pool, block_table, ctx_len)
     Hkv, num_pages, sh, sp = _pool_strides(k_pool, page_size)
@@ -85,11 +86,11 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     if k_pool.dtype != q.dtype or k_pool.shape[-1] != q.shape[-1]:
         raise ValueError("q and the pools must share dtype and head_dim")
     return _decode(q, k_pool, v_pool, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
-                   out, lse, return_lse, workspace, check, ctx_begin)
+                   out, lse, return_lse, workspace, check, ctx_begin, sink_tokens)
 
 
 def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
-            out, lse, return_lse, workspace, check, ctx_begin=None):
+            out, lse, return_lse, workspace, check, ctx_begin=None, sink_tokens=0):
     """Argument checks and the library call; ``k_base`` / ``v_base`` only supply base pointers, the
     pool geometry is given by ``Hkv, num_pages, sh, sp`` (element strides of head and page)."""
     if q.requires_grad:
@@ -132,7 +133,7 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
         _lib.check(lib.ivab_paged_decode_attn(
             q.data_ptr(), q.stride(0), q.stride(1), k_base.data_ptr(), v_base.data_ptr(), sh, sp,
             block_table.data_ptr(), block_table.stride(0), ctx_len.data_ptr(),
-            ctx_begin.data_ptr() if ctx_begin is not None else None,
+            ctx_begin.data_ptr() if ctx_begin is not None else None, int(sink_tokens),
             out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr() if lse is not None else None,
             _lib.dtype_code(q.dtype), B, Hq, Hkv, D, page_size, num_pages, block_table.shape[1],
             float(scale), workspace.data_ptr(), workspace.numel(), stream))
@@ -234,8 +235,11 @@ class AttentionB200(nn.Module):
     cache; with a cache the reference's mask indexes queries from 0 and hides everything but the
     oldest keys, so there the documented meaning is implemented instead.  Keys outside the window
     are not masked but skipped: their pages are never read and a ``PagedKVCache`` can hand them back
-    (``evict_before``).  Padding masks and sink configs raise ``NotImplementedError``; RoPE state is
-    ignored, as in the reference.
+    (``evict_before``).  ``sink_cfg={"sink_tokens": n}`` together with a sliding window keeps the first
+    ``n`` keys visible in front of the window (the reference ANDs its sink mask, attention.py:131-148,
+    with the window mask, which keeps nothing extra; the streaming-attention meaning of the option is
+    implemented).  Padding masks raise ``NotImplementedError``; RoPE state is ignored, as in the
+    reference.
     """
 
     def __init__(self, config):
@@ -257,12 +261,15 @@ class AttentionB200(nn.Module):
                 kv_cache: Optional[Any] = None, rope_state: Optional[torch.Tensor] = None,
                 sliding_window: Optional[int] = None, sink_cfg: Optional[Dict[str, Any]] = None
                 ) -> Tuple[torch.Tensor, Optional[Any]]:
-        if attention_mask is not None or sink_cfg is not None:
-            raise NotImplementedError("AttentionB200 implements the decode path: no padding mask, no sink config")
-        if self.training and self.dropout:
-            raise NotImplementedError("AttentionB200 is inference-only: call .eval()")
         from .paged_cache import PagedKVCache
 
+        if attention_mask is not None:
+            raise NotImplementedError("AttentionB200 implements the decode path: no padding mask")
+        sink = int(sink_cfg.get("sink_tokens", 4)) if sink_cfg is not None else 0
+        if sink and (sliding_window is None or not isinstance(kv_cache, PagedKVCache) or x.shape[1] != 1):
+            raise NotImplementedError("sink_cfg is supported for single-token decode on a PagedKVCache with a sliding window")
+        if self.training and self.dropout:
+            raise NotImplementedError("AttentionB200 is inference-only: call .eval()")
         B, S, dm = x.shape
         H, D = self.n_heads, self.head_dim
         q = self.q_proj(x).view(B, S, H, D)
@@ -276,7 +283,7 @@ class AttentionB200(nn.Module):
             if S == 1:
                 cb = None if sliding_window is None else (cl - int(sliding_window)).clamp_(min=0)
                 o = paged_decode_attention(q.reshape(B, H, D), kv_cache.k_pool, kv_cache.v_pool, bt, cl,
-                                           kv_cache.page_size, self.scale, ctx_begin=cb)
+                                           kv_cache.page_size, self.scale, ctx_begin=cb, sink_tokens=sink)
             else:
                 q2 = q.reshape(B * S, H, D)
                 bt2 = bt.repeat_interleave(S, dim=0)

@@ -164,7 +164,8 @@ __device__ int block_inclusive_scan(int v, int* warp_sums, int* total) {
 }
 
 __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __restrict__ ctx_len,
-                                                            const int32_t* __restrict__ ctx_begin, int B, int page_size,
+                                                            const int32_t* __restrict__ ctx_begin, int sink_tokens, int B,
+                                                            int page_size,
                                                             int max_pages, int target_chunks, int cap, int Hkv,
                                                             Workspace ws) {
     __shared__ int warp_sums[32];
@@ -176,16 +177,27 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; }
     __syncthreads();
 
-    // Sequence s attends the keys [begin, L): L is ctx_len clamped to the block table, begin is
-    // ctx_begin (0 without one) clamped to [0, L].  Only the pages that hold such keys are read.
-    auto seq_range = [&](int s, int* L_out, int* begin_out) {
+    // Sequence s attends the keys [0, sink) and [begin, L): L is ctx_len clamped to the block table,
+    // begin is ctx_begin (0 without one) clamped to [0, L], sink is sink_tokens clamped to begin.
+    // Only the pages that hold such keys are read: `sink_pages` pages from the start of the block
+    // table, then the pages from begin/page_size on.  A sink page that is also the window's first
+    // page is read once, as a window page.
+    auto seq_range = [&](int s, int* L_out, int* begin_out, int* sink_pages_out) {
         int L = ctx_len[s];
         const long long cap_len = (long long)max_pages * page_size;
         L = L < 0 ? 0 : ((long long)L > cap_len ? (int)cap_len : L);
         int b = ctx_begin != nullptr ? ctx_begin[s] : 0;
         b = b < 0 ? 0 : (b > L ? L : b);
-        *L_out = L; *begin_out = b;
-        return b >= L ? 0 : (L + page_size - 1) / page_size - b / page_size;   // pages to read
+        const int sink = sink_tokens < b ? (sink_tokens < 0 ? 0 : sink_tokens) : 0;   // sinks inside the window need no extra pages
+        const int first_window_page = b / page_size;
+        int sp = (sink + page_size - 1) / page_size;
+        if (sp > first_window_page) sp = first_window_page;
+        // (when the window is empty its first page would hold no visible key: read sink pages only;
+        //  a sink that ends on the window's page is then lost with it, so widen sp in that case)
+        int window_pages = b >= L ? 0 : (L + page_size - 1) / page_size - first_window_page;
+        if (window_pages == 0) sp = (sink + page_size - 1) / page_size;
+        *L_out = L; *begin_out = b; *sink_pages_out = sp;
+        return sp + window_pages;   // pages to read
     };
 
     // total pages of the batch
@@ -194,8 +206,8 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         const int L_raw = ctx_len[s];
         if (L_raw < 0 || (long long)L_raw > (long long)max_pages * page_size) s_bad = 1;
         if (ctx_begin != nullptr && (ctx_begin[s] < 0 || ctx_begin[s] > L_raw)) s_bad = 1;
-        int L, b;
-        local += seq_range(s, &L, &b);
+        int L, b, sp;
+        local += seq_range(s, &L, &b, &sp);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
@@ -210,8 +222,8 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     // order, so the CTAs that finish last are working on the shortest items and the tail of the
     // kernel is short even for ragged batches.  Batches beyond kSortMax keep their natural order.
     auto clamped_pages = [&](int s) {
-        int L, b;
-        return seq_range(s, &L, &b);
+        int L, b, sp;
+        return seq_range(s, &L, &b, &sp);
     };
     const bool sorted = B <= kSortMax;
     if (sorted) {
@@ -285,18 +297,19 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         const int first = ws.pos_prefix[lo];
         const int n = ws.pos_prefix[lo + 1] - first;
         const int j = ci - first;
-        int L, begin;
-        const int pages = seq_range(s, &L, &begin);
+        int L, begin, sink_pages;
+        const int pages = seq_range(s, &L, &begin, &sink_pages);
         const int per = pages / n, rem = pages % n;   // even split: first `rem` chunks get one more page
         ChunkDesc d;
         d.seq = s;
-        d.page_begin = begin / page_size + j * per + (j < rem ? j : rem);
+        // position in the list of pages to read; page_of() turns it into a block-table index
+        d.page_begin = j * per + (j < rem ? j : rem);
         d.n_pages = per + (j < rem ? 1 : 0);
         d.chunk_idx = j;
         d.n_chunks = n;
         d.pad0 = L;
         d.pad1 = begin;
-        d.pad2 = 0;
+        d.pad2 = sink_pages;
         ws.chunks[ci] = d;
     }
 }
@@ -311,15 +324,22 @@ struct DecodeParams {
     const int32_t* block_table; int64_t bt_stride;
     void* out; int64_t out_sb, out_sh; float* lse;
     int Hq, num_pages;
+    int sink_tokens;           // keys [0, sink_tokens) stay visible in front of a window (0 = none)
     float scale_log2;          // scale * log2(e): scores are kept in base-2 units
     int stages;
     uint64_t wait_limit_ns;
     Workspace ws;
 };
 
+// v-th page a sequence reads -> index into its block table: `sink_pages` pages from the start, then
+// the window's pages from begin / kPage on.
+__device__ __forceinline__ int page_of(int v, int sink_pages, int begin) {
+    return v < sink_pages ? v : v - sink_pages + begin / kPage;
+}
+
 // item ring entry (ints): what the producer tells the consumers about the next work item
 enum { kItSeq = 0, kItHead = 1, kItPages = 2, kItPageBegin = 3, kItChunks = 4, kItIndex = 5, kItStart = 6, kItLen = 7,
-       kItBegin = 8, kItWords = 16 };
+       kItBegin = 8, kItSinkPages = 9, kItWords = 16 };
 
 template <typename T, int D, int G>
 struct Cfg {
@@ -432,8 +452,9 @@ struct SimtEngine {
         }
     }
 
-    __device__ __forceinline__ void page(const DecodeParams&, const unsigned char* stage, int n_valid, int n_skip,
-                                         int lane, float* p_smem) {
+    // tokens t >= n_valid and hole_lo <= t < hole_hi of the page do not count
+    __device__ __forceinline__ void page(const DecodeParams&, const unsigned char* stage, int n_valid, int hole_lo,
+                                         int hole_hi, int lane, float* p_smem) {
         const uint4* kp = reinterpret_cast<const uint4*>(stage) + lane;
         const uint4* vp = kp + C::PAGE_BYTES / 16;
         // ---- scores: q . k for the page's 16 tokens, all G heads
@@ -454,7 +475,8 @@ struct SimtEngine {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             float s = transpose_reduce<C::NV, C::LPR / 2>(sc[g], c);
-            if (own_tok >= n_valid || own_tok < n_skip) s = -INFINITY;   // select, not arithmetic: stale slots may hold NaN
+            if (own_tok >= n_valid || (own_tok >= hole_lo && own_tok < hole_hi))
+                s = -INFINITY;                           // select, not arithmetic: stale slots may hold NaN
             const float m_page = warp_max_f32(s);
             if (m_page > m_run[g]) {                     // warp-uniform
                 const float alpha = fast_exp2(m_run[g] - m_page);
@@ -468,7 +490,7 @@ struct SimtEngine {
         }
         __syncwarp();
         // ---- weighted sum of V
-        if (n_valid == kPage && n_skip == 0) {
+        if (n_valid == kPage && hole_hi <= hole_lo) {
 #pragma unroll
             for (int i = 0; i < C::NV; ++i) {
                 const uint4 u = vp[i * 32];
@@ -483,11 +505,11 @@ struct SimtEngine {
                 }
             }
         } else {
-            // first / last page of the window: rows outside [n_skip, n_valid) are skipped, never multiplied
+            // a page cut by ctx_len, the sink or the window: rows that do not count are skipped, never multiplied
 #pragma unroll
             for (int i = 0; i < C::NV; ++i) {
                 const int tok = i * C::RPI + r;
-                if (tok < n_valid && tok >= n_skip) {
+                if (tok < n_valid && !(tok >= hole_lo && tok < hole_hi)) {
                     const uint4 u = vp[i * 32];
                     float vf[C::EPL];
                     Elt<T>::unpack(u, vf);
@@ -571,24 +593,24 @@ struct MmaEngine {
         return (uint32_t)((q >> 3) * TILE_BYTES + token * 128 + (((q & 7) ^ (token & 7)) << 4));
     }
 
-    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int n_skip, int lane,
-                                         float*) {
+    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int hole_lo,
+                                         int hole_hi, int lane, float*) {
         const uint32_t kbase = smem_u32(stage);
         const uint32_t vbase = kbase + PAGE_BYTES;
         const int c = lane & 3;
         const int mi = lane >> 3, rr = lane & 7;   // ldmatrix: this lane addresses row rr of matrix mi
 
-        const bool partial = n_valid < kPage || n_skip > 0;
+        const bool partial = n_valid < kPage || hole_hi > hole_lo;
         if (partial) {
-            // First / last page of the window: rows outside [n_skip, n_valid) may hold stale bits (NaN
+            // A page cut by ctx_len, the sink or the window: rows that do not count may hold stale bits (NaN
             // included).  Their weights are exactly zero, but 0 * NaN is NaN inside the MMA, so clear
             // those V rows.  (Rows are 128 bytes in every tile; the swizzle only permutes within a row.)
             for (int t = 0; t < TILES; ++t) {
                 unsigned char* tile = stage + PAGE_BYTES + t * TILE_BYTES;
                 for (int i = lane; i < (kPage - n_valid) * 8; i += 32)
                     *reinterpret_cast<uint4*>(tile + n_valid * 128 + i * 16) = make_uint4(0, 0, 0, 0);
-                for (int i = lane; i < n_skip * 8; i += 32)
-                    *reinterpret_cast<uint4*>(tile + i * 16) = make_uint4(0, 0, 0, 0);
+                for (int i = lane; i < (hole_hi - hole_lo) * 8; i += 32)
+                    *reinterpret_cast<uint4*>(tile + hole_lo * 128 + i * 16) = make_uint4(0, 0, 0, 0);
             }
             __syncwarp();
         }
@@ -609,7 +631,7 @@ struct MmaEngine {
         }
         // this lane: head lane/4, tokens 2c, 2c+1 (block 0) and 8+2c, 9+2c (block 1)
         if (partial) {
-            auto masked = [&](int tok) { return tok >= n_valid || tok < n_skip; };
+            auto masked = [&](int tok) { return tok >= n_valid || (tok >= hole_lo && tok < hole_hi); };
             if (masked(2 * c)) s[0][0] = -INFINITY;
             if (masked(2 * c + 1)) s[0][1] = -INFINITY;
             if (masked(8 + 2 * c)) s[1][0] = -INFINITY;
@@ -691,7 +713,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     auto bar_empty = [&](int s) { return bars + 8u * (kMaxStages + s); };
     auto bar_item_full = [&](int s) { return bars + 8u * (2 * kMaxStages + s); };
     auto bar_item_empty = [&](int s) { return bars + 8u * (2 * kMaxStages + kItemRing + s); };
-    auto bar_merge = [&](int s) { return bars + 8u * (2 * kMaxStages + 2 * kItemRing + s); };
+    const uint32_t bar_combined = bars + 8u * (2 * kMaxStages + 2 * kItemRing);   // phase i completes when item i's states are combined
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT);
     int* merge_cnt = reinterpret_cast<int*>(smem + C::OFF_ABORT + 4);   // warps that have published the current item
     volatile int* items = reinterpret_cast<volatile int*>(smem + C::OFF_ITEMS);
@@ -701,8 +723,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         *abort_flag = 0;
         for (int s = 0; s < stages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
         for (int s = 0; s < kItemRing; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), kConsumerWarps); }
-        mbar_init(bar_merge(0), 1);                // unused
-        mbar_init(bar_merge(1), 1);                // completes when an item's states have been combined
+        mbar_init(bar_combined, 1);
         *merge_cnt = 0;
         fence_mbar_init();
     }
@@ -745,7 +766,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                 const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + (id - h * num_chunks));
                 const int4 a = __ldg(src), b = __ldg(src + 1);
                 d.seq = a.x; d.page_begin = a.y; d.n_pages = a.z; d.chunk_idx = a.w; d.n_chunks = b.x; d.pad0 = b.y;
-                d.pad1 = b.z;
+                d.pad1 = b.z; d.pad2 = b.w;
                 *h_out = h;
             }
             return d;
@@ -754,7 +775,8 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             // (the value is validated where it is used, so that this load stays a prefetch)
             int mine = 0;
             if (p0 + lane < d.n_pages)
-                mine = __ldg(p.block_table + (int64_t)d.seq * p.bt_stride + d.page_begin + p0 + lane);
+                mine = __ldg(p.block_table + (int64_t)d.seq * p.bt_stride +
+                             page_of(d.page_begin + p0 + lane, d.pad2, d.pad1));
             return mine;
         };
         PROF_DECL
@@ -785,7 +807,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                 volatile int* it = items + slot * kItWords;
                 it[kItSeq] = d.seq; it[kItHead] = h; it[kItPages] = done ? -1 : d.n_pages;
                 it[kItPageBegin] = d.page_begin; it[kItChunks] = d.n_chunks; it[kItIndex] = item;
-                it[kItStart] = (d.seq + d.chunk_idx) % kConsumerWarps; it[kItLen] = d.pad0; it[kItBegin] = d.pad1;
+                it[kItStart] = (d.seq + d.chunk_idx) % kConsumerWarps; it[kItLen] = d.pad0; it[kItBegin] = d.pad1; it[kItSinkPages] = d.pad2;
                 mbar_arrive(bar_item_full(slot));
             }
             ++published;
@@ -890,7 +912,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         volatile int* it = items + slot * kItWords;
         const int seq = it[kItSeq], h = it[kItHead], n_pages = it[kItPages], page_begin = it[kItPageBegin];
         const int n_chunks = it[kItChunks], item = it[kItIndex], start = it[kItStart], L = it[kItLen];
-        const int begin = it[kItBegin];
+        const int begin = it[kItBegin], sink_pages = it[kItSinkPages];
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_item_empty(slot));
         if (n_pages < 0) break;   // sentinel: the work list is exhausted
@@ -904,9 +926,14 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             const int stage = (taken % spw) * kConsumerWarps + warp;
             if (!mbar_wait_bounded(bar_full(stage), (taken / spw) & 1, abort_flag, limit)) { ok = false; break; }
             PROF_MARK(2)   // wait for page data
-            const int n_valid = min(kPage, L - (page_begin + k) * kPage);      // tokens [n_skip, n_valid) of the page count
-            const int n_skip = max(0, begin - (page_begin + k) * kPage);        // (non-zero only on the window's first page)
-            eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, n_skip, lane, p_smem);
+            // Token t of this page is key 16*pg + t.  It counts if it lies below L and outside the
+            // hole [sink, begin) between the sink keys and the window; only the last page of the
+            // sequence, the last sink page and the first window page are cut by these bounds.
+            const int pg = page_of(page_begin + k, sink_pages, begin);
+            const int n_valid = min(kPage, L - pg * kPage);
+            const int hole_lo = min(kPage, max(0, min(p.sink_tokens, begin) - pg * kPage));
+            const int hole_hi = min(kPage, max(0, begin - pg * kPage));
+            eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, hole_lo, hole_hi, lane, p_smem);
             if (lane == 0) mbar_arrive(bar_empty(stage));
             PROF_MARK(3)   // page math
         }
@@ -918,7 +945,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         // stalled ring costs bandwidth directly, so three of four sub-rings keep draining while
         // one warp does the combine.  The scratch is reused by the next item: a warp may overwrite
         // its state only after the previous item's combine has finished.
-        if (consumed > 0 && !mbar_wait_bounded(bar_merge(1), (consumed - 1) & 1, abort_flag, limit)) break;
+        if (consumed > 0 && !mbar_wait_bounded(bar_combined, (consumed - 1) & 1, abort_flag, limit)) break;
         PROF_MARK(4)   // wait for the previous combine
         eng.publish(p, mrg_ml + (warp * G) * 2, mrg_o + (size_t)(warp * G) * D, lane);
         __threadfence_block();
@@ -958,7 +985,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                 }
             }
             __syncwarp();
-            if (lane == 0) { *merge_cnt = 0; mbar_arrive(bar_merge(1)); }
+            if (lane == 0) { *merge_cnt = 0; mbar_arrive(bar_combined); }
         }
         PROF_MARK(5)   // publish (+ combine if last)
         ++consumed;
@@ -1210,7 +1237,7 @@ extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t
                                       const void* k_pool, const void* v_pool,
                                       int64_t pool_stride_head, int64_t pool_stride_page,
                                       const int32_t* block_table, int64_t block_table_stride,
-                                      const int32_t* ctx_len, const int32_t* ctx_begin,
+                                      const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
                                       void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
                                       int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                                       int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
@@ -1238,7 +1265,8 @@ extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t
     if ((int64_t)ws.cap * kv_heads >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "%s: too many work items", fn);
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, ctx_begin, (int)batch, (int)page_size, (int)max_pages_per_seq,
+    if (sink_tokens < 0 || sink_tokens >= (1LL << 31)) return set_error(IVAB_ERR_INVALID, "%s: bad sink_tokens", fn);
+    plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, ctx_begin, (int)sink_tokens, (int)batch, (int)page_size, (int)max_pages_per_seq,
                                             ws.target_chunks, ws.cap, (int)kv_heads, ws);
     g_launches++;
     if (int rc = check_cuda(cudaGetLastError(), "plan_kernel launch")) return rc;
@@ -1249,7 +1277,7 @@ extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t
     p.pool_sh_bytes = pool_stride_head * (int64_t)esz; p.pool_sp_bytes = pool_stride_page * (int64_t)esz;
     p.block_table = block_table; p.bt_stride = block_table_stride;
     p.out = out; p.out_sb = out_stride_b; p.out_sh = out_stride_h; p.lse = lse;
-    p.Hq = (int)q_heads; p.num_pages = (int)num_pages;
+    p.Hq = (int)q_heads; p.num_pages = (int)num_pages; p.sink_tokens = (int)sink_tokens;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.wait_limit_ns = kWaitLimitNs;
     p.ws = ws;
@@ -1315,7 +1343,7 @@ extern "C" int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b,
                                               const void* k_pool, const void* v_pool,
                                               int64_t pool_stride_head, int64_t pool_stride_page,
                                               const int32_t* block_table, int64_t block_table_stride,
-                                              const int32_t* ctx_len, const int32_t* ctx_begin,
+                                              const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
                                               void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
                                               int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
                                               int64_t head_dim, int64_t page_size, int64_t num_pages,
@@ -1333,8 +1361,8 @@ extern "C" int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b,
     // Nothing in the scratch has to start at zero: the plan kernel rewrites the header (work counter,
     // status word, chunk count) and every partial that is read was written by this call.
     if (int rc = ivab_paged_decode_attn(q, q_stride_b, q_stride_h, k_pool, v_pool, pool_stride_head, pool_stride_page,
-                                        block_table, block_table_stride, ctx_len, ctx_begin, out, out_stride_b, out_stride_h,
-                                        lse,
+                                        block_table, block_table_stride, ctx_len, ctx_begin, sink_tokens, out, out_stride_b,
+                                        out_stride_h, lse,
                                         dtype, batch, q_heads, kv_heads, head_dim, page_size, num_pages,
                                         max_pages_per_seq, scale, scratch, kStaticScratchBytes, stream))
         return rc;

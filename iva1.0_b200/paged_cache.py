@@ -219,9 +219,10 @@ class PagedKVCache:
         self._sync_device()
 
 
-    def evict_before(self, begin: Sequence[int]) -> int:
+    def evict_before(self, begin: Sequence[int], keep_sink_tokens: int = 0) -> int:
         """Return to the pool every page that lies wholly before position ``begin[s]`` of sequence
-        ``s`` (the keys a sliding window no longer needs).  The block-table entries of those pages
+        ``s`` (the keys a sliding window no longer needs), except the pages that hold the first
+        ``keep_sink_tokens`` keys.  The block-table entries of those pages
         become ``-1``; decode attention called with ``ctx_begin >= begin`` never reads them.  Dense
         views (``.k``, ``gather``) of an evicted range are no longer available.  Returns the number
         of pages freed."""
@@ -229,7 +230,7 @@ class PagedKVCache:
         for s, b in enumerate(begin):
             first_kept = min(int(b), self._lens[s]) // self.page_size
             tab = self._tables[s]
-            for p in range(first_kept):
+            for p in range((keep_sink_tokens + self.page_size - 1) // self.page_size, first_kept):
                 if tab[p] >= 0:
                     self._free.append(tab[p])
                     tab[p] = -1

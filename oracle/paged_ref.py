@@ -136,7 +136,8 @@ def paged_decode_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
                      block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int,
                      scale: Optional[float] = None,
                      seqs: Optional[List[int]] = None,
-                     ctx_begin: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                     ctx_begin: Optional[torch.Tensor] = None,
+                     sink_tokens: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Single-query attention read through the block table.
 
     ``q`` is ``[B,H_q,D]``; pools are ``[1,H_kv,S,D]``.  Per sequence: gather its slots
@@ -147,7 +148,9 @@ def paged_decode_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
 
     ``ctx_begin`` (optional) limits sequence ``s`` to the keys ``ctx_begin[s] <= j < ctx_len[s]``:
     the keys a sliding-window mask leaves visible to the newest query (attention.py:115-129 keeps
-    ``[i-w+1, i]`` for query ``i``); the hidden keys are not gathered at all.
+    ``[i-w+1, i]`` for query ``i``); the hidden keys are not gathered at all.  ``sink_tokens`` keeps
+    the keys ``j < sink_tokens`` as well (the first ``sink_tokens`` columns of the sink mask,
+    attention.py:144-145).
 
     Returns ``out [B,H_q,D]`` fp32 and ``lse [B,H_q]`` fp32.  A sequence of length 0
     (or an empty window) yields zeros and ``-inf``.  ``seqs`` restricts the computation to some sequences
@@ -163,9 +166,12 @@ def paged_decode_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     for s in (range(B) if seqs is None else seqs):
         L = int(ctx_len[s])
         b = 0 if ctx_begin is None else min(max(int(ctx_begin[s]), 0), L)
-        if L == 0 or b >= L:
+        n_sink = min(int(sink_tokens), b)
+        if L == 0 or (b >= L and n_sink == 0):
             continue
         slots = slots_for_sequence(block_table[s], L, page_size, start=b)
+        if n_sink:
+            slots = torch.cat([slots_for_sequence(block_table[s], n_sink, page_size), slots])
         k = kv_gather_ref(k_pool, slots)            # [1,Hkv,L-b,D] fp32
         v = kv_gather_ref(v_pool, slots)
         if group > 1:

@@ -294,3 +294,60 @@ def test_module_sliding_window_matches_attention_torch_golden(golden, golden_inp
     y, cache = mod(golden_inputs.window_inputs().to(DEV), sliding_window=5)
     assert cache is None
     assert (y.cpu() - torch.from_numpy(golden["module_window_out"])).abs().max().item() <= 5e-5
+
+
+@pytest.mark.parametrize("dtype,Hq,Hkv,D", [(torch.bfloat16, 8, 8, 128), (torch.bfloat16, 16, 4, 128), (torch.float32, 4, 2, 64)])
+@pytest.mark.parametrize("sink", [1, 4, 16, 20, 40])
+def test_attention_sinks_in_front_of_a_window(dtype, Hq, Hkv, D, sink):
+    """Keys [0, sink) + [begin, L): sink and window on different pages, on the same page, touching,
+    overlapping (sink >= begin), with an empty window, and without any window."""
+    ctx = torch.tensor([300, 300, 47, 47, 30, 5000, 33, 64])
+    begin = torch.tensor([256, 261, 10, 47, 30, 4000, 0, 17])
+    wl = workloads.make_decode_workload("sink", ctx, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, dtype=dtype,
+                                        seed=Hq + sink, free_frac=0.2, poison_unused=True)
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16, wl.scale,
+                                            ctx_begin=begin, sink_tokens=sink)
+    d = wl.to(DEV)
+    # pages that hold neither sink nor window keys are gone: overwrite them with NaN
+    kp, vp = d.k_pool.clone(), d.v_pool.clone()
+    for s in range(len(ctx)):
+        keep = set(range((min(sink, int(begin[s])) + 15) // 16)) | set(range(int(begin[s]) // 16, (int(ctx[s]) + 15) // 16))
+        for pidx in range((int(ctx[s]) + 15) // 16):
+            if pidx not in keep:
+                pg = int(wl.block_table[s, pidx])
+                kp[:, :, pg * 16:(pg + 1) * 16] = float("nan")
+                vp[:, :, pg * 16:(pg + 1) * 16] = float("nan")
+    out, lse = iva_b200.paged_decode_attention(d.q, kp, vp, d.block_table, d.ctx_len, 16, wl.scale, return_lse=True,
+                                               check=True, ctx_begin=begin.to(DEV), sink_tokens=sink)
+    assert_attn_close(out, out_ref, dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_module_window_with_sinks_on_a_paged_cache():
+    """Single-token decode through AttentionB200 with sliding_window and sink_cfg, after the hidden
+    pages were evicted (sink pages kept)."""
+    torch.manual_seed(2)
+    B, H, hd, w, sink = 2, 4, 64, 48, 4
+    cfg = SimpleNamespace(d_model=H * hd, n_heads=H, dropout=0.0, causal=False, attn_impl="b200")
+    mod = iva_b200.AttentionB200(cfg).to(DEV).eval()
+    wts = [p.detach().cpu() for p in (mod.q_proj.weight, mod.k_proj.weight, mod.v_proj.weight, mod.o_proj.weight)]
+    cache = iva_b200.PagedKVCache(batch_size=B, n_heads=H, head_dim=hd, device=DEV, dtype=torch.float32,
+                                  max_seq_len=256, shuffle_seed=4)
+    xs = [torch.randn(B, 150, H * hd)] + [torch.randn(B, 1, H * hd) for _ in range(5)]
+    dense_k = dense_v = None
+    y, _ = mod(xs[0].to(DEV), kv_cache=cache)
+    _, dense_k, dense_v = ref.attention_module_ref(xs[0], *wts, H, None, None)
+    for x in xs[1:]:
+        L = dense_k.shape[2] + 1
+        cache.evict_before([L - w] * B, keep_sink_tokens=sink)
+        y, _ = mod(x.to(DEV), kv_cache=cache, sliding_window=w, sink_cfg={"sink_tokens": sink})
+        # checker: the module's math on the visible keys only
+        q = torch.nn.functional.linear(x, wts[0]).view(B, 1, H, hd).transpose(1, 2)
+        kn = torch.nn.functional.linear(x, wts[1]).view(B, 1, H, hd).transpose(1, 2)
+        vn = torch.nn.functional.linear(x, wts[2]).view(B, 1, H, hd).transpose(1, 2)
+        dense_k, dense_v = torch.cat([dense_k, kn], 2), torch.cat([dense_v, vn], 2)
+        vis = list(range(sink)) + list(range(L - w, L))
+        o, _ = ref.attention_math_ref(q, dense_k[:, :, vis], dense_v[:, :, vis], hd ** -0.5)
+        y_ref = torch.nn.functional.linear(o.transpose(1, 2).reshape(B, 1, H * hd), wts[3])
+        assert (y.cpu() - y_ref).abs().max().item() <= 1e-4
+    assert cache.free_pages > 0

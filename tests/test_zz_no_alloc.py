@@ -31,7 +31,7 @@ def _call(lib, wl, noalloc):
     lens = wl.ctx_len.contiguous()
     common = (wl.q.data_ptr(), wl.q.stride(0), wl.q.stride(1), wl.k_pool.data_ptr(), wl.v_pool.data_ptr(),
               wl.k_pool.stride(1), wl.page_size * D, wl.block_table.data_ptr(), wl.block_table.stride(0),
-              lens.data_ptr(), None, out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr(),
+              lens.data_ptr(), None, 0, out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr(),
               _lib.dtype_code(wl.dtype),
               B, Hq, Hkv, D, wl.page_size, wl.num_pages, wl.block_table.shape[1], wl.scale)
     if noalloc:
@@ -75,7 +75,7 @@ def test_noalloc_rejects_problems_beyond_the_built_in_scratch():
     lib = iva_b200.load_library()
     need = decode_workspace_bytes(4096, 64, 64, 128)
     assert need > 8 << 20
-    rc = lib.ivab_paged_decode_attn_noalloc(None, 0, 0, None, None, 0, 0, None, 0, None, None, None, 0, 0, None,
+    rc = lib.ivab_paged_decode_attn_noalloc(None, 0, 0, None, None, 0, 0, None, 0, None, None, 0, None, 0, 0, None,
                                             _lib.BF16, 4096, 64, 64, 128, 16, 1, 1, 0.1, None, None)
     assert rc == _lib.ERR_WORKSPACE
     msg = lib.ivab_last_error().decode()
