@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         L = L < 0 ? 0 : ((long long)L > cap_len ? (int)cap_len : L);
         int b = ctx_begin != nullptr ? ctx_begin[s] : 0;
         b = b < 0 ? 0 : (b > L ? L : b);
-        const int sink = sink_tokens < b ? (sink_tokens < 0 ? 0 : sink_tokens) : 0;   // sinks inside the window need no extra pages
+        if (sink_tokens >= b) b = 0;   // the sink keys reach the window: nothing is hidden
+        const int sink = b > 0 ? sink_tokens : 0;
         const int first_window_page = b / page_size;
         int sp = (sink + page_size - 1) / page_size;
         if (sp > first_window_page) sp = first_window_page;
