@@ -172,3 +172,35 @@ def test_kv_compact_keeps_masked_rows_in_order():
     mask[:, [1, 4, 5, 19]] = 1
     out = iva_b200.kv_compact(cache, mask)
     assert torch.equal(out, cache[:, :, [1, 4, 5, 19]].float())
+
+
+def test_canary_guards_around_the_pools_stay_intact():
+    """Pools, new tokens and outputs are carved out of larger buffers whose surroundings hold a
+    sentinel; after append, gather and decode attention every guard byte must be unchanged."""
+    wl = workloads.make_decode_workload("canary", torch.tensor([100, 5, 257]), n_q_heads=8, n_kv_heads=2,
+                                        head_dim=128, dtype=torch.bfloat16, seed=31)
+    guard = 4096
+
+    def guarded(t):
+        flat = torch.full((t.numel() + 2 * guard,), 12345.0, dtype=t.dtype, device=DEV)
+        flat[guard:guard + t.numel()] = t.reshape(-1).to(DEV)
+        return flat, flat[guard:guard + t.numel()].view(t.shape)
+
+    bufs = {}
+    views = {}
+    for name in ("k_pool", "v_pool", "q", "k_new", "v_new"):
+        bufs[name], views[name] = guarded(getattr(wl, name))
+    out_buf, out = guarded(torch.zeros(3, 8, 128, dtype=torch.bfloat16))
+    d = wl.to(DEV)
+    iva_b200.paged_append(views["k_pool"], views["v_pool"], d.slot_mapping, views["k_new"], views["v_new"], 16, check=True)
+    lens = (d.ctx_len + 1).contiguous()
+    iva_b200.paged_decode_attention(views["q"], views["k_pool"], views["v_pool"], d.block_table, lens, 16, out=out,
+                                    check=True)
+    g = iva_b200.paged_gather(views["k_pool"], d.block_table, lens, 16, layout="token_major", check=True)
+    torch.cuda.synchronize()
+    for name, flat in list(bufs.items()) + [("out", out_buf)]:
+        assert (flat[:guard] == 12345.0).all() and (flat[-guard:] == 12345.0).all(), f"guard of {name} was overwritten"
+    k_ref, _, out_ref, _ = ref.decode_step_ref(wl)
+    assert torch.equal(views["k_pool"].cpu(), k_ref)
+    assert (out.float().cpu() - out_ref).abs().max().item() <= 2e-3 + 2 ** -8 * out_ref.abs().max().item()
+    assert g.shape[0] == int(lens.sum())

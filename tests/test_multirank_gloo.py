@@ -70,3 +70,30 @@ def test_head_parallel_all_gather_equals_single_rank():
 
 def test_request_sharding_covers_all_sequences():
     _run(_request_shard_worker)
+
+
+def _lonely_rank(port, ret):
+    """Rank 0 of a world of 2 whose peer never starts: the rendezvous must fail with an error after
+    its timeout instead of hanging."""
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=3))
+        ret["outcome"] = "joined"
+        dist.destroy_process_group()
+    except Exception as e:                                  # noqa: BLE001 - any rendezvous error is the expected outcome
+        ret["outcome"] = "error: " + type(e).__name__
+
+
+def test_missing_peer_is_an_error_not_a_hang():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    proc = mp.get_context("spawn").Process(target=_lonely_rank, args=(_free_port(), ret))
+    proc.start()
+    proc.join(60)
+    alive = proc.is_alive()
+    if alive:
+        proc.kill()
+    assert not alive, "rendezvous with a missing peer did not time out"
+    assert str(ret.get("outcome", "")).startswith("error"), dict(ret)
