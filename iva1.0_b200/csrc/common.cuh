@@ -102,6 +102,30 @@ __device__ __forceinline__ void tma_bulk_g2s(uint32_t dst_smem, const void* src_
         : "memory");
 }
 
+// L2 policy for data that is read exactly once (the K/V stream): evict first, so that the pages do
+// not push the block tables, partials and q out of the cache.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+__device__ __forceinline__ void tma_bulk_g2s_hint(uint32_t dst_smem, const void* src_global, uint32_t bytes,
+                                                  uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(dst_smem), "l"(src_global), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_tile4d_g2s_hint(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
+                                                    int c3, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4, %5}], [%6], %7;"
+        ::"r"(dst_smem), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar), "l"(policy)
+        : "memory");
+}
+
 // Tiled TMA copy (4-D tensor map, no multicast): one box lands in shared memory with the swizzle
 // recorded in the map.  The innermost coordinate times the element size must be a multiple of 16.
 __device__ __forceinline__ void tma_tile4d_g2s(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,

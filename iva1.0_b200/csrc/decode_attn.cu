@@ -781,6 +781,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             return mine;
         };
         PROF_DECL
+        const uint64_t stream_policy = l2_policy_evict_first();   // K/V pages are read once
         int id0 = fetch_id(), id1 = fetch_id(), id2 = fetch_id();
         int h0, h1;
         ChunkDesc d0 = load_desc(id0, &h0);
@@ -850,14 +851,16 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                             if constexpr (Eng::kTiled) {
 #pragma unroll
                                 for (int t = 0; t < Eng::TILES; ++t) {
-                                    tma_tile4d_g2s(dst + t * Eng::TILE_BYTES, &tm.k, t * 64, 0, pid, h, bar_full(stage));
-                                    tma_tile4d_g2s(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * 64, 0, pid, h,
-                                                   bar_full(stage));
+                                    tma_tile4d_g2s_hint(dst + t * Eng::TILE_BYTES, &tm.k, t * 64, 0, pid, h, bar_full(stage),
+                                                        stream_policy);
+                                    tma_tile4d_g2s_hint(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * 64, 0, pid, h,
+                                                        bar_full(stage), stream_policy);
                                 }
                             } else {
-                                tma_bulk_g2s(dst, kbase + (int64_t)pid * p.pool_sp_bytes, Eng::PAGE_BYTES, bar_full(stage));
-                                tma_bulk_g2s(dst + Eng::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes,
-                                             Eng::PAGE_BYTES, bar_full(stage));
+                                tma_bulk_g2s_hint(dst, kbase + (int64_t)pid * p.pool_sp_bytes, Eng::PAGE_BYTES, bar_full(stage),
+                                                  stream_policy);
+                                tma_bulk_g2s_hint(dst + Eng::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes,
+                                                  Eng::PAGE_BYTES, bar_full(stage), stream_policy);
                             }
                         }
                     }
