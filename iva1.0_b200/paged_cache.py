@@ -18,7 +18,7 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
-from .kv_ops import paged_append, paged_gather
+from .kv_ops import kv_ops, paged_append, paged_gather
 
 __all__ = ["PagedKVCache", "PoolExhausted"]
 
@@ -240,3 +240,43 @@ class PagedKVCache:
         if freed:
             self._sync_device()
         return freed
+
+    def compact(self, keep: Sequence[torch.Tensor]) -> List[int]:
+        """Drop tokens inside the sequences: ``keep[s]`` is a boolean mask (or 0/1 tensor) over the
+        ``lengths[s]`` tokens of sequence ``s``; the survivors are packed, in order, into fresh pages
+        and every page that is no longer needed goes back to the pool.
+
+        This is what the reference's ``kv_compact_triton`` (src/kernels_t/kv_ops_triton.py:159-181)
+        is meant to do on its dense cache -- its kernel writes surviving row ``s`` to output row ``s``
+        of a tensor with only ``num_valid`` rows (kv_ops_triton.py:83-92), so it cannot be used as
+        is.  Four launches of this library's kernels: gather the kept rows of K and of V through
+        their slot lists, then one append of both into the new pages.  Returns the new lengths.
+        """
+        if len(keep) != self.batch_size:
+            raise ValueError("one mask per sequence")
+        src_slots: List[int] = []
+        new_lens: List[int] = []
+        for s, m in enumerate(keep):
+            m = torch.as_tensor(m).reshape(-1).cpu() != 0
+            if m.numel() != self._lens[s]:
+                raise ValueError(f"mask of sequence {s} has {m.numel()} entries for {self._lens[s]} tokens")
+            kept = torch.nonzero(m).flatten().tolist()
+            tab, ps = self._tables[s], self.page_size
+            if any(tab[p // ps] < 0 for p in kept):
+                raise ValueError(f"sequence {s}: a kept token lies on an evicted page")
+            src_slots.extend(tab[p // ps] * ps + p % ps for p in kept)
+            new_lens.append(len(kept))
+        idx = torch.tensor(src_slots, dtype=torch.int64).to(self.device)
+        # the survivors are copied out before any page is released, so re-using pages is safe
+        k_rows = kv_ops(self.k_pool, idx, None, "gather", compat=False)      # [1,H,T,D]
+        v_rows = kv_ops(self.v_pool, idx, None, "gather", compat=False)
+        self.reset()
+        self._reserve(new_lens)
+        dst: List[int] = []
+        for s, L in enumerate(new_lens):
+            dst.extend(self.slots(s, 0, L))
+        self._sync_device()
+        if dst:
+            paged_append(self.k_pool, self.v_pool, torch.tensor(dst, dtype=torch.int64).to(self.device),
+                         k_rows[0].permute(1, 0, 2), v_rows[0].permute(1, 0, 2), self.page_size)
+        return new_lens

@@ -204,3 +204,28 @@ def test_canary_guards_around_the_pools_stay_intact():
     assert torch.equal(views["k_pool"].cpu(), k_ref)
     assert (out.float().cpu() - out_ref).abs().max().item() <= 2e-3 + 2 ** -8 * out_ref.abs().max().item()
     assert g.shape[0] == int(lens.sum())
+
+
+def test_cache_compaction_packs_survivors_and_frees_pages():
+    torch.manual_seed(5)
+    B, H, D = 3, 4, 64
+    cache = iva_b200.PagedKVCache(batch_size=B, n_heads=H, head_dim=D, device=DEV, dtype=torch.float16,
+                                  max_seq_len=128, num_pages=24, shuffle_seed=7)
+    k = torch.randn(B, 100, H, D).to(torch.float16)
+    v = torch.randn(B, 100, H, D).to(torch.float16)
+    cache.append(k.to(DEV), v.to(DEV))
+    free0 = cache.free_pages
+    masks = [torch.rand(100) < 0.3, torch.zeros(100, dtype=torch.bool), torch.ones(100, dtype=torch.bool)]
+    new_lens = cache.compact(masks)
+    assert new_lens == [int(m.sum()) for m in masks] and cache.lengths == new_lens
+    assert cache.free_pages == 24 - sum((L + 15) // 16 for L in new_lens) and cache.free_pages > free0
+    ks, vs = cache.gather(layout="head_major")
+    for s, m in enumerate(masks):
+        assert torch.equal(ks[s][0].cpu(), k[s][m].permute(1, 0, 2))         # survivors, in order, bit-exact
+        assert torch.equal(vs[s][0].cpu(), v[s][m].permute(1, 0, 2))
+    # the compacted cache keeps working: append one token and attend
+    cache.append(torch.randn(B, H, D).to(torch.float16).to(DEV), torch.randn(B, H, D).to(torch.float16).to(DEV))
+    q = torch.randn(B, H, D).to(torch.float16).to(DEV)
+    out = iva_b200.paged_decode_attention(q, cache.k_pool, cache.v_pool, cache.block_table_dev, cache.ctx_len_dev, 16,
+                                          check=True)
+    assert torch.isfinite(out.float()).all()
