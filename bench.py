@@ -226,6 +226,20 @@ def run_gpu(args):
     copy_gbs = live_copy_bandwidth(dev)
     wl = build_workload(name, dev, rank, world, args)
     B = wl.batch
+    kv_scales = {}
+    if args.kv_fp8:
+        if name not in ("c2", "c3", "c5a"):
+            raise SystemExit("--kv-fp8 applies to the decode workloads c2, c3, c5a")
+        # N(0,1) data: a scale of 1/64 keeps +-7 sigma inside the e4m3 range
+        kv_scales = {"k_scale": 1.0 / 64, "v_scale": 1.0 / 64}
+        for attr in ("k_pool", "v_pool"):
+            pool = getattr(wl, attr)
+            q8 = torch.empty(pool.shape, dtype=torch.float8_e4m3fn, device=dev)
+            step_rows = 1 << 16
+            for lo in range(0, pool.shape[2], step_rows):      # chunked: no full-size fp32 temporary
+                q8[:, :, lo:lo + step_rows] = (pool[:, :, lo:lo + step_rows].float() * 64.0).clamp(-448, 448).to(torch.float8_e4m3fn)
+            setattr(wl, attr, q8)
+        torch.cuda.empty_cache()
     lens = (wl.ctx_len + wl.new_tokens_per_seq).contiguous()
     out = torch.empty(B, wl.n_q_heads, wl.head_dim, device=dev, dtype=wl.dtype) if wl.q is not None else None
     lse = torch.empty(B, wl.n_q_heads, device=dev, dtype=torch.float32) if wl.q is not None else None
@@ -262,7 +276,7 @@ def run_gpu(args):
         if hp is not None:
             return hp.decode(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
         return iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, wl.page_size,
-                                               wl.scale, out=out, lse=lse)
+                                               wl.scale, out=out, lse=lse, **kv_scales)
 
     gather_offs = None
     if name == "c4":
@@ -318,7 +332,7 @@ def run_gpu(args):
 
     # ---- end to end from pinned host buffers ----
     e2e = None
-    if name in ("c2", "c3", "c5a"):
+    if name in ("c2", "c3", "c5a") and not args.kv_fp8:
         # the public end-to-end call: inputs in pinned host memory, one CUDA-graph replay per step
         # (H2D of q / new K,V / slot mapping / lengths, append, attention, D2H of the output)
         gs = iva_b200.GraphedDecodeStep(wl.k_pool, wl.v_pool, wl.block_table, wl.n_q_heads, wl.page_size, wl.scale)
@@ -464,6 +478,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (small ncu captures)")
     ap.add_argument("--context", type=int, default=0, help="override the context length")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--kv-fp8", action="store_true", help="store K/V as e4m3 with per-tensor scales (c2/c3/c5a)")
     ap.add_argument("--no-graph", action="store_true", help="head-parallel mode: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -16,7 +16,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 
 OK = 0
 ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE = -1, -2, -3, -4, -5
-F32, F16, BF16 = 0, 1, 2
+F32, F16, BF16, F8E4M3 = 0, 1, 2, 3
 STATUS_WAIT_TIMEOUT, STATUS_BAD_PAGE, STATUS_BAD_CTX_LEN, STATUS_BAD_SLOT, STATUS_WORKSPACE_OVERFLOW = 1, 2, 4, 8, 16
 OUT_TOKEN_MAJOR, OUT_HEAD_MAJOR = 0, 1
 
@@ -29,6 +29,8 @@ SIGNATURES = {
     "ivab_kv_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_int64] * 11 + [c_void_p, c_void_p]),
     "ivab_paged_append": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                   c_int64, c_int] + [c_int64] * 5 + [c_void_p, c_void_p]),
+    "ivab_paged_append_fp8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
+                                      c_int64, c_int, c_float, c_float] + [c_int64] * 5 + [c_void_p, c_void_p]),
     "ivab_paged_gather": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int] + [c_int64] * 6 + [c_void_p, c_void_p]),
     "ivab_decode_workspace_bytes": (c_int, [c_int64, c_int64, c_int64, c_int64, POINTER(c_size_t)]),
@@ -38,6 +40,10 @@ SIGNATURES = {
     "ivab_paged_decode_attn_noalloc": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                                c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                                c_int] + [c_int64] * 7 + [c_float, c_void_p, c_void_p]),
+    "ivab_paged_decode_attn_fp8": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                           c_float, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                           c_void_p, c_int64, c_int64, c_void_p, c_int] + [c_int64] * 7 +
+                                   [c_float, c_void_p, c_size_t, c_void_p]),
     "ivab_decode_status": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
     "ivab_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
 }
@@ -97,9 +103,9 @@ def dtype_code(dtype) -> int:
     import torch
 
     try:
-        return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[dtype]
+        return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float8_e4m3fn: F8E4M3}[dtype]
     except KeyError:
-        raise ValueError(f"unsupported KV dtype {dtype}; supported: float32, float16, bfloat16") from None
+        raise ValueError(f"unsupported KV dtype {dtype}; supported: float32, float16, bfloat16, float8_e4m3fn") from None
 
 
 def stream_ptr(device) -> int:

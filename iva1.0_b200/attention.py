@@ -67,7 +67,8 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
                            scale: Optional[float] = None, *, out: Optional[torch.Tensor] = None,
                            lse: Optional[torch.Tensor] = None, return_lse: bool = False,
                            workspace: Optional[torch.Tensor] = None, check: bool = False,
-                           ctx_begin: Optional[torch.Tensor] = None, sink_tokens: int = 0):
+                           ctx_begin: Optional[torch.Tensor] = None, sink_tokens: int = 0,
+                           k_scale: float = 1.0, v_scale: float = 1.0):
     """``out[s,h] = softmax(q[s,h] . K_s^T * scale) . V_s`` over the ``ctx_len[s]`` cached tokens of
     sequence ``s``, K/V read in place from the page pool through ``block_table``.
 
@@ -78,19 +79,25 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     timed-out wait.  ``ctx_begin`` (int32 ``[B]``, optional) restricts sequence ``s`` to the keys
     ``ctx_begin[s] <= j < ctx_len[s]`` -- a sliding window; pages wholly before it are not read.
     ``sink_tokens`` keeps the first keys of every sequence visible in front of the window.
+    Pools of dtype ``torch.float8_e4m3fn`` (written by ``paged_append`` with the same scales) are read
+    as ``K = k_scale * stored``, ``V = v_scale * stored``; q must then be fp16 or bf16.
     """
     _lib.require_cuda(q, k_pool, v_pool, block_table, ctx_len)
     Hkv, num_pages, sh, sp = _pool_strides(k_pool, page_size)
     if _pool_strides(v_pool, page_size) != (Hkv, num_pages, sh, sp) or v_pool.dtype != k_pool.dtype:
         raise ValueError("k_pool and v_pool must have the same shape, strides and dtype")
-    if k_pool.dtype != q.dtype or k_pool.shape[-1] != q.shape[-1]:
+    fp8 = k_pool.dtype == torch.float8_e4m3fn
+    if k_pool.shape[-1] != q.shape[-1] or (k_pool.dtype != q.dtype and not fp8):
         raise ValueError("q and the pools must share dtype and head_dim")
+    if fp8 and q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("8-bit pools need fp16 or bf16 queries")
     return _decode(q, k_pool, v_pool, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
-                   out, lse, return_lse, workspace, check, ctx_begin, sink_tokens)
+                   out, lse, return_lse, workspace, check, ctx_begin, sink_tokens,
+                   (float(k_scale), float(v_scale)) if fp8 else None)
 
 
 def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
-            out, lse, return_lse, workspace, check, ctx_begin=None, sink_tokens=0):
+            out, lse, return_lse, workspace, check, ctx_begin=None, sink_tokens=0, fp8_scales=None):
     """Argument checks and the library call; ``k_base`` / ``v_base`` only supply base pointers, the
     pool geometry is given by ``Hkv, num_pages, sh, sp`` (element strides of head and page)."""
     if q.requires_grad:
@@ -130,13 +137,16 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
         stream = _lib.stream_ptr(dev)
         if workspace is None:
             workspace = _workspace(dev, stream, decode_workspace_bytes(B, Hq, Hkv, D))
-        _lib.check(lib.ivab_paged_decode_attn(
-            q.data_ptr(), q.stride(0), q.stride(1), k_base.data_ptr(), v_base.data_ptr(), sh, sp,
-            block_table.data_ptr(), block_table.stride(0), ctx_len.data_ptr(),
-            ctx_begin.data_ptr() if ctx_begin is not None else None, int(sink_tokens),
-            out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr() if lse is not None else None,
-            _lib.dtype_code(q.dtype), B, Hq, Hkv, D, page_size, num_pages, block_table.shape[1],
-            float(scale), workspace.data_ptr(), workspace.numel(), stream))
+        tail = (block_table.data_ptr(), block_table.stride(0), ctx_len.data_ptr(),
+                ctx_begin.data_ptr() if ctx_begin is not None else None, int(sink_tokens),
+                out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr() if lse is not None else None,
+                _lib.dtype_code(q.dtype), B, Hq, Hkv, D, page_size, num_pages, block_table.shape[1],
+                float(scale), workspace.data_ptr(), workspace.numel(), stream)
+        head = (q.data_ptr(), q.stride(0), q.stride(1), k_base.data_ptr(), v_base.data_ptr(), sh, sp)
+        if fp8_scales is None:
+            _lib.check(lib.ivab_paged_decode_attn(*head, *tail))
+        else:
+            _lib.check(lib.ivab_paged_decode_attn_fp8(*head, fp8_scales[0], fp8_scales[1], *tail))
     if check:
         st = decode_status(workspace)
         if st:

@@ -41,6 +41,7 @@ size_t dtype_size(int dtype) {
         case IVAB_F32: return 4;
         case IVAB_F16: return 2;
         case IVAB_BF16: return 2;
+        case IVAB_F8E4M3: return 1;
         default: return 0;
     }
 }

@@ -3,6 +3,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -276,6 +277,25 @@ template <> struct Elt<__half> {
     __device__ __forceinline__ static float load(const __half* p) { return __half2float(*p); }
     __device__ __forceinline__ static void store(__half* p, float v) { *p = __float2half_rn(v); }
 };
+
+template <> struct Elt<__nv_fp8_e4m3> {
+    static constexpr int kPerVec = 16;
+    // e4m3 -> fp32 is exact: two values per conversion to half2, then widened
+    __device__ __forceinline__ static void unpack(const uint4& u, float* f) {
+        const __nv_fp8x2_storage_t* p2 = reinterpret_cast<const __nv_fp8x2_storage_t*>(&u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p2[i], __NV_E4M3);
+            const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&h));
+            f[2 * i] = t.x; f[2 * i + 1] = t.y;
+        }
+    }
+};
+
+// fp32 -> e4m3 with saturation (round to nearest even), two at a time
+__device__ __forceinline__ uint16_t pack_fp8x2(float lo, float hi) {
+    return __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+}
 
 #endif  // __CUDACC__
 

@@ -326,6 +326,7 @@ struct DecodeParams {
     void* out; int64_t out_sb, out_sh; float* lse;
     int Hq, num_pages;
     int sink_tokens;           // keys [0, sink_tokens) stay visible in front of a window (0 = none)
+    float v_scale;             // 8-bit KV storage: V = v_scale * stored value (1 otherwise); K's scale is folded into scale_log2
     float scale_log2;          // scale * log2(e): scores are kept in base-2 units
     int stages;
     uint64_t wait_limit_ns;
@@ -419,9 +420,12 @@ __device__ __forceinline__ int owned_index(int lane) {
 // the merge / epilogue code of the kernel is shared.
 // ------------------------------------------------------------------------------------------------
 
-template <typename T, int D, int G>
+// TKV: storage type of the pages; TQ: type of q (and of the output).  They differ only for 8-bit KV
+// storage, where a lane's 16-byte vector holds 16 keys' worth of one row and q is still 16-bit.
+template <typename TKV, typename TQ, int D, int G>
 struct SimtEngine {
-    using C = Cfg<T, D, G>;
+    using T = TKV;
+    using C = Cfg<TKV, D, G>;
     static constexpr bool kTiled = false;
     static constexpr int PAGE_BYTES = C::PAGE_BYTES;
     static constexpr int STAGE_BYTES = C::STAGE_BYTES;
@@ -439,12 +443,17 @@ struct SimtEngine {
     }
 
     __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
-        const T* qg = static_cast<const T*>(p.q);
+        const TQ* qg = static_cast<const TQ*>(p.q);
+        constexpr int QV = C::EPL / Elt<TQ>::kPerVec;   // 16-byte loads covering this lane's EPL dims of q
+        static_assert(QV >= 1 && QV * Elt<TQ>::kPerVec == C::EPL, "q type must not be narrower than the KV type");
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            const T* qp = qg + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh + c * C::EPL;
-            const uint4 u = __ldg(reinterpret_cast<const uint4*>(qp));
-            Elt<T>::unpack(u, qf[g]);
+            const TQ* qp = qg + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh + c * C::EPL;
+#pragma unroll
+            for (int v = 0; v < QV; ++v) {
+                const uint4 u = __ldg(reinterpret_cast<const uint4*>(qp) + v);
+                Elt<TQ>::unpack(u, &qf[g][v * Elt<TQ>::kPerVec]);
+            }
 #pragma unroll
             for (int e = 0; e < C::EPL; ++e) qf[g][e] *= p.scale_log2;   // scores in base-2 units
             m_run[g] = -INFINITY; l_run[g] = 0.f;
@@ -698,11 +707,11 @@ struct alignas(64) TensorMaps {
     CUtensorMap k, v;   // 4-D maps of the K and V pools: (dim, token in page, page, head)
 };
 
-template <typename T, int D, int G, bool TC>
-__global__ void __launch_bounds__(kThreads, TC ? 2 : Cfg<T, D, G>::CTAS_PER_SM)
+template <typename T, int D, int G, bool TC, typename TKV = T>
+__global__ void __launch_bounds__(kThreads, TC ? 2 : Cfg<TKV, D, G>::CTAS_PER_SM)
 decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ TensorMaps tm) {
-    using C = Cfg<T, D, G>;
-    using Eng = std::conditional_t<TC, MmaEngine<T, D, G>, SimtEngine<T, D, G>>;
+    using C = Cfg<TKV, D, G>;
+    using Eng = std::conditional_t<TC, MmaEngine<T, D, G>, SimtEngine<TKV, T, D, G>>;
     extern __shared__ unsigned char smem_raw[];
     // the carve-up assumes a 1 KB-aligned base; the launch reserves 1 KB of slack for this
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -974,6 +983,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                     Lsum = fmaf(all_ml[(w * G + g) * 2 + 1], f, Lsum);
                     O = fmaf(all_o[(size_t)(w * G + g) * D + dd], f, O);
                 }
+                O *= p.v_scale;
                 const int hq = h * G + g;
                 if (n_chunks == 1) {
                     const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
@@ -1122,10 +1132,10 @@ int tc_min_group() {
     return v;
 }
 
-template <typename T, int D, int G, bool TC>
+template <typename T, int D, int G, bool TC, typename TKV = T>
 int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStream_t st) {
-    using C = Cfg<T, D, G>;
-    using Eng = std::conditional_t<TC, MmaEngine<T, D, G>, SimtEngine<T, D, G>>;
+    using C = Cfg<TKV, D, G>;
+    using Eng = std::conditional_t<TC, MmaEngine<T, D, G>, SimtEngine<TKV, T, D, G>>;
     constexpr int kCtas = TC ? 2 : C::CTAS_PER_SM;
     DecodeParams p = p0;
     int dev = 0;
@@ -1148,7 +1158,7 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     if (stages < kConsumerWarps) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for the stage ring");
     p.stages = stages;
     const size_t smem = (size_t)C::OFF_STAGES + 1024 + (size_t)stages * Eng::STAGE_BYTES;
-    auto kern = decode_kernel<T, D, G, TC>;
+    auto kern = decode_kernel<T, D, G, TC, TKV>;
     static bool configured[64] = {false};
     if (dev < 64 && !configured[dev]) {
         if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin),
@@ -1237,6 +1247,89 @@ extern "C" int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64
     return IVAB_OK;
 }
 
+namespace {
+
+// 8-bit pools: CUDA-core engine only (q stays 16-bit; see the note on the fp8 entry point)
+template <typename T>
+int dispatch_fp8(int D, int G, const DecodeParams& p, int B, cudaStream_t st) {
+    TensorMaps tm{};
+    using F8 = __nv_fp8_e4m3;
+#define IVAB_FP8_CASE(DD, GG) if (D == DD && G == GG) return launch_decode<T, DD, GG, false, F8>(p, tm, B, st);
+    IVAB_FP8_CASE(64, 1) IVAB_FP8_CASE(64, 2) IVAB_FP8_CASE(64, 4) IVAB_FP8_CASE(64, 8)
+    IVAB_FP8_CASE(128, 1) IVAB_FP8_CASE(128, 2) IVAB_FP8_CASE(128, 4) IVAB_FP8_CASE(128, 8)
+#undef IVAB_FP8_CASE
+    return set_error(IVAB_ERR_UNSUPPORTED,
+                     "8-bit KV decode: head_dim %d with %d query heads per KV head (supported: 64/128, 1/2/4/8)", D, G);
+}
+
+// Shared body of the decode entry points.  kv_dtype is the storage type of the pools (== dtype, or
+// IVAB_F8E4M3 with per-tensor scales); pool strides are in elements of kv_dtype.
+int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                 const void* k_pool, const void* v_pool, int64_t pool_stride_head, int64_t pool_stride_page,
+                 const int32_t* block_table, int64_t block_table_stride,
+                 const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
+                 void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                 int dtype, int kv_dtype, float k_scale, float v_scale,
+                 int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                 int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
+                 void* workspace, size_t workspace_bytes, void* stream) {
+    const size_t esz = dtype_size(dtype);
+    const size_t kv_esz = dtype_size(kv_dtype);
+    if (esz == 0 || kv_esz == 0) return set_error(IVAB_ERR_INVALID, "%s: unknown dtype %d / %d", fn, dtype, kv_dtype);
+    if (dtype == IVAB_F8E4M3) return set_error(IVAB_ERR_UNSUPPORTED, "%s: q and out must be fp32, fp16 or bf16", fn);
+    if (kv_dtype == IVAB_F8E4M3 && dtype != IVAB_F16 && dtype != IVAB_BF16)
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: 8-bit pools need fp16 or bf16 queries", fn);
+    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || num_pages < 0 || max_pages_per_seq < 0)
+        return set_error(IVAB_ERR_INVALID, "%s: bad sizes", fn);
+    if (batch == 0) return IVAB_OK;
+    if (page_size != kPage) return set_error(IVAB_ERR_UNSUPPORTED, "%s: page_size %lld (supported: 16)", fn, (long long)page_size);
+    if (!q || !k_pool || !v_pool || !block_table || !ctx_len || !out || !workspace)
+        return set_error(IVAB_ERR_INVALID, "%s: null pointer", fn);
+    auto mis = [](const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) != 0; };
+    if (mis(q, 16) || mis(k_pool, 16) || mis(v_pool, 16) || mis(workspace, 256) || (q_stride_b * esz) % 16 ||
+        (q_stride_h * esz) % 16 || (pool_stride_head * kv_esz) % 16 || (pool_stride_page * kv_esz) % 16)
+        return set_error(IVAB_ERR_INVALID, "%s: q / pools must be 16-byte aligned (workspace 256) with 16-byte strides", fn);
+    if (batch >= (1LL << 30) || max_pages_per_seq * page_size >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: batch or context too large", fn);
+    if (sink_tokens < 0 || sink_tokens >= (1LL << 31)) return set_error(IVAB_ERR_INVALID, "%s: bad sink_tokens", fn);
+
+    Workspace ws;
+    const size_t need = carve_workspace(workspace, batch, q_heads, kv_heads, head_dim, &ws);
+    if (workspace_bytes < need)
+        return set_error(IVAB_ERR_WORKSPACE, "%s: workspace of %zu bytes, need %zu", fn, workspace_bytes, need);
+    if ((int64_t)ws.cap * kv_heads >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "%s: too many work items", fn);
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, ctx_begin, (int)sink_tokens, (int)batch, (int)page_size,
+                                            (int)max_pages_per_seq, ws.target_chunks, ws.cap, (int)kv_heads, ws);
+    g_launches++;
+    if (int rc = check_cuda(cudaGetLastError(), "plan_kernel launch")) return rc;
+
+    DecodeParams p{};
+    p.q = q; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
+    p.k_pool = static_cast<const char*>(k_pool); p.v_pool = static_cast<const char*>(v_pool);
+    p.pool_sh_bytes = pool_stride_head * (int64_t)kv_esz; p.pool_sp_bytes = pool_stride_page * (int64_t)kv_esz;
+    p.block_table = block_table; p.bt_stride = block_table_stride;
+    p.out = out; p.out_sb = out_stride_b; p.out_sh = out_stride_h; p.lse = lse;
+    p.Hq = (int)q_heads; p.num_pages = (int)num_pages; p.sink_tokens = (int)sink_tokens;
+    p.v_scale = v_scale;
+    p.scale_log2 = scale * k_scale * 1.4426950408889634f;   // K = k_scale * stored value
+    p.wait_limit_ns = kWaitLimitNs;
+    p.ws = ws;
+    const int G = (int)(q_heads / kv_heads);
+    if (kv_dtype == IVAB_F8E4M3) {
+        if (dtype == IVAB_F16) return dispatch_fp8<__half>((int)head_dim, G, p, (int)batch, st);
+        return dispatch_fp8<__nv_bfloat16>((int)head_dim, G, p, (int)batch, st);
+    }
+    switch (dtype) {
+        case IVAB_F32: return dispatch_dim<float>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
+        case IVAB_F16: return dispatch_dim<__half>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
+        default: return dispatch_dim<__nv_bfloat16>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
+    }
+}
+
+}  // namespace
+
 extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                                       const void* k_pool, const void* v_pool,
                                       int64_t pool_stride_head, int64_t pool_stride_page,
@@ -1246,51 +1339,31 @@ extern "C" int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t
                                       int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                                       int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
                                       void* workspace, size_t workspace_bytes, void* stream) {
-    const char* fn = "ivab_paged_decode_attn";
-    const size_t esz = dtype_size(dtype);
-    if (esz == 0) return set_error(IVAB_ERR_INVALID, "%s: unknown dtype %d", fn, dtype);
-    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || num_pages < 0 || max_pages_per_seq < 0)
-        return set_error(IVAB_ERR_INVALID, "%s: bad sizes", fn);
-    if (batch == 0) return IVAB_OK;
-    if (page_size != kPage) return set_error(IVAB_ERR_UNSUPPORTED, "%s: page_size %lld (supported: 16)", fn, (long long)page_size);
-    if (!q || !k_pool || !v_pool || !block_table || !ctx_len || !out || !workspace)
-        return set_error(IVAB_ERR_INVALID, "%s: null pointer", fn);
-    auto mis = [](const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) != 0; };
-    if (mis(q, 16) || mis(k_pool, 16) || mis(v_pool, 16) || mis(workspace, 256) || (q_stride_b * esz) % 16 ||
-        (q_stride_h * esz) % 16 || (pool_stride_head * esz) % 16 || (pool_stride_page * esz) % 16)
-        return set_error(IVAB_ERR_INVALID, "%s: q / pools must be 16-byte aligned (workspace 256) with 16-byte strides", fn);
-    if (batch >= (1LL << 30) || max_pages_per_seq * page_size >= (1LL << 31))
-        return set_error(IVAB_ERR_UNSUPPORTED, "%s: batch or context too large", fn);
+    if (dtype == IVAB_F8E4M3)
+        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_paged_decode_attn: 8-bit pools go through ivab_paged_decode_attn_fp8");
+    return decode_entry("ivab_paged_decode_attn", q, q_stride_b, q_stride_h, k_pool, v_pool, pool_stride_head,
+                        pool_stride_page, block_table, block_table_stride, ctx_len, ctx_begin, sink_tokens, out,
+                        out_stride_b, out_stride_h, lse, dtype, dtype, 1.f, 1.f, batch, q_heads, kv_heads, head_dim,
+                        page_size, num_pages, max_pages_per_seq, scale, workspace, workspace_bytes, stream);
+}
 
-    Workspace ws;
-    const size_t need = carve_workspace(workspace, batch, q_heads, kv_heads, head_dim, &ws);
-    if (workspace_bytes < need)
-        return set_error(IVAB_ERR_WORKSPACE, "%s: workspace of %zu bytes, need %zu", fn, workspace_bytes, need);
-    if ((int64_t)ws.cap * kv_heads >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "%s: too many work items", fn);
-
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (sink_tokens < 0 || sink_tokens >= (1LL << 31)) return set_error(IVAB_ERR_INVALID, "%s: bad sink_tokens", fn);
-    plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, ctx_begin, (int)sink_tokens, (int)batch, (int)page_size, (int)max_pages_per_seq,
-                                            ws.target_chunks, ws.cap, (int)kv_heads, ws);
-    g_launches++;
-    if (int rc = check_cuda(cudaGetLastError(), "plan_kernel launch")) return rc;
-
-    DecodeParams p{};
-    p.q = q; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
-    p.k_pool = static_cast<const char*>(k_pool); p.v_pool = static_cast<const char*>(v_pool);
-    p.pool_sh_bytes = pool_stride_head * (int64_t)esz; p.pool_sp_bytes = pool_stride_page * (int64_t)esz;
-    p.block_table = block_table; p.bt_stride = block_table_stride;
-    p.out = out; p.out_sb = out_stride_b; p.out_sh = out_stride_h; p.lse = lse;
-    p.Hq = (int)q_heads; p.num_pages = (int)num_pages; p.sink_tokens = (int)sink_tokens;
-    p.scale_log2 = scale * 1.4426950408889634f;
-    p.wait_limit_ns = kWaitLimitNs;
-    p.ws = ws;
-    const int G = (int)(q_heads / kv_heads);
-    switch (dtype) {
-        case IVAB_F32: return dispatch_dim<float>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
-        case IVAB_F16: return dispatch_dim<__half>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
-        default: return dispatch_dim<__nv_bfloat16>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
-    }
+extern "C" int ivab_paged_decode_attn_fp8(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                          const void* k_pool, const void* v_pool,
+                                          int64_t pool_stride_head, int64_t pool_stride_page,
+                                          float k_scale, float v_scale,
+                                          const int32_t* block_table, int64_t block_table_stride,
+                                          const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
+                                          void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                                          int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                                          int64_t head_dim, int64_t page_size, int64_t num_pages,
+                                          int64_t max_pages_per_seq, float scale,
+                                          void* workspace, size_t workspace_bytes, void* stream) {
+    if (!(k_scale > 0.f) || !(v_scale > 0.f))
+        return set_error(IVAB_ERR_INVALID, "ivab_paged_decode_attn_fp8: scales must be positive");
+    return decode_entry("ivab_paged_decode_attn_fp8", q, q_stride_b, q_stride_h, k_pool, v_pool, pool_stride_head,
+                        pool_stride_page, block_table, block_table_stride, ctx_len, ctx_begin, sink_tokens, out,
+                        out_stride_b, out_stride_h, lse, dtype, IVAB_F8E4M3, k_scale, v_scale, batch, q_heads, kv_heads,
+                        head_dim, page_size, num_pages, max_pages_per_seq, scale, workspace, workspace_bytes, stream);
 }
 
 extern "C" int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream) {

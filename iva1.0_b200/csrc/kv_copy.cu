@@ -35,6 +35,7 @@ struct RowCopyParams {
     uint32_t page_size;
     int h_fastest;          // row order on the dense side: 1 = (n, h), 0 = (h, n)
     int* status;
+    float inv_scale[2];     // CVT 3/4 (quantising append): 1/scale per tensor
 };
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
@@ -46,7 +47,8 @@ __device__ __forceinline__ void st_stream(void* p, const uint4& v) {
 
 // GATHER: indexed side is the source.  SCATTER: indexed side is the destination.
 // CVT: 0 = raw copy, 1 = fp16 -> fp32, 2 = bf16 -> fp32 (gather only; the reference's gather
-// always returns fp32, src/kernels_t/kv_ops_triton.py:112).
+// always returns fp32, src/kernels_t/kv_ops_triton.py:112), 3 = fp16 -> e4m3, 4 = bf16 -> e4m3
+// (scatter only: quantising append, 8 output bytes per 16-byte source vector).
 template <bool GATHER, int CVT>
 __global__ void __launch_bounds__(kThreads) row_copy_kernel(const RowCopyParams p) {
     const char* __restrict__ src = p.src[blockIdx.z];
@@ -81,7 +83,7 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const RowCopyParams 
                                        (int64_t)(uid % p.page_size) * p.ix_slot;
                     const int64_t dn = b * p.dn_b + h * p.dn_h + (int64_t)n * p.dn_n;
                     const int64_t soff = (GATHER ? ix : dn) + (int64_t)vec * 16;
-                    doff[k] = (GATHER ? dn : ix) + (int64_t)vec * (CVT ? 32 : 16);
+                    doff[k] = (GATHER ? dn : ix) + (int64_t)vec * (CVT == 0 ? 16 : (CVT <= 2 ? 32 : 8));
                     v[k] = ld_stream(src + soff);
                 }
             }
@@ -91,6 +93,14 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const RowCopyParams 
             if (!ok[k]) continue;
             if (CVT == 0) {
                 st_stream(dst + doff[k], v[k]);
+            } else if (CVT >= 3) {
+                float f[8];
+                if (CVT == 3) Elt<__half>::unpack(v[k], f); else Elt<__nv_bfloat16>::unpack(v[k], f);
+                const float is = p.inv_scale[blockIdx.z];
+                uint2 q;
+                q.x = (uint32_t)pack_fp8x2(f[0] * is, f[1] * is) | ((uint32_t)pack_fp8x2(f[2] * is, f[3] * is) << 16);
+                q.y = (uint32_t)pack_fp8x2(f[4] * is, f[5] * is) | ((uint32_t)pack_fp8x2(f[6] * is, f[7] * is) << 16);
+                __stcs(reinterpret_cast<uint2*>(dst + doff[k]), q);
             } else {
                 float f[8];
                 if (CVT == 1) Elt<__half>::unpack(v[k], f); else Elt<__nv_bfloat16>::unpack(v[k], f);
@@ -180,7 +190,9 @@ int launch_row_copy(bool gather, int cvt, const RowCopyParams& p, int64_t batch,
         else if (cvt == 1) row_copy_kernel<true, 1><<<grid, kThreads, 0, st>>>(p);
         else row_copy_kernel<true, 2><<<grid, kThreads, 0, st>>>(p);
     } else {
-        row_copy_kernel<false, 0><<<grid, kThreads, 0, st>>>(p);
+        if (cvt == 0) row_copy_kernel<false, 0><<<grid, kThreads, 0, st>>>(p);
+        else if (cvt == 3) row_copy_kernel<false, 3><<<grid, kThreads, 0, st>>>(p);
+        else row_copy_kernel<false, 4><<<grid, kThreads, 0, st>>>(p);
     }
     g_launches++;
     return check_cuda(cudaGetLastError(), "row_copy_kernel launch");
@@ -214,8 +226,8 @@ extern "C" int ivab_kv_gather(const void* cache, const int64_t* indices, void* o
     int cvt = 0;
     size_t osz = esz;
     if (out_dtype != dtype) {
-        if (out_dtype != IVAB_F32 || dtype == IVAB_F32)
-            return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_gather: out_dtype must equal dtype or be fp32");
+        if (out_dtype != IVAB_F32 || (dtype != IVAB_F16 && dtype != IVAB_BF16))
+            return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_gather: out_dtype must equal dtype, or be fp32 for a 16-bit cache");
         cvt = dtype == IVAB_F16 ? 1 : 2;
         osz = 4;
     }
@@ -333,4 +345,38 @@ extern "C" int ivab_paged_gather(const void* pool, int64_t pool_stride_head, int
     paged_gather_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
     g_launches++;
     return check_cuda(cudaGetLastError(), "paged_gather_kernel launch");
+}
+
+extern "C" int ivab_paged_append_fp8(const void* k_new, const void* v_new, int64_t new_stride_t, int64_t new_stride_h,
+                                     const int64_t* slot_mapping, void* k_pool, void* v_pool,
+                                     int64_t pool_stride_head, int64_t pool_stride_page, int src_dtype,
+                                     float k_scale, float v_scale,
+                                     int64_t n_tokens, int64_t heads, int64_t head_dim, int64_t page_size,
+                                     int64_t num_pages, int32_t* status, void* stream) {
+    const char* fn = "ivab_paged_append_fp8";
+    if (src_dtype != IVAB_F16 && src_dtype != IVAB_BF16)
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: new tokens must be fp16 or bf16", fn);
+    if (!(k_scale > 0.f) || !(v_scale > 0.f)) return set_error(IVAB_ERR_INVALID, "%s: scales must be positive", fn);
+    if (n_tokens < 0 || heads < 0 || page_size <= 0 || num_pages < 0 || head_dim <= 0 || head_dim % 16)
+        return set_error(IVAB_ERR_INVALID, "%s: bad size (head_dim must be a multiple of 16)", fn);
+    if (n_tokens == 0 || heads == 0) return IVAB_OK;
+    if (!k_new || !v_new || !slot_mapping || !k_pool || !v_pool) return set_error(IVAB_ERR_INVALID, "%s: null pointer", fn);
+    if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_pool) || !aligned16(v_pool) ||
+        (new_stride_t * 2) % 16 || (new_stride_h * 2) % 16 || pool_stride_head % 16 || pool_stride_page % 16)
+        return set_error(IVAB_ERR_INVALID, "%s: pointers and strides must be 16-byte aligned", fn);
+    const int64_t vpr = head_dim * 2 / 16;   // source vectors per row
+    const int64_t total = n_tokens * heads * vpr;
+    if (total >= (1LL << 32) - 4096 || num_pages * page_size >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: more than 2^32 vectors; split the call", fn);
+    RowCopyParams p{};
+    p.src[0] = static_cast<const char*>(k_new); p.src[1] = static_cast<const char*>(v_new);
+    p.dst[0] = static_cast<char*>(k_pool); p.dst[1] = static_cast<char*>(v_pool);
+    p.idx = slot_mapping;
+    p.ix_b = 0; p.ix_h = pool_stride_head; p.ix_page = pool_stride_page; p.ix_slot = head_dim;   // 1-byte elements
+    p.dn_b = 0; p.dn_h = new_stride_h * 2; p.dn_n = new_stride_t * 2;
+    p.id_bound = num_pages * page_size; p.N = (uint32_t)n_tokens; p.H = (uint32_t)heads;
+    p.vec_per_row = (uint32_t)vpr; p.total = (uint32_t)total; p.page_size = (uint32_t)page_size;
+    p.h_fastest = new_stride_h < new_stride_t; p.status = status;
+    p.inv_scale[0] = 1.f / k_scale; p.inv_scale[1] = 1.f / v_scale;
+    return launch_row_copy(false, src_dtype == IVAB_F16 ? 3 : 4, p, 1, 2, static_cast<cudaStream_t>(stream));
 }

@@ -152,12 +152,16 @@ def _pool_strides(pool: torch.Tensor, page_size: int):
 
 
 def paged_append(k_pool: torch.Tensor, v_pool: torch.Tensor, slot_mapping: torch.Tensor,
-                 k_new: torch.Tensor, v_new: torch.Tensor, page_size: int, *, check: bool = False) -> None:
+                 k_new: torch.Tensor, v_new: torch.Tensor, page_size: int, *, check: bool = False,
+                 k_scale: float = 1.0, v_scale: float = 1.0) -> None:
     """Write ``T`` new tokens' K and V (``[T,H_kv,D]``) into their slots, in place, one launch.
 
     The slot mapping plays the role of ``indices`` in the reference scatter
     (src/kernels_t/kv_ops_triton.py:58-65) on the flattened slot axis of the pool; this is what
     replaces the O(L) concat of AttentionTorch.forward (src/core/attention.py:61-63).
+
+    Pools of dtype ``torch.float8_e4m3fn`` store ``fp8(x * (1/scale))`` (saturating, round to nearest
+    even) of fp16 / bf16 tokens, K with ``k_scale`` and V with ``v_scale``.
     """
     _lib.require_cuda(k_pool, v_pool, k_new, v_new)
     lib = _lib.load_library()
@@ -167,8 +171,14 @@ def paged_append(k_pool: torch.Tensor, v_pool: torch.Tensor, slot_mapping: torch
         raise ValueError("k_pool and v_pool must have the same shape, strides and dtype")
     if k_new.dim() != 3 or k_new.shape != v_new.shape or k_new.shape[1] != H or k_new.shape[2] != k_pool.shape[-1]:
         raise ValueError("k_new / v_new must be [T, H_kv, D]")
-    k_new = _inner_contiguous(k_new.to(k_pool.dtype))
-    v_new = _inner_contiguous(v_new.to(k_pool.dtype))
+    fp8 = k_pool.dtype == torch.float8_e4m3fn
+    if fp8:
+        if k_new.dtype not in (torch.float16, torch.bfloat16) or v_new.dtype != k_new.dtype:
+            raise ValueError("8-bit pools take fp16 or bf16 tokens")
+        k_new, v_new = _inner_contiguous(k_new), _inner_contiguous(v_new)
+    else:
+        k_new = _inner_contiguous(k_new.to(k_pool.dtype))
+        v_new = _inner_contiguous(v_new.to(k_pool.dtype))
     if v_new.stride() != k_new.stride():
         v_new = v_new.contiguous()
         k_new = k_new.contiguous()
@@ -178,6 +188,13 @@ def paged_append(k_pool: torch.Tensor, v_pool: torch.Tensor, slot_mapping: torch
         raise ValueError(f"slot_mapping has {slots.numel()} entries for {T} tokens")
     status = _status_word(dev)
     with torch.cuda.device(dev):
+        if fp8:
+            _lib.check(lib.ivab_paged_append_fp8(
+                k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0), k_new.stride(1), slots.data_ptr(),
+                k_pool.data_ptr(), v_pool.data_ptr(), sh, sp, _lib.dtype_code(k_new.dtype), float(k_scale),
+                float(v_scale), T, H, k_pool.shape[-1], page_size, num_pages, status.data_ptr(), _lib.stream_ptr(dev)))
+            _check_status(dev, check)
+            return
         _lib.check(lib.ivab_paged_append(
             k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0), k_new.stride(1), slots.data_ptr(),
             k_pool.data_ptr(), v_pool.data_ptr(), sh, sp, _lib.dtype_code(k_pool.dtype),

@@ -27,7 +27,25 @@ from typing import List, Optional, Tuple
 import torch
 import torch.nn.functional as F
 
+FP8_MAX = 448.0   # largest finite e4m3 value
+
+
+def quantize_fp8_ref(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """``fp8_e4m3( clamp(x * (1/scale)) )`` -- the storage format of the 8-bit pools.  The multiply
+    is done in fp32 with the fp32 reciprocal of ``scale``, round to nearest even, saturating at
+    +-448.  (No reference counterpart: fp8 KV is only named in configs/quant_infer.yaml:52.)"""
+    inv = torch.tensor(1.0, dtype=torch.float32) / torch.tensor(scale, dtype=torch.float32)
+    return (x.float() * inv).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+
+
+def dequantize_fp8_ref(pool: torch.Tensor, scale: float) -> torch.Tensor:
+    """fp32 view of an 8-bit pool: ``scale * stored`` (the widening is exact)."""
+    return pool.to(torch.float32) * scale
+
+
 __all__ = [
+    "quantize_fp8_ref",
+    "dequantize_fp8_ref",
     "kv_gather_ref",
     "kv_scatter_ref",
     "kv_ops_ref",
