@@ -229,7 +229,7 @@ class AttentionB200(nn.Module):
     Same parameters (bias-free ``q_proj/k_proj/v_proj/o_proj``, ``d_model -> d_model``), same
     ``forward`` signature and return value ``(output [B,S,d_model], new_kv_cache)``.
 
-    * ``kv_cache`` is a ``PagedKVCache``: the new tokens' K/V are appended to its page pool in
+    * ``kv_cache`` is a ``PagedKVCache`` (or one layer of it, ``cache.layer(i)``): the new tokens' K/V are appended to its page pool in
       place and attention reads the pool through the block table; the same cache object is
       returned.
     * ``kv_cache`` is any object with dense ``.k/.v [B,H,L,D]`` (the reference ``KVCache``): the
@@ -271,12 +271,10 @@ class AttentionB200(nn.Module):
                 kv_cache: Optional[Any] = None, rope_state: Optional[torch.Tensor] = None,
                 sliding_window: Optional[int] = None, sink_cfg: Optional[Dict[str, Any]] = None
                 ) -> Tuple[torch.Tensor, Optional[Any]]:
-        from .paged_cache import PagedKVCache
-
         if attention_mask is not None:
             raise NotImplementedError("AttentionB200 implements the decode path: no padding mask")
         sink = int(sink_cfg.get("sink_tokens", 4)) if sink_cfg is not None else 0
-        if sink and (sliding_window is None or not isinstance(kv_cache, PagedKVCache) or x.shape[1] != 1):
+        if sink and (sliding_window is None or not getattr(kv_cache, "is_paged", False) or x.shape[1] != 1):
             raise NotImplementedError("sink_cfg is supported for single-token decode on a PagedKVCache with a sliding window")
         if self.training and self.dropout:
             raise NotImplementedError("AttentionB200 is inference-only: call .eval()")
@@ -287,7 +285,7 @@ class AttentionB200(nn.Module):
         v = self.v_proj(x).view(B, S, H, D)
         # rope_state is accepted and ignored, like the reference's _apply_rope (attention.py:112-113)
 
-        if isinstance(kv_cache, PagedKVCache):
+        if getattr(kv_cache, "is_paged", False):
             prior = kv_cache.append(k, v)                     # [B] lengths before the append (host list)
             bt, cl = kv_cache.block_table_dev, kv_cache.ctx_len_dev
             if S == 1:

@@ -28,7 +28,15 @@ class PoolExhausted(RuntimeError):
 
 
 class PagedKVCache:
-    """Page pool + block table for ``batch_size`` sequences of one attention layer.
+    """Page pools + block table for ``batch_size`` sequences of one or more attention layers.
+
+    With ``n_layers > 1`` there is still ONE free list, ONE block table and ONE length vector --
+    every layer stores a token in the same slot of its own pool -- so the host bookkeeping and the
+    uploads of a decode step happen once, not once per layer.  ``layer(i)`` gives layer ``i``'s view
+    (its pools, the shared tables), which is what ``AttentionB200`` takes as ``kv_cache``.  (The
+    reference threads one dense cache object through all layers and reassigns it per block,
+    src/core/transformer.py:229-238, so layer ``i+1`` sees layer ``i``'s keys; it also rebuilds the
+    cache every step, transformer.py:273-290.  This is the corrected form.)
 
     Constructor keywords follow ``KVCache(batch_size, n_heads, head_dim, seq_len, device, dtype)``
     (rope_kv.py:73-81; default dtype fp16 as at rope_kv.py:80).  ``seq_len`` is the number of tokens
@@ -41,7 +49,8 @@ class PagedKVCache:
     def __init__(self, batch_size: int, n_heads: int, head_dim: int, seq_len: int = 0,
                  device="cuda", dtype: torch.dtype = torch.float16, *, page_size: int = 16,
                  num_pages: Optional[int] = None, max_seq_len: int = 4096,
-                 shuffle_seed: Optional[int] = None):
+                 shuffle_seed: Optional[int] = None, n_layers: int = 1,
+                 k_scale: float = 1.0, v_scale: float = 1.0):
         self.batch_size = batch_size
         self.n_heads = n_heads
         self.head_dim = head_dim
@@ -54,8 +63,17 @@ class PagedKVCache:
             num_pages = batch_size * self.max_pages_per_seq
         self.num_pages = num_pages
         S = num_pages * page_size
-        self.k_pool = torch.zeros(1, n_heads, S, head_dim, device=self.device, dtype=dtype)
-        self.v_pool = torch.zeros(1, n_heads, S, head_dim, device=self.device, dtype=dtype)
+        self.n_layers = n_layers
+        self.k_scale, self.v_scale = k_scale, v_scale          # used by 8-bit (e4m3) pools only
+        store = torch.uint8 if dtype == torch.float8_e4m3fn else dtype
+
+        def new_pool():
+            return torch.zeros(1, n_heads, S, head_dim, device=self.device, dtype=store).view(dtype)
+
+        self._k_pools = [new_pool() for _ in range(n_layers)]
+        self._v_pools = [new_pool() for _ in range(n_layers)]
+        self.k_pool, self.v_pool = self._k_pools[0], self._v_pools[0]   # layer 0 (the only one by default)
+        self._step = None                                      # an append that not every layer has made yet
         if shuffle_seed is None:
             order = list(range(num_pages))
         else:
@@ -72,6 +90,14 @@ class PagedKVCache:
         if seq_len:
             self._reserve([seq_len] * batch_size)
             self._sync_device()
+
+    is_paged = True
+
+    def layer(self, i: int) -> "_LayerView":
+        """Layer ``i``'s view of the cache: its own pools, the shared block table and lengths."""
+        if not 0 <= i < self.n_layers:
+            raise IndexError(f"layer {i} of {self.n_layers}")
+        return _LayerView(self, i)
 
     # ---- bookkeeping ------------------------------------------------------------------------
 
@@ -126,27 +152,41 @@ class PagedKVCache:
     # ---- the hot path -----------------------------------------------------------------------
 
     def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> List[int]:
-        """Append ``S`` tokens to every sequence.  ``k_new`` / ``v_new`` are ``[B,S,H,D]`` (projection
-        output order), ``[B,H,D]`` for one token, or the reference's ``[B,H,S,D]`` when passed through
-        ``update``.  Returns the lengths before the append."""
+        """Append ``S`` tokens to every sequence (layer 0; use ``layer(i).append`` for the others).
+        ``k_new`` / ``v_new`` are ``[B,S,H,D]`` (projection output order) or ``[B,H,D]`` for one token.
+        Returns the lengths before the append."""
+        return self._append_layer(0, k_new, v_new)
+
+    def _append_layer(self, layer: int, k_new: torch.Tensor, v_new: torch.Tensor) -> List[int]:
+        """One layer's share of a step.  The first layer to arrive reserves pages, computes the slot
+        mapping and uploads it with the new lengths; the others reuse it.  The step is complete when
+        every layer has appended."""
         if k_new.dim() == 3:
             k_new, v_new = k_new.unsqueeze(1), v_new.unsqueeze(1)
         B, S, H, D = k_new.shape
         if B != self.batch_size or H != self.n_heads or D != self.head_dim:
             raise ValueError(f"expected [{self.batch_size},S,{self.n_heads},{self.head_dim}], got {list(k_new.shape)}")
-        prior = list(self._lens)
-        self._reserve([L + S for L in prior])
-        slots: List[int] = []
-        for s in range(B):
-            slots.extend(self.slots(s, prior[s], prior[s] + S))
-        slot_t = torch.tensor(slots, dtype=torch.int64)
-        if self.device.type == "cuda":
-            slot_t = slot_t.pin_memory()
-        slot_dev = slot_t.to(self.device, non_blocking=True)
-        self._sync_device()
-        paged_append(self.k_pool, self.v_pool, slot_dev, k_new.reshape(B * S, H, D), v_new.reshape(B * S, H, D),
-                     self.page_size)
-        return prior
+        if self._step is None:
+            prior = list(self._lens)
+            self._reserve([L + S for L in prior])
+            slots: List[int] = []
+            for s in range(B):
+                slots.extend(self.slots(s, prior[s], prior[s] + S))
+            slot_t = torch.tensor(slots, dtype=torch.int64)
+            if self.device.type == "cuda":
+                slot_t = slot_t.pin_memory()
+            slot_dev = slot_t.to(self.device, non_blocking=True)
+            self._sync_device()
+            self._step = {"prior": prior, "slots": slot_dev, "S": S, "done": set()}
+        st = self._step
+        if S != st["S"] or layer in st["done"]:
+            raise RuntimeError(f"layer {layer} appended twice, or with a different token count, within one step")
+        paged_append(self._k_pools[layer], self._v_pools[layer], st["slots"], k_new.reshape(B * S, H, D),
+                     v_new.reshape(B * S, H, D), self.page_size, k_scale=self.k_scale, v_scale=self.v_scale)
+        st["done"].add(layer)
+        if len(st["done"]) == self.n_layers:
+            self._step = None
+        return st["prior"]
 
     def gather(self, layout: str = "head_major"):
         """Contiguous K and V of every sequence (lists of ``[1,H,L_s,D]`` for ``head_major``, packed
@@ -200,8 +240,8 @@ class PagedKVCache:
     def clear(self) -> None:
         """Zero the pools (rope_kv.py:132-134); lengths and block tables are kept, as the reference
         keeps ``seq_len``."""
-        self.k_pool.zero_()
-        self.v_pool.zero_()
+        for pool in self._k_pools + self._v_pools:
+            pool.view(torch.uint8).zero_() if pool.dtype == torch.float8_e4m3fn else pool.zero_()
 
     def get_slice(self, start: int, end: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """Dense ``[B,H,end-start,D]`` K and V (rope_kv.py:136-137)."""
@@ -267,9 +307,9 @@ class PagedKVCache:
             src_slots.extend(tab[p // ps] * ps + p % ps for p in kept)
             new_lens.append(len(kept))
         idx = torch.tensor(src_slots, dtype=torch.int64).to(self.device)
-        # the survivors are copied out before any page is released, so re-using pages is safe
-        k_rows = kv_ops(self.k_pool, idx, None, "gather", compat=False)      # [1,H,T,D]
-        v_rows = kv_ops(self.v_pool, idx, None, "gather", compat=False)
+        # the survivors of every layer are copied out before any page is released, so re-using pages is safe
+        rows = [(kv_ops(kp, idx, None, "gather", compat=False), kv_ops(vp, idx, None, "gather", compat=False))
+                for kp, vp in zip(self._k_pools, self._v_pools)]                       # [1,H,T,D] each
         self.reset()
         self._reserve(new_lens)
         dst: List[int] = []
@@ -277,6 +317,40 @@ class PagedKVCache:
             dst.extend(self.slots(s, 0, L))
         self._sync_device()
         if dst:
-            paged_append(self.k_pool, self.v_pool, torch.tensor(dst, dtype=torch.int64).to(self.device),
-                         k_rows[0].permute(1, 0, 2), v_rows[0].permute(1, 0, 2), self.page_size)
+            dst_dev = torch.tensor(dst, dtype=torch.int64).to(self.device)
+            for (k_rows, v_rows), kp, vp in zip(rows, self._k_pools, self._v_pools):
+                # the rows are already in storage format: a raw copy, not a second quantisation
+                raw = (lambda t: t.view(torch.uint8)) if kp.dtype == torch.float8_e4m3fn else (lambda t: t)
+                paged_append(raw(kp), raw(vp), dst_dev, raw(k_rows)[0].permute(1, 0, 2), raw(v_rows)[0].permute(1, 0, 2),
+                             self.page_size)
         return new_lens
+
+
+class _LayerView:
+    """Layer ``i`` of a multi-layer ``PagedKVCache``: own pools, shared tables and lengths.  Everything
+    else is forwarded to the parent."""
+
+    is_paged = True
+
+    def __init__(self, parent: PagedKVCache, index: int):
+        self._parent, self._index = parent, index
+        self.k_pool, self.v_pool = parent._k_pools[index], parent._v_pools[index]
+
+    def __getattr__(self, name):
+        return getattr(self._parent, name)
+
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> List[int]:
+        return self._parent._append_layer(self._index, k_new, v_new)
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self._parent._dense(self.k_pool)
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self._parent._dense(self.v_pool)
+
+    def gather(self, layout: str = "head_major"):
+        p = self._parent
+        return (paged_gather(self.k_pool, p.block_table_dev, p.ctx_len_dev, p.page_size, layout=layout),
+                paged_gather(self.v_pool, p.block_table_dev, p.ctx_len_dev, p.page_size, layout=layout))

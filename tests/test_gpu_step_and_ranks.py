@@ -2,6 +2,7 @@
 
 import os
 import socket
+from types import SimpleNamespace
 
 import pytest
 import torch
@@ -50,6 +51,56 @@ def test_graphed_decode_steps_follow_the_dense_reference(use_graph):
         assert_lse_close(lse, lse_ref)
     assert torch.equal(cache.k_pool.cpu(), k_ref) and torch.equal(cache.v_pool.cpu(), v_ref)
     assert (step.graph is not None) == use_graph
+
+
+def test_three_layer_decode_loop_carries_one_cache_across_steps_and_layers():
+    """A prompt and eight decode steps through three stacked attention layers that share one
+    PagedKVCache (one block table, three pools).  Every layer of every step must match the reference
+    module's math on that layer's own dense cache."""
+    torch.manual_seed(4)
+    B, H, hd, L = 2, 4, 64, 3
+    dm = H * hd
+    cfg = SimpleNamespace(d_model=dm, n_heads=H, dropout=0.0, causal=False, attn_impl="b200")
+    layers = [iva_b200.AttentionB200(cfg).to(DEV).eval() for _ in range(L)]
+    wts = [[p.detach().cpu() for p in (m.q_proj.weight, m.k_proj.weight, m.v_proj.weight, m.o_proj.weight)] for m in layers]
+    cache = iva_b200.PagedKVCache(batch_size=B, n_heads=H, head_dim=hd, device=DEV, dtype=torch.float32,
+                                  max_seq_len=64, shuffle_seed=8, n_layers=L)
+    dense = [(None, None)] * L
+    xs = [torch.randn(B, 21, dm)] + [torch.randn(B, 1, dm) for _ in range(8)]
+    for x in xs:
+        h_gpu, h_ref = x.to(DEV), x
+        for i, m in enumerate(layers):
+            y, view = m(h_gpu, kv_cache=cache.layer(i))
+            y_ref, dk, dv = ref.attention_module_ref(h_ref, *wts[i], H, *dense[i])
+            dense[i] = (dk, dv)
+            assert (y.cpu() - y_ref).abs().max().item() <= 2e-4, (i, x.shape)
+            h_gpu, h_ref = h_gpu + y, h_ref + y_ref          # residual stream
+    assert cache.lengths == [29, 29] and cache._step is None
+    for i in range(L):
+        assert torch.allclose(cache.layer(i).k.cpu(), dense[i][0], atol=1e-4)
+    # one allocator: the three layers use the same pages
+    assert cache.free_pages == cache.num_pages - B * 2
+    with pytest.raises(RuntimeError, match="appended twice"):
+        k = torch.zeros(B, 1, H, hd, device=DEV)
+        cache.layer(0).append(k, k)
+        cache.layer(0).append(k, k)
+
+
+def test_fp8_cache_object():
+    cache = iva_b200.PagedKVCache(batch_size=2, n_heads=2, head_dim=128, device=DEV, dtype=torch.float8_e4m3fn,
+                                  max_seq_len=64, k_scale=0.02, v_scale=0.02)
+    g = torch.Generator().manual_seed(1)
+    k = torch.randn(2, 40, 2, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(2, 40, 2, 128, generator=g).to(torch.bfloat16)
+    cache.append(k.to(DEV), v.to(DEV))
+    q = torch.randn(2, 4, 128, generator=g).to(torch.bfloat16)
+    out = iva_b200.paged_decode_attention(q.to(DEV), cache.k_pool, cache.v_pool, cache.block_table_dev, cache.ctx_len_dev,
+                                          16, k_scale=0.02, v_scale=0.02, check=True)
+    kq = ref.dequantize_fp8_ref(ref.quantize_fp8_ref(k, 0.02), 0.02).permute(0, 2, 1, 3)     # [B,H,L,D]
+    vq = ref.dequantize_fp8_ref(ref.quantize_fp8_ref(v, 0.02), 0.02).permute(0, 2, 1, 3)
+    want, _ = ref.attention_math_ref(q.view(2, 2, 2, 1, 128).reshape(2, 4, 1, 128), kq.repeat_interleave(2, 1),
+                                     vq.repeat_interleave(2, 1), 128 ** -0.5)
+    assert_attn_close(out, want.view(2, 4, 128), torch.bfloat16, strict=False)
 
 
 def _free_port():
