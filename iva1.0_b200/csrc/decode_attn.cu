@@ -2,32 +2,39 @@
 //
 // Three kernels per call, all on the caller's stream:
 //
-//   1. plan_kernel   (1 CTA)      reads ctx_len on the device, picks one chunk size (in pages) for
-//                                 the whole batch so that the work list has a few items per
-//                                 resident CTA, and writes the list of (sequence, page range)
-//                                 chunks.  No host synchronisation: ragged batches never stall
-//                                 the stream.
-//   2. decode_kernel (persistent) one CTA per resident slot.  Work items are (kv head, chunk)
-//                                 pairs taken from an atomic counter, kv-head-major so that CTAs
-//                                 running at the same time read the same head's slab of the pool.
-//                                 Warp 4 is the producer: it walks the block table and issues one
-//                                 TMA bulk copy per K page and V page (4 KB each for 16x128 bf16)
-//                                 into a ring of shared-memory stages guarded by mbarriers.  The
-//                                 ring runs across item boundaries, so the copy engine never
-//                                 drains between items.  Warps 0-3 consume pages round-robin;
-//                                 each keeps its own online-softmax state (running max, sum and
-//                                 fp32 accumulators) for all query heads of the kv head, so a
-//                                 page is read from HBM once per GQA group.  At the end of an
-//                                 item the four states are merged through shared memory and either
-//                                 written as the final output (one-chunk sequences) or as an
-//                                 fp32 partial (o, m, l).
-//   3. merge_kernel               one warp per (sequence, query head): logsumexp-merge of the
-//                                 partials of multi-chunk sequences.
+//   1. plan_kernel   (1 CTA)      reads ctx_len (and the optional window start / sink count) on the
+//                                 device, picks one chunk size (in pages) for the whole batch so
+//                                 that the work list has a few items per resident CTA, orders the
+//                                 sequences longest-first and writes the list of (sequence, page
+//                                 range) chunks.  No host synchronisation: ragged batches never
+//                                 stall the stream.
+//   2. decode_kernel (persistent) one CTA per resident slot (2 per SM).  Work items are (kv head,
+//                                 chunk) pairs taken from an atomic counter, kv-head-major so that
+//                                 CTAs running at the same time read the same head's slab of the
+//                                 pool.  Warp 4 is the producer: its item fetches (counter ->
+//                                 descriptor -> block-table entries) are pipelined two items ahead,
+//                                 and it issues a ring's worth of pages at a time with one lane per
+//                                 page, each lane waiting for its own stage and issuing the TMA
+//                                 copies of one K page and one V page (4 KB each for 16x128 bf16)
+//                                 with an L2 evict-first policy.  The ring of shared-memory stages
+//                                 is guarded by mbarriers and runs across item boundaries, so the
+//                                 copy engine never drains between items.  Warps 0-3 consume: page
+//                                 k of an item always goes to warp (seq + chunk + k) mod 4 (each
+//                                 warp owns a quarter of the stages), so results do not depend on
+//                                 scheduling.  Each warp keeps its own online-softmax state (running
+//                                 max, sum and fp32 accumulators) for all query heads of the kv
+//                                 head, so a page is read from HBM once per GQA group.  At the end
+//                                 of an item every warp publishes its state to shared memory and
+//                                 moves on; the warp that arrives last combines the four states (in
+//                                 warp order) and writes the final output (one-chunk sequences) or
+//                                 an fp32 partial (o, m, l).
+//   3. merge_kernel               CTAs of 8 warps walk the list of split (sequence, query head)
+//                                 pairs: logsumexp-merge of their partials.
 //
 // All waits are bounded (see mbar_wait_bounded); a wait that expires raises a CTA-wide abort
 // flag, the status word gets IVAB_STATUS_WAIT_TIMEOUT and every warp unwinds.  Intra-CTA
-// synchronisation uses mbarriers only (no bar.sync), so a warp that unwinds can never leave
-// another one stuck at a barrier.
+// synchronisation uses mbarriers only (no bar.sync after start-up), so a warp that unwinds can
+// never leave another one stuck at a barrier.
 #include <cuda.h>
 
 #include <atomic>
