@@ -405,6 +405,7 @@ def run_gpu(args):
     }
     if args.cpu_baseline and world == 1:
         result["cpu_baseline"] = cpu_baseline(name, args, budget_s=12.0)
+        result["c1_reference_case"] = c1_case(dev)
     print(json.dumps(result))
     if dist is not None:
         dist.barrier()
@@ -443,6 +444,38 @@ def cpu_baseline(name, args, budget_s, kind_label="port"):
                       f"(clone+index_copy append, index_select gather, matmul/softmax/matmul)",
             "ms_per_step": med * 1e3,
             "attn_GBs": attention_bytes(wl, wl.ctx_len + 1) / med / 1e9}
+
+
+def c1_case(dev):
+    """The reference's own CPU-runnable configuration run EXACTLY (batch 4, 16 heads, head_dim 64, fp32,
+    page 16, contexts U[1,512], 256-page pool, seed 0): one decode step on the host cores (checker)
+    and on the GPU (append + attention, CUDA events, L2 flushed between steps)."""
+    from oracle import paged_ref as ref
+
+    wl = workloads.config_c1()
+    ref.decode_step_ref(wl)
+    cpu = []
+    for _ in range(20):
+        t0 = time.perf_counter()
+        ref.decode_step_ref(wl)
+        cpu.append(time.perf_counter() - t0)
+    d = wl.to(dev)
+    lens = (d.ctx_len + 1).contiguous()
+    out = torch.empty(wl.batch, wl.n_q_heads, wl.head_dim, device=dev, dtype=wl.dtype)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        iva_b200.paged_append(d.k_pool, d.v_pool, d.slot_mapping, d.k_new, d.v_new, wl.page_size)
+        iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, lens, wl.page_size, wl.scale, out=out)
+
+    for _ in range(5):
+        step()
+    gpu = time_region(step, 50, lambda: flush_buf.fill_(1))
+    nbytes = attention_bytes(wl, wl.ctx_len + 1) + append_bytes(wl)
+    return {"config": "batch 4, 16 heads, head_dim 64, fp32, contexts " + str(wl.ctx_len.tolist()),
+            "cpu_ms_per_step": statistics.median(cpu) * 1e3, "cpu_cores": torch.get_num_threads(),
+            "gpu_ms_per_step": statistics.median(gpu), "algorithmic_bytes": nbytes,
+            "note": "latency-bound on the GPU: 1 MB of K/V, four kernel launches"}
 
 
 def run_reference(args):
