@@ -81,3 +81,40 @@ def test_c4_full_size_append_gather_roundtrip():
     # the reference-signature operator on the same pool: gather the chunk's slots back
     back = iva_b200.kv_ops(wl.v_pool, wl.slot_mapping[:4096], None, "gather", compat=False, check=True)
     assert torch.equal(back[0].permute(1, 0, 2), wl.v_new[:4096])
+
+
+def test_c5b_single_131072_token_sequence():
+    """One sequence of 131072 tokens, 32 query / 8 KV heads: hundreds of chunks per head, merged by
+    logsumexp; compared with the checker on the whole sequence."""
+    wl = workloads.config_c5b(device=DEV)
+    lens = wl.ctx_len.contiguous()
+    out, lse = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                               return_lse=True, check=True)
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q.cpu(), wl.k_pool.cpu(), wl.v_pool.cpu(), wl.block_table.cpu(),
+                                            lens.cpu(), 16, wl.scale)
+    assert_attn_close(out, out_ref, wl.dtype, strict=True)
+    assert_lse_close(lse, lse_ref)
+    # sliding window over the last 4096 keys plus 4 sink keys: 257 pages read instead of 8192
+    begin = (lens - 4096).clamp(min=0)
+    out_w, lse_w = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                                   return_lse=True, check=True, ctx_begin=begin, sink_tokens=4)
+    ow_ref, lw_ref = ref.paged_decode_ref(wl.q.cpu(), wl.k_pool.cpu(), wl.v_pool.cpu(), wl.block_table.cpu(), lens.cpu(),
+                                          16, wl.scale, ctx_begin=begin.cpu(), sink_tokens=4)
+    assert_attn_close(out_w, ow_ref, wl.dtype, strict=True)
+    assert_lse_close(lse_w, lw_ref)
+
+
+def test_batch_larger_than_the_planner_tiles():
+    """1500 ragged sequences: more than the planner sorts (1024) and more than one scan tile."""
+    g = torch.Generator().manual_seed(5)
+    ctx = torch.randint(0, 300, (1500,), generator=g)
+    ctx[7] = 4000                                            # one long sequence that gets split
+    wl = workloads.make_decode_workload("big", ctx, n_q_heads=8, n_kv_heads=2, head_dim=64, dtype=torch.float16,
+                                        seed=6)
+    _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
+    d = wl.to(DEV)
+    iva_b200.paged_append(d.k_pool, d.v_pool, d.slot_mapping, d.k_new, d.v_new, 16, check=True)
+    out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, (d.ctx_len + 1).contiguous(), 16,
+                                               return_lse=True, check=True)
+    assert_attn_close(out, out_ref, wl.dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
