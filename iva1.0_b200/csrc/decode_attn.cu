@@ -633,18 +633,21 @@ struct MmaEngine {
         }
 
         // ---- S^T[head, token] = Q K^T : two 8-token column blocks, KSTEPS k-steps each
+        // (even and odd k-steps accumulate separately: four independent MMA chains instead of two)
         float s[2][2];
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
-            s[nb][0] = s[nb][1] = 0.f;
+            float se[2] = {0.f, 0.f}, so[2] = {0.f, 0.f};
             const int token = nb * 8 + rr;
 #pragma unroll
             for (int sp = 0; sp < KSTEPS / 2; ++sp) {
                 uint32_t b[4];
                 ldmatrix_x4(kbase + chunk_off(token, 4 * sp + mi), b);     // k-steps 2sp (b0,b1) and 2sp+1 (b2,b3)
-                mma_m16n8k16_top<T>(s[nb], qa[2 * sp][0], qa[2 * sp][1], b[0], b[1]);
-                mma_m16n8k16_top<T>(s[nb], qa[2 * sp + 1][0], qa[2 * sp + 1][1], b[2], b[3]);
+                mma_m16n8k16_top<T>(se, qa[2 * sp][0], qa[2 * sp][1], b[0], b[1]);
+                mma_m16n8k16_top<T>(so, qa[2 * sp + 1][0], qa[2 * sp + 1][1], b[2], b[3]);
             }
+            s[nb][0] = se[0] + so[0];
+            s[nb][1] = se[1] + so[1];
         }
         // this lane: head lane/4, tokens 2c, 2c+1 (block 0) and 8+2c, 9+2c (block 1)
         if (partial) {
