@@ -361,16 +361,21 @@ struct Cfg {
     static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
     static_assert(LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0, "row must map onto a power-of-two lane group");
     static_assert(NV >= 1 && NV <= LPR, "page too large for the transposing reduce");
-    // shared memory carve-up (bytes)
-    static constexpr int OFF_BARS = 0;                                  // 2*kMaxStages + 2*kItemRing + 2 barriers
+};
+
+// shared memory carve-up of the decode kernel (bytes) for an engine with SCRATCH bytes per consumer warp
+template <int SCRATCH, int D, int G>
+struct SmemLayout {
+    static constexpr int OFF_BARS = 0;                                  // 2*kMaxStages + 2*kItemRing + 1 barriers
     static constexpr int OFF_ABORT = 1024 - 16;
     static constexpr int OFF_ITEMS = 1024;                              // kItemRing * kItWords ints
-    static constexpr int OFF_P = OFF_ITEMS + kItemRing * kItWords * 4;  // [W][G][kPage] floats
-    static constexpr int OFF_MRG_ML = OFF_P + kConsumerWarps * G * kPage * 4;       // [W][G][2]
-    static constexpr int OFF_MRG_O = OFF_MRG_ML + kConsumerWarps * G * 2 * 4;       // [W][G][D]
-    static constexpr int OFF_STAGES = (OFF_MRG_O + kConsumerWarps * G * D * 4 + 1023) / 1024 * 1024;  // swizzled tiles need 1 KB alignment
-    static constexpr int CTAS_PER_SM = (G >= 8) ? 1 : 2;
+    static constexpr int OFF_MRG_ML = OFF_ITEMS + kItemRing * kItWords * 4;          // [W][G][2]
+    static constexpr int OFF_MRG_O = OFF_MRG_ML + kConsumerWarps * G * 2 * 4;        // [W][G][D]
+    static constexpr int OFF_SCRATCH = (OFF_MRG_O + kConsumerWarps * G * D * 4 + 127) / 128 * 128;   // [W][SCRATCH]
+    static constexpr int OFF_STAGES = (OFF_SCRATCH + kConsumerWarps * SCRATCH + 1023) / 1024 * 1024;  // swizzled tiles need 1 KB alignment
 };
+
+enum { kEngSimt = 0, kEngMma = 1, kEngMmaFp8 = 2 };
 
 // Sum NV per-lane values across the LPR lanes of a row group.  While more than one value is
 // left, each step trades half of them with the partner lane (so the number of shuffles halves
@@ -436,6 +441,8 @@ struct SimtEngine {
     static constexpr bool kTiled = false;
     static constexpr int PAGE_BYTES = C::PAGE_BYTES;
     static constexpr int STAGE_BYTES = C::STAGE_BYTES;
+    static constexpr int SCRATCH_PER_WARP = G * kPage * 4;   // the page's softmax weights, [G][kPage] floats
+    static constexpr int CTAS_PER_SM = (G >= 8) ? 1 : 2;      // G = 8 needs ~250 registers per thread
 
     float qf[G][C::EPL];
     float m_run[G], l_run[G], acc[G][C::EPL];
@@ -471,7 +478,8 @@ struct SimtEngine {
 
     // tokens t >= n_valid and hole_lo <= t < hole_hi of the page do not count
     __device__ __forceinline__ void page(const DecodeParams&, const unsigned char* stage, int n_valid, int hole_lo,
-                                         int hole_hi, int lane, float* p_smem) {
+                                         int hole_hi, int lane, unsigned char* scratch) {
+        float* p_smem = reinterpret_cast<float*>(scratch);
         const uint4* kp = reinterpret_cast<const uint4*>(stage) + lane;
         const uint4* vp = kp + C::PAGE_BYTES / 16;
         // ---- scores: q . k for the page's 16 tokens, all G heads
@@ -567,10 +575,11 @@ struct SimtEngine {
     }
 };
 
-template <typename T, int D, int G>
-struct MmaEngine {
+// TT: 16-bit type of the tiles fed to the tensor cores; TQ: type of q in global memory.
+template <typename TT, typename TQ, int D, int G>
+struct MmaCore {
+    using T = TT;
     static_assert(sizeof(T) == 2 && D % 64 == 0 && G >= 1 && G <= 8, "tensor-core engine: 16-bit K/V, D % 64 == 0, G <= 8");
-    static constexpr bool kTiled = true;
     static constexpr int TILES = D / 64;               // 64-element (128-byte) column tiles per row
     static constexpr int TILE_BYTES = kPage * 128;     // 16 rows x 128 B, swizzled in 16-byte units
     static constexpr int PAGE_BYTES = TILES * TILE_BYTES;
@@ -586,14 +595,25 @@ struct MmaEngine {
 
     __device__ __forceinline__ void setup(int) {}
 
+    // two consecutive q elements as one register of tile type (bf16 -> fp16 saturates at the fp16 range)
+    __device__ __forceinline__ static uint32_t load_q_pair(const TQ* ptr) {
+        const uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(ptr));
+        if constexpr (std::is_same<TT, TQ>::value) {
+            return raw;
+        } else {
+            const float2 f = unpack2<TQ>(raw);
+            return pack2<TT>(fminf(fmaxf(f.x, -65504.f), 65504.f), fminf(fmaxf(f.y, -65504.f), 65504.f));
+        }
+    }
+
     __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
         const int g = lane >> 2, c = lane & 3;
         if (g < G) {
-            const T* qrow = static_cast<const T*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh;
+            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh;
 #pragma unroll
             for (int s = 0; s < KSTEPS; ++s) {
-                qa[s][0] = __ldg(reinterpret_cast<const uint32_t*>(qrow + 16 * s + 2 * c));
-                qa[s][1] = __ldg(reinterpret_cast<const uint32_t*>(qrow + 16 * s + 2 * c + 8));
+                qa[s][0] = load_q_pair(qrow + 16 * s + 2 * c);
+                qa[s][1] = load_q_pair(qrow + 16 * s + 2 * c + 8);
             }
         } else {
 #pragma unroll
@@ -610,27 +630,13 @@ struct MmaEngine {
         return (uint32_t)((q >> 3) * TILE_BYTES + token * 128 + (((q & 7) ^ (token & 7)) << 4));
     }
 
-    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int hole_lo,
-                                         int hole_hi, int lane, float*) {
-        const uint32_t kbase = smem_u32(stage);
-        const uint32_t vbase = kbase + PAGE_BYTES;
+    // One page whose K and V tiles (swizzled, TILES x 2 KB each) sit at shared addresses kbase / vbase.
+    // Rows of V that do not count must already be zero (see the engines).
+    __device__ __forceinline__ void compute(const DecodeParams& p, uint32_t kbase, uint32_t vbase, int n_valid,
+                                            int hole_lo, int hole_hi, int lane) {
         const int c = lane & 3;
         const int mi = lane >> 3, rr = lane & 7;   // ldmatrix: this lane addresses row rr of matrix mi
-
         const bool partial = n_valid < kPage || hole_hi > hole_lo;
-        if (partial) {
-            // A page cut by ctx_len, the sink or the window: rows that do not count may hold stale bits (NaN
-            // included).  Their weights are exactly zero, but 0 * NaN is NaN inside the MMA, so clear
-            // those V rows.  (Rows are 128 bytes in every tile; the swizzle only permutes within a row.)
-            for (int t = 0; t < TILES; ++t) {
-                unsigned char* tile = stage + PAGE_BYTES + t * TILE_BYTES;
-                for (int i = lane; i < (kPage - n_valid) * 8; i += 32)
-                    *reinterpret_cast<uint4*>(tile + n_valid * 128 + i * 16) = make_uint4(0, 0, 0, 0);
-                for (int i = lane; i < (hole_hi - hole_lo) * 8; i += 32)
-                    *reinterpret_cast<uint4*>(tile + hole_lo * 128 + i * 16) = make_uint4(0, 0, 0, 0);
-            }
-            __syncwarp();
-        }
 
         // ---- S^T[head, token] = Q K^T : two 8-token column blocks, KSTEPS k-steps each
         // (even and odd k-steps accumulate separately: four independent MMA chains instead of two)
@@ -692,8 +698,6 @@ struct MmaEngine {
             mma_m16n8k16<T>(o[2 * jp], pa0, pb0, pa2, pb2, b[0], b[1]);
             mma_m16n8k16<T>(o[2 * jp + 1], pa0, pb0, pa2, pb2, b[2], b[3]);
         }
-        if (partial) fence_proxy_async_smem();   // order the row clearing before the next TMA write
-        __syncwarp();
     }
 
     __device__ __forceinline__ void publish(const DecodeParams& p, float* my_ml, float* my_o, int lane) {
@@ -713,15 +717,103 @@ struct MmaEngine {
     }
 };
 
+
+// 16-bit pools: pages arrive as swizzled tiles straight from the tiled TMA copies.
+template <typename T, int D, int G>
+struct MmaEngine : MmaCore<T, T, D, G> {
+    using Core = MmaCore<T, T, D, G>;
+    static constexpr bool kTiled = true;
+    static constexpr int SCRATCH_PER_WARP = 0;
+    static constexpr int CTAS_PER_SM = 2;
+    using Core::TILES; using Core::TILE_BYTES; using Core::PAGE_BYTES;
+
+    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int hole_lo,
+                                         int hole_hi, int lane, unsigned char*) {
+        const bool partial = n_valid < kPage || hole_hi > hole_lo;
+        if (partial) {
+            // A page cut by ctx_len, the sink or the window: rows that do not count may hold stale bits (NaN
+            // included).  Their weights are exactly zero, but 0 * NaN is NaN inside the MMA, so clear
+            // those V rows.  (Rows are 128 bytes in every tile; the swizzle only permutes within a row.)
+            for (int t = 0; t < TILES; ++t) {
+                unsigned char* tile = stage + PAGE_BYTES + t * TILE_BYTES;
+                for (int i = lane; i < (kPage - n_valid) * 8; i += 32)
+                    *reinterpret_cast<uint4*>(tile + n_valid * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+                for (int i = lane; i < (hole_hi - hole_lo) * 8; i += 32)
+                    *reinterpret_cast<uint4*>(tile + hole_lo * 128 + i * 16) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+        }
+        const uint32_t kbase = smem_u32(stage);
+        this->compute(p, kbase, kbase + PAGE_BYTES, n_valid, hole_lo, hole_hi, lane);
+        if (partial) fence_proxy_async_smem();   // order the row clearing before the next TMA write
+        __syncwarp();
+    }
+};
+
+// 8-bit (e4m3) pools with grouped queries.  Pages arrive row-major (one untiled TMA copy each, 16 x D
+// bytes); every consumer warp widens its page to fp16 -- e4m3 -> f16x2 is one exact instruction per
+// pair -- into a private pair of swizzled tiles in shared memory and then runs the tensor-core code on
+// them.  Rows that do not count are written as zeros during the widening.
+template <typename TQ, int D, int G>
+struct MmaFp8Engine : MmaCore<__half, TQ, D, G> {
+    using Core = MmaCore<__half, TQ, D, G>;
+    static constexpr bool kTiled = false;
+    static constexpr int PAGE_BYTES = kPage * D;             // stored bytes of one K or V page
+    static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+    static constexpr int SCRATCH_PER_WARP = 2 * Core::PAGE_BYTES;   // fp16 K and V tiles
+    static constexpr int CTAS_PER_SM = 2;
+
+    __device__ __forceinline__ static void widen(const unsigned char* src, unsigned char* dst, int n_valid, int hole_lo,
+                                                 int hole_hi, int lane, bool mask_rows) {
+        constexpr int VEC_PER_ROW = D / 16;                   // 16-byte vectors (16 values) per stored row
+#pragma unroll
+        for (int v = lane; v < kPage * VEC_PER_ROW; v += 32) {
+            const int token = v / VEC_PER_ROW, part = v % VEC_PER_ROW;
+            uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+            if (!mask_rows || (token < n_valid && !(token >= hole_lo && token < hole_hi))) {
+                const uint4 u = *reinterpret_cast<const uint4*>(src + v * 16);
+                const __nv_fp8x2_storage_t* p2 = reinterpret_cast<const __nv_fp8x2_storage_t*>(&u);
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p2[i], __NV_E4M3);
+                    w[i] = (uint32_t)h.x | ((uint32_t)h.y << 16);
+                }
+                lo = make_uint4(w[0], w[1], w[2], w[3]);
+                hi = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+            *reinterpret_cast<uint4*>(dst + Core::chunk_off(token, 2 * part)) = lo;
+            *reinterpret_cast<uint4*>(dst + Core::chunk_off(token, 2 * part + 1)) = hi;
+        }
+    }
+
+    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int hole_lo,
+                                         int hole_hi, int lane, unsigned char* scratch) {
+        const bool partial = n_valid < kPage || hole_hi > hole_lo;
+        widen(stage, scratch, n_valid, hole_lo, hole_hi, lane, false);                      // K: scores are masked later
+        widen(stage + PAGE_BYTES, scratch + Core::PAGE_BYTES, n_valid, hole_lo, hole_hi, lane, partial);   // V: zero rows
+        __syncwarp();
+        const uint32_t kbase = smem_u32(scratch);
+        this->compute(p, kbase, kbase + Core::PAGE_BYTES, n_valid, hole_lo, hole_hi, lane);
+        __syncwarp();   // the tiles are rewritten for the next page
+    }
+};
+
 struct alignas(64) TensorMaps {
     CUtensorMap k, v;   // 4-D maps of the K and V pools: (dim, token in page, page, head)
 };
 
-template <typename T, int D, int G, bool TC, typename TKV = T>
-__global__ void __launch_bounds__(kThreads, TC ? 2 : Cfg<TKV, D, G>::CTAS_PER_SM)
+// ENG picks the page engine; T is the type of q and of the output, TKV the storage type of the pools.
+template <int ENG, typename T, typename TKV, int D, int G> struct EngineSelect;
+template <typename T, typename TKV, int D, int G> struct EngineSelect<kEngSimt, T, TKV, D, G> { using type = SimtEngine<TKV, T, D, G>; };
+template <typename T, typename TKV, int D, int G> struct EngineSelect<kEngMma, T, TKV, D, G> { using type = MmaEngine<T, D, G>; };
+template <typename T, typename TKV, int D, int G> struct EngineSelect<kEngMmaFp8, T, TKV, D, G> { using type = MmaFp8Engine<T, D, G>; };
+
+template <typename T, int D, int G, int ENG, typename TKV = T>
+__global__ void __launch_bounds__(kThreads, EngineSelect<ENG, T, TKV, D, G>::type::CTAS_PER_SM)
 decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ TensorMaps tm) {
-    using C = Cfg<TKV, D, G>;
-    using Eng = std::conditional_t<TC, MmaEngine<T, D, G>, SimtEngine<TKV, T, D, G>>;
+    using Eng = typename EngineSelect<ENG, T, TKV, D, G>::type;
+    using C = SmemLayout<Eng::SCRATCH_PER_WARP, D, G>;
     extern __shared__ unsigned char smem_raw[];
     // the carve-up assumes a 1 KB-aligned base; the launch reserves 1 KB of slack for this
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -917,7 +1009,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     }
 
     // ---------------------------------- consumer warps --------------------------------------------
-    float* p_smem = reinterpret_cast<float*>(smem + C::OFF_P) + warp * (G * kPage);
+    unsigned char* scratch = smem + C::OFF_SCRATCH + warp * Eng::SCRATCH_PER_WARP;   // this warp's private scratch
     float* mrg_ml = reinterpret_cast<float*>(smem + C::OFF_MRG_ML);
     float* mrg_o = reinterpret_cast<float*>(smem + C::OFF_MRG_O);
     T* outg = static_cast<T*>(p.out);
@@ -956,7 +1048,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             const int n_valid = min(kPage, L - pg * kPage);
             const int hole_lo = min(kPage, max(0, min(p.sink_tokens, begin) - pg * kPage));
             const int hole_hi = min(kPage, max(0, begin - pg * kPage));
-            eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, hole_lo, hole_hi, lane, p_smem);
+            eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, hole_lo, hole_hi, lane, scratch);
             if (lane == 0) mbar_arrive(bar_empty(stage));
             PROF_MARK(3)   // page math
         }
@@ -1142,11 +1234,11 @@ int tc_min_group() {
     return v;
 }
 
-template <typename T, int D, int G, bool TC, typename TKV = T>
+template <typename T, int D, int G, int ENG, typename TKV = T>
 int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStream_t st) {
-    using C = Cfg<TKV, D, G>;
-    using Eng = std::conditional_t<TC, MmaEngine<T, D, G>, SimtEngine<TKV, T, D, G>>;
-    constexpr int kCtas = TC ? 2 : C::CTAS_PER_SM;
+    using Eng = typename EngineSelect<ENG, T, TKV, D, G>::type;
+    using C = SmemLayout<Eng::SCRATCH_PER_WARP, D, G>;
+    constexpr int kCtas = Eng::CTAS_PER_SM;
     DecodeParams p = p0;
     int dev = 0;
     if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
@@ -1168,7 +1260,7 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     if (stages < kConsumerWarps) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for the stage ring");
     p.stages = stages;
     const size_t smem = (size_t)C::OFF_STAGES + 1024 + (size_t)stages * Eng::STAGE_BYTES;
-    auto kern = decode_kernel<T, D, G, TC, TKV>;
+    auto kern = decode_kernel<T, D, G, ENG, TKV>;
     static bool configured[64] = {false};
     if (dev < 64 && !configured[dev]) {
         if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin),
@@ -1198,9 +1290,9 @@ int choose_engine(const DecodeParams& p, int B, int Hkv, cudaStream_t st) {
                             p.pool_sp_bytes, p.pool_sh_bytes) &&
             encode_pool_map(&tm.v, p.v_pool, std::is_same<T, __nv_bfloat16>::value, D, p.num_pages, Hkv,
                             p.pool_sp_bytes, p.pool_sh_bytes))
-            return launch_decode<T, D, G, true>(p, tm, B, st);
+            return launch_decode<T, D, G, kEngMma>(p, tm, B, st);
     }
-    return launch_decode<T, D, G, false>(p, tm, B, st);
+    return launch_decode<T, D, G, kEngSimt>(p, tm, B, st);
 }
 
 template <typename T, int D>
@@ -1259,12 +1351,17 @@ extern "C" int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64
 
 namespace {
 
-// 8-bit pools: CUDA-core engine only (q stays 16-bit; see the note on the fp8 entry point)
+// 8-bit pools: multi-head attention (one query head per KV head) widens on the fly in the CUDA-core
+// engine; grouped queries widen each page to fp16 tiles and use the tensor cores.
 template <typename T>
 int dispatch_fp8(int D, int G, const DecodeParams& p, int B, cudaStream_t st) {
     TensorMaps tm{};
     using F8 = __nv_fp8_e4m3;
-#define IVAB_FP8_CASE(DD, GG) if (D == DD && G == GG) return launch_decode<T, DD, GG, false, F8>(p, tm, B, st);
+    const bool simt = G < tc_min_group() || !(p.scale_log2 > 0.f);
+#define IVAB_FP8_CASE(DD, GG)                                                                   \
+    if (D == DD && G == GG)                                                                     \
+        return simt ? launch_decode<T, DD, GG, kEngSimt, F8>(p, tm, B, st)                      \
+                    : launch_decode<T, DD, GG, kEngMmaFp8, F8>(p, tm, B, st);
     IVAB_FP8_CASE(64, 1) IVAB_FP8_CASE(64, 2) IVAB_FP8_CASE(64, 4) IVAB_FP8_CASE(64, 8)
     IVAB_FP8_CASE(128, 1) IVAB_FP8_CASE(128, 2) IVAB_FP8_CASE(128, 4) IVAB_FP8_CASE(128, 8)
 #undef IVAB_FP8_CASE
