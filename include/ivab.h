@@ -173,10 +173,11 @@ int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h
  *   K = k_scale * stored, V = v_scale * stored; q, out in `dtype` (IVAB_F16 or IVAB_BF16).
  * Pool strides are in 1-byte elements; head_dim 64 or 128.  The stored values are widened
  * exactly and all arithmetic is fp32, so results equal attention over the dequantised pools to
- * the tolerance of the 16-bit path.  Every group size runs on the CUDA-core engine: per byte of
- * K/V it executes 2.5x the instructions of the bf16 path, so it is issue-bound rather than
- * HBM-bound and gains about 1.3-1.5x in tokens/s for multi-head attention, less for grouped
- * queries.  No counterpart in the reference (fp8 KV is only named in configs/quant_infer.yaml:52).
+ * the tolerance of the 16-bit path.  Multi-head attention widens on the fly in the CUDA-core engine
+ * (issue-bound; about 1.5x the tokens/s of 16-bit storage); grouped queries widen each page to fp16
+ * tiles in shared memory and use the tensor cores (about 0.8-0.9x the tokens/s of 16-bit storage, at
+ * half the memory).  bf16 queries are converted to fp16 (saturating) on that path.
+ * No counterpart in the reference (fp8 KV is only named in configs/quant_infer.yaml:52).
  */
 int ivab_paged_decode_attn_fp8(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                                const void* k_pool, const void* v_pool,
