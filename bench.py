@@ -153,20 +153,44 @@ def build_workload(name, device, rank, world, args):
     raise SystemExit(f"unknown workload {name}")
 
 
-def describe(name, wl, world):
+WORKLOAD_TEXT = {"c2": "1xB200 MHA decode step (append 1 token/seq + paged attention)",
+                 "c3": "1xB200 GQA decode step, ragged log-normal contexts",
+                 "c4": "append/gather stress (512-token fp16 chunks, then gather all)",
+                 "c5a": "request-sharded GQA decode, 1024 seq x 8192 split over ranks",
+                 "c5b": "one 131072-token sequence, KV heads split over ranks + all-gather"}
+
+
+def workload_shape(name, args, rank, world):
+    """Lengths and head layout of a workload without building its pools (the reference arm reports
+    the GPU arm's config although it only times a sample of it)."""
+    if name == "c2":
+        ctx, hq, hkv, dt, new, free = torch.full((args.batch or 64,), args.context or 4096), 32, 32, "bfloat16", 1, 0.0
+    elif name == "c3":
+        ctx, hq, hkv, dt, new, free = workloads.ragged_lengths(args.batch or 128, rank), 32, 8, "bfloat16", 1, 0.10
+    elif name == "c4":
+        g = torch.Generator().manual_seed(rank)
+        ctx, hq, hkv, dt, new, free = torch.randint(0, 8193, (args.batch or 256,), generator=g), 32, 32, "float16", 512, 0.0
+    elif name == "c5a":
+        ctx, hq, hkv, dt, new, free = torch.full(((args.batch or 1024) // world,), args.context or 8192), 32, 8, "bfloat16", 1, 0.0
+    else:
+        ctx, hq, hkv, dt, new, free = torch.full((1,), args.context or 131072), 32, 8, "bfloat16", 1, 0.0
+    pages = int(((ctx + new + 15) // 16).sum())
+    return {"ctx": ctx, "hq": hq, "hkv": hkv, "dtype": dt, "pool_pages": int(-(-pages * (1.0 + free) // 1))}
+
+
+def describe(name, args, rank, world, kv_fp8=False):
+    sh = workload_shape(name, args, rank, world)
+    ctx, elt = sh["ctx"], (1 if kv_fp8 else 2)
+    kv_bytes = 2 * int((ctx + 1).sum()) * sh["hkv"] * 128 * elt
     return {
-        "workload": {"c2": "1xB200 MHA decode step (append 1 token/seq + paged attention)",
-                     "c3": "1xB200 GQA decode step, ragged log-normal contexts",
-                     "c4": "append/gather stress (512-token fp16 chunks, then gather all)",
-                     "c5a": "request-sharded GQA decode, 1024 seq x 8192 split over ranks",
-                     "c5b": "one 131072-token sequence, KV heads split over ranks + all-gather"}[name],
-        "name": name, "batch_per_gpu": wl.batch, "q_heads": wl.n_q_heads, "kv_heads": wl.n_kv_heads,
-        "head_dim": wl.head_dim, "page_size": wl.page_size, "kv_dtype": str(wl.dtype).replace("torch.", ""),
-        "context_min": int(wl.ctx_len.min()), "context_max": int(wl.ctx_len.max()),
-        "context_sum": int(wl.ctx_len.sum()), "pool_pages": wl.num_pages,
+        "workload": WORKLOAD_TEXT[name], "name": name, "batch_per_gpu": int(ctx.numel()), "q_heads": sh["hq"],
+        "kv_heads": sh["hkv"], "head_dim": 128, "page_size": 16,
+        "kv_dtype": "float8_e4m3fn" if kv_fp8 else sh["dtype"],
+        "context_min": int(ctx.min()), "context_max": int(ctx.max()), "context_sum": int(ctx.sum()),
+        "pool_pages": sh["pool_pages"],
         "parallelism": "1 GPU" if world == 1 else f"{world} GPUs, one process each",
         "l2": "K/V read per step exceed the 126 MB L2 and are not reused between steps"
-              if attention_bytes(wl, wl.ctx_len + 1) > 4 * 126e6 else "L2 flushed between timed steps",
+              if kv_bytes > 4 * 126e6 else "L2 flushed between timed steps",
     }
 
 
@@ -391,7 +415,7 @@ def run_gpu(args):
         "scaling": "strong" if name in ("c5a", "c5b") else "weak", "vs_baseline": None,
         "dtype": {"torch.bfloat16": "bf16", "torch.float16": "f16", "torch.float32": "f32"}[str(wl.dtype)],
         "data": "synthetic (seeded N(0,1) K/V/q, shuffled page pool)",
-        "config": describe(name, wl, world),
+        "config": describe(name, args, rank, world, args.kv_fp8),
         "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                      "algorithmic_bytes": dom_bytes, "ms": dom_ms,
@@ -493,7 +517,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": {"torch.bfloat16": "bf16", "torch.float16": "f16", "torch.float32": "f32"}[str(wl.dtype)],
-        "data": "synthetic (seeded N(0,1) K/V/q, shuffled page pool)", "config": describe(name if name != "c4" else "c2", wl, 1),
+        "data": "synthetic (seeded N(0,1) K/V/q, shuffled page pool)", "config": describe(name, args, 0, 1),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "decode tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -28,12 +28,8 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session")
 def built_library():
     """Path of libivab.so, (re)built if its sources are newer."""
-    spec_dir = os.path.join(ROOT, "iva1.0_b200")
-    sys.path.insert(0, spec_dir)
-    try:
-        from iva_b200.build import build_library
-    finally:
-        sys.path.remove(spec_dir)
+    from iva_b200.build import build_library
+
     return build_library()
 
 
