@@ -46,6 +46,14 @@ __device__ __forceinline__ void mbar_inval(uint32_t bar) {
     asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may start while its predecessor in the stream still runs; grid_dependency_wait() then
+// blocks until the predecessor has completed and its writes are visible (a no-op for a kernel
+// launched the ordinary way).  grid_launch_dependents() lets the successor's CTAs be scheduled as
+// soon as every CTA of this grid has called it or exited.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_mbar_init() {
     // Makes the initialised barriers visible to the async (TMA) proxy.
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

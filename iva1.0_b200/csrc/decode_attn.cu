@@ -181,6 +181,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     __shared__ int s_pages[kSortMax];
     __shared__ int s_ragged, s_split;
     const int tid = threadIdx.x;
+    // the attention kernel may be scheduled now: its set-up does not depend on the plan, and it
+    // waits for this grid to complete before it reads the workspace
+    grid_launch_dependents();
     if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; }
     __syncthreads();
 
@@ -841,6 +844,11 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     }
     __syncthreads();   // the only CTA-wide barrier: before any warp can have unwound
 
+    // Everything above overlapped the plan kernel; the work list is read from here on.  The merge
+    // kernel may be scheduled as soon as CTAs of this grid retire (it waits for the whole grid).
+    grid_dependency_wait();
+    grid_launch_dependents();
+
     const int num_chunks = p.ws.header[kHdrNumChunks];
     const int total_items = p.ws.header[kHdrTotalItems];
     int* counter = p.ws.header + kHdrCounter;
@@ -1123,6 +1131,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int Hq, int G, Workspace ws, T* out, int64_t out_sb,
                                                                  int64_t out_sh, float* lse) {
     constexpr int VPL = D / 32;   // dims per lane
+    grid_dependency_wait();   // the attention kernel's partial results
     const int num_chunks = ws.header[kHdrNumChunks];
     const int n_split = ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1234,6 +1243,15 @@ int tc_min_group() {
     return v;
 }
 
+// Programmatic dependent launch of the attention and merge kernels; IVAB_PDL=0 turns it off.
+bool use_dependent_launch() {
+    static bool v = [] {
+        const char* e = std::getenv("IVAB_PDL");
+        return !(e && std::atoi(e) == 0);
+    }();
+    return v;
+}
+
 template <typename T, int D, int G, int ENG, typename TKV = T>
 int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStream_t st) {
     using Eng = typename EngineSelect<ENG, T, TKV, D, G>::type;
@@ -1268,17 +1286,25 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
         configured[dev] = true;
     }
     const int grid = sm_count() * kCtas;
-    kern<<<grid, kThreads, smem, st>>>(p, tm);
+    // Both launches below are programmatic dependents of the kernel before them (plan -> attention
+    // -> merge): the launch latency and set-up of each overlap the tail of its predecessor.
+    cudaLaunchAttribute pdl{};
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.attrs = &pdl; cfg.numAttrs = use_dependent_launch() ? 1 : 0;
+    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, kern, p, tm), "decode_kernel launch")) return rc;
     g_launches++;
-    if (int rc = check_cuda(cudaGetLastError(), "decode_kernel launch")) return rc;
 
     // a fixed, small grid walks the list of split (sequence, head) pairs the plan kernel left behind
     const long long units = (long long)B * p.Hq;
     const int merge_grid = (int)(units < (long long)sm_count() * 32 ? units : (long long)sm_count() * 32);
-    merge_kernel<T, D><<<merge_grid, kMergeWarps * 32, 0, st>>>(p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb, p.out_sh,
-                                                              p.lse);
+    cfg.gridDim = dim3(merge_grid); cfg.blockDim = dim3(kMergeWarps * 32); cfg.dynamicSmemBytes = 0;
+    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb,
+                                               p.out_sh, p.lse), "merge_kernel launch")) return rc;
     g_launches++;
-    return check_cuda(cudaGetLastError(), "merge_kernel launch");
+    return IVAB_OK;
 }
 
 template <typename T, int D, int G>
