@@ -41,3 +41,12 @@ def test_engine_threshold(min_group):
     res = subprocess.run([sys.executable, "-c", CHILD.format(root=ROOT)], env=env, capture_output=True, text=True,
                          timeout=600)
     assert res.returncode == 0 and "engines ok" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
+
+
+def test_plain_stream_order_launches():
+    """IVAB_PDL=0: the attention and merge kernels are launched in plain stream order instead of
+    as programmatic dependents; the same cases pass."""
+    env = dict(os.environ, IVAB_PDL="0")
+    res = subprocess.run([sys.executable, "-c", CHILD.format(root=ROOT)], env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert res.returncode == 0 and "engines ok" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
