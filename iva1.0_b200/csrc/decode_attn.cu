@@ -28,8 +28,9 @@
 //                                 moves on; the warp that arrives last combines the four states (in
 //                                 warp order) and writes the final output (one-chunk sequences) or
 //                                 an fp32 partial (o, m, l).
-//   3. merge_kernel               CTAs of 8 warps walk the list of split (sequence, query head)
-//                                 pairs: logsumexp-merge of their partials.
+//   3. merge_kernel               logsumexp-merge of the partials of split sequences: one warp per
+//                                 (sequence, query head) for up to 32 chunks, one CTA per
+//                                 (sequence, query head, 32-dim slice) beyond that.
 //
 // All waits are bounded (see mbar_wait_bounded); a wait that expires raises a CTA-wide abort
 // flag, the status word gets IVAB_STATUS_WAIT_TIMEOUT and every warp unwinds.  Intra-CTA
@@ -65,6 +66,13 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 #define PROF_DECL long long prof_t0 = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #define PROF_MARK(i) { const long long prof_t1 = clock64(); prof_acc[i] += prof_t1 - prof_t0; prof_t0 = prof_t1; }
 #define PROF_FLUSH(base) if (lane == 0) { for (int i = 0; i < 8; ++i) atomicAdd(reinterpret_cast<unsigned long long*>(p.ws.header + 16) + (base) + i, (unsigned long long)prof_acc[i]); }
+// Timeline stamps (%globaltimer, ns) in header words 48..63: [0] plan start, [1] plan end, [2] first
+// attention CTA started, [3] first CTA past the dependency wait, [4] first page consumed, [5] last
+// consumer warp done, [6] first merge CTA past its wait, [7] last merge CTA done.
+#define PROF_STAMP_PTR(hdr) (reinterpret_cast<unsigned long long*>((hdr) + 48))
+#define PROF_STAMP_SET(hdr, i) { PROF_STAMP_PTR(hdr)[i] = globaltimer_ns(); }
+#define PROF_STAMP_MIN(hdr, i, t) atomicMin(PROF_STAMP_PTR(hdr) + (i), (unsigned long long)(t));
+#define PROF_STAMP_MAX(hdr, i, t) atomicMax(PROF_STAMP_PTR(hdr) + (i), (unsigned long long)(t));
 #else
 #define PROF_DECL
 #define PROF_MARK(i)
@@ -72,7 +80,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 #endif
 
 // header words at the start of the workspace
-enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrNumSplit = 5,
+enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrNumSplit = 5, kHdrNumBig = 6,
        kHdrWords = 64 };
 
 struct ChunkDesc {
@@ -86,7 +94,8 @@ struct Workspace {
     int* order;           // [B]   sequence id at each position of the processing order
     int* seq_first;       // [B]   first chunk index of each sequence
     int* seq_count;       // [B]   number of chunks of each sequence
-    int* split_list;      // [B]   ids of the sequences that were cut into more than one chunk
+    int* split_list;      // [B]   ids of the sequences that were cut into more than one chunk: those with at most
+                          //       kMergeWarpMax chunks from the front, those with more from the back
     ChunkDesc* chunks;    // [cap]
     float* part_ml;       // [cap*Hkv][G][2]   (running max in log2 units, sum)
     float* part_o;        // [cap*Hkv][G][D]
@@ -144,6 +153,7 @@ size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D
 
 constexpr int kPlanThreads = 1024;
 constexpr int kSortMax = 1024;   // largest batch whose sequences are ordered longest-first (rank sort, O(B) per thread)
+constexpr int kMergeWarpMax = 32;    // a sequence of at most this many chunks is merged by a single warp per query head
 
 __device__ int block_inclusive_scan(int v, int* warp_sums, int* total) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -179,12 +189,18 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     __shared__ long long s_total_pages;
     __shared__ int s_bad;
     __shared__ int s_pages[kSortMax];
-    __shared__ int s_ragged, s_split;
+    __shared__ int s_ragged, s_split, s_big;
     const int tid = threadIdx.x;
     // the attention kernel may be scheduled now: its set-up does not depend on the plan, and it
     // waits for this grid to complete before it reads the workspace
     grid_launch_dependents();
-    if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; }
+#ifdef IVAB_PROFILE
+    if (tid == 0) {
+        PROF_STAMP_SET(ws.header, 0)
+        for (int i = 2; i < 8; ++i) PROF_STAMP_PTR(ws.header)[i] = (i == 5 || i == 7) ? 0ull : ~0ull;
+    }
+#endif
+    if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; s_big = 0; }
     __syncthreads();
 
     // Sequence s attends the keys [0, sink) and [begin, L): L is ctx_len clamped to the block table,
@@ -277,7 +293,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
             ws.pos_prefix[pos] = running + incl - n;
             ws.seq_first[s] = running + incl - n;
             ws.seq_count[s] = n;
-            if (n > 1) ws.split_list[atomicAdd(&s_split, 1)] = s;   // order is irrelevant: one CTA per entry
+            // order within either end of the list is irrelevant: every entry is merged on its own
+            if (n > kMergeWarpMax) ws.split_list[B - 1 - atomicAdd(&s_big, 1)] = s;
+            else if (n > 1) ws.split_list[atomicAdd(&s_split, 1)] = s;
         }
         running += tile_total;
     }
@@ -292,6 +310,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         ws.header[kHdrStatus] = (s_bad ? kStatusBadCtxLen : 0) | (overflow ? kStatusOverflow : 0);
         ws.header[kHdrTotalItems] = num_chunks * Hkv;
         ws.header[kHdrNumSplit] = overflow ? 0 : s_split;
+        ws.header[kHdrNumBig] = overflow ? 0 : s_big;
 #ifdef IVAB_PROFILE
         for (int i = 16; i < 48; ++i) ws.header[i] = 0;
 #endif
@@ -323,6 +342,10 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         d.pad2 = sink_pages;
         ws.chunks[ci] = d;
     }
+#ifdef IVAB_PROFILE
+    __syncthreads();
+    if (tid == 0) PROF_STAMP_SET(ws.header, 1)
+#endif
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -822,6 +845,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
+#ifdef IVAB_PROFILE
+    const uint64_t prof_cta_start = globaltimer_ns();
+#endif
 
     const uint32_t bars = smem_u32(smem + C::OFF_BARS);
     auto bar_full = [&](int s) { return bars + 8u * s; };
@@ -848,6 +874,12 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     // kernel may be scheduled as soon as CTAs of this grid retire (it waits for the whole grid).
     grid_dependency_wait();
     grid_launch_dependents();
+#ifdef IVAB_PROFILE
+    if (threadIdx.x == 0) {
+        PROF_STAMP_MIN(p.ws.header, 2, prof_cta_start)
+        PROF_STAMP_MIN(p.ws.header, 3, globaltimer_ns())
+    }
+#endif
 
     const int num_chunks = p.ws.header[kHdrNumChunks];
     const int total_items = p.ws.header[kHdrTotalItems];
@@ -1049,6 +1081,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             const int stage = (taken % spw) * kConsumerWarps + warp;
             if (!mbar_wait_bounded(bar_full(stage), (taken / spw) & 1, abort_flag, limit)) { ok = false; break; }
             PROF_MARK(2)   // wait for page data
+#ifdef IVAB_PROFILE
+            if (taken == 0 && lane == 0) PROF_STAMP_MIN(p.ws.header, 4, globaltimer_ns())
+#endif
             // Token t of this page is key 16*pg + t.  It counts if it lies below L and outside the
             // hole [sink, begin) between the sink keys and the window; only the last page of the
             // sequence, the last sink page and the first window page are cut by these bounds.
@@ -1115,6 +1150,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         ++consumed;
     }
     PROF_FLUSH(8)
+#ifdef IVAB_PROFILE
+    if (lane == 0) PROF_STAMP_MAX(p.ws.header, 5, globaltimer_ns())
+#endif
     if (*abort_flag && threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
 }
 
@@ -1124,71 +1162,152 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
 
 constexpr int kMergeWarps = 8;
 
-// One CTA per (sequence, query head) that was split into several chunks.  Warp w folds chunks
-// w, w+8, ... (independent loads, unrolled), each lane owning D/32 consecutive dims; the eight warp
-// sums are then added in a fixed order, so the result does not depend on scheduling.
+// VPL consecutive floats from a pointer aligned to VPL * 4 bytes (at most 16)
+template <int VPL>
+__device__ __forceinline__ void load_row(const float* src, float (&v)[VPL]) {
+    if constexpr (VPL % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < VPL / 4; ++i) {
+            const float4 t = reinterpret_cast<const float4*>(src)[i];
+            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+    } else if constexpr (VPL == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(src);
+        v[0] = t.x; v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) v[i] = src[i];
+    }
+}
+
+// Folds the partial results of the sequences that were split into chunks.  Two passes over the
+// list the plan kernel left behind, both in a fixed summation order, so the result does not depend
+// on scheduling:
+//   A. a sequence of at most kMergeWarpMax chunks: one warp per (sequence, query head); lane j
+//      holds the (max, sum) pair of chunk j, every lane owns D/32 consecutive dims.  No shared
+//      memory, no barrier -- the common case (a few chunks per sequence) costs one round of loads.
+//   B. a sequence of more chunks (one very long context on an otherwise idle GPU): one CTA per
+//      (sequence, query head, 32-dim slice); warp w folds chunks w, w+8, ... against its own running
+//      maximum, the eight warp results are then combined through shared memory.
 template <typename T, int D>
-__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int Hq, int G, Workspace ws, T* out, int64_t out_sb,
+__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int B, int Hq, int G, Workspace ws, T* out, int64_t out_sb,
                                                                  int64_t out_sh, float* lse) {
-    constexpr int VPL = D / 32;   // dims per lane
+    constexpr int VPL = D / 32;   // dims per lane in pass A, 32-dim slices in pass B
+    constexpr float kLn2 = 0.6931471805599453f;
     grid_dependency_wait();   // the attention kernel's partial results
+#ifdef IVAB_PROFILE
+    if (threadIdx.x == 0) PROF_STAMP_MIN(ws.header, 6, globaltimer_ns())
+#endif
     const int num_chunks = ws.header[kHdrNumChunks];
-    const int n_split = ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
+    const int n_small = ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
+    const int n_big = ws.header[kHdrNumBig];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- pass A
+    for (int unit = blockIdx.x * kMergeWarps + warp; unit < n_small * Hq; unit += gridDim.x * kMergeWarps) {
+        const int s = ws.split_list[unit / Hq], hq = unit % Hq;
+        const int first = ws.seq_first[s];
+        const int n = ws.seq_count[s];
+        const int h = hq / G, g = hq % G;
+        const size_t item0 = (size_t)h * num_chunks + first;
+        const float* ml = ws.part_ml + (item0 * G + g) * 2;               // chunk j at ml + j*G*2
+        const float* po = ws.part_o + (item0 * G + g) * D + lane * VPL;   // chunk j at po + j*G*D
+
+        float mj = -INFINITY, lj = 0.f;
+        if (lane < n) {
+            const float2 v = *reinterpret_cast<const float2*>(ml + (size_t)lane * G * 2);
+            mj = v.x; lj = v.y;
+        }
+        const float M = warp_max_f32(mj);
+        const float f = (mj == -INFINITY) ? 0.f : fast_exp2(mj - M);
+        float L = lj * f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+
+        float acc[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+        int j = 0;
+        for (; j + 4 <= n; j += 4) {   // four rows in flight
+            float r[4][VPL];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) load_row<VPL>(po + (size_t)(j + u) * G * D, r[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float fu = __shfl_sync(0xffffffffu, f, j + u);
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) acc[i] = fmaf(r[u][i], fu, acc[i]);
+            }
+        }
+        for (; j < n; ++j) {
+            float r[VPL];
+            load_row<VPL>(po + (size_t)j * G * D, r);
+            const float fj = __shfl_sync(0xffffffffu, f, j);
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) acc[i] = fmaf(r[i], fj, acc[i]);
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        T* dst = out + (int64_t)s * out_sb + (int64_t)hq * out_sh + lane * VPL;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) Elt<T>::store(dst + i, acc[i] * inv);
+        if (lane == 0 && lse != nullptr) lse[(int64_t)s * Hq + hq] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+    }
+
+    // ---- pass B
+    if (n_big == 0) {
+#ifdef IVAB_PROFILE
+        if (threadIdx.x == 0) PROF_STAMP_MAX(ws.header, 7, globaltimer_ns())
+#endif
+        return;
+    }
     __shared__ float sh_m[kMergeWarps];
     __shared__ float sh_l[kMergeWarps];
-    __shared__ float sh_o[kMergeWarps][D];
-    for (int unit = blockIdx.x; unit < n_split * Hq; unit += gridDim.x) {
-    const int s = ws.split_list[unit / Hq], hq = unit % Hq;
-    const int first = ws.seq_first[s];
-    const int n = ws.seq_count[s];
-    const int h = hq / G, g = hq % G;
-    const size_t item0 = (size_t)h * num_chunks + first;
-    const float* ml = ws.part_ml + (item0 * G + g) * 2;          // chunk j at ml + j*G*2
-    const float* po = ws.part_o + (item0 * G + g) * D + lane * VPL;   // chunk j at po + j*G*D
+    __shared__ float sh_o[kMergeWarps][32];
+    for (int c = blockIdx.x; c < n_big * Hq * VPL; c += gridDim.x) {
+        const int unit = c / VPL, slice = c % VPL;
+        const int s = ws.split_list[B - 1 - unit / Hq], hq = unit % Hq;
+        const int first = ws.seq_first[s];
+        const int n = ws.seq_count[s];
+        const int h = hq / G, g = hq % G;
+        const size_t item0 = (size_t)h * num_chunks + first;
+        const float* ml = ws.part_ml + (item0 * G + g) * 2;
+        const float* po = ws.part_o + (item0 * G + g) * D + slice * 32 + lane;
 
-    float M = -INFINITY;
-    for (int j = threadIdx.x; j < n; j += kMergeWarps * 32) M = fmaxf(M, ml[(size_t)j * G * 2]);
-    M = warp_max_f32(M);
-    if (lane == 0) sh_m[warp] = M;
-    __syncthreads();
+        float mw = -INFINITY;   // maximum over this warp's chunks
+        for (int j = warp + kMergeWarps * lane; j < n; j += kMergeWarps * 32) mw = fmaxf(mw, ml[(size_t)j * G * 2]);
+        mw = warp_max_f32(mw);
+        float lw = 0.f, acc = 0.f;
+#pragma unroll 8
+        for (int j = warp; j < n; j += kMergeWarps) {
+            const float2 v = *reinterpret_cast<const float2*>(ml + (size_t)j * G * 2);
+            const float fj = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - mw);
+            lw = fmaf(v.y, fj, lw);
+            acc = fmaf(po[(size_t)j * G * D], fj, acc);
+        }
+        sh_o[warp][lane] = acc;
+        if (lane == 0) { sh_m[warp] = mw; sh_l[warp] = lw; }
+        __syncthreads();
+        if (warp == 0) {
+            float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kMergeWarps; ++w) M = fmaxf(M, sh_m[w]);
-
-    float Lsum = 0.f;
-    float acc[VPL];
+            for (int w = 0; w < kMergeWarps; ++w) M = fmaxf(M, sh_m[w]);
+            float L = 0.f, O = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
-#pragma unroll 4
-    for (int j = warp; j < n; j += kMergeWarps) {
-        const float mj = ml[(size_t)j * G * 2];
-        const float lj = ml[(size_t)j * G * 2 + 1];
-        const float f = (mj == -INFINITY) ? 0.f : fast_exp2(mj - M);
-        Lsum = fmaf(lj, f, Lsum);
-        const float* row = po + (size_t)j * G * D;
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) acc[i] = fmaf(row[i], f, acc[i]);
+            for (int w = 0; w < kMergeWarps; ++w) {
+                const float fw = (sh_m[w] == -INFINITY) ? 0.f : fast_exp2(sh_m[w] - M);
+                L = fmaf(sh_l[w], fw, L);
+                O = fmaf(sh_o[w][lane], fw, O);
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            Elt<T>::store(out + (int64_t)s * out_sb + (int64_t)hq * out_sh + slice * 32 + lane, O * inv);
+            if (slice == 0 && lane == 0 && lse != nullptr)
+                lse[(int64_t)s * Hq + hq] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+        }
+        __syncthreads();   // the shared scratch is reused by the next unit
     }
-#pragma unroll
-    for (int i = 0; i < VPL; ++i) sh_o[warp][lane * VPL + i] = acc[i];
-    if (lane == 0) sh_l[warp] = Lsum;
-    __syncthreads();
-
-    float L = 0.f;
-#pragma unroll
-    for (int w = 0; w < kMergeWarps; ++w) L += sh_l[w];
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int dd = threadIdx.x; dd < D; dd += kMergeWarps * 32) {
-        float O = 0.f;
-#pragma unroll
-        for (int w = 0; w < kMergeWarps; ++w) O += sh_o[w][dd];
-        Elt<T>::store(out + (int64_t)s * out_sb + (int64_t)hq * out_sh + dd, O * inv);
-    }
-    if (threadIdx.x == 0 && lse != nullptr)
-        lse[(int64_t)s * Hq + hq] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
-    __syncthreads();   // the shared scratch is reused by the next unit
-    }
-    (void)num_chunks;
+#ifdef IVAB_PROFILE
+    if (threadIdx.x == 0) PROF_STAMP_MAX(ws.header, 7, globaltimer_ns())
+#endif
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1297,11 +1416,11 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, kern, p, tm), "decode_kernel launch")) return rc;
     g_launches++;
 
-    // a fixed, small grid walks the list of split (sequence, head) pairs the plan kernel left behind
-    const long long units = (long long)B * p.Hq;
-    const int merge_grid = (int)(units < (long long)sm_count() * 32 ? units : (long long)sm_count() * 32);
+    // pass A needs a warp, pass B D/32 CTAs per split (sequence, head); how many there are is known only on the device
+    const long long units = (long long)B * p.Hq * (D / 32);
+    const int merge_grid = (int)(units < (long long)sm_count() * 4 ? units : (long long)sm_count() * 4);
     cfg.gridDim = dim3(merge_grid); cfg.blockDim = dim3(kMergeWarps * 32); cfg.dynamicSmemBytes = 0;
-    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb,
+    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, B, p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb,
                                                p.out_sh, p.lse), "merge_kernel launch")) return rc;
     g_launches++;
     return IVAB_OK;
