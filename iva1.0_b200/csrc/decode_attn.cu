@@ -198,6 +198,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     if (tid == 0) {
         PROF_STAMP_SET(ws.header, 0)
         for (int i = 2; i < 8; ++i) PROF_STAMP_PTR(ws.header)[i] = (i == 5 || i == 7) ? 0ull : ~0ull;
+        *reinterpret_cast<unsigned long long*>(ws.header + 8) = ~0ull;
     }
 #endif
     if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; s_big = 0; }
@@ -906,7 +907,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         // stream does not pause at item boundaries.
         auto fetch_id_async = [&]() {   // lane 0 holds the result; broadcast it only when it is needed
             int v = 0;
-            if (lane == 0) v = atomicAdd(counter, 1);
+            if (lane == 0) v = (int)gridDim.x + atomicAdd(counter, 1);
             return v;
         };
         auto fetch_id = [&]() { return __shfl_sync(0xffffffffu, fetch_id_async(), 0); };
@@ -933,7 +934,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         };
         PROF_DECL
         const uint64_t stream_policy = l2_policy_evict_first();   // K/V pages are read once
-        int id0 = fetch_id(), id1 = fetch_id(), id2 = fetch_id();
+        // the first item of a CTA is its own index (no round trip to the work counter before the
+        // first page can be requested); the counter hands out the items from gridDim.x on
+        int id0 = (int)blockIdx.x, id1 = fetch_id(), id2 = fetch_id();
         int h0, h1;
         ChunkDesc d0 = load_desc(id0, &h0);
         ChunkDesc d1 = load_desc(id1, &h1);
@@ -1151,7 +1154,10 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     }
     PROF_FLUSH(8)
 #ifdef IVAB_PROFILE
-    if (lane == 0) PROF_STAMP_MAX(p.ws.header, 5, globaltimer_ns())
+    if (lane == 0) {
+        PROF_STAMP_MAX(p.ws.header, 5, globaltimer_ns())
+        atomicMin(reinterpret_cast<unsigned long long*>(p.ws.header + 8), (unsigned long long)globaltimer_ns());   // first warp done
+    }
 #endif
     if (*abort_flag && threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
 }
