@@ -188,6 +188,20 @@ __device__ __forceinline__ void mma_m16n8k16_top<__half>(float (&c)[2], uint32_t
         : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
+// Two e4m3 bytes (low byte first) to two fp16 values in one register; exact.
+__device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint16_t v) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+    return r;
+}
+
+// Bytes of {a, b} picked by the four selector nibbles (0..3 = bytes of a, 4..7 = bytes of b).
+__device__ __forceinline__ uint32_t byte_perm(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
 // Full tile: rows 0..7 take a0/a2, rows 8..15 take a1/a3; all four accumulators are live.
 template <typename T>
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,

@@ -402,7 +402,7 @@ struct SmemLayout {
     static constexpr int OFF_STAGES = (OFF_SCRATCH + kConsumerWarps * SCRATCH + 1023) / 1024 * 1024;  // swizzled tiles need 1 KB alignment
 };
 
-enum { kEngSimt = 0, kEngMma = 1, kEngMmaFp8 = 2 };
+enum { kEngSimt = 0, kEngMma = 1, kEngMmaFp8 = 2, kEngMmaFp8Reg = 3 };
 
 // Sum NV per-lane values across the LPR lanes of a row group.  While more than one value is
 // left, each step trades half of them with the partner lane (so the number of shuffles halves
@@ -608,6 +608,7 @@ struct MmaCore {
     using T = TT;
     static_assert(sizeof(T) == 2 && D % 64 == 0 && G >= 1 && G <= 8, "tensor-core engine: 16-bit K/V, D % 64 == 0, G <= 8");
     static constexpr int TILES = D / 64;               // 64-element (128-byte) column tiles per row
+    static constexpr int TILE_COLS = 64;               // elements per tile row (the TMA box's inner extent)
     static constexpr int TILE_BYTES = kPage * 128;     // 16 rows x 128 B, swizzled in 16-byte units
     static constexpr int PAGE_BYTES = TILES * TILE_BYTES;
     static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
@@ -826,6 +827,176 @@ struct MmaFp8Engine : MmaCore<__half, TQ, D, G> {
     }
 };
 
+// 8-bit (e4m3) pools with grouped queries, head_dim 128: the MMA operands are built in registers
+// straight from the stored bytes -- no widened copy of the page in shared memory.  Pages arrive as
+// one swizzled 16 x 128-byte tile each for K and V (tiled TMA, 128-byte swizzle).  Both products may
+// number their summation index and their output columns freely as long as both operands agree, and
+// the numbering is chosen so that every lane reads whole 16-byte chunks:
+//   * Q K^T: lane (g = lane/4, c = lane%4) holds bytes 32c..32c+31 of key row g; byte pair
+//     (4s, 4s+1) is B-fragment register 0 and pair (4s+2, 4s+3) register 1 of k-step s, and the
+//     query fragments are loaded in the same numbering (32 consecutive elements per lane).
+//   * P^T V: the lane reads chunk g (dims 16g..16g+15) of the four value rows 2c, 2c+1, 2c+8, 2c+9;
+//     byte j of those rows is the B fragment of output block j, so block j, column n is dim 16n + j
+//     and the lane ends up with the 32 consecutive dims 32c..32c+31 of head g.
+// e4m3 -> fp16 is exact (one cvt per pair); the weights are carried as fp16 value + correction in
+// rows 0..7 / 8..15 of the A tile like in the 16-bit engine.
+template <typename TQ, int D, int G>
+struct MmaFp8RegEngine {
+    static_assert(D == 128, "one 128-byte swizzled tile per page row");
+    static_assert(G >= 1 && G <= 8, "query heads of one kv head fill rows 0..7 of the A tile");
+    using TT = __half;
+    static constexpr bool kTiled = true;
+    static constexpr int TILES = 1;
+    static constexpr int TILE_COLS = 128;
+    static constexpr int TILE_BYTES = kPage * 128;
+    static constexpr int PAGE_BYTES = TILE_BYTES;
+    static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+    static constexpr int SCRATCH_PER_WARP = 0;
+    static constexpr int CTAS_PER_SM = 2;
+    static constexpr int KSTEPS = D / 16;
+    static constexpr int NBLK = D / 8;
+
+    uint32_t qa[KSTEPS][2];
+    float o[NBLK][4];          // block j: [0],[1] dims 32c + j and 32c + 16 + j (weights), [2],[3] the corrections
+    float m_run, l_run;
+
+    __device__ __forceinline__ void setup(int) {}
+
+    __device__ __forceinline__ static uint32_t to_half2(uint32_t raw) {
+        if constexpr (std::is_same<TQ, __half>::value) {
+            return raw;
+        } else {
+            const float2 f = unpack2<TQ>(raw);
+            return pack2<TT>(fminf(fmaxf(f.x, -65504.f), 65504.f), fminf(fmaxf(f.y, -65504.f), 65504.f));
+        }
+    }
+
+    __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
+        const int g = lane >> 2, c = lane & 3;
+        if (g < G) {
+            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh + 32 * c;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {   // 4 x 16 bytes = elements 32c + 8v .. 32c + 8v + 7 = k-steps 2v, 2v+1
+                const uint4 u = __ldg(reinterpret_cast<const uint4*>(qrow) + v);
+                qa[2 * v][0] = to_half2(u.x); qa[2 * v][1] = to_half2(u.y);
+                qa[2 * v + 1][0] = to_half2(u.z); qa[2 * v + 1][1] = to_half2(u.w);
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < KSTEPS; ++s) qa[s][0] = qa[s][1] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < NBLK; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+        m_run = -INFINITY;
+        l_run = 0.f;
+    }
+
+    __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int hole_lo,
+                                         int hole_hi, int lane, unsigned char*) {
+        const int g = lane >> 2, c = lane & 3;
+        const bool partial = n_valid < kPage || hole_hi > hole_lo;
+        auto masked = [&](int tok) { return tok >= n_valid || (tok >= hole_lo && tok < hole_hi); };
+
+        // value rows first: their loads overlap the score computation
+        const unsigned char* vt = stage + PAGE_BYTES;
+        uint4 vr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = 2 * c + (i & 1) + (i >> 1) * 8;
+            vr[i] = *reinterpret_cast<const uint4*>(vt + row * 128 + ((g ^ (row & 7)) << 4));
+        }
+
+        // ---- S^T[head, token] = Q K^T
+        float s[2][2];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+            const unsigned char* rp = stage + (nb * 8 + g) * 128;   // key row nb*8 + g; its swizzle term is g
+            const uint4 u0 = *reinterpret_cast<const uint4*>(rp + (((2 * c) ^ g) << 4));
+            const uint4 u1 = *reinterpret_cast<const uint4*>(rp + (((2 * c + 1) ^ g) << 4));
+            const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            float se[2] = {0.f, 0.f}, so[2] = {0.f, 0.f};
+#pragma unroll
+            for (int sp = 0; sp < KSTEPS / 2; ++sp) {
+                mma_m16n8k16_top<TT>(se, qa[2 * sp][0], qa[2 * sp][1], cvt_e4m3x2_to_f16x2((uint16_t)(w[2 * sp] & 0xffffu)),
+                                     cvt_e4m3x2_to_f16x2((uint16_t)(w[2 * sp] >> 16)));
+                mma_m16n8k16_top<TT>(so, qa[2 * sp + 1][0], qa[2 * sp + 1][1],
+                                     cvt_e4m3x2_to_f16x2((uint16_t)(w[2 * sp + 1] & 0xffffu)),
+                                     cvt_e4m3x2_to_f16x2((uint16_t)(w[2 * sp + 1] >> 16)));
+            }
+            s[nb][0] = se[0] + so[0];
+            s[nb][1] = se[1] + so[1];
+        }
+        if (partial) {
+            if (masked(2 * c)) s[0][0] = -INFINITY;
+            if (masked(2 * c + 1)) s[0][1] = -INFINITY;
+            if (masked(8 + 2 * c)) s[1][0] = -INFINITY;
+            if (masked(9 + 2 * c)) s[1][1] = -INFINITY;
+            // rows that do not count may hold stale bytes (NaN included), and 0 * NaN is NaN in the MMA
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (masked(2 * c + (i & 1) + (i >> 1) * 8)) vr[i] = make_uint4(0, 0, 0, 0);
+        }
+        float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float sl2 = p.scale_log2;
+        if (__any_sync(0xffffffffu, m_new > m_run)) {
+            const float alpha = fast_exp2((m_run - m_new) * sl2);
+            l_run *= alpha;
+#pragma unroll
+            for (int j = 0; j < NBLK; ++j) { o[j][0] *= alpha; o[j][1] *= alpha; o[j][2] *= alpha; o[j][3] *= alpha; }
+            m_run = m_new;
+        }
+        const float msl = m_run * sl2;
+        const float p0 = fast_exp2(fmaf(s[0][0], sl2, -msl)), p1 = fast_exp2(fmaf(s[0][1], sl2, -msl));
+        const float p2 = fast_exp2(fmaf(s[1][0], sl2, -msl)), p3 = fast_exp2(fmaf(s[1][1], sl2, -msl));
+        l_run += (p0 + p1) + (p2 + p3);
+        const uint32_t pa0 = pack2<TT>(p0, p1), pa2 = pack2<TT>(p2, p3);
+        const float2 h01 = unpack2<TT>(pa0), h23 = unpack2<TT>(pa2);
+        const uint32_t pb0 = pack2<TT>(p0 - h01.x, p1 - h01.y), pb2 = pack2<TT>(p2 - h23.x, p3 - h23.y);
+
+        // ---- O[head, dim] += P^T V
+        const uint32_t x0[4] = {vr[0].x, vr[0].y, vr[0].z, vr[0].w}, x1[4] = {vr[1].x, vr[1].y, vr[1].z, vr[1].w};
+        const uint32_t y0[4] = {vr[2].x, vr[2].y, vr[2].z, vr[2].w}, y1[4] = {vr[3].x, vr[3].y, vr[3].z, vr[3].w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            // bytes (2c, 2c+1) and (2c+8, 2c+9) of dims 4w..4w+3, interleaved into fragment order
+            const uint32_t a01 = byte_perm(x0[w], x1[w], 0x5140u), a23 = byte_perm(x0[w], x1[w], 0x7362u);
+            const uint32_t b01 = byte_perm(y0[w], y1[w], 0x5140u), b23 = byte_perm(y0[w], y1[w], 0x7362u);
+            mma_m16n8k16<TT>(o[4 * w], pa0, pb0, pa2, pb2, cvt_e4m3x2_to_f16x2((uint16_t)(a01 & 0xffffu)),
+                             cvt_e4m3x2_to_f16x2((uint16_t)(b01 & 0xffffu)));
+            mma_m16n8k16<TT>(o[4 * w + 1], pa0, pb0, pa2, pb2, cvt_e4m3x2_to_f16x2((uint16_t)(a01 >> 16)),
+                             cvt_e4m3x2_to_f16x2((uint16_t)(b01 >> 16)));
+            mma_m16n8k16<TT>(o[4 * w + 2], pa0, pb0, pa2, pb2, cvt_e4m3x2_to_f16x2((uint16_t)(a23 & 0xffffu)),
+                             cvt_e4m3x2_to_f16x2((uint16_t)(b23 & 0xffffu)));
+            mma_m16n8k16<TT>(o[4 * w + 3], pa0, pb0, pa2, pb2, cvt_e4m3x2_to_f16x2((uint16_t)(a23 >> 16)),
+                             cvt_e4m3x2_to_f16x2((uint16_t)(b23 >> 16)));
+        }
+        __syncwarp();   // every lane has read the stage before lane 0 hands it back
+    }
+
+    __device__ __forceinline__ void publish(const DecodeParams& p, float* my_ml, float* my_o, int lane) {
+        const int g = lane >> 2, c = lane & 3;
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        if (g < G) {
+            float* dst = my_o + g * D + 32 * c;
+#pragma unroll
+            for (int j = 0; j < NBLK; j += 4) {
+                *reinterpret_cast<float4*>(dst + j) = make_float4(o[j][0] + o[j][2], o[j + 1][0] + o[j + 1][2],
+                                                                  o[j + 2][0] + o[j + 2][2], o[j + 3][0] + o[j + 3][2]);
+                *reinterpret_cast<float4*>(dst + 16 + j) = make_float4(o[j][1] + o[j][3], o[j + 1][1] + o[j + 1][3],
+                                                                       o[j + 2][1] + o[j + 2][3], o[j + 3][1] + o[j + 3][3]);
+            }
+            if (c == 0) {
+                my_ml[g * 2] = (m_run == -INFINITY) ? -INFINITY : m_run * p.scale_log2;
+                my_ml[g * 2 + 1] = l_run;
+            }
+        }
+    }
+};
+
 struct alignas(64) TensorMaps {
     CUtensorMap k, v;   // 4-D maps of the K and V pools: (dim, token in page, page, head)
 };
@@ -835,6 +1006,7 @@ template <int ENG, typename T, typename TKV, int D, int G> struct EngineSelect;
 template <typename T, typename TKV, int D, int G> struct EngineSelect<kEngSimt, T, TKV, D, G> { using type = SimtEngine<TKV, T, D, G>; };
 template <typename T, typename TKV, int D, int G> struct EngineSelect<kEngMma, T, TKV, D, G> { using type = MmaEngine<T, D, G>; };
 template <typename T, typename TKV, int D, int G> struct EngineSelect<kEngMmaFp8, T, TKV, D, G> { using type = MmaFp8Engine<T, D, G>; };
+template <typename T, typename TKV, int D, int G> struct EngineSelect<kEngMmaFp8Reg, T, TKV, D, G> { using type = MmaFp8RegEngine<T, D, G>; };
 
 template <typename T, int D, int G, int ENG, typename TKV = T>
 __global__ void __launch_bounds__(kThreads, EngineSelect<ENG, T, TKV, D, G>::type::CTAS_PER_SM)
@@ -1005,9 +1177,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                             if constexpr (Eng::kTiled) {
 #pragma unroll
                                 for (int t = 0; t < Eng::TILES; ++t) {
-                                    tma_tile4d_g2s_hint(dst + t * Eng::TILE_BYTES, &tm.k, t * 64, 0, pid, h, bar_full(stage),
+                                    tma_tile4d_g2s_hint(dst + t * Eng::TILE_BYTES, &tm.k, t * Eng::TILE_COLS, 0, pid, h, bar_full(stage),
                                                         stream_policy);
-                                    tma_tile4d_g2s_hint(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * 64, 0, pid, h,
+                                    tma_tile4d_g2s_hint(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * Eng::TILE_COLS, 0, pid, h,
                                                         bar_full(stage), stream_policy);
                                 }
                             } else {
@@ -1338,18 +1510,18 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 4-D map of a page pool: (head_dim, token in page, page, kv head); box = one 64-element column tile
-// of one page (16 rows x 128 bytes), 128-byte swizzle.  Returns false if the driver rejects the
+// 4-D map of a page pool: (head_dim, token in page, page, kv head); box = one 128-byte column tile
+// of one page (16 rows x 128 bytes: 64 16-bit or 128 8-bit elements), 128-byte swizzle.  Returns false if the driver rejects the
 // geometry (the caller then uses the CUDA-core engine).
-bool encode_pool_map(CUtensorMap* tm, const void* pool, bool bf16, int64_t D, int64_t num_pages, int64_t Hkv,
-                     int64_t sp_bytes, int64_t sh_bytes) {
+bool encode_pool_map(CUtensorMap* tm, const void* pool, CUtensorMapDataType type, int64_t esz, int64_t D,
+                     int64_t num_pages, int64_t Hkv, int64_t sp_bytes, int64_t sh_bytes) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t gdim[4] = {(cuuint64_t)D, (cuuint64_t)kPage, (cuuint64_t)num_pages, (cuuint64_t)Hkv};
-    const cuuint64_t gstride[3] = {(cuuint64_t)(D * 2), (cuuint64_t)sp_bytes, (cuuint64_t)sh_bytes};
-    const cuuint32_t box[4] = {64, (cuuint32_t)kPage, 1, 1};
+    const cuuint64_t gstride[3] = {(cuuint64_t)(D * esz), (cuuint64_t)sp_bytes, (cuuint64_t)sh_bytes};
+    const cuuint32_t box[4] = {(cuuint32_t)(128 / esz), (cuuint32_t)kPage, 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    const CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+    const CUresult r = fn(tm, type, 4,
                           const_cast<void*>(pool), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1432,15 +1604,17 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     return IVAB_OK;
 }
 
+template <typename T> CUtensorMapDataType map_type() {
+    return std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
 template <typename T, int D, int G>
 int choose_engine(const DecodeParams& p, int B, int Hkv, cudaStream_t st) {
     TensorMaps tm{};
     if constexpr (sizeof(T) == 2 && D % 64 == 0) {
         if (G >= tc_min_group() && p.scale_log2 > 0.f &&
-            encode_pool_map(&tm.k, p.k_pool, std::is_same<T, __nv_bfloat16>::value, D, p.num_pages, Hkv,
-                            p.pool_sp_bytes, p.pool_sh_bytes) &&
-            encode_pool_map(&tm.v, p.v_pool, std::is_same<T, __nv_bfloat16>::value, D, p.num_pages, Hkv,
-                            p.pool_sp_bytes, p.pool_sh_bytes))
+            encode_pool_map(&tm.k, p.k_pool, map_type<T>(), 2, D, p.num_pages, Hkv, p.pool_sp_bytes, p.pool_sh_bytes) &&
+            encode_pool_map(&tm.v, p.v_pool, map_type<T>(), 2, D, p.num_pages, Hkv, p.pool_sp_bytes, p.pool_sh_bytes))
             return launch_decode<T, D, G, kEngMma>(p, tm, B, st);
     }
     return launch_decode<T, D, G, kEngSimt>(p, tm, B, st);
@@ -1502,13 +1676,36 @@ extern "C" int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64
 
 namespace {
 
+// IVAB_FP8_REG=0 keeps grouped-query 8-bit decode on the engine that widens pages in shared memory.
+bool use_fp8_register_engine() {
+    static bool v = [] {
+        const char* e = std::getenv("IVAB_FP8_REG");
+        return !(e && std::atoi(e) == 0);
+    }();
+    return v;
+}
+
 // 8-bit pools: multi-head attention (one query head per KV head) widens on the fly in the CUDA-core
-// engine; grouped queries widen each page to fp16 tiles and use the tensor cores.
+// engine; grouped queries use the tensor cores -- with head_dim 128 on fragments built in registers
+// from swizzled byte tiles, otherwise on pages widened to fp16 tiles in shared memory.
 template <typename T>
-int dispatch_fp8(int D, int G, const DecodeParams& p, int B, cudaStream_t st) {
+int dispatch_fp8(int D, int G, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
     TensorMaps tm{};
     using F8 = __nv_fp8_e4m3;
     const bool simt = G < tc_min_group() || !(p.scale_log2 > 0.f);
+    if (!simt && D == 128 && use_fp8_register_engine() &&
+        encode_pool_map(&tm.k, p.k_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,
+                        p.pool_sh_bytes) &&
+        encode_pool_map(&tm.v, p.v_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,
+                        p.pool_sh_bytes)) {
+        switch (G) {
+            case 2: return launch_decode<T, 128, 2, kEngMmaFp8Reg, F8>(p, tm, B, st);
+            case 4: return launch_decode<T, 128, 4, kEngMmaFp8Reg, F8>(p, tm, B, st);
+            case 8: return launch_decode<T, 128, 8, kEngMmaFp8Reg, F8>(p, tm, B, st);
+            case 1: return launch_decode<T, 128, 1, kEngMmaFp8Reg, F8>(p, tm, B, st);
+            default: break;
+        }
+    }
 #define IVAB_FP8_CASE(DD, GG)                                                                   \
     if (D == DD && G == GG)                                                                     \
         return simt ? launch_decode<T, DD, GG, kEngSimt, F8>(p, tm, B, st)                      \
@@ -1576,8 +1773,8 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     p.ws = ws;
     const int G = (int)(q_heads / kv_heads);
     if (kv_dtype == IVAB_F8E4M3) {
-        if (dtype == IVAB_F16) return dispatch_fp8<__half>((int)head_dim, G, p, (int)batch, st);
-        return dispatch_fp8<__nv_bfloat16>((int)head_dim, G, p, (int)batch, st);
+        if (dtype == IVAB_F16) return dispatch_fp8<__half>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
+        return dispatch_fp8<__nv_bfloat16>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
     }
     switch (dtype) {
         case IVAB_F32: return dispatch_dim<float>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);

@@ -15,9 +15,9 @@ DEV = "cuda"
 F8 = torch.float8_e4m3fn
 
 
-def _fp8_workload(ctx, Hq, Hkv, D, dtype, seed, k_scale, v_scale):
+def _fp8_workload(ctx, Hq, Hkv, D, dtype, seed, k_scale, v_scale, poison=False):
     wl = workloads.make_decode_workload("fp8", ctx, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, dtype=dtype, seed=seed,
-                                        free_frac=0.2)
+                                        free_frac=0.2, poison_unused=poison)   # poison: NaN bytes in every unused slot
     k8 = ref.quantize_fp8_ref(wl.k_pool, k_scale)
     v8 = ref.quantize_fp8_ref(wl.v_pool, v_scale)
     return wl, k8, v8
@@ -50,11 +50,11 @@ def test_quantising_append_is_bit_exact(dtype, D):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("Hq,Hkv,D", [(4, 4, 128), (8, 2, 128), (8, 4, 64), (16, 2, 128)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(4, 4, 128), (8, 2, 128), (8, 4, 64), (16, 2, 128), (32, 8, 128), (16, 8, 128)])
 def test_decode_on_fp8_pools(dtype, Hq, Hkv, D):
     ctx = torch.tensor([0, 1, 15, 16, 17, 100, 700, 3000])
     k_scale, v_scale = 0.02, 0.025
-    wl, k8, v8 = _fp8_workload(ctx, Hq, Hkv, D, dtype, Hq + D, k_scale, v_scale)
+    wl, k8, v8 = _fp8_workload(ctx, Hq, Hkv, D, dtype, Hq + D, k_scale, v_scale, poison=True)
     kd, vd = k8.to(DEV), v8.to(DEV)
     d = wl.to(DEV)
     iva_b200.paged_append(kd, vd, d.slot_mapping, d.k_new, d.v_new, 16, check=True, k_scale=k_scale, v_scale=v_scale)
@@ -73,9 +73,10 @@ def test_decode_on_fp8_pools(dtype, Hq, Hkv, D):
     assert rel < 0.08, f"quantisation error {rel:.3f}"
 
 
-def test_fp8_window_and_sinks_and_errors():
+@pytest.mark.parametrize("Hkv", [8, 2])
+def test_fp8_window_and_sinks_and_errors(Hkv):
     ctx = torch.tensor([300, 47, 5000])
-    wl, k8, v8 = _fp8_workload(ctx, 8, 8, 128, torch.bfloat16, 9, 0.02, 0.02)
+    wl, k8, v8 = _fp8_workload(ctx, 8, Hkv, 128, torch.bfloat16, 9, 0.02, 0.02)
     begin = torch.tensor([261, 10, 4000])
     d = wl.to(DEV)
     out, lse = iva_b200.paged_decode_attention(d.q, k8.to(DEV), v8.to(DEV), d.block_table, d.ctx_len, 16, wl.scale,
@@ -89,3 +90,15 @@ def test_fp8_window_and_sinks_and_errors():
         iva_b200.paged_decode_attention(d.q.float(), k8.to(DEV), v8.to(DEV), d.block_table, d.ctx_len, 16)
     with pytest.raises(ValueError, match="positive"):
         iva_b200.paged_decode_attention(d.q, k8.to(DEV), v8.to(DEV), d.block_table, d.ctx_len, 16, k_scale=0.0)
+
+
+def test_widening_engine_still_passes():
+    """IVAB_FP8_REG=0 (read once per process): grouped-query decode on 8-bit pools goes through the
+    engine that widens each page to fp16 tiles in shared memory; the same cases pass."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, IVAB_FP8_REG="0")
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_fp8_kv.py"), "-q", "-x",
+                          "-m", "gpu", "-k", "decode_on_fp8_pools or window_and_sinks", "-p", "no:cacheprovider"],
+                         env=env, capture_output=True, text=True, timeout=900, cwd=root)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
