@@ -1528,16 +1528,17 @@ bool encode_pool_map(CUtensorMap* tm, const void* pool, CUtensorMapDataType type
     return r == CUDA_SUCCESS;
 }
 
-// Smallest q_heads/kv_heads ratio that takes the tensor-core engine (16-bit K/V only).  Multi-head
-// attention (ratio 1) stays on CUDA cores, where it is HBM-bound; IVAB_TC_MIN_GROUP overrides the
-// threshold for experiments (1 = always, 99 = never).
-int tc_min_group() {
+// Smallest q_heads/kv_heads ratio that takes a tensor-core engine.  By default multi-head attention
+// (ratio 1) on 16-bit pools stays on CUDA cores, where it is HBM-bound, while 8-bit pools with
+// head_dim 128 use the tensor cores at every ratio (the CUDA-core engine is issue-bound on
+// them).  IVAB_TC_MIN_GROUP overrides both thresholds for experiments (1 = always, 99 = never).
+int tc_min_group(int default_value) {
     static int v = [] {
         const char* e = std::getenv("IVAB_TC_MIN_GROUP");
-        const int n = e ? std::atoi(e) : 2;
-        return n < 1 ? 1 : n;
+        const int n = e ? std::atoi(e) : 0;
+        return n < 1 ? 0 : n;
     }();
-    return v;
+    return v ? v : default_value;
 }
 
 // Programmatic dependent launch of the attention and merge kernels; IVAB_PDL=0 turns it off.
@@ -1612,7 +1613,7 @@ template <typename T, int D, int G>
 int choose_engine(const DecodeParams& p, int B, int Hkv, cudaStream_t st) {
     TensorMaps tm{};
     if constexpr (sizeof(T) == 2 && D % 64 == 0) {
-        if (G >= tc_min_group() && p.scale_log2 > 0.f &&
+        if (G >= tc_min_group(2) && p.scale_log2 > 0.f &&
             encode_pool_map(&tm.k, p.k_pool, map_type<T>(), 2, D, p.num_pages, Hkv, p.pool_sp_bytes, p.pool_sh_bytes) &&
             encode_pool_map(&tm.v, p.v_pool, map_type<T>(), 2, D, p.num_pages, Hkv, p.pool_sp_bytes, p.pool_sh_bytes))
             return launch_decode<T, D, G, kEngMma>(p, tm, B, st);
@@ -1692,8 +1693,8 @@ template <typename T>
 int dispatch_fp8(int D, int G, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
     TensorMaps tm{};
     using F8 = __nv_fp8_e4m3;
-    const bool simt = G < tc_min_group() || !(p.scale_log2 > 0.f);
-    if (!simt && D == 128 && use_fp8_register_engine() &&
+    const bool simt = G < tc_min_group(2) || !(p.scale_log2 > 0.f);
+    if (G >= tc_min_group(1) && p.scale_log2 > 0.f && D == 128 && use_fp8_register_engine() &&
         encode_pool_map(&tm.k, p.k_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,
                         p.pool_sh_bytes) &&
         encode_pool_map(&tm.v, p.v_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,

@@ -30,6 +30,19 @@ for dtype in (torch.bfloat16, torch.float16):
                                                    16, return_lse=True, check=True)
         assert_attn_close(out, out_ref, dtype, strict=False)
         assert_lse_close(lse, lse_ref)
+# 8-bit pools: the same thresholds move these between the CUDA-core and the tensor-core engines
+for hq, hkv, D in ((4, 4, 128), (8, 2, 128), (4, 4, 64)):
+    ctx = torch.tensor([0, 1, 15, 16, 17, 100, 333, 2500])
+    wl = workloads.make_decode_workload("eng8", ctx, n_q_heads=hq, n_kv_heads=hkv, head_dim=D, dtype=torch.bfloat16,
+                                        seed=hq + D, free_frac=0.3, poison_unused=True)
+    k8, v8 = ref.quantize_fp8_ref(wl.k_pool, 0.02).cuda(), ref.quantize_fp8_ref(wl.v_pool, 0.03).cuda()
+    d = wl.to("cuda")
+    out, lse = iva_b200.paged_decode_attention(d.q, k8, v8, d.block_table, d.ctx_len, 16, wl.scale, return_lse=True,
+                                               check=True, k_scale=0.02, v_scale=0.03)
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q, ref.dequantize_fp8_ref(k8.cpu(), 0.02),
+                                            ref.dequantize_fp8_ref(v8.cpu(), 0.03), wl.block_table, wl.ctx_len, 16, wl.scale)
+    assert_attn_close(out, out_ref, torch.bfloat16, strict=False)
+    assert_lse_close(lse, lse_ref)
 print("engines ok")
 """
 
