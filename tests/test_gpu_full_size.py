@@ -118,3 +118,32 @@ def test_batch_larger_than_the_planner_tiles():
                                                return_lse=True, check=True)
     assert_attn_close(out, out_ref, wl.dtype, strict=False)
     assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("config", ["c2", "c3"])
+def test_full_size_on_fp8_pools(config):
+    """The MHA and the ragged GQA benchmark configurations on 8-bit pools: quantising append, decode,
+    sampled comparison against the checker on the dequantised pools; doubling v_scale doubles the
+    output exactly; repeated calls are bit-identical."""
+    wl = workloads.config_c2(device=DEV) if config == "c2" else workloads.config_c3(device=DEV)
+    ks, vs = 0.02, 0.03
+    k8, v8 = ref.quantize_fp8_ref(wl.k_pool, ks), ref.quantize_fp8_ref(wl.v_pool, vs)   # same definition, run by torch on the GPU
+    wl.k_pool = wl.v_pool = None
+    iva_b200.paged_append(k8, v8, wl.slot_mapping, wl.k_new, wl.v_new, 16, check=True, k_scale=ks, v_scale=vs)
+    assert torch.equal(k8[0, :, wl.slot_mapping].view(torch.uint8),
+                       ref.quantize_fp8_ref(wl.k_new, ks).permute(1, 0, 2).view(torch.uint8))
+    lens = (wl.ctx_len + 1).contiguous()
+    out, lse = iva_b200.paged_decode_attention(wl.q, k8, v8, wl.block_table, lens, 16, wl.scale, return_lse=True,
+                                               check=True, k_scale=ks, v_scale=vs)
+    order = torch.argsort(wl.ctx_len.cpu())
+    seqs = [int(order[0]), int(order[len(order) // 2]), int(order[-1])]
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q.cpu(), ref.dequantize_fp8_ref(k8.cpu(), ks),
+                                            ref.dequantize_fp8_ref(v8.cpu(), vs), wl.block_table.cpu(), lens.cpu(), 16,
+                                            wl.scale, seqs=seqs)
+    assert_attn_close(out[seqs], out_ref[seqs], wl.dtype, strict=True)
+    assert_lse_close(lse[seqs], lse_ref[seqs])
+    out2, lse2 = iva_b200.paged_decode_attention(wl.q, k8, v8, wl.block_table, lens, 16, wl.scale, return_lse=True,
+                                                 k_scale=ks, v_scale=2 * vs)
+    assert torch.equal(out2.float(), out.float() * 2) and torch.equal(lse2, lse)
+    out3 = iva_b200.paged_decode_attention(wl.q, k8, v8, wl.block_table, lens, 16, wl.scale, k_scale=ks, v_scale=2 * vs)
+    assert torch.equal(out3, out2)
