@@ -20,6 +20,25 @@ constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 constexpr uint32_t kTile = kThreads * kUnroll;
 
+// Division of a number below 2^31 by a fixed divisor as one widening multiply and a shift:
+// n / d == (n * mul) >> (31 + shift) with shift = ceil(log2 d), mul = ceil(2^(31 + shift) / d).
+// (The rounding error of mul contributes less than n / 2^(31 + shift) * (e / d) < 1 / d, e < d <= 2^shift.)
+struct FastDiv {
+    uint32_t mul, shift, d;
+};
+
+FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f{};
+    f.d = d;
+    while ((1ull << f.shift) < d) ++f.shift;
+    f.mul = (uint32_t)(((1ull << (31 + f.shift)) + d - 1) / d);
+    return f;
+}
+
+__device__ __forceinline__ uint32_t fdiv(uint32_t n, const FastDiv& f) {
+    return (uint32_t)(((uint64_t)n * f.mul) >> (31 + f.shift));
+}
+
 struct RowCopyParams {
     const char* src[2];
     char* dst[2];
@@ -31,8 +50,9 @@ struct RowCopyParams {
     int64_t id_bound;       // valid ids are [0, id_bound)
     uint32_t N, H;
     uint32_t vec_per_row;   // 16-byte vectors per source row
-    uint32_t total;         // N * H * vec_per_row
+    uint32_t total;         // N * H * vec_per_row (below 2^31)
     uint32_t page_size;
+    FastDiv by_vpr, by_rows, by_page;   // divisors vec_per_row, (h_fastest ? H : N), page_size
     int h_fastest;          // row order on the dense side: 1 = (n, h), 0 = (h, n)
     int* status;
     float inv_scale[2];     // CVT 3/4 (quantising append): 1/scale per tensor
@@ -68,10 +88,11 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const RowCopyParams 
             doff[k] = 0;
             v[k] = make_uint4(0, 0, 0, 0);
             if (ok[k]) {
-                const uint32_t vec = i % p.vec_per_row;
-                const uint32_t r = i / p.vec_per_row;
-                uint32_t h, n;
-                if (p.h_fastest) { h = r % p.H; n = r / p.H; } else { n = r % p.N; h = r / p.N; }
+                // all quotients by multiply-and-shift: generic divisions here made the kernel issue-bound
+                const uint32_t r = fdiv(i, p.by_vpr);
+                const uint32_t vec = i - r * p.vec_per_row;
+                const uint32_t outer = fdiv(r, p.by_rows), inner = r - outer * p.by_rows.d;
+                const uint32_t h = p.h_fastest ? inner : outer, n = p.h_fastest ? outer : inner;
                 const int64_t id = __ldg(p.idx + n);
                 if (id < 0 || id >= p.id_bound) {
                     // Out-of-range index: record it and skip the row instead of faulting.
@@ -79,8 +100,8 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const RowCopyParams 
                     ok[k] = false;
                 } else {
                     const uint32_t uid = static_cast<uint32_t>(id);
-                    const int64_t ix = b * p.ix_b + h * p.ix_h + (int64_t)(uid / p.page_size) * p.ix_page +
-                                       (int64_t)(uid % p.page_size) * p.ix_slot;
+                    const uint32_t page = fdiv(uid, p.by_page), in_page = uid - page * p.page_size;
+                    const int64_t ix = b * p.ix_b + h * p.ix_h + (int64_t)page * p.ix_page + (int64_t)in_page * p.ix_slot;
                     const int64_t dn = b * p.dn_b + h * p.dn_h + (int64_t)n * p.dn_n;
                     const int64_t soff = (GATHER ? ix : dn) + (int64_t)vec * 16;
                     doff[k] = (GATHER ? dn : ix) + (int64_t)vec * (CVT == 0 ? 16 : (CVT <= 2 ? 32 : 8));
@@ -180,8 +201,12 @@ __global__ void __launch_bounds__(kThreads) paged_gather_kernel(const PagedGathe
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int launch_row_copy(bool gather, int cvt, const RowCopyParams& p, int64_t batch, int n_tensors, cudaStream_t st) {
-    if (p.total == 0 || batch == 0) return IVAB_OK;
+int launch_row_copy(bool gather, int cvt, const RowCopyParams& p0, int64_t batch, int n_tensors, cudaStream_t st) {
+    if (p0.total == 0 || batch == 0) return IVAB_OK;
+    RowCopyParams p = p0;
+    p.by_vpr = make_fastdiv(p.vec_per_row);
+    p.by_rows = make_fastdiv(p.h_fastest ? p.H : p.N);
+    p.by_page = make_fastdiv(p.page_size);
     const uint32_t n_tiles = (p.total + kTile - 1) / kTile;
     const uint32_t max_x = (uint32_t)sm_count() * 16u;
     dim3 grid(n_tiles < max_x ? n_tiles : max_x, (unsigned)batch, (unsigned)n_tensors);
@@ -238,8 +263,8 @@ extern "C" int ivab_kv_gather(const void* cache, const int64_t* indices, void* o
     if (batch > 65535) return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_gather: batch > 65535");
     const int64_t vpr = head_dim * (int64_t)esz / 16;
     const int64_t total = n_indices * heads * vpr;
-    if (total >= (1LL << 32) - 4096 || seq_len >= (1LL << 31))
-        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_gather: more than 2^32 vectors per batch row; split the call");
+    if (total >= (1LL << 31) - 4096 || seq_len >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_gather: more than 2^31 16-byte vectors per batch row; split the call");
     RowCopyParams p{};
     p.src[0] = static_cast<const char*>(cache);
     p.dst[0] = static_cast<char*>(out);
@@ -269,8 +294,8 @@ extern "C" int ivab_kv_scatter(void* cache, const int64_t* indices, const void* 
     if (batch > 65535) return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_scatter: batch > 65535");
     const int64_t vpr = head_dim * (int64_t)esz / 16;
     const int64_t total = n_indices * heads * vpr;
-    if (total >= (1LL << 32) - 4096 || seq_len >= (1LL << 31))
-        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_scatter: more than 2^32 vectors per batch row; split the call");
+    if (total >= (1LL << 31) - 4096 || seq_len >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_kv_scatter: more than 2^31 16-byte vectors per batch row; split the call");
     RowCopyParams p{};
     p.src[0] = static_cast<const char*>(values);
     p.dst[0] = static_cast<char*>(cache);
@@ -300,8 +325,8 @@ extern "C" int ivab_paged_append(const void* k_new, const void* v_new, int64_t n
         return set_error(IVAB_ERR_INVALID, "ivab_paged_append: pointers and strides must be 16-byte aligned");
     const int64_t vpr = head_dim * (int64_t)esz / 16;
     const int64_t total = n_tokens * heads * vpr;
-    if (total >= (1LL << 32) - 4096 || num_pages * page_size >= (1LL << 31))
-        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_paged_append: more than 2^32 vectors; split the call");
+    if (total >= (1LL << 31) - 4096 || num_pages * page_size >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "ivab_paged_append: more than 2^31 16-byte vectors; split the call");
     RowCopyParams p{};
     p.src[0] = static_cast<const char*>(k_new); p.src[1] = static_cast<const char*>(v_new);
     p.dst[0] = static_cast<char*>(k_pool); p.dst[1] = static_cast<char*>(v_pool);
@@ -366,8 +391,8 @@ extern "C" int ivab_paged_append_fp8(const void* k_new, const void* v_new, int64
         return set_error(IVAB_ERR_INVALID, "%s: pointers and strides must be 16-byte aligned", fn);
     const int64_t vpr = head_dim * 2 / 16;   // source vectors per row
     const int64_t total = n_tokens * heads * vpr;
-    if (total >= (1LL << 32) - 4096 || num_pages * page_size >= (1LL << 31))
-        return set_error(IVAB_ERR_UNSUPPORTED, "%s: more than 2^32 vectors; split the call", fn);
+    if (total >= (1LL << 31) - 4096 || num_pages * page_size >= (1LL << 31))
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: more than 2^31 16-byte vectors; split the call", fn);
     RowCopyParams p{};
     p.src[0] = static_cast<const char*>(k_new); p.src[1] = static_cast<const char*>(v_new);
     p.dst[0] = static_cast<char*>(k_pool); p.dst[1] = static_cast<char*>(v_pool);
