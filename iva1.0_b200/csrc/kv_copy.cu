@@ -211,7 +211,10 @@ int launch_row_copy(bool gather, int cvt, const RowCopyParams& p0, int64_t batch
     p.by_rows = make_fastdiv(p.h_fastest ? p.H : p.N);
     p.by_page = make_fastdiv(p.page_size);
     const uint32_t n_tiles = (p.total + kTile - 1) / kTile;
-    const uint32_t max_x = (uint32_t)sm_count() * 16u;
+    // One tile of kTile vectors per CTA.  A capped, grid-stride launch (148 x 16 CTAs) was measured 6 % slower
+    // on the 131 072-token append (6.10 vs 6.48 TB/s): with plain CTAs the hardware scheduler keeps the SMs'
+    // accesses spread over the whole range instead of marching through it in lockstep.
+    const uint32_t max_x = 0x7fffffffu;
     dim3 grid(n_tiles < max_x ? n_tiles : max_x, (unsigned)batch, (unsigned)n_tensors);
     if (gather) {
         if (cvt == 0) row_copy_kernel<true, 0><<<grid, kThreads, 0, st>>>(p);
