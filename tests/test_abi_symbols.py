@@ -49,3 +49,17 @@ def test_argument_validation_needs_no_gpu(built_library):
     n = ctypes.c_size_t(0)
     assert lib.ivab_decode_workspace_bytes(64, 32, 32, 128, ctypes.byref(n)) == 0 and n.value > 0
     assert lib.ivab_decode_workspace_bytes(64, 32, 5, 128, ctypes.byref(n)) == _lib.ERR_INVALID
+
+
+def test_plain_c_client_binds_and_validates(built_library, tmp_path):
+    """tests/abi_client.c is C99: it includes include/ivab.h, binds the library with dlopen the way a
+    foreign-function layer would, and checks the host-side argument validation.  No GPU needed."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc") or shutil.which("cc")
+    assert gcc, "a C compiler is part of the toolchain this library is built with"
+    exe = str(tmp_path / "abi_client")
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "abi_client.c"), "-o", exe, "-ldl"], check=True)
+    res = subprocess.run([exe, built_library], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "abi client ok" in res.stdout, res.stdout + res.stderr
