@@ -1754,6 +1754,9 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     if (workspace_bytes < need)
         return set_error(IVAB_ERR_WORKSPACE, "%s: workspace of %zu bytes, need %zu", fn, workspace_bytes, need);
     if ((int64_t)ws.cap * kv_heads >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "%s: too many work items", fn);
+    // Pages of an 8-bit pool stream twice as fast, so the fixed work per item weighs more: cut a
+    // quarter fewer, longer items (measured: C2 171.0 k -> 177.0 k, C3 587.2 k -> 594.6 k tokens/s).
+    if (kv_dtype == IVAB_F8E4M3) ws.target_chunks = ws.target_chunks * 3 / 4 > 0 ? ws.target_chunks * 3 / 4 : 1;
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, ctx_begin, (int)sink_tokens, (int)batch, (int)page_size,
