@@ -358,7 +358,8 @@ def run_gpu(args):
     e2e = None
     if name in ("c2", "c3", "c5a") and not args.kv_fp8:
         # the public end-to-end call: inputs in pinned host memory, one CUDA-graph replay per step
-        # (H2D of q / new K,V / slot mapping / lengths, append, attention, D2H of the output)
+        # (H2D of q / new K,V / slot mapping / lengths, append, attention; the kernels store the output
+        # straight into the pinned host buffer, d2h_bytes_per_step counts those bytes)
         gs = iva_b200.GraphedDecodeStep(wl.k_pool, wl.v_pool, wl.block_table, wl.n_q_heads, wl.page_size, wl.scale)
         gs.q_host.copy_(wl.q)
         gs.k_new_host.copy_(wl.k_new)
@@ -391,7 +392,7 @@ def run_gpu(args):
                "h2d_bytes_per_step": gs.h2d_bytes, "d2h_bytes_per_step": gs.d2h_bytes,
                "ms_per_step": wall_ms / args.steps, "device_ms_per_step": e2e_ms / args.steps,
                "api": "GraphedDecodeStep.run() + result(), host clock around K steps (each step ends in a stream sync)"}
-        out.copy_(gs._out)
+        out.copy_(gs.out_host if gs.direct_host_output else gs._out)
 
     clocks.__exit__(None, None, None)
     if rank != 0:

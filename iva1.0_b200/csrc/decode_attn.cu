@@ -1380,6 +1380,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int B, int Hq, 
     const int n_small = ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
     const int n_big = ws.header[kHdrNumBig];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // a lane's VPL outputs go out as one store when every output row is aligned for it
+    constexpr int kVecBytes = VPL * (int)sizeof(T);
+    const bool vec_out = VPL >= 2 && (sizeof(T) == 2 || VPL % 4 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(out) | (uintptr_t)(out_sb * (int64_t)sizeof(T)) |
+                           (uintptr_t)(out_sh * (int64_t)sizeof(T))) % kVecBytes) == 0;
 
     // ---- pass A
     for (int unit = blockIdx.x * kMergeWarps + warp; unit < n_small * Hq; unit += gridDim.x * kMergeWarps) {
@@ -1426,8 +1431,24 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int B, int Hq, 
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
         T* dst = out + (int64_t)s * out_sb + (int64_t)hq * out_sh + lane * VPL;
+        if (vec_out) {
+            // one store per lane (the output may be pinned host memory, where partial writes are expensive)
+            if constexpr (sizeof(T) == 4) {
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) Elt<T>::store(dst + i, acc[i] * inv);
+                for (int i = 0; i < VPL; i += 4)
+                    *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
+            } else if constexpr (VPL == 4) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pack2<T>(acc[0] * inv, acc[1] * inv), pack2<T>(acc[2] * inv, acc[3] * inv));
+            } else if constexpr (VPL == 8) {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(pack2<T>(acc[0] * inv, acc[1] * inv), pack2<T>(acc[2] * inv, acc[3] * inv),
+                                                            pack2<T>(acc[4] * inv, acc[5] * inv), pack2<T>(acc[6] * inv, acc[7] * inv));
+            } else {
+                *reinterpret_cast<uint32_t*>(dst) = pack2<T>(acc[0] * inv, acc[1] * inv);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) Elt<T>::store(dst + i, acc[i] * inv);
+        }
         if (lane == 0 && lse != nullptr) lse[(int64_t)s * Hq + hq] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
     }
 

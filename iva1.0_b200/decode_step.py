@@ -1,7 +1,9 @@
 """One decode step as a single CUDA-graph replay.
 
 A decode step of one attention layer is four small host->device copies, four kernel launches
-(append, plan, attention, merge) and one device->host copy.  Issued one by one from Python they
+(append, plan, attention, merge) and the result's way back to the host (by default the kernels
+store it straight into the pinned output buffer; ``direct_host_output=False`` writes a device
+buffer and copies it).  Issued one by one from Python they
 cost more CPU time than the 64-token append takes on the GPU, so the step is captured once in a
 CUDA graph and replayed: one driver call per step.
 
@@ -36,7 +38,7 @@ class GraphedDecodeStep:
 
     def __init__(self, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, n_q_heads: int,
                  page_size: int = 16, scale: Optional[float] = None, return_lse: bool = False,
-                 use_graph: bool = True):
+                 use_graph: bool = True, direct_host_output: bool = True):
         if not k_pool.is_cuda:
             raise RuntimeError("GraphedDecodeStep needs CUDA tensors; there is no CPU implementation")
         self.k_pool, self.v_pool, self.block_table = k_pool, v_pool, block_table
@@ -75,6 +77,10 @@ class GraphedDecodeStep:
         self.h2d_bytes = total
         self.d2h_bytes = self.out_host.numel() * self.out_host.element_size() + (
             self.lse_host.numel() * 4 if return_lse else 0)
+        # direct_host_output: the kernels store the result straight into the pinned output (pinned
+        # host memory is device-accessible under unified addressing) instead of into a device buffer
+        # that a device->host copy then drains; the same bytes cross the bus, without the extra pass.
+        self.direct_host_output = direct_host_output
         self.stream = torch.cuda.Stream(device=dev)
         self.use_graph = use_graph
         self.graph = None
@@ -84,6 +90,10 @@ class GraphedDecodeStep:
         self._stage_dev.copy_(self._stage_host, non_blocking=True)
         q, k_new, v_new, slots, lens = self._devs
         paged_append(self.k_pool, self.v_pool, slots, k_new, v_new, self.page_size)
+        if self.direct_host_output:
+            paged_decode_attention(q, self.k_pool, self.v_pool, self.block_table, lens, self.page_size, self.scale,
+                                   out=self.out_host, lse=self.lse_host, workspace=self._ws)
+            return
         paged_decode_attention(q, self.k_pool, self.v_pool, self.block_table, lens, self.page_size, self.scale,
                                out=self._out, lse=self._lse, workspace=self._ws)
         self.out_host.copy_(self._out, non_blocking=True)
