@@ -351,3 +351,25 @@ def test_module_window_with_sinks_on_a_paged_cache():
         y_ref = torch.nn.functional.linear(o.transpose(1, 2).reshape(B, 1, H * hd), wts[3])
         assert (y.cpu() - y_ref).abs().max().item() <= 1e-4
     assert cache.free_pages > 0
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float32, 64)])
+def test_long_and_short_chunk_lists_merge_in_one_call(dtype, D):
+    """One sequence cut into hundreds of chunks beside sequences of a few chunks and of one: the merge
+    kernel's CTA-per-slice path, its warp-per-head path and the attention kernel's direct output all
+    run in the same call.  Also with an output tensor that is only 2-byte (4-byte) aligned, which
+    takes the element-wise store path."""
+    ctx = torch.tensor([60000, 3000, 500, 17, 0])
+    wl = workloads.make_decode_workload("mixed", ctx, n_q_heads=8, n_kv_heads=2, head_dim=D, dtype=dtype, seed=77,
+                                        free_frac=0.05, poison_unused=True)
+    _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
+    d, out, lse = run_step(wl)
+    assert_attn_close(out, out_ref, dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
+    B, Hq = 5, 8
+    flat = torch.empty(B * Hq * D + 8, device=DEV, dtype=dtype)
+    odd = flat[1:1 + B * Hq * D].view(B, Hq, D)
+    assert odd.data_ptr() % 8 != 0
+    lens = (d.ctx_len + 1).contiguous()
+    out2 = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, lens, 16, wl.scale, out=odd, check=True)
+    assert torch.equal(out2, out)
