@@ -356,11 +356,12 @@ def run_gpu(args):
 
     # ---- end to end from pinned host buffers ----
     e2e = None
-    if name in ("c2", "c3", "c5a") and not args.kv_fp8:
+    if name in ("c2", "c3", "c5a"):
         # the public end-to-end call: inputs in pinned host memory, one CUDA-graph replay per step
         # (H2D of q / new K,V / slot mapping / lengths, append, attention; the kernels store the output
         # straight into the pinned host buffer, d2h_bytes_per_step counts those bytes)
-        gs = iva_b200.GraphedDecodeStep(wl.k_pool, wl.v_pool, wl.block_table, wl.n_q_heads, wl.page_size, wl.scale)
+        gs = iva_b200.GraphedDecodeStep(wl.k_pool, wl.v_pool, wl.block_table, wl.n_q_heads, wl.page_size, wl.scale,
+                                        token_dtype=wl.dtype, **kv_scales)
         gs.q_host.copy_(wl.q)
         gs.k_new_host.copy_(wl.k_new)
         gs.v_new_host.copy_(wl.v_new)

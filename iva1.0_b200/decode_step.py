@@ -38,12 +38,23 @@ class GraphedDecodeStep:
 
     def __init__(self, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, n_q_heads: int,
                  page_size: int = 16, scale: Optional[float] = None, return_lse: bool = False,
-                 use_graph: bool = True, direct_host_output: bool = True):
+                 use_graph: bool = True, direct_host_output: bool = True,
+                 token_dtype: Optional[torch.dtype] = None, k_scale: float = 1.0, v_scale: float = 1.0):
         if not k_pool.is_cuda:
             raise RuntimeError("GraphedDecodeStep needs CUDA tensors; there is no CPU implementation")
         self.k_pool, self.v_pool, self.block_table = k_pool, v_pool, block_table
         self.page_size = page_size
         dev, dtype = k_pool.device, k_pool.dtype
+        # 8-bit (e4m3) pools: queries and new tokens are 16-bit (``token_dtype``, bf16 unless given), the
+        # append quantises with ``k_scale`` / ``v_scale`` and the attention reads with the same scales
+        self.fp8 = dtype == torch.float8_e4m3fn
+        if self.fp8:
+            dtype = token_dtype or torch.bfloat16
+            if dtype not in (torch.float16, torch.bfloat16):
+                raise ValueError("8-bit pools take fp16 or bf16 queries and tokens")
+        elif token_dtype is not None and token_dtype != dtype:
+            raise ValueError("token_dtype differs from the dtype of the pools")
+        self.k_scale, self.v_scale = float(k_scale), float(v_scale)
         Hkv, _, _, _ = _pool_strides(k_pool, page_size)
         D = k_pool.shape[-1]
         B = block_table.shape[0]
@@ -51,7 +62,7 @@ class GraphedDecodeStep:
 
         # All inputs of a step live in ONE pinned block (and one device block), carved into typed
         # views, so that a step uploads them with a single host->device copy.
-        esz = k_pool.element_size()
+        esz = torch.empty(0, dtype=dtype).element_size()
         sizes = [B * n_q_heads * D * esz, B * Hkv * D * esz, B * Hkv * D * esz, B * 8, B * 4]
         offs, total = [], 0
         for n in sizes:
@@ -89,13 +100,14 @@ class GraphedDecodeStep:
     def _enqueue(self) -> None:
         self._stage_dev.copy_(self._stage_host, non_blocking=True)
         q, k_new, v_new, slots, lens = self._devs
-        paged_append(self.k_pool, self.v_pool, slots, k_new, v_new, self.page_size)
+        scales = dict(k_scale=self.k_scale, v_scale=self.v_scale) if self.fp8 else {}
+        paged_append(self.k_pool, self.v_pool, slots, k_new, v_new, self.page_size, **scales)
         if self.direct_host_output:
             paged_decode_attention(q, self.k_pool, self.v_pool, self.block_table, lens, self.page_size, self.scale,
-                                   out=self.out_host, lse=self.lse_host, workspace=self._ws)
+                                   out=self.out_host, lse=self.lse_host, workspace=self._ws, **scales)
             return
         paged_decode_attention(q, self.k_pool, self.v_pool, self.block_table, lens, self.page_size, self.scale,
-                               out=self._out, lse=self._lse, workspace=self._ws)
+                               out=self._out, lse=self._lse, workspace=self._ws, **scales)
         self.out_host.copy_(self._out, non_blocking=True)
         if self._lse is not None:
             self.lse_host.copy_(self._lse, non_blocking=True)

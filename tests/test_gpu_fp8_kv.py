@@ -102,3 +102,40 @@ def test_widening_engine_still_passes():
                           "-m", "gpu", "-k", "decode_on_fp8_pools or window_and_sinks", "-p", "no:cacheprovider"],
                          env=env, capture_output=True, text=True, timeout=900, cwd=root)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+
+
+def test_graphed_step_on_fp8_pools():
+    """GraphedDecodeStep with e4m3 pools: quantising append + attention replayed from pinned host
+    buffers, three steps, each against the checker on the dequantised pools it should have produced."""
+    ks, vs = 0.02, 0.03
+    B, Hq, Hkv, D = 3, 8, 2, 128
+    ctx = torch.tensor([40, 17, 300])
+    # pools and block tables with room for three more tokens per sequence
+    wl3 = workloads.make_decode_workload("fp8step", ctx + 3, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D,
+                                         dtype=torch.bfloat16, seed=21, free_frac=0.2)
+    k8, v8 = ref.quantize_fp8_ref(wl3.k_pool, ks), ref.quantize_fp8_ref(wl3.v_pool, vs)
+    kd, vd = k8.to(DEV), v8.to(DEV)
+    bt = wl3.block_table.to(DEV)
+    step = iva_b200.GraphedDecodeStep(kd, vd, bt, n_q_heads=Hq, return_lse=True, token_dtype=torch.bfloat16,
+                                      k_scale=ks, v_scale=vs)
+    g = torch.Generator().manual_seed(5)
+    k_ref, v_ref = k8.clone(), v8.clone()
+    for t in range(3):
+        L = ctx + t
+        q = torch.randn(B, Hq, D, generator=g).to(torch.bfloat16)
+        kn = torch.randn(B, Hkv, D, generator=g).to(torch.bfloat16)
+        vn = torch.randn(B, Hkv, D, generator=g).to(torch.bfloat16)
+        slots = torch.tensor([int(wl3.block_table[s, int(L[s]) // 16]) * 16 + int(L[s]) % 16 for s in range(B)])
+        step.q_host.copy_(q); step.k_new_host.copy_(kn); step.v_new_host.copy_(vn)
+        step.slot_mapping_host.copy_(slots); step.ctx_len_host.copy_((L + 1).to(torch.int32))
+        step.run()
+        out = step.result().clone()
+        lse = step.lse_host.clone()
+        k_ref[0, :, slots] = ref.quantize_fp8_ref(kn, ks).permute(1, 0, 2)
+        v_ref[0, :, slots] = ref.quantize_fp8_ref(vn, vs).permute(1, 0, 2)
+        out_ref, lse_ref = ref.paged_decode_ref(q, ref.dequantize_fp8_ref(k_ref, ks), ref.dequantize_fp8_ref(v_ref, vs),
+                                                wl3.block_table, L + 1, 16, wl3.scale)
+        assert_attn_close(out, out_ref, torch.bfloat16, strict=False)
+        assert_lse_close(lse, lse_ref)
+    assert torch.equal(kd.cpu().view(torch.uint8), k_ref.view(torch.uint8))
+    assert step.graph is not None
