@@ -359,6 +359,7 @@ struct DecodeParams {
     const int32_t* block_table; int64_t bt_stride;
     void* out; int64_t out_sb, out_sh; float* lse;
     int Hq, num_pages;
+    int group;               // query heads per KV head; the kernels' template group size is this rounded up to 1, 2, 4 or 8
     int sink_tokens;           // keys [0, sink_tokens) stay visible in front of a window (0 = none)
     float v_scale;             // 8-bit KV storage: V = v_scale * stored value (1 otherwise); K's scale is folded into scale_log2
     float scale_log2;          // scale * log2(e): scores are kept in base-2 units
@@ -489,10 +490,11 @@ struct SimtEngine {
         static_assert(QV >= 1 && QV * Elt<TQ>::kPerVec == C::EPL, "q type must not be narrower than the KV type");
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            const TQ* qp = qg + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh + c * C::EPL;
+            const TQ* qp = qg + (int64_t)seq * p.q_sb + (int64_t)(h * p.group + g) * p.q_sh + c * C::EPL;
 #pragma unroll
             for (int v = 0; v < QV; ++v) {
-                const uint4 u = __ldg(reinterpret_cast<const uint4*>(qp) + v);
+                // heads past the real group size (template G is the group rounded up) are all-zero rows
+                const uint4 u = g < p.group ? __ldg(reinterpret_cast<const uint4*>(qp) + v) : make_uint4(0, 0, 0, 0);
                 Elt<TQ>::unpack(u, &qf[g][v * Elt<TQ>::kPerVec]);
             }
 #pragma unroll
@@ -636,8 +638,8 @@ struct MmaCore {
 
     __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
         const int g = lane >> 2, c = lane & 3;
-        if (g < G) {
-            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh;
+        if (g < p.group) {
+            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * p.group + g) * p.q_sh;
 #pragma unroll
             for (int s = 0; s < KSTEPS; ++s) {
                 qa[s][0] = load_q_pair(qrow + 16 * s + 2 * c);
@@ -873,8 +875,8 @@ struct MmaFp8RegEngine {
 
     __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
         const int g = lane >> 2, c = lane & 3;
-        if (g < G) {
-            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * G + g) * p.q_sh + 32 * c;
+        if (g < p.group) {
+            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * p.group + g) * p.q_sh + 32 * c;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {   // 4 x 16 bytes = elements 32c + 8v .. 32c + 8v + 7 = k-steps 2v, 2v+1
                 const uint4 u = __ldg(reinterpret_cast<const uint4*>(qrow) + v);
@@ -1290,7 +1292,8 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             __threadfence_block();
             const volatile float* all_ml = mrg_ml;
             const volatile float* all_o = mrg_o;
-            for (int idx = lane; idx < G * D; idx += 32) {
+            const int Gr = p.group;   // real heads of this KV head: rows Gr..G-1 of the states are padding
+            for (int idx = lane; idx < Gr * D; idx += 32) {
                 const int g = idx / D, dd = idx % D;
                 float M = -INFINITY;
 #pragma unroll
@@ -1304,17 +1307,17 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                     O = fmaf(all_o[(size_t)(w * G + g) * D + dd], f, O);
                 }
                 O *= p.v_scale;
-                const int hq = h * G + g;
+                const int hq = h * Gr + g;
                 if (n_chunks == 1) {
                     const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
                     Elt<T>::store(outg + (int64_t)seq * p.out_sb + (int64_t)hq * p.out_sh + dd, O * inv);
                     if (dd == 0 && p.lse != nullptr)
                         p.lse[(int64_t)seq * p.Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * 0.6931471805599453f : -INFINITY;
                 } else {
-                    p.ws.part_o[((size_t)item * G + g) * D + dd] = O;
+                    p.ws.part_o[((size_t)item * Gr + g) * D + dd] = O;
                     if (dd == 0) {
-                        p.ws.part_ml[((size_t)item * G + g) * 2] = M;
-                        p.ws.part_ml[((size_t)item * G + g) * 2 + 1] = Lsum;
+                        p.ws.part_ml[((size_t)item * Gr + g) * 2] = M;
+                        p.ws.part_ml[((size_t)item * Gr + g) * 2 + 1] = Lsum;
                     }
                 }
             }
@@ -1620,7 +1623,7 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     const long long units = (long long)B * p.Hq * (D / 32);
     const int merge_grid = (int)(units < (long long)sm_count() * 4 ? units : (long long)sm_count() * 4);
     cfg.gridDim = dim3(merge_grid); cfg.blockDim = dim3(kMergeWarps * 32); cfg.dynamicSmemBytes = 0;
-    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, B, p.Hq, G, p.ws, static_cast<T*>(p.out), p.out_sb,
+    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, B, p.Hq, p.group, p.ws, static_cast<T*>(p.out), p.out_sb,
                                                p.out_sh, p.lse), "merge_kernel launch")) return rc;
     g_launches++;
     return IVAB_OK;
@@ -1644,12 +1647,14 @@ int choose_engine(const DecodeParams& p, int B, int Hkv, cudaStream_t st) {
 
 template <typename T, int D>
 int dispatch_group(int G, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
+    // the kernels are instantiated for groups of 1, 2, 4 and 8 query heads; other ratios run in the
+    // next larger one with the surplus rows empty (p.group holds the real ratio)
     switch (G) {
         case 1: return choose_engine<T, D, 1>(p, B, Hkv, st);
         case 2: return choose_engine<T, D, 2>(p, B, Hkv, st);
-        case 4: return choose_engine<T, D, 4>(p, B, Hkv, st);
-        case 8: return choose_engine<T, D, 8>(p, B, Hkv, st);
-        default: return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: q_heads/kv_heads = %d (supported: 1, 2, 4, 8)", G);
+        case 3: case 4: return choose_engine<T, D, 4>(p, B, Hkv, st);
+        case 5: case 6: case 7: case 8: return choose_engine<T, D, 8>(p, B, Hkv, st);
+        default: return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: q_heads/kv_heads = %d (supported: 1 to 8)", G);
     }
 }
 
@@ -1711,9 +1716,12 @@ bool use_fp8_register_engine() {
 // engine; grouped queries use the tensor cores -- with head_dim 128 on fragments built in registers
 // from swizzled byte tiles, otherwise on pages widened to fp16 tiles in shared memory.
 template <typename T>
-int dispatch_fp8(int D, int G, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
+int dispatch_fp8(int D, int G_real, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
     TensorMaps tm{};
     using F8 = __nv_fp8_e4m3;
+    if (G_real < 1 || G_real > 8)
+        return set_error(IVAB_ERR_UNSUPPORTED, "8-bit KV decode: q_heads/kv_heads = %d (supported: 1 to 8)", G_real);
+    const int G = G_real <= 2 ? G_real : (G_real <= 4 ? 4 : 8);   // instantiated group sizes; p.group keeps the real one
     const bool simt = G < tc_min_group(2) || !(p.scale_log2 > 0.f);
     if (G >= tc_min_group(1) && p.scale_log2 > 0.f && D == 128 && use_fp8_register_engine() &&
         encode_pool_map(&tm.k, p.k_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,
@@ -1736,7 +1744,7 @@ int dispatch_fp8(int D, int G, int Hkv, const DecodeParams& p, int B, cudaStream
     IVAB_FP8_CASE(128, 1) IVAB_FP8_CASE(128, 2) IVAB_FP8_CASE(128, 4) IVAB_FP8_CASE(128, 8)
 #undef IVAB_FP8_CASE
     return set_error(IVAB_ERR_UNSUPPORTED,
-                     "8-bit KV decode: head_dim %d with %d query heads per KV head (supported: 64/128, 1/2/4/8)", D, G);
+                     "8-bit KV decode: head_dim %d (supported: 64, 128)", D);
 }
 
 // Shared body of the decode entry points.  kv_dtype is the storage type of the pools (== dtype, or
@@ -1792,6 +1800,7 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     p.block_table = block_table; p.bt_stride = block_table_stride;
     p.out = out; p.out_sb = out_stride_b; p.out_sh = out_stride_h; p.lse = lse;
     p.Hq = (int)q_heads; p.num_pages = (int)num_pages; p.sink_tokens = (int)sink_tokens;
+    p.group = (int)(q_heads / kv_heads);
     p.v_scale = v_scale;
     p.scale_log2 = scale * k_scale * 1.4426950408889634f;   // K = k_scale * stored value
     p.wait_limit_ns = kWaitLimitNs;
