@@ -152,8 +152,10 @@ int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t kv_heads
  * The math is AttentionTorch.forward lines 77, 99, 102 (src/core/attention.py) for one query
  * and no mask; it takes the place of the unusable attention_kernel
  * (src/kernels_t/attention_triton.py:18-71).  kvh(hq) = hq / (q_heads/kv_heads); the group
- * size must be 1 to 8 (3 runs in the kernels built for 4, 5-7 in those for 8), head_dim 32, 64, 128
- * (or 256 for 16-bit types), page_size 16.
+ * size may be 1 to 8 (3 runs in the kernels built for 4, 5-7 in those for 8) or a larger one that
+ * splits into equal groups of at most 8 (16 = 2 x 8, 12 = 2 x 6, 64 = 8 x 8; each group is a work item
+ * of its own, so the K/V of that head are read once per group); head_dim 32, 64, 128 (or 256 for
+ * 16-bit types), page_size 16.
  * Enqueues three kernels (plan, split-K attention, logsumexp merge).  ctx_len[s] == 0
  * (or an empty window)
  * yields zeros and -inf.  `workspace` must be 256-byte aligned and hold

@@ -73,7 +73,7 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     sequence ``s``, K/V read in place from the page pool through ``block_table``.
 
     q ``[B,H_q,D]``; pools ``[1,H_kv,num_pages*page_size,D]`` (or ``[num_pages,H_kv,page_size,D]``);
-    ``block_table`` int32 ``[B,max_pages]``; ``ctx_len`` int32 ``[B]``.  ``H_q/H_kv`` from 1 to 8.
+    ``block_table`` int32 ``[B,max_pages]``; ``ctx_len`` int32 ``[B]``.  ``H_q/H_kv`` from 1 to 8, or larger and divisible into equal groups of at most 8 (12, 16, 32, 64 ...).
     Returns ``out`` (dtype of q) or ``(out, lse)`` with ``lse`` fp32 ``[B,H_q]`` (natural log).
     ``check=True`` synchronises and raises if the kernels flagged a bad page id / length or a
     timed-out wait.  ``ctx_begin`` (int32 ``[B]``, optional) restricts sequence ``s`` to the keys

@@ -105,6 +105,18 @@ struct Workspace {
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// The kernels handle up to 8 query heads per KV head.  A larger ratio is served by cutting the query
+// heads of a KV head into `div` equal groups of at most 8, each a work item of its own that reads the
+// same K/V slab ("virtual" KV heads: kv_heads * div of them, group = ratio / div query heads each).
+// Returns div, or 0 when the ratio has no such split (a prime above 8, for example).
+int split_ratio(int64_t ratio) {
+    if (ratio < 1) return 0;
+    if (ratio <= 8) return 1;
+    for (int64_t div = (ratio + 7) / 8; div <= ratio / 2 + 1 && div <= 64; ++div)
+        if (ratio % div == 0 && ratio / div <= 8) return (int)div;
+    return 0;
+}
+
 int resident_slots() { return sm_count() * 2; }
 
 // Work items per resident CTA the planner aims for.  More items = finer chunks = a shorter tail
@@ -360,6 +372,7 @@ struct DecodeParams {
     void* out; int64_t out_sb, out_sh; float* lse;
     int Hq, num_pages;
     int group;               // query heads per KV head; the kernels' template group size is this rounded up to 1, 2, 4 or 8
+    int kv_div;              // work items number virtual KV heads; virtual head h reads the slab of KV head h / kv_div
     int sink_tokens;           // keys [0, sink_tokens) stay visible in front of a window (0 = none)
     float v_scale;             // 8-bit KV storage: V = v_scale * stored value (1 otherwise); K's scale is folded into scale_log2
     float scale_log2;          // scale * log2(e): scores are kept in base-2 units
@@ -1143,8 +1156,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             ++published;
             if (done) break;
 
-            const char* kbase = p.k_pool + (int64_t)h * p.pool_sh_bytes;
-            const char* vbase = p.v_pool + (int64_t)h * p.pool_sh_bytes;
+            const int slab = h / p.kv_div;   // the KV head whose pages this item reads
+            const char* kbase = p.k_pool + (int64_t)slab * p.pool_sh_bytes;
+            const char* vbase = p.v_pool + (int64_t)slab * p.pool_sh_bytes;
             const int start = (d.seq + d.chunk_idx) % kConsumerWarps;
             for (int p0 = 0; p0 < d.n_pages && !aborted; p0 += 32) {
                 const int mine = p0 == 0 ? bt0 : load_pages(d, p0);
@@ -1179,9 +1193,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                             if constexpr (Eng::kTiled) {
 #pragma unroll
                                 for (int t = 0; t < Eng::TILES; ++t) {
-                                    tma_tile4d_g2s_hint(dst + t * Eng::TILE_BYTES, &tm.k, t * Eng::TILE_COLS, 0, pid, h, bar_full(stage),
+                                    tma_tile4d_g2s_hint(dst + t * Eng::TILE_BYTES, &tm.k, t * Eng::TILE_COLS, 0, pid, slab, bar_full(stage),
                                                         stream_policy);
-                                    tma_tile4d_g2s_hint(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * Eng::TILE_COLS, 0, pid, h,
+                                    tma_tile4d_g2s_hint(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * Eng::TILE_COLS, 0, pid, slab,
                                                         bar_full(stage), stream_policy);
                                 }
                             } else {
@@ -1697,7 +1711,8 @@ extern "C" int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64
     if (!bytes_out) return set_error(IVAB_ERR_INVALID, "ivab_decode_workspace_bytes: null bytes_out");
     if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || q_heads % kv_heads)
         return set_error(IVAB_ERR_INVALID, "ivab_decode_workspace_bytes: bad sizes");
-    *bytes_out = carve_workspace(nullptr, batch, q_heads, kv_heads, head_dim, nullptr);
+    const int div = split_ratio(q_heads / kv_heads);
+    *bytes_out = carve_workspace(nullptr, batch, q_heads, kv_heads * (div > 0 ? div : 1), head_dim, nullptr);
     return IVAB_OK;
 }
 
@@ -1778,18 +1793,25 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
         return set_error(IVAB_ERR_UNSUPPORTED, "%s: batch or context too large", fn);
     if (sink_tokens < 0 || sink_tokens >= (1LL << 31)) return set_error(IVAB_ERR_INVALID, "%s: bad sink_tokens", fn);
 
+    const int64_t ratio = q_heads / kv_heads;
+    const int kv_div = split_ratio(ratio);
+    if (kv_div == 0)
+        return set_error(IVAB_ERR_UNSUPPORTED,
+                         "%s: q_heads/kv_heads = %lld (supported: 1 to 8, and larger ratios that split into equal groups of at most 8)",
+                         fn, (long long)ratio);
+    const int64_t virt_heads = kv_heads * kv_div;   // work items are (virtual KV head, chunk) pairs
     Workspace ws;
-    const size_t need = carve_workspace(workspace, batch, q_heads, kv_heads, head_dim, &ws);
+    const size_t need = carve_workspace(workspace, batch, q_heads, virt_heads, head_dim, &ws);
     if (workspace_bytes < need)
         return set_error(IVAB_ERR_WORKSPACE, "%s: workspace of %zu bytes, need %zu", fn, workspace_bytes, need);
-    if ((int64_t)ws.cap * kv_heads >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "%s: too many work items", fn);
+    if ((int64_t)ws.cap * virt_heads >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "%s: too many work items", fn);
     // Pages of an 8-bit pool stream twice as fast, so the fixed work per item weighs more: cut a
     // quarter fewer, longer items (measured: C2 171.0 k -> 177.0 k, C3 587.2 k -> 594.6 k tokens/s).
     if (kv_dtype == IVAB_F8E4M3) ws.target_chunks = ws.target_chunks * 3 / 4 > 0 ? ws.target_chunks * 3 / 4 : 1;
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, ctx_begin, (int)sink_tokens, (int)batch, (int)page_size,
-                                            (int)max_pages_per_seq, ws.target_chunks, ws.cap, (int)kv_heads, ws);
+                                            (int)max_pages_per_seq, ws.target_chunks, ws.cap, (int)virt_heads, ws);
     g_launches++;
     if (int rc = check_cuda(cudaGetLastError(), "plan_kernel launch")) return rc;
 
@@ -1800,12 +1822,13 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     p.block_table = block_table; p.bt_stride = block_table_stride;
     p.out = out; p.out_sb = out_stride_b; p.out_sh = out_stride_h; p.lse = lse;
     p.Hq = (int)q_heads; p.num_pages = (int)num_pages; p.sink_tokens = (int)sink_tokens;
-    p.group = (int)(q_heads / kv_heads);
+    p.group = (int)(ratio / kv_div);
+    p.kv_div = kv_div;
     p.v_scale = v_scale;
     p.scale_log2 = scale * k_scale * 1.4426950408889634f;   // K = k_scale * stored value
     p.wait_limit_ns = kWaitLimitNs;
     p.ws = ws;
-    const int G = (int)(q_heads / kv_heads);
+    const int G = p.group;
     if (kv_dtype == IVAB_F8E4M3) {
         if (dtype == IVAB_F16) return dispatch_fp8<__half>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
         return dispatch_fp8<__nv_bfloat16>((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
@@ -1917,7 +1940,8 @@ extern "C" int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b,
     const char* fn = "ivab_paged_decode_attn_noalloc";
     if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || q_heads % kv_heads)
         return set_error(IVAB_ERR_INVALID, "%s: bad sizes", fn);
-    const size_t need = carve_workspace(nullptr, batch, q_heads, kv_heads, head_dim, nullptr);
+    const int div = split_ratio(q_heads / kv_heads);   // (an unsupported ratio is reported by the call below)
+    const size_t need = carve_workspace(nullptr, batch, q_heads, kv_heads * (div > 0 ? div : 1), head_dim, nullptr);
     if (need > kStaticScratchBytes)
         return set_error(IVAB_ERR_WORKSPACE,
                          "%s: this problem needs %zu bytes of scratch, the built-in buffer holds %zu; use "

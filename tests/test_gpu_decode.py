@@ -58,6 +58,19 @@ def test_page_boundary_contexts(dtype, D, group):
     assert_lse_close(lse, lse_ref)
 
 
+@pytest.mark.parametrize("dtype,Hq,Hkv,D", [(torch.bfloat16, 32, 2, 128), (torch.float16, 24, 2, 64),
+                                            (torch.bfloat16, 64, 1, 128), (torch.float32, 18, 2, 64)])
+def test_head_ratios_above_eight(dtype, Hq, Hkv, D):
+    """16, 12, 64 (multi-query) and 9 query heads per KV head: served as equal groups of at most 8."""
+    ctx = torch.tensor([0, 1, 16, 33, 200, 5000])
+    wl = workloads.make_decode_workload("ratio", ctx, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, dtype=dtype,
+                                        seed=Hq + D, free_frac=0.2, poison_unused=True)
+    _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
+    _, out, lse = run_step(wl)
+    assert_attn_close(out, out_ref, dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
+
+
 def test_empty_sequence_gives_zeros_and_minus_inf():
     wl = workloads.make_decode_workload("z", torch.tensor([5, 0, 9]), n_q_heads=4, n_kv_heads=4, head_dim=128, seed=1)
     d = wl.to(DEV)
@@ -144,8 +157,8 @@ def test_bad_page_id_and_length_are_flagged_not_dereferenced():
 
 
 def test_argument_errors():
-    wl = workloads.make_decode_workload("e", torch.tensor([20]), n_q_heads=18, n_kv_heads=2, head_dim=128, seed=2).to(DEV)
-    with pytest.raises(ValueError, match="supported: 1 to 8"):
+    wl = workloads.make_decode_workload("e", torch.tensor([20]), n_q_heads=22, n_kv_heads=2, head_dim=128, seed=2).to(DEV)
+    with pytest.raises(ValueError, match="supported: 1 to 8"):      # 11 query heads per KV head: no equal groups of <= 8
         iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16)
     wl = workloads.make_decode_workload("e", torch.tensor([20]), n_q_heads=2, n_kv_heads=2, head_dim=128, seed=2).to(DEV)
     with pytest.raises(ValueError):

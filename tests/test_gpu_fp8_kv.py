@@ -51,7 +51,7 @@ def test_quantising_append_is_bit_exact(dtype, D):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("Hq,Hkv,D", [(4, 4, 128), (8, 2, 128), (8, 4, 64), (16, 2, 128), (32, 8, 128), (16, 8, 128),
-                                      (6, 2, 128), (14, 2, 128), (10, 2, 64)])
+                                      (6, 2, 128), (14, 2, 128), (10, 2, 64), (32, 2, 128)])
 def test_decode_on_fp8_pools(dtype, Hq, Hkv, D):
     ctx = torch.tensor([0, 1, 15, 16, 17, 100, 700, 3000])
     k_scale, v_scale = 0.02, 0.025
