@@ -842,37 +842,39 @@ struct MmaFp8Engine : MmaCore<__half, TQ, D, G> {
     }
 };
 
-// 8-bit (e4m3) pools with grouped queries, head_dim 128: the MMA operands are built in registers
-// straight from the stored bytes -- no widened copy of the page in shared memory.  Pages arrive as
-// one swizzled 16 x 128-byte tile each for K and V (tiled TMA, 128-byte swizzle).  Both products may
-// number their summation index and their output columns freely as long as both operands agree, and
-// the numbering is chosen so that every lane reads whole 16-byte chunks:
-//   * Q K^T: lane (g = lane/4, c = lane%4) holds bytes 32c..32c+31 of key row g; byte pair
+// 8-bit (e4m3) pools, head_dim 64 or 128: the MMA operands are built in registers straight from the
+// stored bytes -- no widened copy of the page in shared memory.  Pages arrive as one swizzled tile of
+// 16 rows x D bytes each for K and V (tiled TMA; 128-byte swizzle for D = 128, 64-byte for D = 64).
+// Both products may number their summation index and their output columns freely as long as both
+// operands agree, and the numbering is chosen so that every lane reads whole chunks (D = 128 in
+// brackets, D = 64 halves every figure):
+//   * Q K^T: lane (g = lane/4, c = lane%4) holds bytes [32c, 32c+32) of key row g; byte pair
 //     (4s, 4s+1) is B-fragment register 0 and pair (4s+2, 4s+3) register 1 of k-step s, and the
-//     query fragments are loaded in the same numbering (32 consecutive elements per lane).
-//   * P^T V: the lane reads chunk g (dims 16g..16g+15) of the four value rows 2c, 2c+1, 2c+8, 2c+9;
-//     byte j of those rows is the B fragment of output block j, so block j, column n is dim 16n + j
-//     and the lane ends up with the 32 consecutive dims 32c..32c+31 of head g.
+//     query fragments are loaded in the same numbering ([32] consecutive elements per lane).
+//   * P^T V: the lane reads dims [16g, 16g+16) of the four value rows 2c, 2c+1, 2c+8, 2c+9; byte j
+//     of those rows is the B fragment of output block j, so block j, column n is dim [16]n + j and
+//     the lane ends up with the [32] consecutive dims from [32]c on of head g.
 // e4m3 -> fp16 is exact (one cvt per pair); the weights are carried as fp16 value + correction in
 // rows 0..7 / 8..15 of the A tile like in the 16-bit engine.
 template <typename TQ, int D, int G>
 struct MmaFp8RegEngine {
-    static_assert(D == 128, "one 128-byte swizzled tile per page row");
+    static_assert(D == 128 || D == 64, "one swizzled tile of 128- or 64-byte rows per page");
     static_assert(G >= 1 && G <= 8, "query heads of one kv head fill rows 0..7 of the A tile");
     using TT = __half;
     static constexpr bool kTiled = true;
     static constexpr int TILES = 1;
-    static constexpr int TILE_COLS = 128;
-    static constexpr int TILE_BYTES = kPage * 128;
+    static constexpr int TILE_COLS = D;
+    static constexpr int TILE_BYTES = kPage * D;
     static constexpr int PAGE_BYTES = TILE_BYTES;
     static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
     static constexpr int SCRATCH_PER_WARP = 0;
     static constexpr int CTAS_PER_SM = 2;
     static constexpr int KSTEPS = D / 16;
     static constexpr int NBLK = D / 8;
+    static constexpr int LANE_DIMS = D / 4;    // consecutive dims of q and of the output one lane holds
 
     uint32_t qa[KSTEPS][2];
-    float o[NBLK][4];          // block j: [0],[1] dims 32c + j and 32c + 16 + j (weights), [2],[3] the corrections
+    float o[NBLK][4];          // block j: [0],[1] dims LANE_DIMS*c + j and + NBLK + j (weights), [2],[3] the corrections
     float m_run, l_run;
 
     __device__ __forceinline__ void setup(int) {}
@@ -886,12 +888,18 @@ struct MmaFp8RegEngine {
         }
     }
 
+    // byte offset of 16-byte chunk `chunk` of row `row` inside a swizzled tile
+    __device__ __forceinline__ static int chunk_off(int row, int chunk) {
+        if constexpr (D == 128) return row * 128 + ((chunk ^ (row & 7)) << 4);
+        else return row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4);
+    }
+
     __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
         const int g = lane >> 2, c = lane & 3;
         if (g < p.group) {
-            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * p.group + g) * p.q_sh + 32 * c;
+            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * p.group + g) * p.q_sh + LANE_DIMS * c;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {   // 4 x 16 bytes = elements 32c + 8v .. 32c + 8v + 7 = k-steps 2v, 2v+1
+            for (int v = 0; v < LANE_DIMS / 8; ++v) {   // 16 bytes = elements 8v .. 8v + 7 of the lane's dims = k-steps 2v, 2v+1
                 const uint4 u = __ldg(reinterpret_cast<const uint4*>(qrow) + v);
                 qa[2 * v][0] = to_half2(u.x); qa[2 * v][1] = to_half2(u.y);
                 qa[2 * v + 1][0] = to_half2(u.z); qa[2 * v + 1][1] = to_half2(u.w);
@@ -912,23 +920,33 @@ struct MmaFp8RegEngine {
         const bool partial = n_valid < kPage || hole_hi > hole_lo;
         auto masked = [&](int tok) { return tok >= n_valid || (tok >= hole_lo && tok < hole_hi); };
 
-        // value rows first: their loads overlap the score computation
+        // value rows first: their loads overlap the score computation.  NBLK bytes per row: dims
+        // [NBLK*g, NBLK*(g+1)) -- a whole 16-byte chunk for D = 128, half a chunk for D = 64.
         const unsigned char* vt = stage + PAGE_BYTES;
-        uint4 vr[4];
+        uint32_t vw[4][NBLK / 4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int row = 2 * c + (i & 1) + (i >> 1) * 8;
-            vr[i] = *reinterpret_cast<const uint4*>(vt + row * 128 + ((g ^ (row & 7)) << 4));
+            if constexpr (D == 128) {
+                const uint4 u = *reinterpret_cast<const uint4*>(vt + chunk_off(row, g));
+                vw[i][0] = u.x; vw[i][1] = u.y; vw[i][2] = u.z; vw[i][3] = u.w;
+            } else {
+                const uint2 u = *reinterpret_cast<const uint2*>(vt + chunk_off(row, g >> 1) + (g & 1) * 8);
+                vw[i][0] = u.x; vw[i][1] = u.y;
+            }
         }
 
         // ---- S^T[head, token] = Q K^T
         float s[2][2];
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
-            const unsigned char* rp = stage + (nb * 8 + g) * 128;   // key row nb*8 + g; its swizzle term is g
-            const uint4 u0 = *reinterpret_cast<const uint4*>(rp + (((2 * c) ^ g) << 4));
-            const uint4 u1 = *reinterpret_cast<const uint4*>(rp + (((2 * c + 1) ^ g) << 4));
-            const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            const int row = nb * 8 + g;
+            uint32_t w[KSTEPS];   // the lane's LANE_DIMS bytes of this key row: word t is k-step t
+#pragma unroll
+            for (int i = 0; i < KSTEPS / 4; ++i) {
+                const uint4 u = *reinterpret_cast<const uint4*>(stage + chunk_off(row, (KSTEPS / 4) * c + i));
+                w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
+            }
             float se[2] = {0.f, 0.f}, so[2] = {0.f, 0.f};
 #pragma unroll
             for (int sp = 0; sp < KSTEPS / 2; ++sp) {
@@ -949,7 +967,10 @@ struct MmaFp8RegEngine {
             // rows that do not count may hold stale bytes (NaN included), and 0 * NaN is NaN in the MMA
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                if (masked(2 * c + (i & 1) + (i >> 1) * 8)) vr[i] = make_uint4(0, 0, 0, 0);
+                if (masked(2 * c + (i & 1) + (i >> 1) * 8)) {
+#pragma unroll
+                    for (int k = 0; k < NBLK / 4; ++k) vw[i][k] = 0u;
+                }
         }
         float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -972,13 +993,11 @@ struct MmaFp8RegEngine {
         const uint32_t pb0 = pack2<TT>(p0 - h01.x, p1 - h01.y), pb2 = pack2<TT>(p2 - h23.x, p3 - h23.y);
 
         // ---- O[head, dim] += P^T V
-        const uint32_t x0[4] = {vr[0].x, vr[0].y, vr[0].z, vr[0].w}, x1[4] = {vr[1].x, vr[1].y, vr[1].z, vr[1].w};
-        const uint32_t y0[4] = {vr[2].x, vr[2].y, vr[2].z, vr[2].w}, y1[4] = {vr[3].x, vr[3].y, vr[3].z, vr[3].w};
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            // bytes (2c, 2c+1) and (2c+8, 2c+9) of dims 4w..4w+3, interleaved into fragment order
-            const uint32_t a01 = byte_perm(x0[w], x1[w], 0x5140u), a23 = byte_perm(x0[w], x1[w], 0x7362u);
-            const uint32_t b01 = byte_perm(y0[w], y1[w], 0x5140u), b23 = byte_perm(y0[w], y1[w], 0x7362u);
+        for (int w = 0; w < NBLK / 4; ++w) {
+            // bytes of rows (2c, 2c+1) and (2c+8, 2c+9) for dims 4w..4w+3 of the lane's chunk, interleaved into fragment order
+            const uint32_t a01 = byte_perm(vw[0][w], vw[1][w], 0x5140u), a23 = byte_perm(vw[0][w], vw[1][w], 0x7362u);
+            const uint32_t b01 = byte_perm(vw[2][w], vw[3][w], 0x5140u), b23 = byte_perm(vw[2][w], vw[3][w], 0x7362u);
             mma_m16n8k16<TT>(o[4 * w], pa0, pb0, pa2, pb2, cvt_e4m3x2_to_f16x2((uint16_t)(a01 & 0xffffu)),
                              cvt_e4m3x2_to_f16x2((uint16_t)(b01 & 0xffffu)));
             mma_m16n8k16<TT>(o[4 * w + 1], pa0, pb0, pa2, pb2, cvt_e4m3x2_to_f16x2((uint16_t)(a01 >> 16)),
@@ -996,13 +1015,13 @@ struct MmaFp8RegEngine {
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
         if (g < G) {
-            float* dst = my_o + g * D + 32 * c;
+            float* dst = my_o + g * D + LANE_DIMS * c;
 #pragma unroll
             for (int j = 0; j < NBLK; j += 4) {
                 *reinterpret_cast<float4*>(dst + j) = make_float4(o[j][0] + o[j][2], o[j + 1][0] + o[j + 1][2],
                                                                   o[j + 2][0] + o[j + 2][2], o[j + 3][0] + o[j + 3][2]);
-                *reinterpret_cast<float4*>(dst + 16 + j) = make_float4(o[j][1] + o[j][3], o[j + 1][1] + o[j + 1][3],
-                                                                       o[j + 2][1] + o[j + 2][3], o[j + 3][1] + o[j + 3][3]);
+                *reinterpret_cast<float4*>(dst + NBLK + j) = make_float4(o[j][1] + o[j][3], o[j + 1][1] + o[j + 1][3],
+                                                                         o[j + 2][1] + o[j + 2][3], o[j + 3][1] + o[j + 3][3]);
             }
             if (c == 0) {
                 my_ml[g * 2] = (m_run == -INFINITY) ? -INFINITY : m_run * p.scale_log2;
@@ -1549,20 +1568,23 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // 4-D map of a page pool: (head_dim, token in page, page, kv head); box = one 128-byte column tile
-// of one page (16 rows x 128 bytes: 64 16-bit or 128 8-bit elements), 128-byte swizzle.  Returns false if the driver rejects the
-// geometry (the caller then uses the CUDA-core engine).
+// of one page (16 rows x 128 bytes: 64 16-bit or 128 8-bit elements), 128-byte swizzle -- or, for 8-bit
+// pools with head_dim 64, the whole 16 x 64-byte page with 64-byte swizzle.  Returns false if the driver
+// rejects the geometry (the caller then uses another engine).
 bool encode_pool_map(CUtensorMap* tm, const void* pool, CUtensorMapDataType type, int64_t esz, int64_t D,
                      int64_t num_pages, int64_t Hkv, int64_t sp_bytes, int64_t sh_bytes) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t gdim[4] = {(cuuint64_t)D, (cuuint64_t)kPage, (cuuint64_t)num_pages, (cuuint64_t)Hkv};
     const cuuint64_t gstride[3] = {(cuuint64_t)(D * esz), (cuuint64_t)sp_bytes, (cuuint64_t)sh_bytes};
-    const cuuint32_t box[4] = {(cuuint32_t)(128 / esz), (cuuint32_t)kPage, 1, 1};
+    const int64_t row_bytes = D * esz < 128 ? D * esz : 128;   // 64 only for 8-bit pools with head_dim 64
+    if (row_bytes != 128 && row_bytes != 64) return false;
+    const cuuint32_t box[4] = {(cuuint32_t)(row_bytes / esz), (cuuint32_t)kPage, 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = fn(tm, type, 4,
                           const_cast<void*>(pool), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
@@ -1738,17 +1760,28 @@ int dispatch_fp8(int D, int G_real, int Hkv, const DecodeParams& p, int B, cudaS
         return set_error(IVAB_ERR_UNSUPPORTED, "8-bit KV decode: q_heads/kv_heads = %d (supported: 1 to 8)", G_real);
     const int G = G_real <= 2 ? G_real : (G_real <= 4 ? 4 : 8);   // instantiated group sizes; p.group keeps the real one
     const bool simt = G < tc_min_group(2) || !(p.scale_log2 > 0.f);
-    if (G >= tc_min_group(1) && p.scale_log2 > 0.f && D == 128 && use_fp8_register_engine() &&
+    // head_dim 128: every ratio; head_dim 64: grouped queries (multi-head attention stays on CUDA cores there)
+    if ((D == 128 || D == 64) && G >= tc_min_group(D == 128 ? 1 : 2) && p.scale_log2 > 0.f && use_fp8_register_engine() &&
         encode_pool_map(&tm.k, p.k_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,
                         p.pool_sh_bytes) &&
         encode_pool_map(&tm.v, p.v_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,
                         p.pool_sh_bytes)) {
-        switch (G) {
-            case 2: return launch_decode<T, 128, 2, kEngMmaFp8Reg, F8>(p, tm, B, st);
-            case 4: return launch_decode<T, 128, 4, kEngMmaFp8Reg, F8>(p, tm, B, st);
-            case 8: return launch_decode<T, 128, 8, kEngMmaFp8Reg, F8>(p, tm, B, st);
-            case 1: return launch_decode<T, 128, 1, kEngMmaFp8Reg, F8>(p, tm, B, st);
-            default: break;
+        if (D == 128) {
+            switch (G) {
+                case 2: return launch_decode<T, 128, 2, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 4: return launch_decode<T, 128, 4, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 8: return launch_decode<T, 128, 8, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 1: return launch_decode<T, 128, 1, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                default: break;
+            }
+        } else {
+            switch (G) {
+                case 2: return launch_decode<T, 64, 2, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 4: return launch_decode<T, 64, 4, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 8: return launch_decode<T, 64, 8, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 1: return launch_decode<T, 64, 1, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                default: break;
+            }
         }
     }
 #define IVAB_FP8_CASE(DD, GG)                                                                   \

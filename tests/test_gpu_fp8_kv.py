@@ -50,7 +50,7 @@ def test_quantising_append_is_bit_exact(dtype, D):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("Hq,Hkv,D", [(4, 4, 128), (8, 2, 128), (8, 4, 64), (16, 2, 128), (32, 8, 128), (16, 8, 128),
+@pytest.mark.parametrize("Hq,Hkv,D", [(4, 4, 128), (8, 2, 128), (8, 4, 64), (16, 2, 128), (32, 8, 128), (16, 8, 128), (16, 4, 64), (16, 2, 64),
                                       (6, 2, 128), (14, 2, 128), (10, 2, 64), (32, 2, 128)])
 def test_decode_on_fp8_pools(dtype, Hq, Hkv, D):
     ctx = torch.tensor([0, 1, 15, 16, 17, 100, 700, 3000])
@@ -74,10 +74,10 @@ def test_decode_on_fp8_pools(dtype, Hq, Hkv, D):
     assert rel < 0.08, f"quantisation error {rel:.3f}"
 
 
-@pytest.mark.parametrize("Hkv", [8, 2])
-def test_fp8_window_and_sinks_and_errors(Hkv):
+@pytest.mark.parametrize("Hkv,D", [(8, 128), (2, 128), (2, 64)])
+def test_fp8_window_and_sinks_and_errors(Hkv, D):
     ctx = torch.tensor([300, 47, 5000])
-    wl, k8, v8 = _fp8_workload(ctx, 8, Hkv, 128, torch.bfloat16, 9, 0.02, 0.02)
+    wl, k8, v8 = _fp8_workload(ctx, 8, Hkv, D, torch.bfloat16, 9, 0.02, 0.02)
     begin = torch.tensor([261, 10, 4000])
     d = wl.to(DEV)
     out, lse = iva_b200.paged_decode_attention(d.q, k8.to(DEV), v8.to(DEV), d.block_table, d.ctx_len, 16, wl.scale,
