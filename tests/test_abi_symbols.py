@@ -63,3 +63,20 @@ def test_plain_c_client_binds_and_validates(built_library, tmp_path):
                     os.path.join(ROOT, "tests", "abi_client.c"), "-o", exe, "-ldl"], check=True)
     res = subprocess.run([exe, built_library], capture_output=True, text=True, timeout=120)
     assert res.returncode == 0 and "abi client ok" in res.stdout, res.stdout + res.stderr
+
+
+def test_workspace_size_follows_the_head_grouping(built_library):
+    """Head ratios above 8 are served as equal groups of at most 8 query heads, each numbered like a
+    KV head of its own: 32 query / 2 KV heads (ratio 16 = 2 x 8) plans -- and sizes its workspace --
+    like 32 / 4.  Host-side arithmetic only."""
+    lib = iva_b200.load_library()
+
+    def need(b, hq, hkv, d):
+        n = ctypes.c_size_t(0)
+        assert lib.ivab_decode_workspace_bytes(b, hq, hkv, d, ctypes.byref(n)) == 0
+        return n.value
+
+    assert need(8, 32, 2, 128) == need(8, 32, 4, 128)        # 16 -> 2 groups of 8
+    assert need(8, 24, 2, 128) == need(8, 24, 4, 128)        # 12 -> 2 groups of 6
+    assert need(8, 64, 1, 128) == need(8, 64, 8, 128)        # multi-query, 64 -> 8 groups of 8
+    assert need(8, 18, 2, 64) == need(8, 18, 6, 64)          # 9 -> 3 groups of 3
