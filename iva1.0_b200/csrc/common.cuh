@@ -101,7 +101,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
 }
 
-// ---- TMA bulk copy (global -> shared, no multicast) --------------------------------------------
+// ---- TMA bulk copy (global -> shared, this CTA only) --------------------------------------------
 
 __device__ __forceinline__ void tma_bulk_g2s(uint32_t dst_smem, const void* src_global, uint32_t bytes,
                                              uint32_t bar) {
@@ -135,7 +135,7 @@ __device__ __forceinline__ void tma_tile4d_g2s_hint(uint32_t dst_smem, const voi
         : "memory");
 }
 
-// Tiled TMA copy (4-D tensor map, no multicast): one box lands in shared memory with the swizzle
+// Tiled TMA copy (4-D tensor map, this CTA only): one box lands in shared memory with the swizzle
 // recorded in the map.  The innermost coordinate times the element size must be a multiple of 16.
 __device__ __forceinline__ void tma_tile4d_g2s(uint32_t dst_smem, const void* tensor_map, int c0, int c1, int c2,
                                                int c3, uint32_t bar) {
