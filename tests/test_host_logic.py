@@ -59,6 +59,27 @@ def test_cache_bookkeeping_without_a_gpu():
         c._reserve([65, 1])                # beyond the block table
 
 
+def test_window_eviction_bookkeeping_without_a_gpu():
+    c = PagedKVCache(batch_size=2, n_heads=1, head_dim=16, seq_len=0, device="cpu", dtype=torch.float32,
+                     num_pages=12, max_seq_len=96, shuffle_seed=3)
+    c._reserve([80, 40])                      # 5 + 3 pages
+    assert c.free_pages == 4
+    pages0 = list(c._tables[0])
+    # window starts at 50 / 20: pages wholly before it go back, page 0 stays for the 4 sink tokens
+    freed = c.evict_before([50, 20], keep_sink_tokens=4)
+    assert freed == 2 and c.free_pages == 6
+    assert c._tables[0][:4] == [pages0[0], -1, -1, pages0[3]] and c._tables[1][0] >= 0
+    assert c._bt_host[0, 1].item() == -1 and c._bt_host[0, 2].item() == -1
+    assert c.evict_before([50, 20], keep_sink_tokens=4) == 0          # idempotent
+    assert c.lengths == [80, 40]                                      # positions keep their numbering
+    # a begin beyond the length is clipped to it: the 80 tokens fill pages 0-4 exactly, all of them go
+    assert c.evict_before([10 ** 6, 0]) == 3 and c._tables[0] == [-1] * 5
+    c._reserve([81, 40])                                              # the next token opens page 5
+    assert len(c._tables[0]) == 6 and c._tables[0][5] >= 0 and c.slots(0, 80, 81)[0] == c._tables[0][5] * 16
+    with pytest.raises(ValueError):
+        c.compact([torch.ones(80), torch.ones(40)])                   # kept tokens on evicted pages
+
+
 def test_partitioners():
     assert [len(shard_requests(10, 4, r)) for r in range(4)] == [3, 3, 2, 2]
     assert list(shard_requests(10, 4, 3)) == [8, 9]
