@@ -8,7 +8,9 @@
  *
  * Conventions
  *   - All data pointers are CUDA device pointers owned by the caller.  The library
- *     allocates no device memory; scratch space is passed in as `workspace`.
+ *     allocates no device memory at run time; scratch space is passed in as `workspace`.
+ *     (One exception is static: the 8 MiB array behind ivab_paged_decode_attn_noalloc is part
+ *     of the library image and occupies device memory on every GPU that loads the library.)
  *   - Strides are in ELEMENTS of `dtype`.  The innermost (head_dim) axis is contiguous.
  *   - `stream` is a cudaStream_t (NULL = legacy default stream).  Calls only enqueue work.
  *   - Return value: IVAB_OK (0) or a negative IVAB_ERR_* code; ivab_last_error() then
@@ -156,6 +158,10 @@ int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t kv_heads
  * splits into equal groups of at most 8 (16 = 2 x 8, 12 = 2 x 6, 64 = 8 x 8; each group is a work item
  * of its own, so the K/V of that head are read once per group); head_dim 32, 64, 128 (or 256 for
  * 16-bit types), page_size 16.
+ * `dtype` is the type of q and of the pools.  `out_dtype` is the type of `out`: `dtype`, or
+ * IVAB_F32 to receive the kernels' fp32 result without the final rounding to a 16-bit type (the
+ * reference computes and returns fp32 for fp32 inputs, and its gather always returns fp32,
+ * src/kernels_t/kv_ops_triton.py:112); out strides are in elements of `out_dtype`.
  * Enqueues three kernels (plan, split-K attention, logsumexp merge).  ctx_len[s] == 0
  * (or an empty window)
  * yields zeros and -inf.  `workspace` must be 256-byte aligned and hold
@@ -167,19 +173,20 @@ int ivab_paged_decode_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h
                            const int32_t* block_table, int64_t block_table_stride,
                            const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
                            void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
-                           int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
-                           int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
-                           void* workspace, size_t workspace_bytes, void* stream);
+                           int dtype, int out_dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                           int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq,
+                           float scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * ivab_paged_decode_attn on 8-bit (e4m3) pools written by ivab_paged_append_fp8:
  *   K = k_scale * stored, V = v_scale * stored; q, out in `dtype` (IVAB_F16 or IVAB_BF16).
  * Pool strides are in 1-byte elements; head_dim 64 or 128.  The stored values are widened
  * exactly and all arithmetic is fp32, so results equal attention over the dequantised pools to
- * the tolerance of the 16-bit path.  Multi-head attention widens on the fly in the CUDA-core engine
- * (issue-bound; about 1.5x the tokens/s of 16-bit storage); grouped queries widen each page to fp16
- * tiles in shared memory and use the tensor cores (about 0.8-0.9x the tokens/s of 16-bit storage, at
- * half the memory).  bf16 queries are converted to fp16 (saturating) on that path.
+ * the tolerance of the 16-bit path.  With head_dim 128 (every head ratio) and head_dim 64 (grouped
+ * queries) the tensor-core operands are built in registers straight from the stored bytes
+ * (e4m3 -> fp16 is exact), about 1.35-1.7x the tokens/s of 16-bit storage at half the memory;
+ * head_dim 64 multi-head attention widens on the fly on CUDA cores.  bf16 queries are converted to
+ * fp16 (saturating) on the tensor-core path.
  * No counterpart in the reference (fp8 KV is only named in configs/quant_infer.yaml:52).
  */
 int ivab_paged_decode_attn_fp8(const void* q, int64_t q_stride_b, int64_t q_stride_h,
@@ -189,9 +196,9 @@ int ivab_paged_decode_attn_fp8(const void* q, int64_t q_stride_b, int64_t q_stri
                                const int32_t* block_table, int64_t block_table_stride,
                                const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
                                void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
-                               int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
-                               int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
-                               void* workspace, size_t workspace_bytes, void* stream);
+                               int dtype, int out_dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                               int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq,
+                               float scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Copies the status word of the last ivab_paged_decode_attn call on `workspace` to the host
@@ -212,7 +219,7 @@ int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream)
  * 8 MiB until the process exits, whether or not this entry point is ever called.
  *
  * Arguments as ivab_paged_decode_attn; `status` (device int32, may be NULL) receives the
- * IVAB_STATUS_* bits of this call on `stream`.  Limits and rules:
+ * IVAB_STATUS_* bits of this call on `stream` (0 when batch is 0).  Limits and rules:
  *   - the problem must fit: ivab_decode_workspace_bytes(batch, ...) <= 8 MiB, else
  *     IVAB_ERR_WORKSPACE (e.g. 128 sequences x 32 query / 8 KV heads x head_dim 128 needs 6.9 MiB);
  *   - calls no cudaMalloc / cudaFree or other allocating routine;
@@ -220,7 +227,8 @@ int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream)
  *     current); make that first call outside any stream capture;
  *   - all calls on a device share the one array, which keeps the previous call's contents (the
  *     kernels re-initialise what they read): two calls that overlap on the GPU -- different
- *     streams, or different host threads -- race.  Serialise them.
+ *     streams, or different host threads -- race.  Serialise them.  (Looking up the array's
+ *     address is itself safe from several host threads at once.)
  */
 int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                                    const void* k_pool, const void* v_pool,
@@ -228,9 +236,9 @@ int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b, int64_t q_
                                    const int32_t* block_table, int64_t block_table_stride,
                                    const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
                                    void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
-                                   int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
-                                   int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
-                                   int32_t* status, void* stream);
+                                   int dtype, int out_dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                                   int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq,
+                                   float scale, int32_t* status, void* stream);
 
 /*
  * Number of kernels of this library launched by the calling process since load

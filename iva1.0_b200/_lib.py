@@ -36,13 +36,13 @@ SIGNATURES = {
     "ivab_decode_workspace_bytes": (c_int, [c_int64, c_int64, c_int64, c_int64, POINTER(c_size_t)]),
     "ivab_paged_decode_attn": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                        c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
-                                       c_int] + [c_int64] * 7 + [c_float, c_void_p, c_size_t, c_void_p]),
+                                       c_int, c_int] + [c_int64] * 7 + [c_float, c_void_p, c_size_t, c_void_p]),
     "ivab_paged_decode_attn_noalloc": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                                c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
-                                               c_int] + [c_int64] * 7 + [c_float, c_void_p, c_void_p]),
+                                               c_int, c_int] + [c_int64] * 7 + [c_float, c_void_p, c_void_p]),
     "ivab_paged_decode_attn_fp8": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                            c_float, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
-                                           c_void_p, c_int64, c_int64, c_void_p, c_int] + [c_int64] * 7 +
+                                           c_void_p, c_int64, c_int64, c_void_p, c_int, c_int] + [c_int64] * 7 +
                                    [c_float, c_void_p, c_size_t, c_void_p]),
     "ivab_decode_status": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
     "ivab_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),

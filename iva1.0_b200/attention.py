@@ -28,7 +28,8 @@ from .kv_ops import _pool_strides
 __all__ = ["paged_decode_attention", "attention", "AttentionB200", "get_attention", "decode_workspace_bytes",
            "decode_status"]
 
-_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}   # insertion order = least recently used first
+_MAX_WORKSPACES = 8
 
 
 def decode_workspace_bytes(batch: int, q_heads: int, kv_heads: int, head_dim: int) -> int:
@@ -43,10 +44,14 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
     """One scratch buffer per (device, stream), grown on demand.  Calls on the same stream are
     ordered, so they can share it; calls on different streams get different buffers."""
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
-    ws = _workspaces.get(key)
+    ws = _workspaces.pop(key, None)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+    _workspaces[key] = ws                       # (re)inserted as the most recently used
+    # Streams come and go; keep the cache bounded.  A dropped buffer was allocated while its stream was
+    # current, so the caching allocator only reuses it in that stream's order -- after the calls that used it.
+    while len(_workspaces) > _MAX_WORKSPACES:
+        _workspaces.pop(next(iter(_workspaces)))
     return ws
 
 
@@ -68,13 +73,15 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
                            lse: Optional[torch.Tensor] = None, return_lse: bool = False,
                            workspace: Optional[torch.Tensor] = None, check: bool = False,
                            ctx_begin: Optional[torch.Tensor] = None, sink_tokens: int = 0,
-                           k_scale: float = 1.0, v_scale: float = 1.0):
+                           k_scale: float = 1.0, v_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None):
     """``out[s,h] = softmax(q[s,h] . K_s^T * scale) . V_s`` over the ``ctx_len[s]`` cached tokens of
     sequence ``s``, K/V read in place from the page pool through ``block_table``.
 
     q ``[B,H_q,D]``; pools ``[1,H_kv,num_pages*page_size,D]`` (or ``[num_pages,H_kv,page_size,D]``);
     ``block_table`` int32 ``[B,max_pages]``; ``ctx_len`` int32 ``[B]``.  ``H_q/H_kv`` from 1 to 8, or larger and divisible into equal groups of at most 8 (12, 16, 32, 64 ...).
     Returns ``out`` (dtype of q) or ``(out, lse)`` with ``lse`` fp32 ``[B,H_q]`` (natural log).
+    ``out_dtype=torch.float32`` (or an fp32 ``out`` tensor) returns the kernels' fp32 result without the
+    final rounding to q's 16-bit type, as the reference does for fp32 inputs.
     ``check=True`` synchronises and raises if the kernels flagged a bad page id / length or a
     timed-out wait.  ``ctx_begin`` (int32 ``[B]``, optional) restricts sequence ``s`` to the keys
     ``ctx_begin[s] <= j < ctx_len[s]`` -- a sliding window; pages wholly before it are not read.
@@ -93,11 +100,11 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         raise ValueError("8-bit pools need fp16 or bf16 queries")
     return _decode(q, k_pool, v_pool, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
                    out, lse, return_lse, workspace, check, ctx_begin, sink_tokens,
-                   (float(k_scale), float(v_scale)) if fp8 else None)
+                   (float(k_scale), float(v_scale)) if fp8 else None, out_dtype)
 
 
 def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
-            out, lse, return_lse, workspace, check, ctx_begin=None, sink_tokens=0, fp8_scales=None):
+            out, lse, return_lse, workspace, check, ctx_begin=None, sink_tokens=0, fp8_scales=None, out_dtype=None):
     """Argument checks and the library call; ``k_base`` / ``v_base`` only supply base pointers, the
     pool geometry is given by ``Hkv, num_pages, sh, sp`` (element strides of head and page)."""
     if q.requires_grad:
@@ -125,10 +132,14 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
             raise ValueError("ctx_begin batch size does not match q")
     if scale is None:
         scale = 1.0 / math.sqrt(D)
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else q.dtype
+    if out_dtype not in (q.dtype, torch.float32):
+        raise ValueError("out_dtype must be q's dtype or torch.float32")
     if out is None:
-        out = torch.empty(B, Hq, D, device=dev, dtype=q.dtype)
-    elif out.shape != (B, Hq, D) or out.dtype != q.dtype or out.stride(-1) != 1:
-        raise ValueError("out must be [B,H_q,D] in q's dtype with a contiguous last axis")
+        out = torch.empty(B, Hq, D, device=dev, dtype=out_dtype)
+    elif out.shape != (B, Hq, D) or out.dtype != out_dtype or out.stride(-1) != 1:
+        raise ValueError("out must be [B,H_q,D] in q's dtype (or fp32) with a contiguous last axis")
     if lse is None and return_lse:
         lse = torch.empty(B, Hq, device=dev, dtype=torch.float32)
     if lse is not None and (lse.shape != (B, Hq) or lse.dtype != torch.float32 or not lse.is_contiguous()):
@@ -140,7 +151,8 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
         tail = (block_table.data_ptr(), block_table.stride(0), ctx_len.data_ptr(),
                 ctx_begin.data_ptr() if ctx_begin is not None else None, int(sink_tokens),
                 out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr() if lse is not None else None,
-                _lib.dtype_code(q.dtype), B, Hq, Hkv, D, page_size, num_pages, block_table.shape[1],
+                _lib.dtype_code(q.dtype), _lib.dtype_code(out_dtype), B, Hq, Hkv, D, page_size, num_pages,
+                block_table.shape[1],
                 float(scale), workspace.data_ptr(), workspace.numel(), stream)
         head = (q.data_ptr(), q.stride(0), q.stride(1), k_base.data_ptr(), v_base.data_ptr(), sh, sp)
         if fp8_scales is None:
@@ -181,14 +193,16 @@ def _dense_as_pool(k: torch.Tensor, v: torch.Tensor):
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, dropout_prob: float = 0.0,
               training: bool = True, *, ctx_len: Optional[torch.Tensor] = None,
-              ctx_begin: Optional[torch.Tensor] = None, return_lse: bool = False):
+              ctx_begin: Optional[torch.Tensor] = None, return_lse: bool = False,
+              out_dtype: Optional[torch.dtype] = None):
     """``softmax(q k^T * scale) v`` on ``[B,H,S,D]`` queries against ``[B,H,L,D]`` keys/values.
 
     Signature of ``attention_triton`` (src/kernels_t/attention_triton.py:215-223).  Every query
     row sees all ``L`` keys (the reference module's behaviour with ``causal=False``,
     src/core/attention.py:77-102); pass ``ctx_len`` (int32 ``[B,S]`` or ``[B]``) to limit the keys
     each query sees, e.g. ``prior + i + 1`` for causal prefill, and ``ctx_begin`` (same shapes) for
-    the first key it sees (sliding window).  Dropout is not implemented:
+    the first key it sees (sliding window).  ``out_dtype=torch.float32`` returns the fp32 result for
+    16-bit inputs.  Dropout is not implemented:
     a non-zero ``dropout_prob`` with ``training=True`` raises, as does ``requires_grad``.
     """
     _lib.require_cuda(q, k, v)
@@ -215,7 +229,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, d
     if ctx_begin is not None:
         cb = ctx_begin.to(device=q.device, dtype=torch.int32)
         cb = (cb.view(B, 1).expand(B, S) if cb.numel() == B else cb.reshape(B, S)).reshape(-1).contiguous()
-    res = _decode(q2, kd, vd, Hkv, n_pages, sh, sp, bt2, cl, _PAGE, scale, None, None, return_lse, None, False, cb)
+    res = _decode(q2, kd, vd, Hkv, n_pages, sh, sp, bt2, cl, _PAGE, scale, None, None, return_lse, None, False, cb,
+                  out_dtype=out_dtype)
     o2, lse = res if return_lse else (res, None)
     o = o2.view(B, S, Hq, D).permute(0, 2, 1, 3)
     if return_lse:

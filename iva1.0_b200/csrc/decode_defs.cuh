@@ -1,6 +1,7 @@
 // Definitions shared by the plan, attention and merge kernels of decode_attn.cu and by the page
 // engines in decode_engines.cuh: constants, the workspace layout, the kernel parameter block and the
-// optional phase-timing macros.  Included by decode_attn.cu only (internal linkage).
+// optional phase-timing macros.  The structs are shared by several translation units (the host side in
+// decode_attn.cu and one unit of kernel instantiations per dtype); constants and helpers are internal.
 #pragma once
 
 #include <cstdint>
@@ -19,6 +20,7 @@ static_assert(kMaxStages % kConsumerWarps == 0, "stage ring must divide among th
 constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
 constexpr int kMinChunkPages = 8;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
+constexpr int kMaxDevices = 64;      // device ordinals the per-device host caches cover
 
 // Optional phase timing (debug builds only, -DIVAB_PROFILE): lane 0 of every warp accumulates
 // clock64() deltas per phase and adds them to 64-bit counters in header words 16..47.
@@ -42,6 +44,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 // header words at the start of the workspace
 enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrNumSplit = 5, kHdrNumBig = 6,
        kHdrWords = 64 };
+
+}  // namespace
 
 struct ChunkDesc {
     int seq, page_begin, n_pages, chunk_idx, n_chunks, pad0, pad1, pad2;
@@ -69,6 +73,7 @@ struct DecodeParams {
     const char* k_pool; const char* v_pool; int64_t pool_sh_bytes, pool_sp_bytes;
     const int32_t* block_table; int64_t bt_stride;
     void* out; int64_t out_sb, out_sh; float* lse;
+    int out_f32;             // out holds fp32 (strides in fp32 elements) instead of q's type
     int Hq, num_pages;
     int group;               // query heads per KV head; the kernels' template group size is this rounded up to 1, 2, 4 or 8
     int kv_div;              // work items number virtual KV heads; virtual head h reads the slab of KV head h / kv_div
@@ -79,6 +84,8 @@ struct DecodeParams {
     uint64_t wait_limit_ns;
     Workspace ws;
 };
+
+namespace {
 
 // v-th page a sequence reads -> index into its block table: `sink_pages` pages from the start, then
 // the window's pages from begin / kPage on.

@@ -1,0 +1,763 @@
+// The persistent split-K attention kernel, the logsumexp merge kernel and their launch code.
+// Included by the per-dtype instantiation units (decode_inst_*.cu); everything here has internal
+// linkage, the units export one dispatch function each (decode_dispatch.h).
+#pragma once
+
+#include <cuda.h>
+
+#include <atomic>
+#include <cstdlib>
+#include <type_traits>
+
+#include "common.cuh"
+#include "decode_defs.cuh"      // constants, workspace layout, kernel parameters
+#include "decode_engines.cuh"   // the page engines and the kernel's shared-memory layout
+
+namespace ivab {
+
+extern std::atomic<long long> g_launches;
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// 2. persistent split-K attention
+// ------------------------------------------------------------------------------------------------
+
+template <typename T, int D, int G, int ENG, typename TKV = T>
+__global__ void __launch_bounds__(kThreads, EngineSelect<ENG, T, TKV, D, G>::type::CTAS_PER_SM)
+decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ TensorMaps tm) {
+    using Eng = typename EngineSelect<ENG, T, TKV, D, G>::type;
+    using C = SmemLayout<Eng::SCRATCH_PER_WARP, D, G>;
+    extern __shared__ unsigned char smem_raw[];
+    // the carve-up assumes a 1 KB-aligned base; the launch reserves 1 KB of slack for this
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stages = p.stages;
+#ifdef IVAB_PROFILE
+    const uint64_t prof_cta_start = globaltimer_ns();
+#endif
+
+    const uint32_t bars = smem_u32(smem + C::OFF_BARS);
+    auto bar_full = [&](int s) { return bars + 8u * s; };
+    auto bar_empty = [&](int s) { return bars + 8u * (kMaxStages + s); };
+    auto bar_item_full = [&](int s) { return bars + 8u * (2 * kMaxStages + s); };
+    auto bar_item_empty = [&](int s) { return bars + 8u * (2 * kMaxStages + kItemRing + s); };
+    const uint32_t bar_combined = bars + 8u * (2 * kMaxStages + 2 * kItemRing);   // phase i completes when item i's states are combined
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT);
+    int* merge_cnt = reinterpret_cast<int*>(smem + C::OFF_ABORT + 4);   // warps that have published the current item
+    volatile int* items = reinterpret_cast<volatile int*>(smem + C::OFF_ITEMS);
+    unsigned char* stage_base = smem + C::OFF_STAGES;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < stages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int s = 0; s < kItemRing; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), kConsumerWarps); }
+        mbar_init(bar_combined, 1);
+        *merge_cnt = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();   // the only CTA-wide barrier: before any warp can have unwound
+
+    // Everything above overlapped the plan kernel; the work list is read from here on.  The merge
+    // kernel may be scheduled as soon as CTAs of this grid retire (it waits for the whole grid).
+    grid_dependency_wait();
+    grid_launch_dependents();
+#ifdef IVAB_PROFILE
+    if (threadIdx.x == 0) {
+        PROF_STAMP_MIN(p.ws.header, 2, prof_cta_start)
+        PROF_STAMP_MIN(p.ws.header, 3, globaltimer_ns())
+    }
+#endif
+
+    const int num_chunks = p.ws.header[kHdrNumChunks];
+    const int total_items = p.ws.header[kHdrTotalItems];
+    int* counter = p.ws.header + kHdrCounter;
+    int* status = p.ws.header + kHdrStatus;
+    const uint64_t limit = p.wait_limit_ns;
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------ producer warp ------------------------------------------
+        // The stage ring is split into one sub-ring per consumer warp (stage = slot*W + warp).
+        // Page k of an item goes to warp (start + k) % W with start = (seq + chunk) % W, so which
+        // warp sums which pages -- and therefore every fp32 rounding -- depends only on the
+        // inputs, never on which CTA happened to pick the item up: results are bit-reproducible.
+        int cnt[kConsumerWarps];   // pages issued to each warp so far
+#pragma unroll
+        for (int i = 0; i < kConsumerWarps; ++i) cnt[i] = 0;
+        const int spw = stages / kConsumerWarps;   // stages per warp
+        int published = 0;  // items published so far
+        bool aborted = false;
+        // The fetch of an item is three dependent global accesses (work counter -> chunk descriptor ->
+        // block-table entries), about a microsecond each under load.  They are software-pipelined
+        // across items: while the pages of item i are being issued, the block-table entries of item
+        // i+1, the descriptor of item i+2 and the id of item i+3 are in flight, so the TMA issue
+        // stream does not pause at item boundaries.
+        auto fetch_id_async = [&]() {   // lane 0 holds the result; broadcast it only when it is needed
+            int v = 0;
+            if (lane == 0) v = (int)gridDim.x + atomicAdd(counter, 1);
+            return v;
+        };
+        auto fetch_id = [&]() { return __shfl_sync(0xffffffffu, fetch_id_async(), 0); };
+        auto load_desc = [&](int id, int* h_out) {
+            ChunkDesc d{};
+            *h_out = 0;
+            if (id < total_items) {
+                const int h = id / num_chunks;
+                const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + (id - h * num_chunks));
+                // written by the plan kernel of this call, which may still have been running when this
+                // CTA started: not read-only data, so no ld.global.nc here
+                const int4 a = __ldcg(src), b = __ldcg(src + 1);
+                d.seq = a.x; d.page_begin = a.y; d.n_pages = a.z; d.chunk_idx = a.w; d.n_chunks = b.x; d.pad0 = b.y;
+                d.pad1 = b.z; d.pad2 = b.w;
+                *h_out = h;
+            }
+            return d;
+        };
+        auto load_pages = [&](const ChunkDesc& d, int p0) {   // this lane's entry of a 32-page batch
+            // (the value is validated where it is used, so that this load stays a prefetch)
+            int mine = 0;
+            if (p0 + lane < d.n_pages)
+                mine = __ldg(p.block_table + (int64_t)d.seq * p.bt_stride +
+                             page_of(d.page_begin + p0 + lane, d.pad2, d.pad1));
+            return mine;
+        };
+        PROF_DECL
+        const uint64_t stream_policy = l2_policy_evict_first();   // K/V pages are read once
+        // the first item of a CTA is its own index (no round trip to the work counter before the
+        // first page can be requested); the counter hands out the items from gridDim.x on
+        int id0 = (int)blockIdx.x, id1 = fetch_id(), id2 = fetch_id();
+        int h0, h1;
+        ChunkDesc d0 = load_desc(id0, &h0);
+        ChunkDesc d1 = load_desc(id1, &h1);
+        int bt0 = id0 < total_items ? load_pages(d0, 0) : 0;
+        for (;;) {
+            const int item = id0, h = h0;
+            const ChunkDesc d = d0;
+            const bool done = item >= total_items;
+            // prefetch for the following items (ids past the end of the list load nothing)
+            int bt1 = 0, h2 = 0, id3_raw = 0;
+            ChunkDesc d2{};
+            if (!done) {
+                if (id1 < total_items) bt1 = load_pages(d1, 0);
+                d2 = load_desc(id2, &h2);
+                id3_raw = fetch_id_async();
+            }
+            PROF_MARK(0)   // fetch / prefetch issue
+            const int slot = published % kItemRing;
+            if (!mbar_wait_bounded(bar_item_empty(slot), ((published / kItemRing) & 1) ^ 1, abort_flag, limit)) {
+                aborted = true; break;
+            }
+            PROF_MARK(1)   // wait for a free item slot
+            if (lane == 0) {
+                volatile int* it = items + slot * kItWords;
+                it[kItSeq] = d.seq; it[kItHead] = h; it[kItPages] = done ? -1 : d.n_pages;
+                it[kItPageBegin] = d.page_begin; it[kItChunks] = d.n_chunks; it[kItIndex] = item;
+                it[kItStart] = (d.seq + d.chunk_idx) % kConsumerWarps; it[kItLen] = d.pad0; it[kItBegin] = d.pad1; it[kItSinkPages] = d.pad2;
+                mbar_arrive(bar_item_full(slot));
+            }
+            ++published;
+            if (done) break;
+
+            const int slab = h / p.kv_div;   // the KV head whose pages this item reads
+            const char* kbase = p.k_pool + (int64_t)slab * p.pool_sh_bytes;
+            const char* vbase = p.v_pool + (int64_t)slab * p.pool_sh_bytes;
+            const int start = (d.seq + d.chunk_idx) % kConsumerWarps;
+            for (int p0 = 0; p0 < d.n_pages && !aborted; p0 += 32) {
+                const int mine = p0 == 0 ? bt0 : load_pages(d, p0);
+                const int in_batch = min(32, d.n_pages - p0);
+                PROF_MARK(2)   // block-table entries available
+                // Pages are issued a ring's worth at a time, ONE LANE PER PAGE: every lane waits for
+                // its own stage and issues its own copies, so the issue cost of up to `stages` pages
+                // overlaps.  A sub-batch never exceeds the ring (spw pages per consumer warp): a lane
+                // must not wait two phases ahead of a stage's barrier.
+                for (int q0 = 0; q0 < in_batch && !aborted; q0 += stages) {
+                    const int nb = min(stages, in_batch - q0);
+                    int pid = __shfl_sync(0xffffffffu, mine, (q0 + lane) & 31);
+                    if (lane < nb && (pid < 0 || pid >= p.num_pages)) {
+                        atomicOr(status, kStatusBadPage);   // flagged, and page 0 is read instead of faulting
+                        pid = 0;
+                    }
+                    const int b0 = (start + p0 + q0) & (kConsumerWarps - 1);
+                    const int w = (b0 + lane) & (kConsumerWarps - 1);          // consumer warp of this lane's page
+                    const int nth = lane >> 2;                                  // its rank among that warp's pages here
+                    int base_c = 0;
+#pragma unroll
+                    for (int i = 0; i < kConsumerWarps; ++i) if (i == w) base_c = cnt[i];
+                    const int c = base_c + nth;
+                    bool fail = false;
+                    if (lane < nb) {
+                        const int stage = (c % spw) * kConsumerWarps + w;
+                        if (!mbar_wait_bounded(bar_empty(stage), ((c / spw) & 1) ^ 1, abort_flag, limit)) {
+                            fail = true;
+                        } else {
+                            const uint32_t dst = smem_u32(stage_base + (size_t)stage * Eng::STAGE_BYTES);
+                            mbar_arrive_expect_tx(bar_full(stage), Eng::STAGE_BYTES);
+                            if constexpr (Eng::kTiled) {
+#pragma unroll
+                                for (int t = 0; t < Eng::TILES; ++t) {
+                                    tma_tile4d_g2s_hint(dst + t * Eng::TILE_BYTES, &tm.k, t * Eng::TILE_COLS, 0, pid, slab, bar_full(stage),
+                                                        stream_policy);
+                                    tma_tile4d_g2s_hint(dst + Eng::PAGE_BYTES + t * Eng::TILE_BYTES, &tm.v, t * Eng::TILE_COLS, 0, pid, slab,
+                                                        bar_full(stage), stream_policy);
+                                }
+                            } else {
+                                tma_bulk_g2s_hint(dst, kbase + (int64_t)pid * p.pool_sp_bytes, Eng::PAGE_BYTES, bar_full(stage),
+                                                  stream_policy);
+                                tma_bulk_g2s_hint(dst + Eng::PAGE_BYTES, vbase + (int64_t)pid * p.pool_sp_bytes,
+                                                  Eng::PAGE_BYTES, bar_full(stage), stream_policy);
+                            }
+                        }
+                    }
+                    if (__any_sync(0xffffffffu, fail)) aborted = true;
+                    // pages handed to consumer warp i in this sub-batch: lanes r_i, r_i+4, ... below nb
+#pragma unroll
+                    for (int i = 0; i < kConsumerWarps; ++i) {
+                        const int r_i = (i - b0) & (kConsumerWarps - 1);
+                        cnt[i] += nb > r_i ? (nb - r_i + kConsumerWarps - 1) / kConsumerWarps : 0;
+                    }
+                    PROF_MARK(3)   // stage wait + TMA issue of a sub-batch
+                }
+            }
+            PROF_MARK(4)   // TMA issue
+            if (aborted) break;
+            id0 = id1; h0 = h1; d0 = d1; bt0 = bt1;
+            id1 = id2; h1 = h2; d1 = d2;
+            id2 = __shfl_sync(0xffffffffu, id3_raw, 0);
+        }
+        PROF_FLUSH(0)
+        if (aborted) {
+            if (lane == 0) atomicOr(status, kStatusWaitTimeout);
+            // Copies already issued still target this CTA's shared memory: give each of the
+            // most recent `stages` copies a bounded chance to land before the CTA retires.
+            volatile int no_abort = 0;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                // the copy whose empty-wait just failed was counted but never issued
+                for (int m = cnt[w] > spw ? cnt[w] - spw : 0; m < cnt[w]; ++m)
+                    mbar_wait_bounded(bar_full((m % spw) * kConsumerWarps + w), (m / spw) & 1, &no_abort,
+                                      limit < 100000000ull ? limit : 100000000ull);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------- consumer warps --------------------------------------------
+    unsigned char* scratch = smem + C::OFF_SCRATCH + warp * Eng::SCRATCH_PER_WARP;   // this warp's private scratch
+    float* mrg_ml = reinterpret_cast<float*>(smem + C::OFF_MRG_ML);
+    float* mrg_o = reinterpret_cast<float*>(smem + C::OFF_MRG_O);
+    T* outg = static_cast<T*>(p.out);
+    Eng eng;
+    eng.setup(lane);
+
+    const int spw = stages / kConsumerWarps;   // stages of this warp's sub-ring
+    int taken = 0;      // pages this warp has consumed so far (position in its sub-ring)
+    int consumed = 0;   // items consumed
+    PROF_DECL
+    for (;;) {
+        const int slot = consumed % kItemRing;
+        if (!mbar_wait_bounded(bar_item_full(slot), (consumed / kItemRing) & 1, abort_flag, limit)) break;
+        PROF_MARK(0)   // wait for the next item
+        volatile int* it = items + slot * kItWords;
+        const int seq = it[kItSeq], h = it[kItHead], n_pages = it[kItPages], page_begin = it[kItPageBegin];
+        const int n_chunks = it[kItChunks], item = it[kItIndex], start = it[kItStart], L = it[kItLen];
+        const int begin = it[kItBegin], sink_pages = it[kItSinkPages];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_item_empty(slot));
+        if (n_pages < 0) break;   // sentinel: the work list is exhausted
+
+        eng.begin_item(p, seq, h, lane);   // query heads of this kv head into registers, state reset
+        PROF_MARK(1)   // q load issue
+
+        bool ok = true;
+        const int k0 = (warp - start + kConsumerWarps) % kConsumerWarps;
+        for (int k = k0; k < n_pages; k += kConsumerWarps, ++taken) {
+            const int stage = (taken % spw) * kConsumerWarps + warp;
+            if (!mbar_wait_bounded(bar_full(stage), (taken / spw) & 1, abort_flag, limit)) { ok = false; break; }
+            PROF_MARK(2)   // wait for page data
+#ifdef IVAB_PROFILE
+            if (taken == 0 && lane == 0) PROF_STAMP_MIN(p.ws.header, 4, globaltimer_ns())
+#endif
+            // Token t of this page is key 16*pg + t.  It counts if it lies below L and outside the
+            // hole [sink, begin) between the sink keys and the window; only the last page of the
+            // sequence, the last sink page and the first window page are cut by these bounds.
+            const int pg = page_of(page_begin + k, sink_pages, begin);
+            const int n_valid = min(kPage, L - pg * kPage);
+            const int hole_lo = min(kPage, max(0, min(p.sink_tokens, begin) - pg * kPage));
+            const int hole_hi = min(kPage, max(0, begin - pg * kPage));
+            eng.page(p, stage_base + (size_t)stage * Eng::STAGE_BYTES, n_valid, hole_lo, hole_hi, lane, scratch);
+            if (lane == 0) mbar_arrive(bar_empty(stage));
+            PROF_MARK(3)   // page math
+        }
+        if (!ok) break;
+
+        // ---- end of item: no CTA-wide barrier.  Every warp publishes its state and moves on to the
+        // next item at once; the warp that arrives LAST combines the four states (always in warp
+        // order 0..3, so the sum does not depend on who arrived when) and writes the result.  A
+        // stalled ring costs bandwidth directly, so three of four sub-rings keep draining while
+        // one warp does the combine.  The scratch is reused by the next item: a warp may overwrite
+        // its state only after the previous item's combine has finished.
+        if (consumed > 0 && !mbar_wait_bounded(bar_combined, (consumed - 1) & 1, abort_flag, limit)) break;
+        PROF_MARK(4)   // wait for the previous combine
+        eng.publish(p, mrg_ml + (warp * G) * 2, mrg_o + (size_t)(warp * G) * D, lane);
+        __threadfence_block();
+        __syncwarp();
+        int arrival = 0;
+        if (lane == 0) arrival = atomicAdd(merge_cnt, 1);
+        arrival = __shfl_sync(0xffffffffu, arrival, 0);
+        if (arrival == kConsumerWarps - 1) {
+            __threadfence_block();
+            const volatile float* all_ml = mrg_ml;
+            const volatile float* all_o = mrg_o;
+            const int Gr = p.group;   // real heads of this KV head: rows Gr..G-1 of the states are padding
+            for (int idx = lane; idx < Gr * D; idx += 32) {
+                const int g = idx / D, dd = idx % D;
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, all_ml[(w * G + g) * 2]);
+                float Lsum = 0.f, O = 0.f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    const float mw = all_ml[(w * G + g) * 2];
+                    const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+                    Lsum = fmaf(all_ml[(w * G + g) * 2 + 1], f, Lsum);
+                    O = fmaf(all_o[(size_t)(w * G + g) * D + dd], f, O);
+                }
+                O *= p.v_scale;
+                const int hq = h * Gr + g;
+                if (n_chunks == 1) {
+                    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+                    const int64_t oi = (int64_t)seq * p.out_sb + (int64_t)hq * p.out_sh + dd;
+                    if (p.out_f32) static_cast<float*>(p.out)[oi] = O * inv;
+                    else Elt<T>::store(outg + oi, O * inv);
+                    if (dd == 0 && p.lse != nullptr)
+                        p.lse[(int64_t)seq * p.Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * 0.6931471805599453f : -INFINITY;
+                } else {
+                    p.ws.part_o[((size_t)item * Gr + g) * D + dd] = O;
+                    if (dd == 0) {
+                        p.ws.part_ml[((size_t)item * Gr + g) * 2] = M;
+                        p.ws.part_ml[((size_t)item * Gr + g) * 2 + 1] = Lsum;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) { *merge_cnt = 0; mbar_arrive(bar_combined); }
+        }
+        PROF_MARK(5)   // publish (+ combine if last)
+        ++consumed;
+    }
+    PROF_FLUSH(8)
+#ifdef IVAB_PROFILE
+    if (lane == 0) {
+        PROF_STAMP_MAX(p.ws.header, 5, globaltimer_ns())
+        atomicMin(reinterpret_cast<unsigned long long*>(p.ws.header + 8), (unsigned long long)globaltimer_ns());   // first warp done
+    }
+#endif
+    if (*abort_flag && threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
+}
+
+// ------------------------------------------------------------------------------------------------
+// 3. logsumexp merge of split-K partials
+// ------------------------------------------------------------------------------------------------
+
+constexpr int kMergeWarps = 8;
+
+// VPL consecutive floats from a pointer aligned to VPL * 4 bytes (at most 16)
+template <int VPL>
+__device__ __forceinline__ void load_row(const float* src, float (&v)[VPL]) {
+    if constexpr (VPL % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < VPL / 4; ++i) {
+            const float4 t = reinterpret_cast<const float4*>(src)[i];
+            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+    } else if constexpr (VPL == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(src);
+        v[0] = t.x; v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) v[i] = src[i];
+    }
+}
+
+// Folds the partial results of the sequences that were split into chunks.  Two passes over the
+// list the plan kernel left behind, both in a fixed summation order, so the result does not depend
+// on scheduling:
+//   A. a sequence of at most kMergeWarpMax chunks: one warp per (sequence, query head); lane j
+//      holds the (max, sum) pair of chunk j, every lane owns D/32 consecutive dims.  No shared
+//      memory, no barrier -- the common case (a few chunks per sequence) costs one round of loads.
+//   B. a sequence of more chunks (one very long context on an otherwise idle GPU): one CTA per
+//      (sequence, query head, 32-dim slice); warp w folds chunks w, w+8, ... against its own running
+//      maximum, the eight warp results are then combined through shared memory.
+template <typename T, int D>
+__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int B, int Hq, int G, Workspace ws, void* out_raw, int out_f32,
+                                                                 int64_t out_sb, int64_t out_sh, float* lse) {
+    T* out = static_cast<T*>(out_raw);          // the output is of q's type T ...
+    float* out32 = static_cast<float*>(out_raw);   // ... or fp32 when out_f32 is set (strides in elements either way)
+    constexpr int VPL = D / 32;   // dims per lane in pass A, 32-dim slices in pass B
+    constexpr float kLn2 = 0.6931471805599453f;
+    grid_dependency_wait();   // the attention kernel's partial results
+#ifdef IVAB_PROFILE
+    if (threadIdx.x == 0) PROF_STAMP_MIN(ws.header, 6, globaltimer_ns())
+#endif
+    const int num_chunks = ws.header[kHdrNumChunks];
+    const int n_small = ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
+    const int n_big = ws.header[kHdrNumBig];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // a lane's VPL outputs go out as one store when every output row is aligned for it
+    constexpr int kVecBytes = VPL * (int)sizeof(T);
+    const bool vec_out = !out_f32 && VPL >= 2 && (sizeof(T) == 2 || VPL % 4 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(out) | (uintptr_t)(out_sb * (int64_t)sizeof(T)) |
+                           (uintptr_t)(out_sh * (int64_t)sizeof(T))) % kVecBytes) == 0;
+
+    // ---- pass A
+    for (int unit = blockIdx.x * kMergeWarps + warp; unit < n_small * Hq; unit += gridDim.x * kMergeWarps) {
+        const int s = ws.split_list[unit / Hq], hq = unit % Hq;
+        const int first = ws.seq_first[s];
+        const int n = ws.seq_count[s];
+        const int h = hq / G, g = hq % G;
+        const size_t item0 = (size_t)h * num_chunks + first;
+        const float* ml = ws.part_ml + (item0 * G + g) * 2;               // chunk j at ml + j*G*2
+        const float* po = ws.part_o + (item0 * G + g) * D + lane * VPL;   // chunk j at po + j*G*D
+
+        float mj = -INFINITY, lj = 0.f;
+        if (lane < n) {
+            const float2 v = *reinterpret_cast<const float2*>(ml + (size_t)lane * G * 2);
+            mj = v.x; lj = v.y;
+        }
+        const float M = warp_max_f32(mj);
+        const float f = (mj == -INFINITY) ? 0.f : fast_exp2(mj - M);
+        float L = lj * f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+
+        float acc[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+        int j = 0;
+        for (; j + 4 <= n; j += 4) {   // four rows in flight
+            float r[4][VPL];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) load_row<VPL>(po + (size_t)(j + u) * G * D, r[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float fu = __shfl_sync(0xffffffffu, f, j + u);
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) acc[i] = fmaf(r[u][i], fu, acc[i]);
+            }
+        }
+        for (; j < n; ++j) {
+            float r[VPL];
+            load_row<VPL>(po + (size_t)j * G * D, r);
+            const float fj = __shfl_sync(0xffffffffu, f, j);
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) acc[i] = fmaf(r[i], fj, acc[i]);
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        const int64_t dst_i = (int64_t)s * out_sb + (int64_t)hq * out_sh + lane * VPL;
+        T* dst = out + dst_i;
+        if (out_f32) {
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) out32[dst_i + i] = acc[i] * inv;
+        } else if (vec_out) {
+            // one store per lane (the output may be pinned host memory, where partial writes are expensive)
+            if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                for (int i = 0; i < VPL; i += 4)
+                    *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
+            } else if constexpr (VPL == 4) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pack2<T>(acc[0] * inv, acc[1] * inv), pack2<T>(acc[2] * inv, acc[3] * inv));
+            } else if constexpr (VPL == 8) {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(pack2<T>(acc[0] * inv, acc[1] * inv), pack2<T>(acc[2] * inv, acc[3] * inv),
+                                                            pack2<T>(acc[4] * inv, acc[5] * inv), pack2<T>(acc[6] * inv, acc[7] * inv));
+            } else {
+                *reinterpret_cast<uint32_t*>(dst) = pack2<T>(acc[0] * inv, acc[1] * inv);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) Elt<T>::store(dst + i, acc[i] * inv);
+        }
+        if (lane == 0 && lse != nullptr) lse[(int64_t)s * Hq + hq] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+    }
+
+    // ---- pass B
+    if (n_big == 0) {
+#ifdef IVAB_PROFILE
+        if (threadIdx.x == 0) PROF_STAMP_MAX(ws.header, 7, globaltimer_ns())
+#endif
+        return;
+    }
+    __shared__ float sh_m[kMergeWarps];
+    __shared__ float sh_l[kMergeWarps];
+    __shared__ float sh_o[kMergeWarps][32];
+    for (int c = blockIdx.x; c < n_big * Hq * VPL; c += gridDim.x) {
+        const int unit = c / VPL, slice = c % VPL;
+        const int s = ws.split_list[B - 1 - unit / Hq], hq = unit % Hq;
+        const int first = ws.seq_first[s];
+        const int n = ws.seq_count[s];
+        const int h = hq / G, g = hq % G;
+        const size_t item0 = (size_t)h * num_chunks + first;
+        const float* ml = ws.part_ml + (item0 * G + g) * 2;
+        const float* po = ws.part_o + (item0 * G + g) * D + slice * 32 + lane;
+
+        float mw = -INFINITY;   // maximum over this warp's chunks
+        for (int j = warp + kMergeWarps * lane; j < n; j += kMergeWarps * 32) mw = fmaxf(mw, ml[(size_t)j * G * 2]);
+        mw = warp_max_f32(mw);
+        float lw = 0.f, acc = 0.f;
+#pragma unroll 8
+        for (int j = warp; j < n; j += kMergeWarps) {
+            const float2 v = *reinterpret_cast<const float2*>(ml + (size_t)j * G * 2);
+            const float fj = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - mw);
+            lw = fmaf(v.y, fj, lw);
+            acc = fmaf(po[(size_t)j * G * D], fj, acc);
+        }
+        sh_o[warp][lane] = acc;
+        if (lane == 0) { sh_m[warp] = mw; sh_l[warp] = lw; }
+        __syncthreads();
+        if (warp == 0) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kMergeWarps; ++w) M = fmaxf(M, sh_m[w]);
+            float L = 0.f, O = 0.f;
+#pragma unroll
+            for (int w = 0; w < kMergeWarps; ++w) {
+                const float fw = (sh_m[w] == -INFINITY) ? 0.f : fast_exp2(sh_m[w] - M);
+                L = fmaf(sh_l[w], fw, L);
+                O = fmaf(sh_o[w][lane], fw, O);
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            const int64_t oi = (int64_t)s * out_sb + (int64_t)hq * out_sh + slice * 32 + lane;
+            if (out_f32) out32[oi] = O * inv;
+            else Elt<T>::store(out + oi, O * inv);
+            if (slice == 0 && lane == 0 && lse != nullptr)
+                lse[(int64_t)s * Hq + hq] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+        }
+        __syncthreads();   // the shared scratch is reused by the next unit
+    }
+#ifdef IVAB_PROFILE
+    if (threadIdx.x == 0) PROF_STAMP_MAX(ws.header, 7, globaltimer_ns())
+#endif
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+
+// cuTensorMapEncodeTiled is a driver entry point; it is looked up through the runtime so that the
+// library does not link against libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// 4-D map of a page pool: (head_dim, token in page, page, kv head); box = one 128-byte column tile
+// of one page (16 rows x 128 bytes: 64 16-bit or 128 8-bit elements), 128-byte swizzle -- or, for 8-bit
+// pools with head_dim 64, the whole 16 x 64-byte page with 64-byte swizzle.  Returns false if the driver
+// rejects the geometry (the caller then uses another engine).
+bool encode_pool_map(CUtensorMap* tm, const void* pool, CUtensorMapDataType type, int64_t esz, int64_t D,
+                     int64_t num_pages, int64_t Hkv, int64_t sp_bytes, int64_t sh_bytes) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[4] = {(cuuint64_t)D, (cuuint64_t)kPage, (cuuint64_t)num_pages, (cuuint64_t)Hkv};
+    const cuuint64_t gstride[3] = {(cuuint64_t)(D * esz), (cuuint64_t)sp_bytes, (cuuint64_t)sh_bytes};
+    const int64_t row_bytes = D * esz < 128 ? D * esz : 128;   // 64 only for 8-bit pools with head_dim 64
+    if (row_bytes != 128 && row_bytes != 64) return false;
+    const cuuint32_t box[4] = {(cuuint32_t)(row_bytes / esz), (cuuint32_t)kPage, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = fn(tm, type, 4,
+                          const_cast<void*>(pool), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Smallest q_heads/kv_heads ratio that takes a tensor-core engine.  By default multi-head attention
+// (ratio 1) on 16-bit pools stays on CUDA cores, where it is HBM-bound, while 8-bit pools with
+// head_dim 128 use the tensor cores at every ratio (the CUDA-core engine is issue-bound on
+// them).  IVAB_TC_MIN_GROUP overrides both thresholds for experiments (1 = always, 99 = never).
+int tc_min_group(int default_value) {
+    static int v = [] {
+        const char* e = std::getenv("IVAB_TC_MIN_GROUP");
+        const int n = e ? std::atoi(e) : 0;
+        return n < 1 ? 0 : n;
+    }();
+    return v ? v : default_value;
+}
+
+// Programmatic dependent launch of the attention and merge kernels; IVAB_PDL=0 turns it off.
+bool use_dependent_launch() {
+    static bool v = [] {
+        const char* e = std::getenv("IVAB_PDL");
+        return !(e && std::atoi(e) == 0);
+    }();
+    return v;
+}
+
+template <typename T, int D, int G, int ENG, typename TKV = T>
+int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStream_t st) {
+    using Eng = typename EngineSelect<ENG, T, TKV, D, G>::type;
+    using C = SmemLayout<Eng::SCRATCH_PER_WARP, D, G>;
+    constexpr int kCtas = Eng::CTAS_PER_SM;
+    DecodeParams p = p0;
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    int max_optin = 0;
+    if (int rc = check_cuda(cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev),
+                            "cudaDeviceGetAttribute")) return rc;
+    int per_sm = 0;
+    if (int rc = check_cuda(cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev),
+                            "cudaDeviceGetAttribute")) return rc;
+    // each resident CTA also pays 1 KB of system-reserved shared memory; 1 KB more is alignment slack
+    int budget = per_sm / kCtas - 1024;
+    if (budget > max_optin) budget = max_optin;
+    int stages = (budget - C::OFF_STAGES - 1024) / Eng::STAGE_BYTES;
+    if (stages > kMaxStages) stages = kMaxStages;
+    // Pages go to consumer warps round-robin.  With a stage count that is a multiple of the warp
+    // count, a stage is always consumed by the same warp, so a warp waiting for the next phase of a
+    // stage has itself consumed the previous one -- the precondition of a parity wait.
+    stages -= stages % kConsumerWarps;
+    if (stages < kConsumerWarps) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for the stage ring");
+    p.stages = stages;
+    const size_t smem = (size_t)C::OFF_STAGES + 1024 + (size_t)stages * Eng::STAGE_BYTES;
+    auto kern = decode_kernel<T, D, G, ENG, TKV>;
+    // one flag per (kernel instantiation, device); concurrent host threads may both set the attribute, which is harmless
+    static std::atomic<bool> configured[kMaxDevices];
+    if (dev < 0 || dev >= kMaxDevices) return set_error(IVAB_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+    if (!configured[dev].load(std::memory_order_acquire)) {
+        if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin),
+                                "cudaFuncSetAttribute")) return rc;
+        configured[dev].store(true, std::memory_order_release);
+    }
+    const int grid = sm_count() * kCtas;
+    // Both launches below are programmatic dependents of the kernel before them (plan -> attention
+    // -> merge): the launch latency and set-up of each overlap the tail of its predecessor.
+    cudaLaunchAttribute pdl{};
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.attrs = &pdl; cfg.numAttrs = use_dependent_launch() ? 1 : 0;
+    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, kern, p, tm), "decode_kernel launch")) return rc;
+    g_launches++;
+
+    // pass A needs a warp, pass B D/32 CTAs per split (sequence, head); how many there are is known only on the device
+    const long long units = (long long)B * p.Hq * (D / 32);
+    const int merge_grid = (int)(units < (long long)sm_count() * 4 ? units : (long long)sm_count() * 4);
+    cfg.gridDim = dim3(merge_grid); cfg.blockDim = dim3(kMergeWarps * 32); cfg.dynamicSmemBytes = 0;
+    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, B, p.Hq, p.group, p.ws, p.out, p.out_f32, p.out_sb,
+                                               p.out_sh, p.lse), "merge_kernel launch")) return rc;
+    g_launches++;
+    return IVAB_OK;
+}
+
+template <typename T> CUtensorMapDataType map_type() {
+    return std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+template <typename T, int D, int G>
+int choose_engine(const DecodeParams& p, int B, int Hkv, cudaStream_t st) {
+    TensorMaps tm{};
+    if constexpr (sizeof(T) == 2 && D % 64 == 0) {
+        if (G >= tc_min_group(2) && p.scale_log2 > 0.f &&
+            encode_pool_map(&tm.k, p.k_pool, map_type<T>(), 2, D, p.num_pages, Hkv, p.pool_sp_bytes, p.pool_sh_bytes) &&
+            encode_pool_map(&tm.v, p.v_pool, map_type<T>(), 2, D, p.num_pages, Hkv, p.pool_sp_bytes, p.pool_sh_bytes))
+            return launch_decode<T, D, G, kEngMma>(p, tm, B, st);
+    }
+    return launch_decode<T, D, G, kEngSimt>(p, tm, B, st);
+}
+
+template <typename T, int D>
+int dispatch_group(int G, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
+    // the kernels are instantiated for groups of 1, 2, 4 and 8 query heads; other ratios run in the
+    // next larger one with the surplus rows empty (p.group holds the real ratio)
+    switch (G) {
+        case 1: return choose_engine<T, D, 1>(p, B, Hkv, st);
+        case 2: return choose_engine<T, D, 2>(p, B, Hkv, st);
+        case 3: case 4: return choose_engine<T, D, 4>(p, B, Hkv, st);
+        case 5: case 6: case 7: case 8: return choose_engine<T, D, 8>(p, B, Hkv, st);
+        default: return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: q_heads/kv_heads = %d (supported: 1 to 8)", G);
+    }
+}
+
+template <typename T>
+int dispatch_dim(int D, int G, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
+    switch (D) {
+        case 32: return dispatch_group<T, 32>(G, Hkv, p, B, st);
+        case 64: return dispatch_group<T, 64>(G, Hkv, p, B, st);
+        case 128: return dispatch_group<T, 128>(G, Hkv, p, B, st);
+        case 256:
+            if constexpr (sizeof(T) == 2) return dispatch_group<T, 256>(G, Hkv, p, B, st);
+            [[fallthrough]];
+        default:
+            return set_error(IVAB_ERR_UNSUPPORTED,
+                             "decode attention: head_dim %d (supported: 32, 64, 128; 256 for 16-bit types)", D);
+    }
+}
+
+// IVAB_FP8_REG=0 keeps grouped-query 8-bit decode on the engine that widens pages in shared memory.
+bool use_fp8_register_engine() {
+    static bool v = [] {
+        const char* e = std::getenv("IVAB_FP8_REG");
+        return !(e && std::atoi(e) == 0);
+    }();
+    return v;
+}
+
+// 8-bit pools: multi-head attention (one query head per KV head) widens on the fly in the CUDA-core
+// engine; grouped queries use the tensor cores -- with head_dim 128 on fragments built in registers
+// from swizzled byte tiles, otherwise on pages widened to fp16 tiles in shared memory.
+template <typename T>
+int dispatch_fp8(int D, int G_real, int Hkv, const DecodeParams& p, int B, cudaStream_t st) {
+    TensorMaps tm{};
+    using F8 = __nv_fp8_e4m3;
+    if (G_real < 1 || G_real > 8)
+        return set_error(IVAB_ERR_UNSUPPORTED, "8-bit KV decode: q_heads/kv_heads = %d (supported: 1 to 8)", G_real);
+    const int G = G_real <= 2 ? G_real : (G_real <= 4 ? 4 : 8);   // instantiated group sizes; p.group keeps the real one
+    const bool simt = G < tc_min_group(2) || !(p.scale_log2 > 0.f);
+    // head_dim 128: every ratio; head_dim 64: grouped queries (multi-head attention stays on CUDA cores there)
+    if ((D == 128 || D == 64) && G >= tc_min_group(D == 128 ? 1 : 2) && p.scale_log2 > 0.f && use_fp8_register_engine() &&
+        encode_pool_map(&tm.k, p.k_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,
+                        p.pool_sh_bytes) &&
+        encode_pool_map(&tm.v, p.v_pool, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, D, p.num_pages, Hkv, p.pool_sp_bytes,
+                        p.pool_sh_bytes)) {
+        if (D == 128) {
+            switch (G) {
+                case 2: return launch_decode<T, 128, 2, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 4: return launch_decode<T, 128, 4, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 8: return launch_decode<T, 128, 8, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 1: return launch_decode<T, 128, 1, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                default: break;
+            }
+        } else {
+            switch (G) {
+                case 2: return launch_decode<T, 64, 2, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 4: return launch_decode<T, 64, 4, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 8: return launch_decode<T, 64, 8, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                case 1: return launch_decode<T, 64, 1, kEngMmaFp8Reg, F8>(p, tm, B, st);
+                default: break;
+            }
+        }
+    }
+#define IVAB_FP8_CASE(DD, GG)                                                                   \
+    if (D == DD && G == GG)                                                                     \
+        return simt ? launch_decode<T, DD, GG, kEngSimt, F8>(p, tm, B, st)                      \
+                    : launch_decode<T, DD, GG, kEngMmaFp8, F8>(p, tm, B, st);
+    IVAB_FP8_CASE(64, 1) IVAB_FP8_CASE(64, 2) IVAB_FP8_CASE(64, 4) IVAB_FP8_CASE(64, 8)
+    IVAB_FP8_CASE(128, 1) IVAB_FP8_CASE(128, 2) IVAB_FP8_CASE(128, 4) IVAB_FP8_CASE(128, 8)
+#undef IVAB_FP8_CASE
+    return set_error(IVAB_ERR_UNSUPPORTED,
+                     "8-bit KV decode: head_dim %d (supported: 64, 128)", D);
+}
+
+}  // namespace
+}  // namespace ivab

@@ -250,7 +250,8 @@ class PagedKVCache:
     def reset(self, seq: Optional[int] = None) -> None:
         """Return the pages of one sequence (or of all) to the free list."""
         for s in (range(self.batch_size) if seq is None else [seq]):
-            self._free.extend(reversed(self._tables[s]))
+            # entries that evict_before() already handed back are -1: they are not pages
+            self._free.extend(p for p in reversed(self._tables[s]) if p >= 0)
             self._tables[s] = []
             self._lens[s] = 0
             self._len_host[s] = 0

@@ -127,10 +127,17 @@ class HeadParallelDecoder:
         Hl, D = q.shape[1], q.shape[2]
         packed = torch.empty(B, Hl, D + 1, dtype=torch.float32, device=dev)
         gathered = torch.empty(self.world * B, Hl, D + 1, dtype=torch.float32, device=dev)
+        # The graph records the scratch pointer: it must be a buffer this object owns, not the shared
+        # per-stream one, which a later call on the same stream may replace.
+        extra = {}
+        if dev.type == "cuda":
+            from .attention import decode_workspace_bytes
+            n_kv_local = k_pool_local.shape[1]      # both pool layouts keep the KV heads on axis 1
+            extra["workspace"] = torch.empty(decode_workspace_bytes(B, Hl, n_kv_local, D), dtype=torch.uint8, device=dev)
 
         def local():
             out_l, lse_l = self.attn_fn(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale,
-                                        return_lse=True)
+                                        return_lse=True, **extra)
             packed[:, :, :D] = out_l
             packed[:, :, D] = lse_l
 
@@ -144,7 +151,7 @@ class HeadParallelDecoder:
             local()
         full = gathered.view(self.world, B, Hl, D + 1).permute(1, 0, 2, 3)
 
-        def step():
+        def step(_keep=(side, extra)):           # the capture stream and the scratch live as long as the closure
             graph.replay()
             if self.world > 1:
                 dist.all_gather_into_tensor(gathered, packed, group=self.group)

@@ -20,7 +20,7 @@ typedef int (*ivab_paged_append_fn)(const void*, const void*, int64_t, int64_t, 
                                     int64_t, int, int64_t, int64_t, int64_t, int64_t, int64_t, int32_t*, void*);
 typedef int (*ivab_paged_decode_attn_fn)(const void*, int64_t, int64_t, const void*, const void*, int64_t, int64_t,
                                          const int32_t*, int64_t, const int32_t*, const int32_t*, int64_t, void*,
-                                         int64_t, int64_t, float*, int, int64_t, int64_t, int64_t, int64_t, int64_t,
+                                         int64_t, int64_t, float*, int, int, int64_t, int64_t, int64_t, int64_t, int64_t,
                                          int64_t, int64_t, float, void*, size_t, void*);
 
 int main(int argc, char** argv) {
@@ -39,7 +39,7 @@ int main(int argc, char** argv) {
     (void)sizeof(ivab_paged_decode_attn_p == &ivab_paged_decode_attn);
     (void)sizeof(ivab_decode_workspace_bytes_p == &ivab_decode_workspace_bytes);
 
-    if (ivab_version_p() < 100) { fprintf(stderr, "version %d\n", ivab_version_p()); return 1; }
+    if (ivab_version_p() < 110) { fprintf(stderr, "version %d\n", ivab_version_p()); return 1; }
 
     size_t bytes = 0;
     if (ivab_decode_workspace_bytes_p(64, 32, 32, 128, &bytes) != IVAB_OK || bytes == 0) return 1;
@@ -62,8 +62,8 @@ int main(int argc, char** argv) {
     {
         int dummy;
         int rc = ivab_paged_decode_attn_p(&dummy, 4096, 128, &dummy, &dummy, 1 << 20, 4096, (const int32_t*)&dummy, 8,
-                                          (const int32_t*)&dummy, NULL, 0, &dummy, 4096, 128, NULL, IVAB_BF16, 1, 32, 8,
-                                          128, 32, 8, 8, 0.088f, &dummy, 1 << 20, NULL);
+                                          (const int32_t*)&dummy, NULL, 0, &dummy, 4096, 128, NULL, IVAB_BF16, IVAB_BF16, 1,
+                                          32, 8, 128, 32, 8, 8, 0.088f, &dummy, 1 << 20, NULL);
         if (rc != IVAB_ERR_UNSUPPORTED || strstr(ivab_last_error_p(), "page_size") == NULL) {
             fprintf(stderr, "decode rc %d: %s\n", rc, ivab_last_error_p());
             return 1;

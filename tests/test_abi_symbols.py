@@ -33,7 +33,7 @@ def test_library_exports_every_declared_symbol(built_library):
 def test_python_binding_covers_the_header(built_library):
     assert sorted(_lib.SIGNATURES) == _declared()
     lib = iva_b200.load_library()
-    assert lib.ivab_version() >= 100
+    assert lib.ivab_version() >= 110
     assert lib.ivab_last_error() is not None
 
 

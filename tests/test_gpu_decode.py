@@ -11,7 +11,7 @@ import iva_b200
 from iva_b200 import workloads
 from iva_b200.attention import decode_status, decode_workspace_bytes
 from oracle import paged_ref as ref
-from util import assert_attn_close, assert_lse_close
+from util import assert_attn_close, assert_lse_close, check_decode
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -24,6 +24,17 @@ def run_step(wl, check=True):
     lens = (d.ctx_len + 1).contiguous()
     out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, lens, wl.page_size,
                                                wl.scale, return_lse=True, check=check)
+    return d, out, lse
+
+
+def step_and_check(wl, out_ref, lse_ref):
+    """run_step, checked with the output in q's type and again with the fp32 output (check_decode)."""
+    d = wl.to(DEV)
+    iva_b200.paged_append(d.k_pool, d.v_pool, d.slot_mapping, d.k_new, d.v_new, wl.page_size, check=True)
+    lens = (d.ctx_len + 1).contiguous()
+    out, lse = check_decode(lambda od: iva_b200.paged_decode_attention(
+        d.q, d.k_pool, d.v_pool, d.block_table, lens, wl.page_size, wl.scale, return_lse=True, check=True,
+        out_dtype=od), out_ref, lse_ref, wl.dtype)
     return d, out, lse
 
 
@@ -53,9 +64,7 @@ def test_page_boundary_contexts(dtype, D, group):
     wl = workloads.make_decode_workload("edge", ctx, n_q_heads=2 * group, n_kv_heads=2, head_dim=D, dtype=dtype,
                                         seed=group * 10 + D, free_frac=0.2, poison_unused=True)
     _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
-    _, out, lse = run_step(wl)
-    assert_attn_close(out, out_ref, dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    step_and_check(wl, out_ref, lse_ref)
 
 
 @pytest.mark.parametrize("dtype,Hq,Hkv,D", [(torch.bfloat16, 32, 2, 128), (torch.float16, 24, 2, 64),
@@ -66,9 +75,7 @@ def test_head_ratios_above_eight(dtype, Hq, Hkv, D):
     wl = workloads.make_decode_workload("ratio", ctx, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, dtype=dtype,
                                         seed=Hq + D, free_frac=0.2, poison_unused=True)
     _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
-    _, out, lse = run_step(wl)
-    assert_attn_close(out, out_ref, dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    step_and_check(wl, out_ref, lse_ref)
 
 
 def test_empty_sequence_gives_zeros_and_minus_inf():
@@ -78,8 +85,9 @@ def test_empty_sequence_gives_zeros_and_minus_inf():
                                                return_lse=True, check=True)
     assert not out[1].any() and torch.isinf(lse[1]).all() and (lse[1] < 0).all()
     out_ref, lse_ref = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16)
-    assert_attn_close(out, out_ref, wl.dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    check_decode(lambda od: iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16,
+                                                            return_lse=True, check=True, out_dtype=od),
+                 out_ref, lse_ref, wl.dtype)
 
 
 @pytest.mark.parametrize("dtype,Hq,Hkv", [(torch.bfloat16, 32, 32), (torch.bfloat16, 32, 8), (torch.float16, 16, 4)])
@@ -135,10 +143,10 @@ def test_page_major_pool_layout():
     P = wl.num_pages
     to_pm = lambda t: t.view(4, P, 16, 128).permute(1, 0, 2, 3).contiguous().to(DEV)
     d = wl.to(DEV)
-    out, lse = iva_b200.paged_decode_attention(d.q, to_pm(wl.k_pool[0]), to_pm(wl.v_pool[0]), d.block_table,
-                                               d.ctx_len, 16, return_lse=True, check=True)
-    assert_attn_close(out, out_ref, wl.dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    kpm, vpm = to_pm(wl.k_pool[0]), to_pm(wl.v_pool[0])
+    check_decode(lambda od: iva_b200.paged_decode_attention(d.q, kpm, vpm, d.block_table, d.ctx_len, 16,
+                                                            return_lse=True, check=True, out_dtype=od),
+                 out_ref, lse_ref, wl.dtype)
 
 
 def test_bad_page_id_and_length_are_flagged_not_dereferenced():
@@ -195,10 +203,9 @@ def test_attention_operator_on_dense_tensors(dtype, L):
     v = torch.randn(B, H, L, D, generator=g).to(dtype)
     scale = 1 / math.sqrt(D)
     want, lse_want = ref.attention_math_ref(q, k, v, scale)
-    got, lse = iva_b200.attention(q.to(DEV), k.to(DEV), v.to(DEV), scale, 0.0, False, return_lse=True)
+    got, lse = check_decode(lambda od: iva_b200.attention(q.to(DEV), k.to(DEV), v.to(DEV), scale, 0.0, False,
+                                                          return_lse=True, out_dtype=od), want, lse_want, dtype)
     assert got.shape == (B, H, 1, D) and got.dtype == dtype
-    assert_attn_close(got, want, dtype, strict=False)
-    assert_lse_close(lse, lse_want)
 
 
 def test_attention_operator_multi_query_and_errors():
@@ -265,10 +272,9 @@ def test_sliding_window_begin(dtype, Hq, Hkv, D):
     out_ref, lse_ref = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16, wl.scale,
                                             ctx_begin=begin)
     d = wl.to(DEV)
-    out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16, wl.scale,
-                                               return_lse=True, check=True, ctx_begin=begin.to(DEV))
-    assert_attn_close(out, out_ref, dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    out, lse = check_decode(lambda od: iva_b200.paged_decode_attention(
+        d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16, wl.scale, return_lse=True, check=True,
+        ctx_begin=begin.to(DEV), out_dtype=od), out_ref, lse_ref, dtype)
     assert not out[4].any() and torch.isinf(lse[4]).all()
 
 
@@ -330,10 +336,9 @@ def test_attention_sinks_in_front_of_a_window(dtype, Hq, Hkv, D, sink):
                 pg = int(wl.block_table[s, pidx])
                 kp[:, :, pg * 16:(pg + 1) * 16] = float("nan")
                 vp[:, :, pg * 16:(pg + 1) * 16] = float("nan")
-    out, lse = iva_b200.paged_decode_attention(d.q, kp, vp, d.block_table, d.ctx_len, 16, wl.scale, return_lse=True,
-                                               check=True, ctx_begin=begin.to(DEV), sink_tokens=sink)
-    assert_attn_close(out, out_ref, dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    check_decode(lambda od: iva_b200.paged_decode_attention(
+        d.q, kp, vp, d.block_table, d.ctx_len, 16, wl.scale, return_lse=True, check=True, ctx_begin=begin.to(DEV),
+        sink_tokens=sink, out_dtype=od), out_ref, lse_ref, dtype)
 
 
 def test_module_window_with_sinks_on_a_paged_cache():
@@ -376,9 +381,7 @@ def test_long_and_short_chunk_lists_merge_in_one_call(dtype, D):
     wl = workloads.make_decode_workload("mixed", ctx, n_q_heads=8, n_kv_heads=2, head_dim=D, dtype=dtype, seed=77,
                                         free_frac=0.05, poison_unused=True)
     _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
-    d, out, lse = run_step(wl)
-    assert_attn_close(out, out_ref, dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    d, out, lse = step_and_check(wl, out_ref, lse_ref)
     B, Hq = 5, 8
     flat = torch.empty(B * Hq * D + 8, device=DEV, dtype=dtype)
     odd = flat[1:1 + B * Hq * D].view(B, Hq, D)

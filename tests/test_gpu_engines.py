@@ -17,7 +17,7 @@ sys.path.insert(0, {root!r}); sys.path.insert(0, {root!r} + "/tests")
 import iva_b200
 from iva_b200 import workloads
 from oracle import paged_ref as ref
-from util import assert_attn_close, assert_lse_close
+from util import check_decode
 for dtype in (torch.bfloat16, torch.float16):
     for hq, hkv, D in ((4, 4, 128), (8, 2, 128), (16, 2, 64), (8, 4, 256)):
         ctx = torch.tensor([0, 1, 15, 16, 17, 100, 333, 2500])
@@ -26,10 +26,10 @@ for dtype in (torch.bfloat16, torch.float16):
         _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
         d = wl.to("cuda")
         iva_b200.paged_append(d.k_pool, d.v_pool, d.slot_mapping, d.k_new, d.v_new, 16, check=True)
-        out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, (d.ctx_len + 1).contiguous(),
-                                                   16, return_lse=True, check=True)
-        assert_attn_close(out, out_ref, dtype, strict=False)
-        assert_lse_close(lse, lse_ref)
+        lens = (d.ctx_len + 1).contiguous()
+        check_decode(lambda od: iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, lens, 16,
+                                                                return_lse=True, check=True, out_dtype=od),
+                     out_ref, lse_ref, dtype)
 # 8-bit pools: the same thresholds move these between the CUDA-core and the tensor-core engines
 for hq, hkv, D in ((4, 4, 128), (8, 2, 128), (4, 4, 64)):
     ctx = torch.tensor([0, 1, 15, 16, 17, 100, 333, 2500])
@@ -37,12 +37,11 @@ for hq, hkv, D in ((4, 4, 128), (8, 2, 128), (4, 4, 64)):
                                         seed=hq + D, free_frac=0.3, poison_unused=True)
     k8, v8 = ref.quantize_fp8_ref(wl.k_pool, 0.02).cuda(), ref.quantize_fp8_ref(wl.v_pool, 0.03).cuda()
     d = wl.to("cuda")
-    out, lse = iva_b200.paged_decode_attention(d.q, k8, v8, d.block_table, d.ctx_len, 16, wl.scale, return_lse=True,
-                                               check=True, k_scale=0.02, v_scale=0.03)
     out_ref, lse_ref = ref.paged_decode_ref(wl.q, ref.dequantize_fp8_ref(k8.cpu(), 0.02),
                                             ref.dequantize_fp8_ref(v8.cpu(), 0.03), wl.block_table, wl.ctx_len, 16, wl.scale)
-    assert_attn_close(out, out_ref, torch.bfloat16, strict=False)
-    assert_lse_close(lse, lse_ref)
+    check_decode(lambda od: iva_b200.paged_decode_attention(d.q, k8, v8, d.block_table, d.ctx_len, 16, wl.scale,
+                                                            return_lse=True, check=True, k_scale=0.02, v_scale=0.03,
+                                                            out_dtype=od), out_ref, lse_ref, torch.bfloat16)
 print("engines ok")
 """
 

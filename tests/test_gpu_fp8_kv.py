@@ -8,7 +8,7 @@ import torch
 import iva_b200
 from iva_b200 import workloads
 from oracle import paged_ref as ref
-from util import assert_attn_close, assert_lse_close
+from util import assert_attn_close, assert_lse_close, check_decode
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -60,14 +60,13 @@ def test_decode_on_fp8_pools(dtype, Hq, Hkv, D):
     d = wl.to(DEV)
     iva_b200.paged_append(kd, vd, d.slot_mapping, d.k_new, d.v_new, 16, check=True, k_scale=k_scale, v_scale=v_scale)
     lens = (d.ctx_len + 1).contiguous()
-    out, lse = iva_b200.paged_decode_attention(d.q, kd, vd, d.block_table, lens, 16, wl.scale, return_lse=True,
-                                               check=True, k_scale=k_scale, v_scale=v_scale)
     # checker: the same attention on the dequantised pools (what the kernel must reproduce) ...
     kf = ref.dequantize_fp8_ref(kd.cpu(), k_scale)
     vf = ref.dequantize_fp8_ref(vd.cpu(), v_scale)
     out_ref, lse_ref = ref.paged_decode_ref(wl.q, kf, vf, wl.block_table, wl.ctx_len + 1, 16, wl.scale)
-    assert_attn_close(out, out_ref, dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    out, lse = check_decode(lambda od: iva_b200.paged_decode_attention(
+        d.q, kd, vd, d.block_table, lens, 16, wl.scale, return_lse=True, check=True, k_scale=k_scale, v_scale=v_scale,
+        out_dtype=od), out_ref, lse_ref, dtype)
     # ... and, for the record, the cost of storing 8 bits: against the 16-bit pools
     _, _, out16, _ = ref.decode_step_ref(wl)
     rel = (out.float().cpu() - out16).norm() / out16.norm()
@@ -80,13 +79,12 @@ def test_fp8_window_and_sinks_and_errors(Hkv, D):
     wl, k8, v8 = _fp8_workload(ctx, 8, Hkv, D, torch.bfloat16, 9, 0.02, 0.02)
     begin = torch.tensor([261, 10, 4000])
     d = wl.to(DEV)
-    out, lse = iva_b200.paged_decode_attention(d.q, k8.to(DEV), v8.to(DEV), d.block_table, d.ctx_len, 16, wl.scale,
-                                               return_lse=True, check=True, ctx_begin=begin.to(DEV), sink_tokens=4,
-                                               k_scale=0.02, v_scale=0.02)
     out_ref, lse_ref = ref.paged_decode_ref(wl.q, ref.dequantize_fp8_ref(k8, 0.02), ref.dequantize_fp8_ref(v8, 0.02),
                                             wl.block_table, wl.ctx_len, 16, wl.scale, ctx_begin=begin, sink_tokens=4)
-    assert_attn_close(out, out_ref, torch.bfloat16, strict=False)
-    assert_lse_close(lse, lse_ref)
+    kd8, vd8 = k8.to(DEV), v8.to(DEV)
+    check_decode(lambda od: iva_b200.paged_decode_attention(
+        d.q, kd8, vd8, d.block_table, d.ctx_len, 16, wl.scale, return_lse=True, check=True, ctx_begin=begin.to(DEV),
+        sink_tokens=4, k_scale=0.02, v_scale=0.02, out_dtype=od), out_ref, lse_ref, torch.bfloat16)
     with pytest.raises(ValueError, match="fp16 or bf16"):
         iva_b200.paged_decode_attention(d.q.float(), k8.to(DEV), v8.to(DEV), d.block_table, d.ctx_len, 16)
     with pytest.raises(ValueError, match="positive"):

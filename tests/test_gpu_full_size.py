@@ -7,7 +7,7 @@ import torch
 import iva_b200
 from iva_b200 import workloads
 from oracle import paged_ref as ref
-from util import assert_attn_close, assert_lse_close
+from util import assert_attn_close, assert_lse_close, check_decode
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -43,16 +43,79 @@ def test_c2_full_size_step():
     assert torch.equal(out3, out2)
 
 
-def test_c3_full_size_ragged_gqa():
-    wl = workloads.config_c3(device=DEV)
+@pytest.mark.parametrize("seed", [0, 1])
+def test_c3_full_size_ragged_gqa(seed):
+    """128 ragged sequences (log-normal lengths, 16 .. 32768), 32 query / 8 KV heads.  Checked against
+    the checker on every sequence shorter than 64 tokens, the eight shortest, the longest, and eight
+    more spread over the length order -- with the fp32 output at the plain 2e-3 bar, so that short
+    contexts (outputs of order 1) are not excused by the bf16 rounding of the result."""
+    wl = workloads.config_c3(device=DEV, seed=seed)
     iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, 16, check=True)
     lens = (wl.ctx_len + 1).contiguous()
     out, lse = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
                                                return_lse=True, check=True)
-    order = torch.argsort(wl.ctx_len.cpu())
-    seqs = [int(order[0]), int(order[len(order) // 2]), int(order[-1])]          # shortest, median, longest
-    _sampled_oracle(wl, lens, seqs, out, lse)
+    out32, lse32 = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                                   return_lse=True, check=True, out_dtype=torch.float32)
+    assert torch.equal(out32.to(out.dtype), out) and torch.equal(lse32, lse)
+    ctx = wl.ctx_len.cpu()
+    order = torch.argsort(ctx)
+    n = len(order)
+    picks = {int(s) for s in torch.nonzero(ctx < 64).flatten()} | {int(s) for s in order[:8]} | {int(order[-1])}
+    picks |= {int(order[i]) for i in range(n // 9, n, n // 9)}
+    seqs = sorted(picks)
+    assert len(seqs) >= 16
+    _sampled_oracle(wl, lens, seqs, out32, lse32)        # fp32 output: the plain bar on every sampled sequence
+    order_l = [int(order[n // 2]), int(order[-1])]
+    _sampled_oracle(wl, lens, order_l, out, lse)          # bf16 output on the median and the longest
     assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+
+
+def test_c5a_per_gpu_share_at_eight_gpus():
+    """The request-sharded configuration at the size one of eight GPUs gets: 128 sequences x 8192
+    tokens, 32 query / 8 KV heads (4.3 GB of K/V); append + attention, sampled checker, bit-reproducible."""
+    wl = workloads.config_c5a(device=DEV, n_seq=1024, context=8192, rank=3, world=8)
+    assert wl.batch == 128
+    iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, 16, check=True)
+    assert torch.equal(wl.v_pool[0, :, wl.slot_mapping], wl.v_new.permute(1, 0, 2))
+    lens = (wl.ctx_len + 1).contiguous()
+    out, lse = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                               return_lse=True, check=True)
+    _sampled_oracle(wl, lens, [0, 61, 127], out, lse)
+    out2 = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16)
+    assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_head_parallel_split_on_one_gpu(world):
+    """The head-parallel mode's arithmetic without a second GPU: every rank's KV-head slab (and the query
+    heads that follow it) goes through the kernels in turn on this device and the results are
+    concatenated.  A head's result may not depend on which other heads share its launch beyond the
+    split-K summation order (the chunk size follows the number of KV heads in the call), so the
+    concatenation must agree with the unsplit call to fp32 rounding noise, and both must meet the
+    checker's bar.  The long sequence is cut into many chunks per slab (the single-131072-token
+    configuration scaled to 32768 tokens), the short one into none."""
+    from iva_b200.sharding import head_slice
+
+    wl = workloads.make_decode_workload("hp1", torch.tensor([32768, 777]), n_q_heads=32, n_kv_heads=8, head_dim=128,
+                                        dtype=torch.bfloat16, seed=12, device=DEV)
+    lens = wl.ctx_len.contiguous()
+    full, full_lse = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                                     return_lse=True, check=True, out_dtype=torch.float32)
+    parts, parts_lse = [], []
+    for rank in range(world):
+        qs, kvs = head_slice(32, 8, world, rank)
+        o, l = iva_b200.paged_decode_attention(wl.q[:, qs].contiguous(), wl.k_pool[:, kvs].contiguous(),
+                                               wl.v_pool[:, kvs].contiguous(), wl.block_table, lens, 16,
+                                               return_lse=True, check=True, out_dtype=torch.float32)
+        parts.append(o)
+        parts_lse.append(l)
+    got, got_lse = torch.cat(parts, 1), torch.cat(parts_lse, 1)
+    assert (got - full).abs().max().item() <= 1e-5 and (got_lse - full_lse).abs().max().item() <= 1e-5
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q.cpu(), wl.k_pool.cpu(), wl.v_pool.cpu(), wl.block_table.cpu(),
+                                            lens.cpu(), 16, wl.scale)
+    for o, l in ((full, full_lse), (got, got_lse)):
+        assert_attn_close(o, out_ref, wl.dtype, strict=True)
+        assert_lse_close(l, lse_ref)
 
 
 def test_c4_full_size_append_gather_roundtrip():
@@ -114,10 +177,10 @@ def test_batch_larger_than_the_planner_tiles():
     _, _, out_ref, lse_ref = ref.decode_step_ref(wl)
     d = wl.to(DEV)
     iva_b200.paged_append(d.k_pool, d.v_pool, d.slot_mapping, d.k_new, d.v_new, 16, check=True)
-    out, lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, (d.ctx_len + 1).contiguous(), 16,
-                                               return_lse=True, check=True)
-    assert_attn_close(out, out_ref, wl.dtype, strict=False)
-    assert_lse_close(lse, lse_ref)
+    lens = (d.ctx_len + 1).contiguous()
+    check_decode(lambda od: iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, lens, 16,
+                                                            return_lse=True, check=True, out_dtype=od),
+                 out_ref, lse_ref, wl.dtype)
 
 
 @pytest.mark.parametrize("config", ["c2", "c3"])

@@ -12,7 +12,7 @@ import torch.multiprocessing as mp
 import iva_b200
 from iva_b200 import workloads
 from oracle import paged_ref as ref
-from util import assert_attn_close, assert_lse_close
+from util import OUT_TOL, assert_attn_close, assert_lse_close, check_decode
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -94,13 +94,15 @@ def test_fp8_cache_object():
     v = torch.randn(2, 40, 2, 128, generator=g).to(torch.bfloat16)
     cache.append(k.to(DEV), v.to(DEV))
     q = torch.randn(2, 4, 128, generator=g).to(torch.bfloat16)
-    out = iva_b200.paged_decode_attention(q.to(DEV), cache.k_pool, cache.v_pool, cache.block_table_dev, cache.ctx_len_dev,
-                                          16, k_scale=0.02, v_scale=0.02, check=True)
+    qd = q.to(DEV)
     kq = ref.dequantize_fp8_ref(ref.quantize_fp8_ref(k, 0.02), 0.02).permute(0, 2, 1, 3)     # [B,H,L,D]
     vq = ref.dequantize_fp8_ref(ref.quantize_fp8_ref(v, 0.02), 0.02).permute(0, 2, 1, 3)
-    want, _ = ref.attention_math_ref(q.view(2, 2, 2, 1, 128).reshape(2, 4, 1, 128), kq.repeat_interleave(2, 1),
-                                     vq.repeat_interleave(2, 1), 128 ** -0.5)
-    assert_attn_close(out, want.view(2, 4, 128), torch.bfloat16, strict=False)
+    want, lse_want = ref.attention_math_ref(q.view(2, 2, 2, 1, 128).reshape(2, 4, 1, 128), kq.repeat_interleave(2, 1),
+                                            vq.repeat_interleave(2, 1), 128 ** -0.5)
+    check_decode(lambda od: iva_b200.paged_decode_attention(qd, cache.k_pool, cache.v_pool, cache.block_table_dev,
+                                                            cache.ctx_len_dev, 16, k_scale=0.02, v_scale=0.02, check=True,
+                                                            return_lse=True, out_dtype=od),
+                 want.view(2, 4, 128), lse_want.view(2, 4), torch.bfloat16)
 
 
 def _free_port():
@@ -153,4 +155,5 @@ def test_two_gpus_head_parallel_and_request_sharding():
     mp.spawn(_nccl_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     for r in range(2):
         ok, err, lerr, err2, covered = ret[r]
-        assert ok and covered and err <= 2e-3 + 2 ** -8 * 4 and lerr <= 1e-3 and err2 <= 2e-3, ret[r]
+        # contexts of 5000, 77 and 300 keys: the plain bf16 bar, no allowance for the output's rounding
+        assert ok and covered and err <= OUT_TOL[torch.bfloat16] and lerr <= 1e-3 and err2 <= OUT_TOL[torch.bfloat16], ret[r]

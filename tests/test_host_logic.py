@@ -80,6 +80,31 @@ def test_window_eviction_bookkeeping_without_a_gpu():
         c.compact([torch.ones(80), torch.ones(40)])                   # kept tokens on evicted pages
 
 
+def test_pages_are_conserved_across_evict_reset_and_reserve():
+    """Evicted block-table entries are -1; resetting the sequence afterwards must not hand those back
+    as page ids (every page is either free or in exactly one table, and no id is negative)."""
+    def conserved(c):
+        live = [p for t in c._tables for p in t if p >= 0]
+        assert all(p >= 0 for p in c._free)
+        assert sorted(live + c._free) == list(range(c.num_pages))
+
+    c = PagedKVCache(batch_size=2, n_heads=1, head_dim=16, seq_len=64, device="cpu", dtype=torch.float32,
+                     num_pages=16, max_seq_len=128)
+    conserved(c)
+    assert c.evict_before([48, 48]) == 6
+    conserved(c)
+    c.reset()                                  # the sequences finish
+    conserved(c)
+    assert c.free_pages == 16
+    c._reserve([90, 30])
+    conserved(c)
+    assert all(p >= 0 for t in c._tables for p in t)
+    c.evict_before([40, 0])
+    c.reset(0)                                 # one sequence finishes after an eviction
+    conserved(c)
+    assert c.lengths == [0, 30]
+
+
 def test_partitioners():
     assert [len(shard_requests(10, 4, r)) for r in range(4)] == [3, 3, 2, 2]
     assert list(shard_requests(10, 4, 3)) == [8, 9]

@@ -32,3 +32,25 @@ def assert_lse_close(got, ref):
     err = (got[~inf] - ref[~inf]).abs()
     if err.numel():
         assert err.max().item() <= LSE_TOL, f"lse: max-abs {err.max().item():.3e} > {LSE_TOL}"
+
+
+def check_decode(call, out_ref, lse_ref, dtype):
+    """``call(out_dtype) -> (out, lse)`` runs one decode-attention call.  The fp32 output is held to
+    the plain bar (2e-3 for bf16 inputs, 1e-3 for fp16, 2e-5 for fp32; logsumexp 1e-3), i.e. the
+    kernels' arithmetic is checked BEFORE the final rounding; the output in q's own 16-bit type may
+    differ from the checker by that bar plus one rounding step of the stored value, and must be
+    exactly the fp32 output rounded to that type."""
+    out, lse = call(None)
+    assert out.dtype == dtype
+    assert_attn_close(out, out_ref, dtype, strict=False)
+    assert_lse_close(lse, lse_ref)
+    if dtype == torch.float32:
+        assert_attn_close(out, out_ref, dtype, strict=True)
+        return out, lse
+    out32, lse32 = call(torch.float32)
+    assert out32.dtype == torch.float32
+    assert_attn_close(out32, out_ref, dtype, strict=True, what="fp32 out")
+    assert_lse_close(lse32, lse_ref)
+    assert torch.equal(out32.to(dtype), out), "the 16-bit output is not the rounded fp32 output"
+    assert torch.equal(lse32, lse)
+    return out, lse
