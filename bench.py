@@ -1,26 +1,35 @@
-"""Benchmark of the paged-KV decode step on B200.
+"""Benchmark of the paged-KV decode path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5a|c5b] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload all|c2|c3|c4|c5a|c5b] [--impl reference]
 
 One step = the hot path on one batch: append one token per sequence into its page, then
 single-query attention over the whole cache through the block table.  Prints ONE JSON line.
 
+The headline (``value``, ``e2e``, ``roofline``) is the multi-head decode configuration "c2"
+(64 sequences x 32 heads x 4096 keys, bf16), one copy per GPU.  With ``--workload all`` (the
+default) the same line carries one sub-record per other configuration:
+
+* ``c3``         ragged grouped-query decode, 128 sequences (1 GPU runs only)
+* ``c4``         append / gather stress: 131072 tokens appended, 1.18 M tokens gathered (1 GPU runs only)
+* ``c5a``        1024 sequences x 8192 keys split over the N ranks (strong scaling, no collective)
+* ``c5b``        one 131072-token sequence, KV heads split over the N ranks + one NCCL all-gather
+* ``sustained``  c2 steps back to back for at least two seconds, with the clocks seen
+* ``module_path``  the same c2 decode driven through ``AttentionB200`` + ``PagedKVCache``
+
 * ``value``     decode tokens/s, whole job, inputs resident in HBM (CUDA events, max over ranks).
-* ``e2e``       the same step driven from pinned HOST buffers: q / new K,V / slot mapping / lengths
-                copied in, result copied out, every step.
+* ``e2e``       the same step driven from pinned HOST buffers through ``GraphedDecodeStep``: q / new K,V /
+                slot mapping / lengths copied in, result copied out, every step.
 * ``roofline``  algorithmic bytes of the attention call / its mean duration, against the measured
                 HBM copy bandwidth of this pool's B200s.
-* ``cpu_baseline``  the CPU checker (the reference's torch path restated) on a bounded sample.
-
-With ``--gpus N`` (under torchrun) every rank runs the same per-GPU workload on its own page pool
-with no collective on the data path ("weak" scaling); ``--workload c5b`` is the head-parallel form
-of one long sequence with an NCCL all-gather of the outputs.
+* ``cpu_baseline``  the CPU checker (the reference's torch path restated) timed on the host cores.
 """
 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -82,6 +91,18 @@ def gather_bytes(wl, lens):
     return 2 * (2 * tokens * wl.n_kv_heads * wl.head_dim * elt) + 2 * pages * 4
 
 
+def roofline_record(nbytes, ms, kernel=None, traffic_ratio=None):
+    peak, kind = measured_peak()
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    rec = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+           "peak_kind": f"of {kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+           "algorithmic_bytes": int(nbytes), "ms": ms,
+           "traffic": None if traffic_ratio is None else int(nbytes * traffic_ratio)}
+    if kernel:
+        rec["kernel"] = kernel
+    return rec
+
+
 # ---- clocks ----------------------------------------------------------------------------------------
 
 class ClockSampler:
@@ -119,20 +140,27 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
-    def summary(self):
-        if not self.rows:
+    def mark(self):
+        """Index of the next sample (to summarise a sub-interval later)."""
+        return len(self.rows)
+
+    def summary(self, start=0, stop=None):
+        rows = self.rows[start:stop]
+        if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+
         def num(x):
             try:
                 return float(x)
             except ValueError:
                 return None
-        power = [num(r[6]) for r in self.rows if len(r) > 6 and num(r[6]) is not None]
-        mem = [num(r[7]) for r in self.rows if len(r) > 7 and num(r[7]) is not None]
-        return {"sm_mhz": statistics.median(int(r[0]) for r in self.rows), "sm_min_mhz": min(int(r[0]) for r in self.rows),
-                "sm_max_mhz": int(self.rows[0][1]), "reasons": reasons, "samples": len(self.rows),
+
+        power = [num(r[6]) for r in rows if len(r) > 6 and num(r[6]) is not None]
+        mem = [num(r[7]) for r in rows if len(r) > 7 and num(r[7]) is not None]
+        return {"sm_mhz": statistics.median(int(r[0]) for r in rows), "sm_min_mhz": min(int(r[0]) for r in rows),
+                "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows),
                 "power_w_max": max(power) if power else None, "mem_mhz": statistics.median(mem) if mem else None}
 
 
@@ -161,8 +189,7 @@ WORKLOAD_TEXT = {"c2": "1xB200 MHA decode step (append 1 token/seq + paged atten
 
 
 def workload_shape(name, args, rank, world):
-    """Lengths and head layout of a workload without building its pools (the reference arm reports
-    the GPU arm's config although it only times a sample of it)."""
+    """Lengths and head layout of a workload without building its pools."""
     if name == "c2":
         ctx, hq, hkv, dt, new, free = torch.full((args.batch or 64,), args.context or 4096), 32, 32, "bfloat16", 1, 0.0
     elif name == "c3":
@@ -215,10 +242,10 @@ def live_copy_bandwidth(dev):
     return 2 * n * 2 / (best * 1e-3) / 1e9
 
 
-# ---- the GPU arm --------------------------------------------------------------------------------------
+# ---- timing helpers -----------------------------------------------------------------------------------
 
 def time_region(fn, steps, flush=None):
-    """CUDA-event time of ``steps`` calls on the current stream, in ms (sum of per-call events so
+    """CUDA-event time of ``steps`` calls on the current stream, in ms (one event pair per call so
     that an optional L2 flush between calls stays outside the measurement)."""
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     for a, b in evs:
@@ -231,217 +258,463 @@ def time_region(fn, steps, flush=None):
     return [a.elapsed_time(b) for a, b in evs]
 
 
-def run_gpu(args):
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+class Ranks:
+    """The process group (if any) and the max-over-ranks reduction every multi-GPU figure goes through."""
 
+    def __init__(self, dev):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.dev = dev
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=dev)
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max(self, *values):
+        if self.dist is None:
+            return values if len(values) > 1 else values[0]
+        t = torch.tensor(list(values), device=self.dev, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        out = [float(v) for v in t.tolist()]
+        return out if len(out) > 1 else out[0]
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def quantise_pools(wl, dev):
+    """--kv-fp8: replace the 16-bit pools by e4m3 pools (N(0,1) data, scale 1/64 keeps +-7 sigma in range)."""
+    for attr in ("k_pool", "v_pool"):
+        pool = getattr(wl, attr)
+        q8 = torch.empty(pool.shape, dtype=torch.float8_e4m3fn, device=dev)
+        step_rows = 1 << 16
+        for lo in range(0, pool.shape[2], step_rows):      # chunked: no full-size fp32 temporary
+            q8[:, :, lo:lo + step_rows] = (pool[:, :, lo:lo + step_rows].float() * 64.0).clamp(-448, 448).to(torch.float8_e4m3fn)
+        setattr(wl, attr, q8)
+    torch.cuda.empty_cache()
+    return {"k_scale": 1.0 / 64, "v_scale": 1.0 / 64}
+
+
+def flusher(dev, nbytes_read):
+    """An L2 flush (a write larger than the 126 MB L2) for workloads whose K/V would otherwise stay cached."""
+    if nbytes_read > 4 * 126e6:
+        return None, None
+    buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    return buf, (lambda: buf.fill_(1))
+
+
+# ---- decode workloads (c2, c3, c5a) ----------------------------------------------------------------------
+
+def measure_decode(name, wl, ranks, steps, warmup, kv_scales, seqs_total):
+    """Device-resident timing of append + attention on one decode workload.  Returns a dict with the
+    whole step (max over ranks) and the per-kernel legs of this rank."""
+    dev = ranks.dev
     lib = iva_b200.load_library()
-    name = args.workload
-    copy_gbs = live_copy_bandwidth(dev)
-    wl = build_workload(name, dev, rank, world, args)
     B = wl.batch
-    kv_scales = {}
-    if args.kv_fp8:
-        if name not in ("c2", "c3", "c5a"):
-            raise SystemExit("--kv-fp8 applies to the decode workloads c2, c3, c5a")
-        # N(0,1) data: a scale of 1/64 keeps +-7 sigma inside the e4m3 range
-        kv_scales = {"k_scale": 1.0 / 64, "v_scale": 1.0 / 64}
-        for attr in ("k_pool", "v_pool"):
-            pool = getattr(wl, attr)
-            q8 = torch.empty(pool.shape, dtype=torch.float8_e4m3fn, device=dev)
-            step_rows = 1 << 16
-            for lo in range(0, pool.shape[2], step_rows):      # chunked: no full-size fp32 temporary
-                q8[:, :, lo:lo + step_rows] = (pool[:, :, lo:lo + step_rows].float() * 64.0).clamp(-448, 448).to(torch.float8_e4m3fn)
-            setattr(wl, attr, q8)
-        torch.cuda.empty_cache()
     lens = (wl.ctx_len + wl.new_tokens_per_seq).contiguous()
-    out = torch.empty(B, wl.n_q_heads, wl.head_dim, device=dev, dtype=wl.dtype) if wl.q is not None else None
-    lse = torch.empty(B, wl.n_q_heads, device=dev, dtype=torch.float32) if wl.q is not None else None
-    flush_buf = None
-    need_flush = wl.q is not None and attention_bytes(wl, lens) <= 4 * 126e6
-    if need_flush:
-        flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-    flush = (lambda: flush_buf.fill_(1)) if need_flush else None
-
-    hp = None
-    if name == "c5b":
-        from iva_b200.sharding import HeadParallelDecoder
-        if world > 1:
-            hp = HeadParallelDecoder(wl.n_q_heads, wl.n_kv_heads)
-            k_loc, v_loc = hp.local_pools(wl.k_pool, wl.v_pool)
-            k_loc, v_loc = k_loc.contiguous(), v_loc.contiguous()      # each rank keeps only its slab
-            k_new_loc, v_new_loc = wl.k_new[:, hp.kv_slice].contiguous(), wl.v_new[:, hp.kv_slice].contiguous()
-            wl.k_pool, wl.v_pool = k_loc, v_loc                        # drop the full pools
-            torch.cuda.empty_cache()
+    out = torch.empty(B, wl.n_q_heads, wl.head_dim, device=dev, dtype=wl.dtype)
+    lse = torch.empty(B, wl.n_q_heads, device=dev, dtype=torch.float32)
+    nbytes = attention_bytes(wl, lens)
+    flush_buf, flush = flusher(dev, nbytes)
 
     def append():
-        if hp is not None:
-            iva_b200.paged_append(k_loc, v_loc, wl.slot_mapping, k_new_loc, v_new_loc, wl.page_size)
-        else:
-            iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, wl.page_size)
-
-    hp_step = None
-    if hp is not None and not args.no_graph:
-        hp_step = hp.capture_local(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
+        iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, wl.page_size, **kv_scales)
 
     def attend():
-        if hp_step is not None:
-            return hp_step()
-        if hp is not None:
-            return hp.decode(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
-        return iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, wl.page_size,
-                                               wl.scale, out=out, lse=lse, **kv_scales)
-
-    gather_offs = None
-    if name == "c4":
-        gather_offs = torch.zeros(B + 1, dtype=torch.int64, device=dev)
-        gather_offs[1:] = torch.cumsum(lens.long(), 0)
-        total_tokens = int(gather_offs[-1])
-
-    def gather():
-        k = iva_b200.paged_gather(wl.k_pool, wl.block_table, lens, wl.page_size, layout="token_major",
-                                  out_offsets=gather_offs, total_tokens=total_tokens)
-        v = iva_b200.paged_gather(wl.v_pool, wl.block_table, lens, wl.page_size, layout="token_major",
-                                  out_offsets=gather_offs, total_tokens=total_tokens)
-        return k, v
+        iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, wl.page_size, wl.scale,
+                                        out=out, lse=lse, **kv_scales)
 
     def step():
         append()
-        if name == "c4":
-            gather()
-        else:
-            attend()
+        attend()
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
-    barrier()
-
-    # ---- device-resident timing (the headline `value`) ----
+    ranks.barrier()
     launches0 = lib.ivab_launch_count()
-    # clocks are sampled from here to the end of the end-to-end leg (a K-step region alone can be
-    # shorter than one nvidia-smi sampling period)
+    per_step = time_region(step, steps, flush)
+    ranks.barrier()
+    launches = lib.ivab_launch_count() - launches0
+    attn_ms = time_region(attend, steps, flush)
+    app_ms = time_region(append, steps, flush)
+    total_ms = ranks.max(sum(per_step))
+    ms_per_step = total_ms / steps
+    rec = {"ms_per_step": ms_per_step, "value": seqs_total * wl.new_tokens_per_seq / (ms_per_step * 1e-3),
+           "unit": "decode tok/s", "attention_ms": statistics.mean(attn_ms), "attention_ms_min": min(attn_ms),
+           "append_ms": statistics.mean(app_ms), "append_GBs": append_bytes(wl) / (statistics.mean(app_ms) * 1e-3) / 1e9,
+           "gpu_launches": int(launches), "l2": "flushed between timed steps" if flush else "K/V per step exceed L2",
+           "roofline": roofline_record(nbytes, statistics.mean(attn_ms),
+                                       "plan_kernel + decode_kernel + merge_kernel (one attention call)",
+                                       NCU_TRAFFIC_RATIO.get(name))}
+    return rec, step, out, lens
+
+
+def measure_sustained(step, batch, ranks, clocks, ms_per_step, seconds=2.5):
+    """Steps back to back for a few seconds: the figure a long-running server sees, with the clocks and
+    power-cap state sampled over exactly this interval."""
+    n = max(50, int(math.ceil(seconds * 1e3 / ms_per_step)))
+    ranks.barrier()
+    m0 = clocks.mark()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    time.sleep(0.06)
+    m1 = clocks.mark()
+    ms = ranks.max(a.elapsed_time(b))
+    ranks.barrier()
+    c = clocks.summary(m0, m1)
+    rec = {"steps": n, "seconds": ms * 1e-3, "ms_per_step": ms / n, "value": batch * ranks.world / (ms / n * 1e-3),
+           "unit": "decode tok/s", "clocks": c}
+    if c.get("sm_mhz"):
+        rec["ms_per_step_x_sm_ghz"] = ms / n * c["sm_mhz"] * 1e-3      # clock-normalised: compare across runs
+    return rec
+
+
+def measure_e2e(wl, lens, ranks, steps, warmup, kv_scales, seqs_total, out_check=None):
+    """The public end-to-end call: inputs in pinned host memory, one CUDA-graph replay per step (H2D of
+    q / new K,V / slot mapping / lengths, append, attention; the kernels store the output straight into
+    the pinned host buffer, d2h_bytes_per_step counts those bytes).
+
+    ``value``: one batch, strictly serial -- the host waits for step k's output before it enqueues step
+    k+1, as a decode loop must (the next query depends on it).  ``two_batches_in_flight``: two independent
+    copies of the batch (own pools, own stream) alternate, each still waiting for its own previous output;
+    one batch's upload and host turn-around hide under the other's attention."""
+    def make(k_pool, v_pool):
+        gs = iva_b200.GraphedDecodeStep(k_pool, v_pool, wl.block_table, wl.n_q_heads, wl.page_size, wl.scale,
+                                        token_dtype=wl.dtype, **kv_scales)
+        for b in range(gs.n_buffers):
+            io = gs.inputs(b)
+            io.q_host.copy_(wl.q)
+            io.k_new_host.copy_(wl.k_new)
+            io.v_new_host.copy_(wl.v_new)
+            io.slot_mapping_host.copy_(wl.slot_mapping)
+            io.ctx_len_host.copy_(lens)
+        return gs
+
+    gs = make(wl.k_pool, wl.v_pool)
+    torch.cuda.synchronize()
+
+    def e2e_step():
+        gs.run(0)
+        return gs.result(0)                                # the host consumes the result every step
+
+    for _ in range(max(warmup, 3)):
+        e2e_step()
+    ranks.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        res = e2e_step()
+    torch.cuda.synchronize()
+    wall_ms = ranks.max((time.perf_counter() - t0) * 1e3)
+    if out_check is not None:
+        assert torch.equal(res.to(out_check.device), out_check), "end-to-end result differs from the device-resident one"
+    rec = {"value": seqs_total / (wall_ms / steps * 1e-3), "unit": "decode tok/s",
+           "h2d_bytes_per_step": gs.h2d_bytes, "d2h_bytes_per_step": gs.d2h_bytes,
+           "ms_per_step": wall_ms / steps,
+           "api": "GraphedDecodeStep.run() + result(): host clock around K steps; the host waits for each step's "
+                  "output (an event behind its last kernel) before it enqueues the next"}
+
+    # two independent batches in flight
+    free, _ = torch.cuda.mem_get_info()
+    need = 2 * wl.k_pool.numel() * wl.k_pool.element_size()
+    if free > need + (8 << 30):
+        gs2 = make(wl.k_pool.clone(), wl.v_pool.clone())
+        pair = (gs, gs2)
+        for g in pair:
+            g.run(0)
+            g.result(0)
+        ranks.barrier()
+        t0 = time.perf_counter()
+        for g in pair:
+            g.run(0)
+        for _ in range(steps):
+            for g in pair:
+                g.result(0)
+                g.run(0)
+        for g in pair:
+            g.result(0)
+        wall2 = ranks.max((time.perf_counter() - t0) * 1e3)
+        n_steps = 2 * (steps + 1)
+        rec["two_batches_in_flight"] = {
+            "value": (seqs_total * n_steps) / (wall2 * 1e-3), "unit": "decode tok/s", "ms_per_batch_step": wall2 / n_steps,
+            "note": "two independent batches of this configuration (own pools, own stream) alternate; each batch "
+                    "still reads its own step-k output before its step k+1 is enqueued"}
+        assert torch.equal(gs2.result(0), gs.result(0))
+        del gs2
+    return rec
+
+
+def measure_module_path(dev, ranks, steps, warmup):
+    """c2 decode through the drop-in module contract: ``AttentionB200.forward(x, kv_cache=PagedKVCache)``
+    with real bias-free projections (d_model 4096), 64 sequences at context 4096 growing by one token per
+    step.  ``value`` is pipelined (the layer's output stays on the device, as inside a model; one
+    synchronisation at the end); ``synced`` forces the host to wait for every step."""
+    from types import SimpleNamespace
+    B, H, D, ctx = 64, 32, 128, 4096
+    cfg = SimpleNamespace(d_model=H * D, n_heads=H, dropout=0.0, causal=False, attn_impl="b200")
+    mod = iva_b200.AttentionB200(cfg).to(device=dev, dtype=torch.bfloat16).eval()
+    n_total = 2 * (steps + max(warmup, 3)) + 8
+    cache = iva_b200.PagedKVCache(batch_size=B, n_heads=H, head_dim=D, seq_len=ctx, device=dev, dtype=torch.bfloat16,
+                                  max_seq_len=ctx + n_total, shuffle_seed=1)
+    cache.k_pool.normal_()
+    cache.v_pool.normal_()
+    x = torch.randn(B, 1, H * D, device=dev, dtype=torch.bfloat16)
+
+    def proj_only():
+        mod.o_proj(mod.q_proj(x) + mod.k_proj(x) + mod.v_proj(x))
+
+    def step():
+        y, _ = mod(x, kv_cache=cache)
+        return y
+
+    for _ in range(max(warmup, 3)):
+        step()
+    ranks.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        y = step()
+    torch.cuda.synchronize()
+    pipelined = (time.perf_counter() - t0) * 1e3 / steps
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        y = step()
+        torch.cuda.current_stream().synchronize()
+    synced = (time.perf_counter() - t0) * 1e3 / steps
+    proj = statistics.mean(time_region(proj_only, steps))
+    pipelined, synced = ranks.max(pipelined, synced)
+    assert torch.isfinite(y.float()).all()
+    return {"value": B * ranks.world / (pipelined * 1e-3), "unit": "decode tok/s", "ms_per_step": pipelined,
+            "synced": {"value": B * ranks.world / (synced * 1e-3), "ms_per_step": synced},
+            "projections_ms": proj, "context_at_end": cache.seq_len,
+            "api": "AttentionB200.forward(x [64,1,4096] bf16, kv_cache=PagedKVCache): q/k/v projections, paged append, "
+                   "paged decode attention, o projection; host clock around K steps"}
+
+
+# ---- c4: append / gather stress ----------------------------------------------------------------------
+
+def measure_c4(wl, ranks, steps, warmup):
+    dev = ranks.dev
+    B = wl.batch
+    lens = (wl.ctx_len + wl.new_tokens_per_seq).contiguous()
+    offs = torch.zeros(B + 1, dtype=torch.int64, device=dev)
+    offs[1:] = torch.cumsum(lens.long(), 0)
+    total_tokens = int(offs[-1])
+
+    def append():
+        iva_b200.paged_append(wl.k_pool, wl.v_pool, wl.slot_mapping, wl.k_new, wl.v_new, wl.page_size)
+
+    def gather():
+        k = iva_b200.paged_gather(wl.k_pool, wl.block_table, lens, wl.page_size, layout="token_major",
+                                  out_offsets=offs, total_tokens=total_tokens)
+        v = iva_b200.paged_gather(wl.v_pool, wl.block_table, lens, wl.page_size, layout="token_major",
+                                  out_offsets=offs, total_tokens=total_tokens)
+        return k, v
+
+    for _ in range(max(warmup, 3)):
+        append()
+    gather()
+    ranks.barrier()
+    app_ms = time_region(append, steps)
+    gat_ms = time_region(gather, max(3, steps // 4))
+    app, gat = statistics.mean(app_ms), statistics.mean(gat_ms)
+    return {"tokens_appended": int(wl.k_new.shape[0]), "tokens_gathered": total_tokens,
+            "append": roofline_record(append_bytes(wl), app, "row_copy_kernel<scatter> (K and V in one launch)"),
+            "gather": roofline_record(gather_bytes(wl, lens), gat, "paged_gather_kernel (K, then V)"),
+            "append_ms_min": min(app_ms), "gather_ms_min": min(gat_ms),
+            "note": "a copy cannot exceed the measured copy bandwidth of the part (the 'peak' above), which is "
+                    "0.81 of the nominal 8 TB/s; frac_of_nominal_8TBs is therefore capped near 0.81-0.83"}
+
+
+# ---- c5b: head-parallel decode of one long sequence ---------------------------------------------------------
+
+def measure_c5b(wl, ranks, steps, warmup, use_graph=True):
+    from iva_b200.sharding import HeadParallelDecoder
+    dev = ranks.dev
+    world = ranks.world
+    lens = (wl.ctx_len + 1).contiguous()
+    nbytes = attention_bytes(wl, lens) // world
+    if world > 1:
+        hp = HeadParallelDecoder(wl.n_q_heads, wl.n_kv_heads)
+        k_loc, v_loc = hp.local_pools(wl.k_pool, wl.v_pool)
+        k_loc, v_loc = k_loc.contiguous(), v_loc.contiguous()          # each rank keeps only its slab
+        k_new, v_new = wl.k_new[:, hp.kv_slice].contiguous(), wl.v_new[:, hp.kv_slice].contiguous()
+        wl.k_pool = wl.v_pool = None
+        torch.cuda.empty_cache()
+    else:
+        hp = None
+        k_loc, v_loc, k_new, v_new = wl.k_pool, wl.v_pool, wl.k_new, wl.v_new
+    flush_buf, flush = flusher(dev, nbytes)
+
+    def append():
+        iva_b200.paged_append(k_loc, v_loc, wl.slot_mapping, k_new, v_new, wl.page_size)
+
+    if hp is not None:
+        hp_step = hp.capture_local(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale) if use_graph else None
+
+        def attend():
+            if hp_step is not None:
+                return hp_step()
+            return hp.decode(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
+    else:
+        out = torch.empty(1, wl.n_q_heads, wl.head_dim, device=dev, dtype=wl.dtype)
+        lse = torch.empty(1, wl.n_q_heads, device=dev, dtype=torch.float32)
+
+        def attend():
+            return iva_b200.paged_decode_attention(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale,
+                                                   out=out, lse=lse)
+
+    def local_only():
+        iva_b200.paged_decode_attention(wl.q[:, hp.q_slice] if hp is not None else wl.q, k_loc, v_loc, wl.block_table,
+                                        lens, wl.page_size, wl.scale, return_lse=True)
+
+    def step():
+        append()
+        attend()
+
+    for _ in range(max(warmup, 3)):
+        step()
+    ranks.barrier()
+    per_step = time_region(step, steps, flush)
+    ranks.barrier()
+    attn_ms = time_region(attend, steps, flush)          # local kernels + the all-gather
+    kern_ms = time_region(local_only, steps, flush)      # this rank's attention kernels only
+    ms_per_step = ranks.max(sum(per_step)) / steps
+    attn, kern = ranks.max(statistics.mean(attn_ms), statistics.mean(kern_ms))
+    return {"ms_per_step": ms_per_step, "attention_incl_allgather_ms": attn, "attention_kernels_ms": kern,
+            "value": 1.0 / (ms_per_step * 1e-3), "unit": "decode tok/s (one sequence)",
+            "roofline_local_kernels": roofline_record(nbytes, kern, "this rank's plan + decode + merge kernels"),
+            "kv_heads_per_rank": wl.n_kv_heads // world, "collective": None if world == 1 else
+            "one NCCL all_gather_into_tensor of [1, H_q/N, D+1] fp32 per step (eager; local kernels in a CUDA graph)",
+            "l2": "flushed between timed steps" if flush else "K/V per step exceed L2"}
+
+
+# ---- the GPU arm --------------------------------------------------------------------------------------
+
+def free_gpu(*objs):
+    del objs
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def run_gpu(args):
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world_env = int(os.environ.get("WORLD_SIZE", "1"))
+    if world_env != args.gpus and world_env == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    ranks = Ranks(dev)
+    world, rank = ranks.world, ranks.rank
+    iva_b200.load_library()
+    name = "c2" if args.workload == "all" else args.workload
+    everything = args.workload == "all"
+    copy_gbs = live_copy_bandwidth(dev)
     clocks = ClockSampler(local)
     clocks.__enter__()
-    barrier()
-    per_step = time_region(step, args.steps, flush)
-    barrier()
-    launches = lib.ivab_launch_count() - launches0
-    total_ms = sum(per_step)
-    # per-kernel legs, same stream, same conditions
-    attn_ms = time_region(attend, args.steps, flush) if name != "c4" else None
-    app_ms = time_region(append, args.steps, flush)
-    gat_ms = time_region(gather, max(2, args.steps // 4)) if name == "c4" else None
-    if dist is not None:
-        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
-    seqs_total = B * world if name != "c5b" else B
-    value = seqs_total * wl.new_tokens_per_seq / (ms_per_step * 1e-3)
+    result = None
 
-    # ---- end to end from pinned host buffers ----
-    e2e = None
     if name in ("c2", "c3", "c5a"):
-        # the public end-to-end call: inputs in pinned host memory, one CUDA-graph replay per step
-        # (H2D of q / new K,V / slot mapping / lengths, append, attention; the kernels store the output
-        # straight into the pinned host buffer, d2h_bytes_per_step counts those bytes)
-        gs = iva_b200.GraphedDecodeStep(wl.k_pool, wl.v_pool, wl.block_table, wl.n_q_heads, wl.page_size, wl.scale,
-                                        token_dtype=wl.dtype, **kv_scales)
-        gs.q_host.copy_(wl.q)
-        gs.k_new_host.copy_(wl.k_new)
-        gs.v_new_host.copy_(wl.v_new)
-        gs.slot_mapping_host.copy_(wl.slot_mapping)
-        gs.ctx_len_host.copy_(lens)
-        torch.cuda.synchronize()
+        wl = build_workload(name, dev, rank, world, args)
+        kv_scales = quantise_pools(wl, dev) if args.kv_fp8 else {}
+        seqs_total = wl.batch * world
+        rec, step, out, lens = measure_decode(name, wl, ranks, args.steps, args.warmup, kv_scales, seqs_total)
+        m_end = clocks.mark()
+        e2e = measure_e2e(wl, lens, ranks, args.steps, args.warmup, kv_scales, seqs_total, out_check=out)
+        sustained = measure_sustained(step, wl.batch, ranks, clocks, rec["ms_per_step"]) if everything or args.sustained else None
+        roof = rec.pop("roofline")
+        roof.update({"live_copy_GBs_this_gpu": copy_gbs, "frac_of_live_copy": roof["achieved"] / copy_gbs})
+        result = {
+            "metric": METRIC, "value": rec["value"], "unit": "decode tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": rec["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong" if name == "c5a" else "weak", "vs_baseline": None,
+            "dtype": {"torch.bfloat16": "bf16", "torch.float16": "f16", "torch.float32": "f32"}[str(wl.dtype)],
+            "data": "synthetic (seeded N(0,1) K/V/q, shuffled page pool)",
+            "config": describe(name, args, rank, world, args.kv_fp8),
+            "roofline": roof,
+            "kernels": {k: rec[k] for k in ("append_ms", "append_GBs", "attention_ms", "attention_ms_min")},
+            "e2e": e2e, "gpu_launches": rec["gpu_launches"],
+        }
+        if sustained is not None:
+            result["sustained"] = sustained
+        del wl, step, out, lens
+        free_gpu()
+        if everything:
+            result["module_path"] = measure_module_path(dev, ranks, args.steps, args.warmup)
+            free_gpu()
+    elif name == "c4":
+        wl = build_workload("c4", dev, rank, world, args)
+        c4 = measure_c4(wl, ranks, args.steps, args.warmup)
+        result = {"metric": METRIC, "value": c4["gather"]["achieved"], "unit": "GB/s (paged gather)", "n_gpus": world,
+                  "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": c4["gather"]["ms"] + c4["append"]["ms"],
+                  "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+                  "data": "synthetic (seeded N(0,1) K/V, shuffled page pool)", "config": describe("c4", args, rank, world),
+                  "roofline": c4["gather"], "c4": c4, "gpu_launches": 3 * args.steps}
+        del wl
+        free_gpu()
+    else:   # c5b alone
+        wl = build_workload("c5b", dev, rank, world, args)
+        c5b = measure_c5b(wl, ranks, args.steps, args.warmup, use_graph=not args.no_graph)
+        result = {"metric": METRIC, "value": c5b["value"], "unit": c5b["unit"], "n_gpus": world, "steps": args.steps,
+                  "warmup": max(args.warmup, 3), "ms_per_step": c5b["ms_per_step"], "higher_is_better": True,
+                  "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                  "data": "synthetic (seeded N(0,1) K/V/q, shuffled page pool)", "config": describe("c5b", args, rank, world),
+                  "roofline": c5b["roofline_local_kernels"], "c5b": c5b, "gpu_launches": 4 * args.steps}
+        del wl
+        free_gpu()
 
-        def e2e_step():
-            gs.run()
-            return gs.result()                              # the host consumes the result every step
-
-        for _ in range(max(args.warmup, 3)):
-            e2e_step()
-        barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        a.record(gs.stream)
-        for _ in range(args.steps):
-            e2e_step()
-        b.record(gs.stream)
-        torch.cuda.synchronize()
-        wall_ms = (time.perf_counter() - t0) * 1e3
-        e2e_ms = max(a.elapsed_time(b), 0.0)
-        if dist is not None:
-            t = torch.tensor([e2e_ms, wall_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms, wall_ms = float(t[0].item()), float(t[1].item())
-        e2e = {"value": seqs_total / (wall_ms / args.steps * 1e-3), "unit": "decode tok/s",
-               "h2d_bytes_per_step": gs.h2d_bytes, "d2h_bytes_per_step": gs.d2h_bytes,
-               "ms_per_step": wall_ms / args.steps, "device_ms_per_step": e2e_ms / args.steps,
-               "api": "GraphedDecodeStep.run() + result(), host clock around K steps (each step ends in a stream sync)"}
-        out.copy_(gs.out_host if gs.direct_host_output else gs._out)
+    if everything:
+        sub_steps = max(10, min(args.steps, 30))
+        if world == 1:
+            wl = build_workload("c3", dev, rank, world, args)
+            rec, _, _, _ = measure_decode("c3", wl, ranks, sub_steps, args.warmup, {}, wl.batch)
+            rec["config"] = describe("c3", args, rank, world)
+            result["c3"] = rec
+            del wl
+            free_gpu()
+            wl = build_workload("c4", dev, rank, world, args)
+            result["c4"] = measure_c4(wl, ranks, sub_steps, args.warmup)
+            del wl
+            free_gpu()
+        wl = build_workload("c5a", dev, rank, world, args)
+        rec, _, _, _ = measure_decode("c5a", wl, ranks, sub_steps, args.warmup, {}, wl.batch * world)
+        rec["config"] = describe("c5a", args, rank, world)
+        rec["scaling"] = "strong: 1024 sequences x 8192 keys split evenly over the ranks, slowest rank's time"
+        result["c5a"] = rec
+        del wl
+        free_gpu()
+        wl = build_workload("c5b", dev, rank, world, args)
+        result["c5b"] = measure_c5b(wl, ranks, sub_steps, args.warmup, use_graph=not args.no_graph)
+        del wl
+        free_gpu()
 
     clocks.__exit__(None, None, None)
+    result["clocks"] = clocks.summary()
     if rank != 0:
-        if dist is not None:
-            dist.barrier()
-            dist.destroy_process_group()
+        ranks.close()
         return
-
-    peak, peak_kind = measured_peak()
-    if name == "c4":
-        dom_bytes, dom_ms, dom_name = gather_bytes(wl, lens), statistics.mean(gat_ms), "paged_gather_kernel (K and V)"
-    else:
-        wl_local = wl
-        dom_bytes = attention_bytes(wl_local, lens) // (world if name == "c5b" else 1)
-        dom_ms, dom_name = statistics.mean(attn_ms), "plan_kernel + decode_kernel + merge_kernel (one attention call)"
-    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-    ratio = NCU_TRAFFIC_RATIO.get(name)
-    result = {
-        "metric": METRIC, "value": value, "unit": "decode tok/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if name in ("c5a", "c5b") else "weak", "vs_baseline": None,
-        "dtype": {"torch.bfloat16": "bf16", "torch.float16": "f16", "torch.float32": "f32"}[str(wl.dtype)],
-        "data": "synthetic (seeded N(0,1) K/V/q, shuffled page pool)",
-        "config": describe(name, args, rank, world, args.kv_fp8),
-        "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                     "algorithmic_bytes": dom_bytes, "ms": dom_ms,
-                     "live_copy_GBs_this_gpu": copy_gbs, "frac_of_live_copy": achieved / copy_gbs,
-                     "traffic": None if ratio is None else int(dom_bytes * ratio)},
-        "kernels": {"append_ms": statistics.mean(app_ms), "append_GBs": append_bytes(wl) / (statistics.mean(app_ms) * 1e-3) / 1e9,
-                    "attention_ms": None if attn_ms is None else statistics.mean(attn_ms),
-                    "attention_ms_min": None if attn_ms is None else min(attn_ms),
-                    "gather_ms": None if gat_ms is None else statistics.mean(gat_ms)},
-        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
-    }
     if args.cpu_baseline and world == 1:
         result["cpu_baseline"] = cpu_baseline(name, args, budget_s=12.0)
         result["c1_reference_case"] = c1_case(dev)
     print(json.dumps(result))
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    ranks.close()
 
 
 # ---- the CPU arm (checker timed as a baseline) ------------------------------------------------------------
 
-def cpu_sample(name, args):
-    """A bounded sample of the workload: same heads, dtype, page size and context, fewer sequences."""
+def cpu_sample(name, args, full):
+    """The CPU arm's workload: the whole configuration when the host can hold it, else a bounded sample
+    of it (same heads, dtype, page size and contexts, fewer sequences)."""
     if name == "c3":
         return workloads.config_c3(device="cpu", batch=8), "8 of 128 sequences (same length distribution)"
     if name == "c5a":
@@ -449,25 +722,52 @@ def cpu_sample(name, args):
     if name == "c5b":
         return workloads.config_c5b(device="cpu", context=16384), "one sequence cut to 16384 tokens"
     ctx = args.context or 4096
-    return workloads.config_c2(device="cpu", batch=4, context=ctx), f"4 of 64 sequences, context {ctx}, own pool"
+    batch = args.batch or 64
+    if full:
+        return workloads.config_c2(device="cpu", batch=batch, context=ctx), f"all {batch} sequences, context {ctx}"
+    return workloads.config_c2(device="cpu", batch=4, context=ctx), f"4 of {batch} sequences, context {ctx}, own pool"
 
 
-def cpu_baseline(name, args, budget_s, kind_label="port"):
+def host_can_hold_full_c2(args):
+    """The full c2 step on the host needs the two pools (4.3 GB) and their clones inside the restated
+    scatter (another 4.3 GB) plus fp32 temporaries: ask for 24 GB of free memory."""
+    try:
+        import psutil
+        return psutil.virtual_memory().available > 24 * (1 << 30) * max(1, (args.batch or 64) * (args.context or 4096)) / (64 * 4096)
+    except Exception:
+        return False
+
+
+def cpu_baseline(name, args, budget_s, kind_label="port", full=False, exact_steps=None):
     from oracle import paged_ref as ref
 
     torch.set_num_threads(os.cpu_count() or 1)
-    wl, sample = cpu_sample(name if name != "c4" else "c2", args)
+    wl, sample = cpu_sample(name if name != "c4" else "c2", args, full)
+    t0 = time.perf_counter()
     ref.decode_step_ref(wl)                                    # warm-up
+    first = time.perf_counter() - t0
     times = []
-    t_end = time.perf_counter() + budget_s
-    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 200):
-        t0 = time.perf_counter()
-        ref.decode_step_ref(wl)
-        times.append(time.perf_counter() - t0)
+    if exact_steps is not None:
+        warm, k = exact_steps
+        # keep the whole run within a few minutes: cut the step count if a step is slower than expected
+        k = max(3, min(k, int(240.0 / max(first, 1e-3))))
+        for _ in range(max(0, warm - 1)):
+            ref.decode_step_ref(wl)
+        for _ in range(k):
+            t0 = time.perf_counter()
+            ref.decode_step_ref(wl)
+            times.append(time.perf_counter() - t0)
+    else:
+        t_end = time.perf_counter() + budget_s
+        while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 200):
+            t0 = time.perf_counter()
+            ref.decode_step_ref(wl)
+            times.append(time.perf_counter() - t0)
     med = statistics.median(times)
     return {"value": wl.batch / med, "unit": "decode tok/s", "cores": torch.get_num_threads(), "kind": kind_label,
             "sample": f"{sample}; median of {len(times)} steps of the torch-CPU restatement of the reference path "
                       f"(clone+index_copy append, index_select gather, matmul/softmax/matmul)",
+            "sample_batch": wl.batch, "timed_steps": len(times),
             "ms_per_step": med * 1e3,
             "attn_GBs": attention_bytes(wl, wl.ctx_len + 1) / med / 1e9}
 
@@ -497,29 +797,48 @@ def c1_case(dev):
     for _ in range(5):
         step()
     gpu = time_region(step, 50, lambda: flush_buf.fill_(1))
+    # the same two calls replayed as one CUDA graph (what a serving loop does with a launch-bound step)
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        step()
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step()
+    for _ in range(5):
+        graph.replay()
+    gpu_graph = time_region(graph.replay, 50, lambda: flush_buf.fill_(1))
     nbytes = attention_bytes(wl, wl.ctx_len + 1) + append_bytes(wl)
     return {"config": "batch 4, 16 heads, head_dim 64, fp32, contexts " + str(wl.ctx_len.tolist()),
             "cpu_ms_per_step": statistics.median(cpu) * 1e3, "cpu_cores": torch.get_num_threads(),
-            "gpu_ms_per_step": statistics.median(gpu), "algorithmic_bytes": nbytes,
-            "note": "latency-bound on the GPU: 1 MB of K/V, four kernel launches"}
+            "gpu_ms_per_step": statistics.median(gpu), "gpu_ms_per_step_graph_replay": statistics.median(gpu_graph),
+            "algorithmic_bytes": nbytes,
+            "note": "latency-bound on the GPU: 1 MB of K/V"}
 
 
 def run_reference(args):
     """``--impl reference``: the reference's own path on the host cores.  The reference is pure
-    Python whose package cannot be imported (syntax errors in three of its modules), so the timed
-    code is the checker's restatement of it on PyTorch CPU operators."""
+    Python whose package cannot be imported (syntax errors in three of its modules) and is not present
+    where this benchmark runs, so the timed code is the checker's restatement of it on PyTorch CPU
+    operators -- on the whole configuration when the host's memory allows, else on a sample of it that
+    the line names."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    name = args.workload
-    base = cpu_baseline(name, args, budget_s=max(5.0, min(60.0, 2.0 * (args.steps + args.warmup))))
-    wl, _ = cpu_sample(name if name != "c4" else "c2", args)
+    name = "c2" if args.workload == "all" else args.workload
+    full = name in ("c2", "c4") and host_can_hold_full_c2(args)
+    base = cpu_baseline(name, args, budget_s=0.0, full=full, exact_steps=(args.warmup, args.steps))
+    wl_dtype = "f16" if name == "c4" else "bf16"
+    cfg = describe(name, args, 0, 1)
+    cfg["timed_batch"] = base["sample_batch"]
+    cfg["timed"] = base["sample"]
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "decode tok/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+        "n_gpus": args.gpus, "steps": base["timed_steps"], "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": {"torch.bfloat16": "bf16", "torch.float16": "f16", "torch.float32": "f32"}[str(wl.dtype)],
-        "data": "synthetic (seeded N(0,1) K/V/q, shuffled page pool)", "config": describe(name, args, 0, 1),
+        "dtype": wl_dtype,
+        "data": "synthetic (seeded N(0,1) K/V/q, shuffled page pool)", "config": cfg,
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "decode tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -533,11 +852,13 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5a", "c5b"])
+    ap.add_argument("--workload", default="all", choices=["all", "c2", "c3", "c4", "c5a", "c5b"],
+                    help="all = the c2 headline plus one sub-record per other configuration")
     ap.add_argument("--batch", type=int, default=0, help="override the number of sequences (small ncu captures)")
     ap.add_argument("--context", type=int, default=0, help="override the context length")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--kv-fp8", action="store_true", help="store K/V as e4m3 with per-tensor scales (c2/c3/c5a)")
+    ap.add_argument("--sustained", action="store_true", help="add the seconds-long leg to a single-workload run")
     ap.add_argument("--no-graph", action="store_true", help="head-parallel mode: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -24,6 +24,7 @@ from .attention import (  # noqa: F401
 )
 from .paged_cache import PagedKVCache  # noqa: F401
 from .decode_step import GraphedDecodeStep  # noqa: F401
+from .decode_loop import decode_loop  # noqa: F401
 from .sharding import HeadParallelDecoder, shard_requests  # noqa: F401
 
 __version__ = "0.1.0"

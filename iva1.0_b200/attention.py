@@ -169,6 +169,24 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
 _PAGE = 16
 
 
+def _mask_to_key_range(attention_mask: torch.Tensor, B: int, L: int):
+    """A key padding mask ``[B,L]`` (non-zero = visible, src/core/attention.py:95-97) as the key range
+    ``[begin_b, end_b)`` of every row.  Only what padding produces is representable without a mask
+    tensor in the kernels: one contiguous run of visible keys per row (right padding, left padding, or
+    both).  Anything else raises.  Costs one host synchronisation (the check)."""
+    m = attention_mask.reshape(B, -1) != 0
+    if m.shape[1] != L:
+        raise ValueError(f"attention_mask covers {m.shape[1]} keys, the layer sees {L}")
+    idx = torch.arange(L, device=m.device, dtype=torch.int32)
+    count = m.sum(1, dtype=torch.int32)
+    begin = torch.where(m, idx, L).amin(1).to(torch.int32)
+    end = (torch.where(m, idx, -1).amax(1) + 1).to(torch.int32)
+    begin = torch.where(count > 0, begin, torch.zeros_like(begin))
+    if not bool((end - begin == count).all()):
+        raise NotImplementedError("attention_mask must keep one contiguous run of keys per row (padding at either end)")
+    return begin.contiguous(), end.contiguous()
+
+
 def _dense_as_pool(k: torch.Tensor, v: torch.Tensor):
     """View dense ``[B,H,L,D]`` K/V as a page pool plus a block table.
 
@@ -263,8 +281,10 @@ class AttentionB200(nn.Module):
     (``evict_before``).  ``sink_cfg={"sink_tokens": n}`` together with a sliding window keeps the first
     ``n`` keys visible in front of the window (the reference ANDs its sink mask, attention.py:131-148,
     with the window mask, which keeps nothing extra; the streaming-attention meaning of the option is
-    implemented).  Padding masks raise ``NotImplementedError``; RoPE state is ignored, as in the
-    reference.
+    implemented).  ``attention_mask`` is the reference's key padding mask ``[B,L]`` (attention.py:95-97):
+    it is translated into a key range per row (padding at either end; a mask with holes raises), which
+    costs one host synchronisation per call.  A row whose mask hides every key yields zeros (the
+    reference's softmax over an all-masked row yields NaN).  RoPE state is ignored, as in the reference.
     """
 
     def __init__(self, config):
@@ -286,8 +306,6 @@ class AttentionB200(nn.Module):
                 kv_cache: Optional[Any] = None, rope_state: Optional[torch.Tensor] = None,
                 sliding_window: Optional[int] = None, sink_cfg: Optional[Dict[str, Any]] = None
                 ) -> Tuple[torch.Tensor, Optional[Any]]:
-        if attention_mask is not None:
-            raise NotImplementedError("AttentionB200 implements the decode path: no padding mask")
         sink = int(sink_cfg.get("sink_tokens", 4)) if sink_cfg is not None else 0
         if sink and (sliding_window is None or not getattr(kv_cache, "is_paged", False) or x.shape[1] != 1):
             raise NotImplementedError("sink_cfg is supported for single-token decode on a PagedKVCache with a sliding window")
@@ -303,7 +321,18 @@ class AttentionB200(nn.Module):
         if getattr(kv_cache, "is_paged", False):
             prior = kv_cache.append(k, v)                     # [B] lengths before the append (host list)
             bt, cl = kv_cache.block_table_dev, kv_cache.ctx_len_dev
-            if S == 1:
+            if attention_mask is not None:
+                # padding: keys [m_begin, m_end) of each row are real (attention.py:95-97 hides the others)
+                if S != 1:
+                    raise NotImplementedError("attention_mask with a paged cache is supported for single-token decode")
+                m_begin, m_end = _mask_to_key_range(attention_mask, B, max(prior) + 1)
+                cl = torch.minimum(cl, m_end)
+                cb = m_begin if sliding_window is None else torch.maximum(m_begin, (cl - int(sliding_window)).clamp_(min=0))
+                if sink:
+                    raise NotImplementedError("sink_cfg together with attention_mask")
+                o = paged_decode_attention(q.reshape(B, H, D), kv_cache.k_pool, kv_cache.v_pool, bt, cl,
+                                           kv_cache.page_size, self.scale, ctx_begin=cb)
+            elif S == 1:
                 cb = None if sliding_window is None else (cl - int(sliding_window)).clamp_(min=0)
                 o = paged_decode_attention(q.reshape(B, H, D), kv_cache.k_pool, kv_cache.v_pool, bt, cl,
                                            kv_cache.page_size, self.scale, ctx_begin=cb, sink_tokens=sink)
@@ -343,6 +372,11 @@ class AttentionB200(nn.Module):
                 cl = pos1                       # the window mask also hides the keys after the query
             if sliding_window is not None:
                 cb = (pos1 - int(sliding_window)).clamp(min=0)
+            if attention_mask is not None:
+                m_begin, m_end = _mask_to_key_range(attention_mask, B, kh.shape[2])
+                m_begin, m_end = m_begin.view(B, 1).expand(B, S), m_end.view(B, 1).expand(B, S)
+                cl = m_end if cl is None else torch.minimum(cl.to(torch.int32), m_end)
+                cb = m_begin if cb is None else torch.maximum(cb.to(torch.int32), m_begin)
             o = attention(q.transpose(1, 2), kh, vh, self.scale, 0.0, False, ctx_len=cl, ctx_begin=cb)
             o = o.transpose(1, 2).reshape(B, S, dm)
         return self.o_proj(o), new_cache

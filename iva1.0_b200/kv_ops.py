@@ -204,7 +204,7 @@ def paged_append(k_pool: torch.Tensor, v_pool: torch.Tensor, slot_mapping: torch
 
 def paged_gather(pool: torch.Tensor, block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int,
                  *, layout: str = "token_major", out_offsets: Optional[torch.Tensor] = None,
-                 total_tokens: Optional[int] = None, check: bool = False
+                 total_tokens: Optional[int] = None, check: bool = False, out: Optional[torch.Tensor] = None
                  ) -> Union[torch.Tensor, List[torch.Tensor]]:
     """Gather every sequence's tokens from the pool to contiguous storage in one launch.
 
@@ -213,7 +213,8 @@ def paged_gather(pool: torch.Tensor, block_table: torch.Tensor, ctx_len: torch.T
     ``[1,H,L_s,D]`` views, the reference gather's output layout
     (src/kernels_t/kv_ops_triton.py:112-123).  Pass ``out_offsets`` (int64 ``[B+1]`` on the
     device) and ``total_tokens`` to avoid the host synchronisation that sizing the output
-    otherwise needs.
+    otherwise needs.  ``out`` (with both of those) is a contiguous tensor of ``total_tokens * H * D`` elements
+    to gather into; it is returned as it is.
     """
     _lib.require_cuda(pool, block_table, ctx_len)
     if layout not in ("token_major", "head_major"):
@@ -235,9 +236,15 @@ def paged_gather(pool: torch.Tensor, block_table: torch.Tensor, ctx_len: torch.T
         total_tokens = int(lens_host.sum())
     else:
         offs = out_offsets.to(device=dev, dtype=torch.int64).contiguous()
-    # (an empty result still needs a real base pointer for the library's argument check)
-    buf = torch.empty(max(total_tokens, 1), H, D, device=dev, dtype=pool.dtype)
-    out = buf[:total_tokens]
+    given = out
+    if given is not None:
+        if out_offsets is None or not given.is_contiguous() or given.dtype != pool.dtype or given.numel() != total_tokens * H * D:
+            raise ValueError("out must be contiguous, of the pool's dtype, hold total_tokens*H*D elements, and come with out_offsets")
+        buf = given
+    else:
+        # (an empty result still needs a real base pointer for the library's argument check)
+        buf = torch.empty(max(total_tokens, 1), H, D, device=dev, dtype=pool.dtype)
+        out = buf[:total_tokens]
     status = _status_word(dev)
     with torch.cuda.device(dev):
         _lib.check(lib.ivab_paged_gather(
@@ -246,6 +253,8 @@ def paged_gather(pool: torch.Tensor, block_table: torch.Tensor, ctx_len: torch.T
             _lib.dtype_code(pool.dtype), B, H, D, page_size, num_pages, bt.shape[1],
             status.data_ptr(), _lib.stream_ptr(dev)))
     _check_status(dev, check)
+    if given is not None:
+        return given
     if layout == "token_major":
         return out
     if lens_host is None:

@@ -87,6 +87,11 @@ class PagedKVCache:
                                           device=self.device)
         self.ctx_len_dev = torch.zeros(batch_size, dtype=torch.int32, device=self.device)
         self._bt_dirty = False
+        # Uploads of the host tables go through a small ring of pinned blocks that are allocated once:
+        # an asynchronous copy reads host memory when it EXECUTES, so the block it reads must not be
+        # rewritten before then; every block carries an event recorded behind its last copy.
+        self._ring: List[dict] = []
+        self._ring_pos = 0
         if seq_len:
             self._reserve([seq_len] * batch_size)
             self._sync_device()
@@ -134,20 +139,63 @@ class PagedKVCache:
             self._lens[s] = L
             self._len_host[s] = L
 
-    def _staged(self, t: torch.Tensor) -> torch.Tensor:
-        """A private pinned snapshot of a host table: the asynchronous upload reads host memory
-        when the copy executes, so it must not alias a buffer the next step will overwrite."""
-        return t.clone().pin_memory() if self.device.type == "cuda" else t.clone()
+    _RING = 4
 
-    def _sync_device(self) -> None:
+    def _stage_block(self, n_slots: int) -> dict:
+        """The next pinned block of the upload ring, free to be rewritten (its previous copies have run)
+        and large enough for ``n_slots`` slot ids."""
+        if not self._ring:
+            self._ring = [None] * self._RING
+        i = self._ring_pos
+        self._ring_pos = (i + 1) % self._RING
+        blk = self._ring[i]
+        cuda = self.device.type == "cuda"
+        if blk is None or blk["slots"].numel() < n_slots:
+            def pinned(*shape, dtype):
+                t = torch.empty(*shape, dtype=dtype)
+                return t.pin_memory() if cuda else t
+            blk = {"bt": pinned(self.batch_size, self.max_pages_per_seq, dtype=torch.int32),
+                   "len": pinned(self.batch_size, dtype=torch.int32),
+                   "slots": pinned(max(n_slots, self.batch_size), dtype=torch.int64),
+                   "event": torch.cuda.Event() if cuda else None, "used": False}
+            self._ring[i] = blk
+        elif blk["used"] and blk["event"] is not None:
+            blk["event"].synchronize()          # normally long complete: the ring is several steps deep
+        return blk
+
+    def _sync_device(self, slots: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Upload the lengths, the block table if it changed, and optionally a slot mapping (int64 host
+        tensor); returns the slot mapping on the device.  One pinned staging block per call."""
+        n = 0 if slots is None else slots.numel()
+        blk = self._stage_block(n)
+        slot_dev = None
         if self._bt_dirty:
-            self.block_table_dev.copy_(self._staged(self._bt_host), non_blocking=True)
+            blk["bt"].copy_(self._bt_host)
+            self.block_table_dev.copy_(blk["bt"], non_blocking=True)
             self._bt_dirty = False
-        self.ctx_len_dev.copy_(self._staged(self._len_host), non_blocking=True)
+        blk["len"].copy_(self._len_host)
+        self.ctx_len_dev.copy_(blk["len"], non_blocking=True)
+        if slots is not None:
+            blk["slots"][:n].copy_(slots)
+            slot_dev = blk["slots"][:n].to(self.device, non_blocking=True)
+        if blk["event"] is not None:
+            blk["event"].record(torch.cuda.current_stream(self.device))
+            blk["used"] = True
+        return slot_dev
 
     def slots(self, seq: int, start: int, stop: int) -> List[int]:
         ps, tab = self.page_size, self._tables[seq]
         return [tab[p // ps] * ps + p % ps for p in range(start, stop)]
+
+    def _slots_all(self, start, count: int) -> torch.Tensor:
+        """Slot ids of positions ``start[s] .. start[s]+count-1`` of every sequence, flattened sequence-major
+        (int64 host tensor); ``start`` is an int or one int per sequence.  Tensor arithmetic on the host
+        block table: no per-token Python loop."""
+        ps = self.page_size
+        st = torch.as_tensor(start, dtype=torch.int64).reshape(-1, 1).expand(self.batch_size, 1)
+        pos = st + torch.arange(count, dtype=torch.int64).view(1, count)
+        pages = torch.gather(self._bt_host, 1, (pos // ps).clamp_(max=self.max_pages_per_seq - 1)).to(torch.int64)
+        return (pages * ps + pos % ps).reshape(-1)
 
     # ---- the hot path -----------------------------------------------------------------------
 
@@ -169,14 +217,7 @@ class PagedKVCache:
         if self._step is None:
             prior = list(self._lens)
             self._reserve([L + S for L in prior])
-            slots: List[int] = []
-            for s in range(B):
-                slots.extend(self.slots(s, prior[s], prior[s] + S))
-            slot_t = torch.tensor(slots, dtype=torch.int64)
-            if self.device.type == "cuda":
-                slot_t = slot_t.pin_memory()
-            slot_dev = slot_t.to(self.device, non_blocking=True)
-            self._sync_device()
+            slot_dev = self._sync_device(self._slots_all(prior, S))
             self._step = {"prior": prior, "slots": slot_dev, "S": S, "done": set()}
         st = self._step
         if S != st["S"] or layer in st["done"]:
@@ -198,9 +239,18 @@ class PagedKVCache:
     # ---- KVCache duck type (rope_kv.py:83-137) ----------------------------------------------------
 
     def _dense(self, pool: torch.Tensor) -> torch.Tensor:
-        seqs = paged_gather(pool, self.block_table_dev, self.ctx_len_dev, self.page_size, layout="head_major")
         L = self.seq_len
-        out = torch.zeros(self.batch_size, self.n_heads, L, self.head_dim, device=self.device, dtype=self.dtype)
+        B, H, D = self.batch_size, self.n_heads, self.head_dim
+        if L and min(self._lens) == L:
+            # every sequence has the same length (the reference cache knows no other case): sequence s of the
+            # head-major gather is [H,L,D] at offset s*L*H*D, i.e. the kernel writes the dense tensor itself
+            out = torch.empty(B, H, L, D, device=self.device, dtype=self.dtype)
+            offs = torch.arange(B + 1, dtype=torch.int64, device=self.device) * L
+            paged_gather(pool, self.block_table_dev, self.ctx_len_dev, self.page_size, layout="head_major",
+                         out_offsets=offs, total_tokens=B * L, out=out)
+            return out
+        seqs = paged_gather(pool, self.block_table_dev, self.ctx_len_dev, self.page_size, layout="head_major")
+        out = torch.zeros(B, H, L, D, device=self.device, dtype=self.dtype)
         for s, t in enumerate(seqs):
             out[s, :, :t.shape[2]] = t[0]
         return out
@@ -221,11 +271,7 @@ class PagedKVCache:
         B, H, S, D = new_k.shape
         end = start_pos + S
         self._reserve([max(L, end) for L in self._lens])
-        slots: List[int] = []
-        for s in range(B):
-            slots.extend(self.slots(s, start_pos, end))
-        slot_dev = torch.tensor(slots, dtype=torch.int64).to(self.device)
-        self._sync_device()
+        slot_dev = self._sync_device(self._slots_all(start_pos, S))
         paged_append(self.k_pool, self.v_pool, slot_dev,
                      new_k.permute(0, 2, 1, 3).reshape(B * S, H, D).contiguous(),
                      new_v.permute(0, 2, 1, 3).reshape(B * S, H, D).contiguous(), self.page_size)

@@ -250,11 +250,12 @@ class KVCacheRef:
         return self.k[:, :, start:end], self.v[:, :, start:end]
 
 
-def attention_module_ref(x, wq, wk, wv, wo, n_heads, cache_k=None, cache_v=None, sliding_window=None):
+def attention_module_ref(x, wq, wk, wv, wo, n_heads, cache_k=None, cache_v=None, sliding_window=None,
+                         attention_mask=None):
     """AttentionTorch.forward (src/core/attention.py:46-110) with ``causal=False``, eval mode:
     projections (:49-55), cache concat (:61-63), attention (:77,99,102), optional sliding-window
-    mask (:83-87,115-129; query ``i`` keeps keys ``max(0,i-w+1)..i``), output projection
-    (:104-108).  Returns ``(output, k_all, v_all)``."""
+    mask (:83-87,115-129; query ``i`` keeps keys ``max(0,i-w+1)..i``), optional key padding mask
+    ``[B,L]`` (:95-97), output projection (:104-108).  Returns ``(output, k_all, v_all)``."""
     B, S, dm = x.shape
     hd = dm // n_heads
     q = F.linear(x, wq).view(B, S, n_heads, hd).transpose(1, 2)
@@ -269,6 +270,8 @@ def attention_module_ref(x, wq, wk, wv, wo, n_heads, cache_k=None, cache_v=None,
         for i in range(S):
             mask[i, max(0, i - sliding_window + 1):min(k.size(2), i + 1)] = 1
         scores = scores.masked_fill(mask == 0, float("-inf"))
+    if attention_mask is not None:
+        scores = scores.masked_fill(attention_mask.unsqueeze(1).unsqueeze(2) == 0, float("-inf"))
     w = F.softmax(scores, dim=-1)
     o = torch.matmul(w, v).transpose(1, 2).contiguous().view(B, S, dm)
     return F.linear(o, wo), k, v

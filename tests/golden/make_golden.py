@@ -84,6 +84,18 @@ def window_inputs(seed=14):
     return torch.randn(2, 12, 4 * 32, generator=g)
 
 
+def padding_masks():
+    """Key padding masks (attention.py:95-97) for the 12-token input (row 0 padded on the right, row 1 on
+    the left) and for the 7-key cache plus one new token (row 0 left, row 1 right)."""
+    m12 = torch.ones(2, 12)
+    m12[0, 9:] = 0
+    m12[1, :3] = 0
+    m8 = torch.ones(2, 8)
+    m8[0, :2] = 0
+    m8[1, 6:] = 0
+    return m12, m8
+
+
 def c1_module_workload():
     """Config C1 with the new token's K and V equal to q: with identity projections the
     reference module appends ``k = v = x`` (attention.py:50-51,62-63)."""
@@ -157,6 +169,16 @@ def main(ref_root):
         yw, none_cache = mod(xw, sliding_window=5)
     assert none_cache is None
     out["module_window_out"] = yw.numpy()
+
+    # key padding masks (attention.py:95-97): the 12-token input alone, and one token on the 7-key cache
+    m12, m8 = padding_masks()
+    with torch.no_grad():
+        yp, _ = mod(xw, attention_mask=m12)
+        cache = _Cache(B, H, hd, L, "cpu")
+        cache.k, cache.v = ck, cv
+        ypc, _ = mod(x, kv_cache=cache, attention_mask=m8)
+    out["module_padding_out"] = yp.numpy()
+    out["module_padding_cache_out"] = ypc.numpy()
 
     wl = c1_module_workload()
     Hh, D = wl.n_q_heads, wl.head_dim

@@ -315,6 +315,35 @@ def test_module_sliding_window_matches_attention_torch_golden(golden, golden_inp
     assert (y.cpu() - torch.from_numpy(golden["module_window_out"])).abs().max().item() <= 5e-5
 
 
+def test_module_padding_masks_match_attention_torch_golden(golden, golden_inputs):
+    """AttentionB200 with the reference's key padding mask (attention.py:95-97), against the reference
+    module's own outputs: a 12-token input without a cache (row 0 padded right, row 1 left), one token
+    on the dense 7-key cache, and the same step on a PagedKVCache.  A mask with a hole is refused."""
+    B, H, hd, L, w, x, ck, cv = golden_inputs.module_inputs()
+    m12, m8 = golden_inputs.padding_masks()
+    cfg = SimpleNamespace(d_model=H * hd, n_heads=H, dropout=0.0, causal=False, attn_impl="triton")
+    mod = iva_b200.get_attention(cfg).to(DEV).eval()
+    mod.load_state_dict({"q_proj.weight": w[0], "k_proj.weight": w[1], "v_proj.weight": w[2], "o_proj.weight": w[3]})
+    y, _ = mod(golden_inputs.window_inputs().to(DEV), attention_mask=m12.to(DEV))
+    assert (y.cpu() - torch.from_numpy(golden["module_padding_out"])).abs().max().item() <= 5e-5
+    cache = ref.KVCacheRef(B, H, hd, L, DEV, torch.float32)
+    cache.k, cache.v = ck.to(DEV), cv.to(DEV)
+    y, _ = mod(x.to(DEV), kv_cache=cache, attention_mask=m8.to(DEV))
+    assert (y.cpu() - torch.from_numpy(golden["module_padding_cache_out"])).abs().max().item() <= 5e-5
+    # the same cache contents in pages: K/V of the 7 cached tokens are what the projections of some
+    # prompt would have produced, so they are written straight into the pool
+    paged = iva_b200.PagedKVCache(batch_size=B, n_heads=H, head_dim=hd, device=DEV, dtype=torch.float32,
+                                  max_seq_len=32, shuffle_seed=9)
+    paged.update(ck.to(DEV), cv.to(DEV), 0)
+    y, same = mod(x.to(DEV), kv_cache=paged, attention_mask=m8.to(DEV))
+    assert same is paged and paged.lengths == [L + 1] * B
+    assert (y.cpu() - torch.from_numpy(golden["module_padding_cache_out"])).abs().max().item() <= 5e-5
+    holes = m8.clone()
+    holes[0, 4] = 0
+    with pytest.raises(NotImplementedError, match="contiguous"):
+        mod(x.to(DEV), kv_cache=cache, attention_mask=holes.to(DEV))
+
+
 @pytest.mark.parametrize("dtype,Hq,Hkv,D", [(torch.bfloat16, 8, 8, 128), (torch.bfloat16, 16, 4, 128), (torch.float32, 4, 2, 64)])
 @pytest.mark.parametrize("sink", [1, 4, 16, 20, 40])
 def test_attention_sinks_in_front_of_a_window(dtype, Hq, Hkv, D, sink):

@@ -86,6 +86,76 @@ def test_three_layer_decode_loop_carries_one_cache_across_steps_and_layers():
         cache.layer(0).append(k, k)
 
 
+def test_decode_loop_function_matches_the_layer_by_layer_checker():
+    """``decode_loop``: a 13-token prompt and six autoregressive steps through two layers on one shared
+    cache, each step's input built from the previous step's output, against the checker's dense caches."""
+    torch.manual_seed(7)
+    B, H, hd, L = 2, 2, 64, 2
+    dm = H * hd
+    cfg = SimpleNamespace(d_model=dm, n_heads=H, dropout=0.0, causal=False, attn_impl="b200")
+    layers = [iva_b200.AttentionB200(cfg).to(DEV).eval() for _ in range(L)]
+    wts = [[p.detach().cpu() for p in (m.q_proj.weight, m.k_proj.weight, m.v_proj.weight, m.o_proj.weight)] for m in layers]
+    cache = iva_b200.PagedKVCache(batch_size=B, n_heads=H, head_dim=hd, device=DEV, dtype=torch.float32,
+                                  max_seq_len=48, shuffle_seed=2, n_layers=L)
+    prompt = torch.randn(B, 13, dm)
+
+    def next_x(prev, t):                                  # step t+1 is a function of step t's output
+        if t == 0:
+            return prompt.to(DEV)
+        return torch.tanh(prev[:, -1:, :]) if t <= 6 else None
+
+    outs = iva_b200.decode_loop(layers, cache, next_x)
+    assert len(outs) == 7 and cache.lengths == [19, 19]
+    dense = [(None, None)] * L
+    x = prompt
+    for t in range(7):
+        h = x
+        for i in range(L):
+            y, dk, dv = ref.attention_module_ref(h, *wts[i], H, *dense[i])
+            dense[i] = (dk, dv)
+            h = h + y
+        assert (outs[t].cpu() - h).abs().max().item() <= 5e-4, t
+        x = torch.tanh(h[:, -1:, :])
+    with pytest.raises(ValueError, match="layers"):
+        iva_b200.decode_loop(layers[:1], cache, [prompt.to(DEV)])
+
+
+def test_step_buffers_keep_two_steps_apart():
+    """Two steps enqueued back to back from the two staging buffers, then read in order: each result is
+    the one of its own inputs (the second step sees the first step's appended token), also with fp32 output."""
+    g = torch.Generator().manual_seed(11)
+    wl = workloads.make_decode_workload("buf", torch.tensor([70, 31, 300]) + 6, n_q_heads=8, n_kv_heads=2, head_dim=128,
+                                        dtype=torch.bfloat16, seed=5, free_frac=0.1)
+    d = wl.to(DEV)
+    ctx = torch.tensor([70, 31, 300])
+    step = iva_b200.GraphedDecodeStep(d.k_pool, d.v_pool, d.block_table, n_q_heads=8, return_lse=True,
+                                      out_dtype=torch.float32)
+    assert step.n_buffers == 2
+    k_ref, v_ref = wl.k_pool.clone(), wl.v_pool.clone()
+    for rounds in range(3):                                # eager, capture, replay
+        feeds = []
+        for b in range(2):
+            L = ctx + 2 * rounds + b
+            q = torch.randn(3, 8, 128, generator=g).to(torch.bfloat16)
+            kn = torch.randn(3, 2, 128, generator=g).to(torch.bfloat16)
+            vn = torch.randn(3, 2, 128, generator=g).to(torch.bfloat16)
+            slots = torch.tensor([int(wl.block_table[s, int(L[s]) // 16]) * 16 + int(L[s]) % 16 for s in range(3)])
+            io = step.inputs(b)
+            io.q_host.copy_(q); io.k_new_host.copy_(kn); io.v_new_host.copy_(vn)
+            io.slot_mapping_host.copy_(slots); io.ctx_len_host.copy_((L + 1).to(torch.int32))
+            step.run(b)                                   # both steps are in flight before either is read
+            feeds.append((q, kn, vn, slots, L))
+        for b, (q, kn, vn, slots, L) in enumerate(feeds):
+            out = step.result(b)
+            assert out.dtype == torch.float32
+            k_ref = ref.paged_append_ref(k_ref, slots, kn)
+            v_ref = ref.paged_append_ref(v_ref, slots, vn)
+            out_ref, lse_ref = ref.paged_decode_ref(q, k_ref, v_ref, wl.block_table, L + 1, 16)
+            assert_attn_close(out, out_ref, torch.bfloat16, strict=True)      # fp32 output: the plain bar
+            assert_lse_close(step.inputs(b).lse_host, lse_ref)
+    assert step.graph is not None and step.inputs(1).graph is not None
+
+
 def test_fp8_cache_object():
     cache = iva_b200.PagedKVCache(batch_size=2, n_heads=2, head_dim=128, device=DEV, dtype=torch.float8_e4m3fn,
                                   max_seq_len=64, k_scale=0.02, v_scale=0.02)

@@ -119,3 +119,14 @@ def test_kv_cache_restatement():
     assert torch.equal(a, k[:, :, :2]) and torch.equal(b, -k[:, :, :2])
     c.clear()
     assert not c.k.any() and c.seq_len == 6
+
+
+def test_padding_masks_match_attention_torch(golden, golden_inputs):
+    """The checker's key padding mask against the reference module's own outputs (attention.py:95-97):
+    a 12-token input without a cache, and one token on the 7-key cache."""
+    B, H, hd, L, w, x, ck, cv = golden_inputs.module_inputs()
+    m12, m8 = golden_inputs.padding_masks()
+    y, _, _ = ref.attention_module_ref(golden_inputs.window_inputs(), *w, H, attention_mask=m12)
+    assert (y - _t(golden["module_padding_out"])).abs().max().item() <= 1e-6
+    y, _, _ = ref.attention_module_ref(x, *w, H, ck, cv, attention_mask=m8)
+    assert (y - _t(golden["module_padding_cache_out"])).abs().max().item() <= 1e-6
