@@ -303,12 +303,25 @@ def quantise_pools(wl, dev):
     return {"k_scale": 1.0 / 64, "v_scale": 1.0 / 64}
 
 
-def flusher(dev, nbytes_read):
-    """An L2 flush (a write larger than the 126 MB L2) for workloads whose K/V would otherwise stay cached."""
-    if nbytes_read > 4 * 126e6:
+_flush_bufs = {}
+
+
+def flusher(dev, nbytes_read=0, always=False):
+    """An L2 flush (two writes of 512 MB, the L2 holds 126 MB) for workloads whose K/V would otherwise
+    stay cached.  ``always``: also for legs whose GPU time per call is shorter than the host's launch
+    cost -- the ~170 us of flush keep the host ahead of the GPU, so the event pair around the call
+    measures the device and not the launch path."""
+    if nbytes_read > 4 * 126e6 and not always:
         return None, None
-    buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-    return buf, (lambda: buf.fill_(1))
+    buf = _flush_bufs.get(dev)
+    if buf is None:
+        buf = _flush_bufs[dev] = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def flush():
+        buf.fill_(1)
+        buf.fill_(2)
+
+    return buf, flush
 
 
 # ---- decode workloads (c2, c3, c5a) ----------------------------------------------------------------------
@@ -344,7 +357,7 @@ def measure_decode(name, wl, ranks, steps, warmup, kv_scales, seqs_total):
     ranks.barrier()
     launches = lib.ivab_launch_count() - launches0
     attn_ms = time_region(attend, steps, flush)
-    app_ms = time_region(append, steps, flush)
+    app_ms = time_region(append, steps, flusher(dev, always=True)[1])   # microseconds of GPU time: keep the host ahead
     total_ms = ranks.max(sum(per_step))
     ms_per_step = total_ms / steps
     rec = {"ms_per_step": ms_per_step, "value": seqs_total * wl.new_tokens_per_seq / (ms_per_step * 1e-3),
@@ -554,7 +567,7 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True):
     else:
         hp = None
         k_loc, v_loc, k_new, v_new = wl.k_pool, wl.v_pool, wl.k_new, wl.v_new
-    flush_buf, flush = flusher(dev, nbytes)
+    flush_buf, flush = flusher(dev, nbytes, always=True)   # a step is ~0.1 ms or less: see flusher()
 
     def append():
         iva_b200.paged_append(k_loc, v_loc, wl.slot_mapping, k_new, v_new, wl.page_size)
@@ -596,7 +609,7 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True):
             "roofline_local_kernels": roofline_record(nbytes, kern, "this rank's plan + decode + merge kernels"),
             "kv_heads_per_rank": wl.n_kv_heads // world, "collective": None if world == 1 else
             "one NCCL all_gather_into_tensor of [1, H_q/N, D+1] fp32 per step (eager; local kernels in a CUDA graph)",
-            "l2": "flushed between timed steps" if flush else "K/V per step exceed L2"}
+            "l2": "flushed between timed steps"}
 
 
 # ---- the GPU arm --------------------------------------------------------------------------------------
@@ -788,7 +801,7 @@ def c1_case(dev):
     d = wl.to(dev)
     lens = (d.ctx_len + 1).contiguous()
     out = torch.empty(wl.batch, wl.n_q_heads, wl.head_dim, device=dev, dtype=wl.dtype)
-    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    _, flush = flusher(dev, always=True)
 
     def step():
         iva_b200.paged_append(d.k_pool, d.v_pool, d.slot_mapping, d.k_new, d.v_new, wl.page_size)
@@ -796,7 +809,7 @@ def c1_case(dev):
 
     for _ in range(5):
         step()
-    gpu = time_region(step, 50, lambda: flush_buf.fill_(1))
+    gpu = time_region(step, 50, flush)
     # the same two calls replayed as one CUDA graph (what a serving loop does with a launch-bound step)
     side = torch.cuda.Stream(device=dev)
     side.wait_stream(torch.cuda.current_stream(dev))
@@ -808,13 +821,14 @@ def c1_case(dev):
         step()
     for _ in range(5):
         graph.replay()
-    gpu_graph = time_region(graph.replay, 50, lambda: flush_buf.fill_(1))
+    gpu_graph = time_region(graph.replay, 50, flush)
     nbytes = attention_bytes(wl, wl.ctx_len + 1) + append_bytes(wl)
     return {"config": "batch 4, 16 heads, head_dim 64, fp32, contexts " + str(wl.ctx_len.tolist()),
             "cpu_ms_per_step": statistics.median(cpu) * 1e3, "cpu_cores": torch.get_num_threads(),
             "gpu_ms_per_step": statistics.median(gpu), "gpu_ms_per_step_graph_replay": statistics.median(gpu_graph),
             "algorithmic_bytes": nbytes,
-            "note": "latency-bound on the GPU: 1 MB of K/V"}
+            "note": "latency-bound on the GPU: 1 MB of K/V; the graph replay is the device time (two kernels), the "
+                    "eager figure includes what the Python launch path adds when the GPU is faster than the host"}
 
 
 def run_reference(args):

@@ -80,6 +80,29 @@ int ivab_kv_gather(const void* cache, const int64_t* indices, void* out, int dty
                    int32_t* status, void* stream);
 
 /*
+ * ivab_kv_gather with one index vector PER BATCH ROW: row b uses indices + b*indices_stride_b, and an
+ * index of -1 is padding (the output row is left untouched, no status bit).  Together with
+ * ivab_compact_indices this is the corrected form of kv_compact_kernel / kv_compact_triton
+ * (src/kernels_t/kv_ops_triton.py:68-92,159-181), whose mask is [B,S] with independent rows.
+ */
+int ivab_kv_gather_rows(const void* cache, const int64_t* indices, int64_t indices_stride_b, void* out,
+                        int dtype, int out_dtype,
+                        int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
+                        int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
+                        int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
+                        int32_t* status, void* stream);
+
+/*
+ * Positions kept by a compaction mask: for every row b of `mask` (uint8 [batch, seq_len], non-zero = keep)
+ *   indices[b, j] = position of the j-th kept entry for j < counts[b], and -1 behind them
+ * (`indices` is int64 [batch, seq_len], `counts` int32 [batch]; one prefix scan per row, one launch).
+ * This is the mask test of kv_compact_kernel (src/kernels_t/kv_ops_triton.py:82-84) turned into the
+ * destination rows that kernel fails to compute (it writes survivor s to output row s, :86).
+ */
+int ivab_compact_indices(const uint8_t* mask, int64_t batch, int64_t seq_len, int64_t* indices,
+                         int32_t* counts, void* stream);
+
+/*
  * cache[b,h,indices[n],:] = values[b,h,n,:]   (IN PLACE)
  * Replaces kv_scatter_kernel (src/kernels_t/kv_ops_triton.py:43-65).  The reference clones
  * the whole cache first (kv_ops_triton.py:129); a caller that wants that behaviour clones

@@ -26,6 +26,8 @@ SIGNATURES = {
     "ivab_version": (c_int, []),
     "ivab_launch_count": (c_int64, []),
     "ivab_kv_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int] + [c_int64] * 11 + [c_void_p, c_void_p]),
+    "ivab_kv_gather_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int] + [c_int64] * 11 + [c_void_p, c_void_p]),
+    "ivab_compact_indices": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "ivab_kv_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_int] + [c_int64] * 11 + [c_void_p, c_void_p]),
     "ivab_paged_append": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                   c_int64, c_int] + [c_int64] * 5 + [c_void_p, c_void_p]),

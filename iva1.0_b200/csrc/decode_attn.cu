@@ -86,6 +86,35 @@ int target_chunks_for(int64_t kv_heads) {
     return (int)(t < 1 ? 1 : t);
 }
 
+// IVAB_DIRECT=0 sends small batches through the plan kernel as well (experiments, A/B runs).
+bool use_direct_mode() {
+    static bool v = [] {
+        const char* e = std::getenv("IVAB_DIRECT");
+        return !(e && std::atoi(e) == 0);
+    }();
+    return v;
+}
+
+// IVAB_PLAN_PDL=0 launches the plan kernel in plain stream order.
+bool use_plan_pdl() {
+    static bool v = [] {
+        const char* e = std::getenv("IVAB_PLAN_PDL");
+        const char* all = std::getenv("IVAB_PDL");
+        return !(e && std::atoi(e) == 0) && !(all && std::atoi(all) == 0);
+    }();
+    return v;
+}
+
+// Smallest chunk (pages) the plan-free mode cuts; IVAB_DIRECT_MIN_CHUNK overrides it for experiments.
+int direct_min_chunk_pages() {
+    static int v = [] {
+        const char* e = std::getenv("IVAB_DIRECT_MIN_CHUNK");
+        const int n = e ? std::atoi(e) : kDirectMinChunkPages;
+        return n < 1 ? 1 : n;
+    }();
+    return v;
+}
+
 size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D, Workspace* ws) {
     const int target = target_chunks_for(Hkv);
     const int64_t cap = B + target;
@@ -93,6 +122,7 @@ size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D
     char* p = static_cast<char*>(base);
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return p ? p + o : nullptr; };
     int* header = reinterpret_cast<int*>(take(kHdrWords * sizeof(int)));
+    int* slots = reinterpret_cast<int*>(take(kStatusSlots * sizeof(int)));   // (ivab_decode_status reads header + slots in one copy)
     int* prefix = reinterpret_cast<int*>(take((B + 1) * sizeof(int)));
     int* order = reinterpret_cast<int*>(take(B * sizeof(int)));
     int* seq_first = reinterpret_cast<int*>(take(B * sizeof(int)));
@@ -103,7 +133,7 @@ size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D
     float* po = reinterpret_cast<float*>(take((size_t)cap * Hq * D * sizeof(float)));
     if (ws) { ws->header = header; ws->pos_prefix = prefix; ws->order = order; ws->seq_first = seq_first; ws->seq_count = seq_count;
               ws->split_list = split_list;
-              ws->chunks = chunks; ws->part_ml = ml; ws->part_o = po;
+              ws->chunks = chunks; ws->part_ml = ml; ws->part_o = po; ws->status_slots = slots;
               ws->cap = (int)cap; ws->target_chunks = target; }
     return off;
 }
@@ -114,7 +144,6 @@ size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D
 
 constexpr int kPlanThreads = 1024;
 constexpr int kSortMax = 1024;   // largest batch whose sequences are ordered longest-first (rank sort, O(B) per thread)
-constexpr int kMergeWarpMax = 32;    // a sequence of at most this many chunks is merged by a single warp per query head
 
 __device__ int block_inclusive_scan(int v, int* warp_sums, int* total) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -165,28 +194,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; s_big = 0; }
     __syncthreads();
 
-    // Sequence s attends the keys [0, sink) and [begin, L): L is ctx_len clamped to the block table,
-    // begin is ctx_begin (0 without one) clamped to [0, L], sink is sink_tokens clamped to begin.
-    // Only the pages that hold such keys are read: `sink_pages` pages from the start of the block
-    // table, then the pages from begin/page_size on.  A sink page that is also the window's first
-    // page is read once, as a window page.
+    // (pages a sequence reads: seq_page_range in decode_defs.cuh; page_size is always kPage here)
     auto seq_range = [&](int s, int* L_out, int* begin_out, int* sink_pages_out) {
-        int L = ctx_len[s];
-        const long long cap_len = (long long)max_pages * page_size;
-        L = L < 0 ? 0 : ((long long)L > cap_len ? (int)cap_len : L);
-        int b = ctx_begin != nullptr ? ctx_begin[s] : 0;
-        b = b < 0 ? 0 : (b > L ? L : b);
-        if (sink_tokens >= b) b = 0;   // the sink keys reach the window: nothing is hidden
-        const int sink = b > 0 ? sink_tokens : 0;
-        const int first_window_page = b / page_size;
-        int sp = (sink + page_size - 1) / page_size;
-        if (sp > first_window_page) sp = first_window_page;
-        // (when the window is empty its first page would hold no visible key: read sink pages only;
-        //  a sink that ends on the window's page is then lost with it, so widen sp in that case)
-        int window_pages = b >= L ? 0 : (L + page_size - 1) / page_size - first_window_page;
-        if (window_pages == 0) sp = (sink + page_size - 1) / page_size;
-        *L_out = L; *begin_out = b; *sink_pages_out = sp;
-        return sp + window_pages;   // pages to read
+        return seq_page_range(ctx_len, ctx_begin, sink_tokens, max_pages, s, L_out, begin_out, sink_pages_out, nullptr);
     };
 
     // total pages of the batch
@@ -308,6 +318,19 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     __syncthreads();
     if (tid == 0) PROF_STAMP_SET(ws.header, 1)
 #endif
+    // This kernel may itself have been launched as a programmatic dependent of the kernel before it in
+    // the stream (typically the append of the same step, which it does not depend on).  The attention
+    // kernel waits for THIS grid only, so this grid must not complete before its predecessor has.
+    grid_dependency_wait();
+}
+
+// OR of the header's status word and of the per-CTA slots of the last call, into one device word.
+__global__ void __launch_bounds__(kStatusSlots) status_fold_kernel(const int* ws, int n_slots, int* out) {
+    const int mine = (int)threadIdx.x < n_slots ? ws[kHdrWords + threadIdx.x] : 0;
+    int any = 0;
+#pragma unroll
+    for (int bit = 0; bit < 5; ++bit) any |= __syncthreads_or(mine & (1 << bit)) ? (1 << bit) : 0;
+    if (threadIdx.x == 0) *out = any | ws[kHdrStatus];
 }
 
 __global__ void bounded_wait_selftest_kernel(int* status, uint64_t limit_ns) {
@@ -392,12 +415,29 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     if (kv_dtype == IVAB_F8E4M3) ws.target_chunks = ws.target_chunks * 3 / 4 > 0 ? ws.target_chunks * 3 / 4 : 1;
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    plan_kernel<<<1, kPlanThreads, 0, st>>>(ctx_len, ctx_begin, (int)sink_tokens, (int)batch, (int)page_size,
-                                            (int)max_pages_per_seq, ws.target_chunks, ws.cap, (int)virt_heads, ws);
-    g_launches++;
-    if (int rc = check_cuda(cudaGetLastError(), "plan_kernel launch")) return rc;
+    // Small batches skip the plan kernel: every CTA derives the chunking itself (decode_defs.cuh).  The
+    // chunk list then holds at most target_items / heads + batch entries, which the capacity covers.
+    const bool direct = batch <= kDirectMaxBatch && use_direct_mode();
+    if (!direct) {
+        // a programmatic dependent of whatever kernel precedes it in the stream (the append of the same
+        // step): it reads none of that kernel's output and waits for it before it exits
+        cudaLaunchAttribute pdl{};
+        pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        pdl.val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(1); cfg.blockDim = dim3(kPlanThreads); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+        cfg.attrs = &pdl; cfg.numAttrs = use_plan_pdl() ? 1 : 0;
+        if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, plan_kernel, ctx_len, ctx_begin, (int)sink_tokens, (int)batch,
+                                                   (int)page_size, (int)max_pages_per_seq, ws.target_chunks, ws.cap,
+                                                   (int)virt_heads, ws), "plan_kernel launch")) return rc;
+        g_launches++;
+    }
 
     DecodeParams p{};
+    p.direct = direct ? 1 : 0;
+    p.batch = (int)batch; p.max_pages = (int)max_pages_per_seq; p.n_virt_heads = (int)virt_heads;
+    p.direct_min_chunk = direct_min_chunk_pages();
+    p.ctx_len = ctx_len; p.ctx_begin = ctx_begin;
     p.q = q; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
     p.k_pool = static_cast<const char*>(k_pool); p.v_pool = static_cast<const char*>(v_pool);
     p.pool_sh_bytes = pool_stride_head * (int64_t)kv_esz; p.pool_sp_bytes = pool_stride_page * (int64_t)kv_esz;
@@ -464,10 +504,15 @@ extern "C" int ivab_paged_decode_attn_fp8(const void* q, int64_t q_stride_b, int
 extern "C" int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream) {
     if (!workspace || !status_out) return set_error(IVAB_ERR_INVALID, "ivab_decode_status: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int32_t v = 0;
-    if (int rc = check_cuda(cudaMemcpyAsync(&v, static_cast<const int*>(workspace) + kHdrStatus, sizeof(int),
+    // the header, and behind it the per-CTA slots of which every call rewrites the first 2 x SMs
+    static_assert(kHdrWords * sizeof(int) % 256 == 0, "the slots follow the header without a gap");
+    int32_t words[kHdrWords + kStatusSlots];
+    const int n_slots = 2 * sm_count() < kStatusSlots ? 2 * sm_count() : kStatusSlots;
+    if (int rc = check_cuda(cudaMemcpyAsync(words, workspace, (kHdrWords + n_slots) * sizeof(int),
                                             cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)")) return rc;
     if (int rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return rc;
+    int32_t v = words[kHdrStatus];
+    for (int i = 0; i < n_slots; ++i) v |= words[kHdrWords + i];
     *status_out = v;
     if (v != 0) return set_error(IVAB_ERR_DEVICE, "device status 0x%x", v);
     return IVAB_OK;
@@ -546,7 +591,8 @@ extern "C" int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b,
     if (status == nullptr) return IVAB_OK;
     if (batch == 0)   // nothing was launched, so nothing can have gone wrong: the caller still gets a defined word
         return check_cuda(cudaMemsetAsync(status, 0, sizeof(int), static_cast<cudaStream_t>(stream)), "cudaMemsetAsync(status)");
-    return check_cuda(cudaMemcpyAsync(status, reinterpret_cast<int*>(scratch) + kHdrStatus, sizeof(int),
-                                      cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)),
-                      "cudaMemcpyAsync(status)");
+    const int n_slots = 2 * sm_count() < kStatusSlots ? 2 * sm_count() : kStatusSlots;
+    status_fold_kernel<<<1, kStatusSlots, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const int*>(scratch), n_slots, status);
+    g_launches++;
+    return check_cuda(cudaGetLastError(), "status_fold_kernel launch");
 }

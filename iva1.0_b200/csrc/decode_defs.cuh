@@ -19,6 +19,12 @@ constexpr int kMaxStages = 32;
 static_assert(kMaxStages % kConsumerWarps == 0, "stage ring must divide among the consumer warps");
 constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
 constexpr int kMinChunkPages = 8;
+// Plan-free ("direct") mode, for batches small enough that one warp holds a sequence per lane:
+constexpr int kDirectMaxBatch = 32;
+constexpr int kDirectItemsPerSlot = 2;       // work items per resident CTA the chunk size aims for
+constexpr int kDirectMinChunkPages = 32;     // below this an item is cheaper to finish than to split and merge
+constexpr int kStatusSlots = 512;            // per-CTA status words behind the header (at least 2 x SMs)
+constexpr int kMergeWarpMax = 32;            // a sequence of at most this many chunks is merged by a single warp per query head
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 constexpr int kMaxDevices = 64;      // device ordinals the per-device host caches cover
 
@@ -44,6 +50,11 @@ constexpr int kMaxDevices = 64;      // device ordinals the per-device host cach
 // header words at the start of the workspace
 enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrNumSplit = 5, kHdrNumBig = 6,
        kHdrWords = 64 };
+// Status protocol.  header[kHdrStatus] holds the bits of the planning step: written by the plan kernel,
+// or (plan-free mode) by CTA 0 of the attention kernel.  Every CTA of the attention kernel additionally
+// stores its own bits -- bad page ids, an expired wait -- into slot blockIdx.x of `status_slots` when its
+// last warp leaves, unconditionally, so no word has to be cleared before a call: the status of a call is
+// the OR of the header word and of the first 2 x SMs slots (a grid of one CTA per SM writes two each).
 
 }  // namespace
 
@@ -63,6 +74,7 @@ struct Workspace {
     ChunkDesc* chunks;    // [cap]
     float* part_ml;       // [cap*Hkv][G][2]   (running max in log2 units, sum)
     float* part_o;        // [cap*Hkv][G][D]
+    int* status_slots;    // [kStatusSlots] per-CTA status words, directly behind the header
     int cap;
     int target_chunks;
 };
@@ -83,6 +95,13 @@ struct DecodeParams {
     int stages;
     uint64_t wait_limit_ns;
     Workspace ws;
+    // Plan-free mode (direct != 0): there is no plan kernel; every CTA derives the chunking from ctx_len
+    // itself and takes the items blockIdx.x, blockIdx.x + gridDim.x, ... of the (kv head, chunk) list.
+    int direct;
+    int batch, max_pages, n_virt_heads;        // sequences, block-table width, KV heads the items number
+    int direct_target_items, direct_min_chunk; // chunk size = max(min_chunk, ceil(total_pages * heads / target_items))
+    int status_slots_per_cta;                  // 2 when the grid is one CTA per SM, else 1
+    const int32_t* ctx_len; const int32_t* ctx_begin;
 };
 
 namespace {
@@ -91,6 +110,88 @@ namespace {
 // the window's pages from begin / kPage on.
 __device__ __forceinline__ int page_of(int v, int sink_pages, int begin) {
     return v < sink_pages ? v : v - sink_pages + begin / kPage;
+}
+
+// Sequence s attends the keys [0, sink) and [begin, L): L is ctx_len clamped to the block table, begin is
+// ctx_begin (0 without one) clamped to [0, L], sink is sink_tokens clamped to begin.  Only the pages that
+// hold such keys are read: `sink_pages` pages from the start of the block table, then the pages from
+// begin / kPage on.  A sink page that is also the window's first page is read once, as a window page.
+// Returns the number of pages to read; sets *bad when the raw values lie outside their ranges.
+__device__ __forceinline__ int seq_page_range(const int32_t* ctx_len, const int32_t* ctx_begin, int sink_tokens, int max_pages,
+                                              int s, int* L_out, int* begin_out, int* sink_pages_out, bool* bad) {
+    const int L_raw = ctx_len[s];
+    const long long cap_len = (long long)max_pages * kPage;
+    int L = L_raw < 0 ? 0 : ((long long)L_raw > cap_len ? (int)cap_len : L_raw);
+    const int b_raw = ctx_begin != nullptr ? ctx_begin[s] : 0;
+    if (bad != nullptr) *bad = L_raw < 0 || (long long)L_raw > cap_len || b_raw < 0 || b_raw > L_raw;
+    int b = b_raw < 0 ? 0 : (b_raw > L ? L : b_raw);
+    if (sink_tokens >= b) b = 0;   // the sink keys reach the window: nothing is hidden
+    const int sink = b > 0 ? sink_tokens : 0;
+    const int first_window_page = b / kPage;
+    int sp = (sink + kPage - 1) / kPage;
+    if (sp > first_window_page) sp = first_window_page;
+    // (when the window is empty its first page would hold no visible key: read sink pages only;
+    //  a sink that ends on the window's page is then lost with it, so widen sp in that case)
+    const int window_pages = b >= L ? 0 : (L + kPage - 1) / kPage - first_window_page;
+    if (window_pages == 0) sp = (sink + kPage - 1) / kPage;
+    *L_out = L; *begin_out = b; *sink_pages_out = sp;
+    return sp + window_pages;
+}
+
+// The plan of the plan-free mode, held by one warp: lane s describes sequence s (lanes >= batch are empty).
+struct DirectPlan {
+    int pages, first, n;          // pages to read, index of the first chunk, number of chunks (>= 1 for lanes < batch)
+    int L, begin, sink_pages;
+    int num_chunks;               // warp-uniform: chunks of the whole batch
+    bool bad;                     // warp-uniform: some ctx_len / ctx_begin was out of range
+};
+
+// Must be called by all 32 lanes.  Deterministic in its inputs, so every CTA of the attention kernel and of
+// the merge kernel arrives at the same plan.  Sequences are split evenly into ceil(pages / c) chunks with
+// c = max(min_chunk, ceil(total_pages * heads / target_items)) pages.
+__device__ __forceinline__ DirectPlan direct_plan(const int32_t* ctx_len, const int32_t* ctx_begin, int sink_tokens, int max_pages,
+                                                  int batch, int heads, int target_items, int min_chunk, int lane) {
+    DirectPlan d{};
+    bool bad = false;
+    if (lane < batch) d.pages = seq_page_range(ctx_len, ctx_begin, sink_tokens, max_pages, lane, &d.L, &d.begin, &d.sink_pages, &bad);
+    d.bad = __any_sync(0xffffffffu, bad);
+    long long total = d.pages;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    long long c64 = (total * heads + target_items - 1) / target_items;
+    if (c64 < min_chunk) c64 = min_chunk;
+    const int c = (int)(c64 > 0x3fffffff ? 0x3fffffff : c64);
+    d.n = lane < batch ? (d.pages + c - 1) / c : 0;
+    if (lane < batch && d.n < 1) d.n = 1;   // an empty sequence still gets one (empty) item, which writes zeros / -inf
+    int incl = d.n;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+    }
+    d.first = incl - d.n;
+    d.num_chunks = __shfl_sync(0xffffffffu, incl, 31);
+    return d;
+}
+
+// Chunk `ci` of the batch-wide chunk list as a descriptor (all lanes, warp-uniform result).
+__device__ __forceinline__ ChunkDesc direct_desc(const DirectPlan& d, int ci, int batch, int lane) {
+    const unsigned owners = __ballot_sync(0xffffffffu, lane < batch && d.first <= ci);
+    const int s = owners ? 31 - __clz(owners) : 0;    // `first` increases strictly with the lane
+    const int first = __shfl_sync(0xffffffffu, d.first, s), n = __shfl_sync(0xffffffffu, d.n, s);
+    const int pages = __shfl_sync(0xffffffffu, d.pages, s);
+    const int j = ci - first;
+    const int per = n > 0 ? pages / n : 0, rem = n > 0 ? pages % n : 0;   // even split: the first `rem` chunks get one more page
+    ChunkDesc c;
+    c.seq = s;
+    c.page_begin = j * per + (j < rem ? j : rem);
+    c.n_pages = per + (j < rem ? 1 : 0);
+    c.chunk_idx = j;
+    c.n_chunks = n;
+    c.pad0 = __shfl_sync(0xffffffffu, d.L, s);
+    c.pad1 = __shfl_sync(0xffffffffu, d.begin, s);
+    c.pad2 = __shfl_sync(0xffffffffu, d.sink_pages, s);
+    return c;
 }
 
 // item ring entry (ints): what the producer tells the consumers about the next work item

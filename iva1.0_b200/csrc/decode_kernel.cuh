@@ -45,6 +45,8 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     const uint32_t bar_combined = bars + 8u * (2 * kMaxStages + 2 * kItemRing);   // phase i completes when item i's states are combined
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT);
     int* merge_cnt = reinterpret_cast<int*>(smem + C::OFF_ABORT + 4);   // warps that have published the current item
+    int* cta_status = reinterpret_cast<int*>(smem + C::OFF_ABORT + 8);  // IVAB_STATUS_* bits raised by this CTA
+    int* exit_cnt = reinterpret_cast<int*>(smem + C::OFF_ABORT + 12);   // warps that have left the kernel
     volatile int* items = reinterpret_cast<volatile int*>(smem + C::OFF_ITEMS);
     unsigned char* stage_base = smem + C::OFF_STAGES;
 
@@ -54,6 +56,8 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         for (int s = 0; s < kItemRing; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), kConsumerWarps); }
         mbar_init(bar_combined, 1);
         *merge_cnt = 0;
+        *cta_status = 0;
+        *exit_cnt = 0;
         fence_mbar_init();
     }
     __syncthreads();   // the only CTA-wide barrier: before any warp can have unwound
@@ -69,11 +73,26 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     }
 #endif
 
-    const int num_chunks = p.ws.header[kHdrNumChunks];
-    const int total_items = p.ws.header[kHdrTotalItems];
+    const bool direct = p.direct != 0;
+    int num_chunks = direct ? 0 : p.ws.header[kHdrNumChunks];
+    int total_items = direct ? 0 : p.ws.header[kHdrTotalItems];
     int* counter = p.ws.header + kHdrCounter;
-    int* status = p.ws.header + kHdrStatus;
     const uint64_t limit = p.wait_limit_ns;
+    // Every warp calls this exactly once, as the last thing it does.  The warp that arrives last stores the
+    // bits this CTA raised into the CTA's status slot(s) -- unconditionally, so that the slots never need
+    // clearing; in plan-free mode CTA 0 also defines the header's status word, which no plan kernel wrote.
+    auto leave = [&]() {
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence_block();
+            if (atomicAdd(exit_cnt, 1) == kConsumerWarps) {
+                __threadfence_block();
+                const int st = *reinterpret_cast<volatile int*>(cta_status) | (*abort_flag ? kStatusWaitTimeout : 0);
+                for (int k = 0; k < p.status_slots_per_cta; ++k) p.ws.status_slots[blockIdx.x + k * gridDim.x] = st;
+                if (direct && blockIdx.x == 0) p.ws.header[kHdrStatus] = 0;
+            }
+        }
+    };
 
     if (warp == kConsumerWarps) {
         // ------------------------------ producer warp ------------------------------------------
@@ -92,16 +111,38 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         // across items: while the pages of item i are being issued, the block-table entries of item
         // i+1, the descriptor of item i+2 and the id of item i+3 are in flight, so the TMA issue
         // stream does not pause at item boundaries.
+        // Plan-free mode: this warp derives the chunking from ctx_len itself (lane s holds sequence s) and
+        // the CTA takes the items blockIdx.x, blockIdx.x + gridDim.x, ...: two dependent global accesses
+        // (ctx_len, block-table entries) before the first page is requested, no work counter.
+        DirectPlan dplan{};
+        int static_next = (int)blockIdx.x;
+        if (direct) {
+            dplan = direct_plan(p.ctx_len, p.ctx_begin, p.sink_tokens, p.max_pages, p.batch, p.n_virt_heads,
+                                p.direct_target_items, p.direct_min_chunk, lane);
+            num_chunks = dplan.num_chunks;
+            total_items = num_chunks * p.n_virt_heads;
+            if (dplan.bad && lane == 0) atomicOr(cta_status, kStatusBadCtxLen);
+            if (num_chunks > p.ws.cap) {   // cannot happen while target_items <= kItemsPerSlot x resident CTAs
+                if (lane == 0) atomicOr(cta_status, kStatusOverflow);
+                total_items = 0;
+            }
+        }
         auto fetch_id_async = [&]() {   // lane 0 holds the result; broadcast it only when it is needed
             int v = 0;
-            if (lane == 0) v = (int)gridDim.x + atomicAdd(counter, 1);
+            if (direct) { static_next += (int)gridDim.x; v = static_next; }
+            else if (lane == 0) v = (int)gridDim.x + atomicAdd(counter, 1);
             return v;
         };
         auto fetch_id = [&]() { return __shfl_sync(0xffffffffu, fetch_id_async(), 0); };
         auto load_desc = [&](int id, int* h_out) {
             ChunkDesc d{};
             *h_out = 0;
-            if (id < total_items) {
+            if (direct) {      // (every lane takes part in the shuffles, whatever the id)
+                const int h = id < total_items ? id / num_chunks : 0;
+                d = direct_desc(dplan, id < total_items ? id - h * num_chunks : 0, p.batch, lane);
+                if (id >= total_items) d = ChunkDesc{};
+                *h_out = h;
+            } else if (id < total_items) {
                 const int h = id / num_chunks;
                 const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + (id - h * num_chunks));
                 // written by the plan kernel of this call, which may still have been running when this
@@ -174,7 +215,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                     const int nb = min(stages, in_batch - q0);
                     int pid = __shfl_sync(0xffffffffu, mine, (q0 + lane) & 31);
                     if (lane < nb && (pid < 0 || pid >= p.num_pages)) {
-                        atomicOr(status, kStatusBadPage);   // flagged, and page 0 is read instead of faulting
+                        atomicOr(cta_status, kStatusBadPage);   // flagged, and page 0 is read instead of faulting
                         pid = 0;
                     }
                     const int b0 = (start + p0 + q0) & (kConsumerWarps - 1);
@@ -226,7 +267,6 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         }
         PROF_FLUSH(0)
         if (aborted) {
-            if (lane == 0) atomicOr(status, kStatusWaitTimeout);
             // Copies already issued still target this CTA's shared memory: give each of the
             // most recent `stages` copies a bounded chance to land before the CTA retires.
             volatile int no_abort = 0;
@@ -238,6 +278,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                                       limit < 100000000ull ? limit : 100000000ull);
             }
         }
+        leave();
         return;
     }
 
@@ -352,7 +393,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         atomicMin(reinterpret_cast<unsigned long long*>(p.ws.header + 8), (unsigned long long)globaltimer_ns());   // first warp done
     }
 #endif
-    if (*abort_flag && threadIdx.x == 0) atomicOr(status, kStatusWaitTimeout);
+    leave();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -389,20 +430,33 @@ __device__ __forceinline__ void load_row(const float* src, float (&v)[VPL]) {
 //      (sequence, query head, 32-dim slice); warp w folds chunks w, w+8, ... against its own running
 //      maximum, the eight warp results are then combined through shared memory.
 template <typename T, int D>
-__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int B, int Hq, int G, Workspace ws, void* out_raw, int out_f32,
-                                                                 int64_t out_sb, int64_t out_sh, float* lse) {
-    T* out = static_cast<T*>(out_raw);          // the output is of q's type T ...
-    float* out32 = static_cast<float*>(out_raw);   // ... or fp32 when out_f32 is set (strides in elements either way)
+__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_constant__ DecodeParams p, int B) {
+    const Workspace& ws = p.ws;
+    const int Hq = p.Hq, G = p.group, out_f32 = p.out_f32;
+    const int64_t out_sb = p.out_sb, out_sh = p.out_sh;
+    float* lse = p.lse;
+    T* out = static_cast<T*>(p.out);              // the output is of q's type T ...
+    float* out32 = static_cast<float*>(p.out);    // ... or fp32 when out_f32 is set (strides in elements either way)
     constexpr int VPL = D / 32;   // dims per lane in pass A, 32-dim slices in pass B
     constexpr float kLn2 = 0.6931471805599453f;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool direct = p.direct != 0;
+    // Plan-free mode: every warp re-derives the chunking from ctx_len (inputs of the call, so this runs
+    // before the wait below, under the attention kernel's tail) instead of reading the plan kernel's lists.
+    DirectPlan dplan{};
+    if (direct)
+        dplan = direct_plan(p.ctx_len, p.ctx_begin, p.sink_tokens, p.max_pages, p.batch, p.n_virt_heads,
+                            p.direct_target_items, p.direct_min_chunk, lane);
     grid_dependency_wait();   // the attention kernel's partial results
 #ifdef IVAB_PROFILE
     if (threadIdx.x == 0) PROF_STAMP_MIN(ws.header, 6, globaltimer_ns())
 #endif
-    const int num_chunks = ws.header[kHdrNumChunks];
-    const int n_small = ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
-    const int n_big = ws.header[kHdrNumBig];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_chunks = direct ? dplan.num_chunks : ws.header[kHdrNumChunks];
+    if (direct && num_chunks > ws.cap) return;   // flagged by the attention kernel; nothing was computed
+    // units of pass A / B: the plan kernel's lists of split sequences, or (plan-free) every sequence, of
+    // which those with a fitting chunk count are taken
+    const int n_small = direct ? B : ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
+    const int n_big = direct ? (__any_sync(0xffffffffu, dplan.n > kMergeWarpMax) ? B : 0) : ws.header[kHdrNumBig];
     // a lane's VPL outputs go out as one store when every output row is aligned for it
     constexpr int kVecBytes = VPL * (int)sizeof(T);
     const bool vec_out = !out_f32 && VPL >= 2 && (sizeof(T) == 2 || VPL % 4 == 0) &&
@@ -411,9 +465,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int B, int Hq, 
 
     // ---- pass A
     for (int unit = blockIdx.x * kMergeWarps + warp; unit < n_small * Hq; unit += gridDim.x * kMergeWarps) {
-        const int s = ws.split_list[unit / Hq], hq = unit % Hq;
-        const int first = ws.seq_first[s];
-        const int n = ws.seq_count[s];
+        const int s = direct ? unit / Hq : ws.split_list[unit / Hq], hq = unit % Hq;
+        const int first = direct ? __shfl_sync(0xffffffffu, dplan.first, s) : ws.seq_first[s];
+        const int n = direct ? __shfl_sync(0xffffffffu, dplan.n, s) : ws.seq_count[s];
+        if (direct && (n < 2 || n > kMergeWarpMax)) continue;            // (warp-uniform)
         const int h = hq / G, g = hq % G;
         const size_t item0 = (size_t)h * num_chunks + first;
         const float* ml = ws.part_ml + (item0 * G + g) * 2;               // chunk j at ml + j*G*2
@@ -491,9 +546,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(int B, int Hq, 
     __shared__ float sh_o[kMergeWarps][32];
     for (int c = blockIdx.x; c < n_big * Hq * VPL; c += gridDim.x) {
         const int unit = c / VPL, slice = c % VPL;
-        const int s = ws.split_list[B - 1 - unit / Hq], hq = unit % Hq;
-        const int first = ws.seq_first[s];
-        const int n = ws.seq_count[s];
+        const int s = direct ? unit / Hq : ws.split_list[B - 1 - unit / Hq], hq = unit % Hq;
+        const int first = direct ? __shfl_sync(0xffffffffu, dplan.first, s) : ws.seq_first[s];
+        const int n = direct ? __shfl_sync(0xffffffffu, dplan.n, s) : ws.seq_count[s];
+        if (direct && n <= kMergeWarpMax) continue;                      // (uniform over the CTA: no barrier is skipped by some)
         const int h = hq / G, g = hq % G;
         const size_t item0 = (size_t)h * num_chunks + first;
         const float* ml = ws.part_ml + (item0 * G + g) * 2;
@@ -594,6 +650,17 @@ int tc_min_group(int default_value) {
     return v ? v : default_value;
 }
 
+// Work items per resident CTA that the plan-free mode's chunk size aims for (IVAB_DIRECT_IPS overrides
+// the default for experiments; read once per process).
+int direct_items_per_slot() {
+    static int v = [] {
+        const char* e = std::getenv("IVAB_DIRECT_IPS");
+        const int n = e ? std::atoi(e) : kDirectItemsPerSlot;
+        return n < 1 ? 1 : (n > kItemsPerSlot ? kItemsPerSlot : n);   // the workspace is sized for kItemsPerSlot
+    }();
+    return v;
+}
+
 // Programmatic dependent launch of the attention and merge kernels; IVAB_PDL=0 turns it off.
 bool use_dependent_launch() {
     static bool v = [] {
@@ -639,6 +706,9 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
         configured[dev].store(true, std::memory_order_release);
     }
     const int grid = sm_count() * kCtas;
+    if (2 * sm_count() > kStatusSlots) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: %d SMs (status slots for %d)", sm_count(), kStatusSlots / 2);
+    p.status_slots_per_cta = 2 / kCtas;   // the first 2 x SMs slots are written by every call, whatever the engine
+    if (p.direct) p.direct_target_items = grid * direct_items_per_slot();
     // Both launches below are programmatic dependents of the kernel before them (plan -> attention
     // -> merge): the launch latency and set-up of each overlap the tail of its predecessor.
     cudaLaunchAttribute pdl{};
@@ -654,8 +724,9 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     const long long units = (long long)B * p.Hq * (D / 32);
     const int merge_grid = (int)(units < (long long)sm_count() * 4 ? units : (long long)sm_count() * 4);
     cfg.gridDim = dim3(merge_grid); cfg.blockDim = dim3(kMergeWarps * 32); cfg.dynamicSmemBytes = 0;
-    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, B, p.Hq, p.group, p.ws, p.out, p.out_f32, p.out_sb,
-                                               p.out_sh, p.lse), "merge_kernel launch")) return rc;
+    // plan-free mode with a block table no wider than the smallest chunk: no sequence can be split, nothing to merge
+    if (p.direct && p.max_pages <= p.direct_min_chunk) return IVAB_OK;
+    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, p, B), "merge_kernel launch")) return rc;
     g_launches++;
     return IVAB_OK;
 }

@@ -43,6 +43,8 @@ struct RowCopyParams {
     const char* src[2];
     char* dst[2];
     const int64_t* idx;
+    int64_t idx_stride_b;   // batch row b reads idx + b * idx_stride_b (0: one index vector for all rows)
+    int pad_ok;             // an index of -1 is padding: its row is skipped without raising a status bit
     // indexed side: offset(b,h,id) = b*ix_b + h*ix_h + (id / page_size)*ix_page + (id % page_size)*ix_slot
     int64_t ix_b, ix_h, ix_page, ix_slot;
     // dense side: offset(b,h,n) = b*dn_b + h*dn_h + n*dn_n
@@ -56,6 +58,7 @@ struct RowCopyParams {
     int h_fastest;          // row order on the dense side: 1 = (n, h), 0 = (h, n)
     int* status;
     float inv_scale[2];     // CVT 3/4 (quantising append): 1/scale per tensor
+    int early_dependents;   // small grids: let a programmatically dependent kernel be scheduled at once
 };
 
 // Loads through the read-only path and default-policy stores: measured on the append/gather stress
@@ -78,6 +81,10 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const RowCopyParams 
     char* __restrict__ dst = p.dst[blockIdx.z];
     const int64_t b = blockIdx.y;
     const uint32_t n_tiles = (p.total + kTile - 1) / kTile;
+    // A kernel launched behind this one as a programmatic dependent (the planning / attention kernels of
+    // the same decode step) may be placed on the SMs this small grid leaves free; it waits for this grid
+    // to complete before it reads the pool.  Large grids keep the SMs to themselves until they retire.
+    if (p.early_dependents) grid_launch_dependents();
 
     for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const uint32_t base = tile * kTile + threadIdx.x;
@@ -96,10 +103,10 @@ __global__ void __launch_bounds__(kThreads) row_copy_kernel(const RowCopyParams 
                 const uint32_t vec = i - r * p.vec_per_row;
                 const uint32_t outer = fdiv(r, p.by_rows), inner = r - outer * p.by_rows.d;
                 const uint32_t h = p.h_fastest ? inner : outer, n = p.h_fastest ? outer : inner;
-                const int64_t id = __ldg(p.idx + n);
+                const int64_t id = __ldg(p.idx + b * p.idx_stride_b + n);
                 if (id < 0 || id >= p.id_bound) {
                     // Out-of-range index: record it and skip the row instead of faulting.
-                    if (p.status != nullptr && vec == 0) atomicOr(p.status, kStatusBadSlot);
+                    if (p.status != nullptr && vec == 0 && !(p.pad_ok && id == -1)) atomicOr(p.status, kStatusBadSlot);
                     ok[k] = false;
                 } else {
                     const uint32_t uid = static_cast<uint32_t>(id);
@@ -202,6 +209,51 @@ __global__ void __launch_bounds__(kThreads) paged_gather_kernel(const PagedGathe
     }
 }
 
+// Positions of the non-zero entries of each mask row, in order: indices[b, j] = position of the j-th survivor of
+// row b for j < counts[b], -1 behind them.  One CTA per batch row; the row is scanned in tiles of kScanThreads
+// entries with a running offset.
+constexpr int kScanThreads = 1024;
+
+__global__ void __launch_bounds__(kScanThreads) compact_index_kernel(const uint8_t* __restrict__ mask, int64_t S,
+                                                                     int64_t* __restrict__ indices, int32_t* __restrict__ counts) {
+    __shared__ int warp_sums[32];
+    __shared__ int tile_total;
+    const int64_t b = blockIdx.x;
+    const uint8_t* row = mask + b * S;
+    int64_t* out = indices + b * S;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int running = 0;
+    for (int64_t base = 0; base < S; base += kScanThreads) {
+        const int64_t pos = base + threadIdx.x;
+        const int keep = pos < S && row[pos] != 0;
+        int v = keep;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, v, off);
+            if (lane >= off) v += t;
+        }
+        if (lane == 31) warp_sums[warp] = v;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_sums[lane];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, w, off);
+                if (lane >= off) w += t;
+            }
+            warp_sums[lane] = w;
+            if (lane == 31) tile_total = w;
+        }
+        __syncthreads();
+        if (warp > 0) v += warp_sums[warp - 1];
+        if (keep) out[running + v - 1] = pos;
+        running += tile_total;
+        __syncthreads();   // warp_sums / tile_total are rewritten by the next tile
+    }
+    for (int64_t j = running + threadIdx.x; j < S; j += kScanThreads) out[j] = -1;
+    if (threadIdx.x == 0) counts[b] = running;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int launch_row_copy(bool gather, int cvt, const RowCopyParams& p0, int64_t batch, int n_tensors, cudaStream_t st) {
@@ -216,6 +268,7 @@ int launch_row_copy(bool gather, int cvt, const RowCopyParams& p0, int64_t batch
     // accesses spread over the whole range instead of marching through it in lockstep.
     const uint32_t max_x = 0x7fffffffu;
     dim3 grid(n_tiles < max_x ? n_tiles : max_x, (unsigned)batch, (unsigned)n_tensors);
+    p.early_dependents = (uint64_t)grid.x * grid.y * grid.z <= (uint64_t)sm_count() ? 1 : 0;
     if (gather) {
         if (cvt == 0) row_copy_kernel<true, 0><<<grid, kThreads, 0, st>>>(p);
         else if (cvt == 1) row_copy_kernel<true, 1><<<grid, kThreads, 0, st>>>(p);
@@ -243,11 +296,53 @@ int common_checks(const char* fn, int dtype, int64_t head_dim, size_t* esz) {
 
 using namespace ivab;
 
+static int kv_gather_body(const char* fn, const void* cache, const int64_t* indices, int64_t indices_stride_b, int pad_ok,
+                          void* out, int dtype, int out_dtype,
+                          int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
+                          int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
+                          int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
+                          int32_t* status, void* stream);
+
 extern "C" int ivab_kv_gather(const void* cache, const int64_t* indices, void* out, int dtype, int out_dtype,
                               int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
                               int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
                               int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
                               int32_t* status, void* stream) {
+    return kv_gather_body("ivab_kv_gather", cache, indices, 0, 0, out, dtype, out_dtype, batch, heads, seq_len, head_dim,
+                          n_indices, cache_stride_b, cache_stride_h, cache_stride_s, out_stride_b, out_stride_h,
+                          out_stride_n, status, stream);
+}
+
+extern "C" int ivab_kv_gather_rows(const void* cache, const int64_t* indices, int64_t indices_stride_b, void* out,
+                                   int dtype, int out_dtype,
+                                   int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
+                                   int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
+                                   int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
+                                   int32_t* status, void* stream) {
+    if (indices_stride_b < 0) return set_error(IVAB_ERR_INVALID, "ivab_kv_gather_rows: negative indices_stride_b");
+    return kv_gather_body("ivab_kv_gather_rows", cache, indices, indices_stride_b, 1, out, dtype, out_dtype, batch, heads,
+                          seq_len, head_dim, n_indices, cache_stride_b, cache_stride_h, cache_stride_s, out_stride_b,
+                          out_stride_h, out_stride_n, status, stream);
+}
+
+extern "C" int ivab_compact_indices(const uint8_t* mask, int64_t batch, int64_t seq_len, int64_t* indices,
+                                    int32_t* counts, void* stream) {
+    if (batch < 0 || seq_len < 0) return set_error(IVAB_ERR_INVALID, "ivab_compact_indices: negative size");
+    if (batch == 0) return IVAB_OK;
+    if (!mask || !indices || !counts) return set_error(IVAB_ERR_INVALID, "ivab_compact_indices: null pointer");
+    if (batch >= (1LL << 31)) return set_error(IVAB_ERR_UNSUPPORTED, "ivab_compact_indices: batch too large");
+    compact_index_kernel<<<(unsigned)batch, kScanThreads, 0, static_cast<cudaStream_t>(stream)>>>(mask, seq_len, indices, counts);
+    g_launches++;
+    return check_cuda(cudaGetLastError(), "compact_index_kernel launch");
+}
+
+static int kv_gather_body(const char* fn_name, const void* cache, const int64_t* indices, int64_t indices_stride_b, int pad_ok,
+                          void* out, int dtype, int out_dtype,
+                          int64_t batch, int64_t heads, int64_t seq_len, int64_t head_dim, int64_t n_indices,
+                          int64_t cache_stride_b, int64_t cache_stride_h, int64_t cache_stride_s,
+                          int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
+                          int32_t* status, void* stream) {
+    (void)fn_name;
     size_t esz;
     if (int rc = common_checks("ivab_kv_gather", dtype, head_dim, &esz)) return rc;
     if (batch < 0 || heads < 0 || seq_len < 0 || n_indices < 0)
@@ -274,7 +369,7 @@ extern "C" int ivab_kv_gather(const void* cache, const int64_t* indices, void* o
     RowCopyParams p{};
     p.src[0] = static_cast<const char*>(cache);
     p.dst[0] = static_cast<char*>(out);
-    p.idx = indices;
+    p.idx = indices; p.idx_stride_b = indices_stride_b; p.pad_ok = pad_ok;
     p.ix_b = cache_stride_b * esz; p.ix_h = cache_stride_h * esz; p.ix_page = cache_stride_s * esz; p.ix_slot = 0;
     p.dn_b = out_stride_b * osz; p.dn_h = out_stride_h * osz; p.dn_n = out_stride_n * osz;
     p.id_bound = seq_len; p.N = (uint32_t)n_indices; p.H = (uint32_t)heads; p.vec_per_row = (uint32_t)vpr;

@@ -118,24 +118,47 @@ def kv_ops(kv_cache: torch.Tensor, indices: torch.Tensor, values: Optional[torch
         return out
 
 
-def kv_compact(kv_cache: torch.Tensor, mask: torch.Tensor, *, compat: bool = True) -> torch.Tensor:
+def kv_compact(kv_cache: torch.Tensor, mask: torch.Tensor, *, compat: bool = True, return_counts: bool = False):
     """Keep the positions where ``mask`` is non-zero: ``[B,H,S,D] -> [B,H,num_valid,D]``.
 
-    Signature of ``kv_compact_triton`` (src/kernels_t/kv_ops_triton.py:159-181).  The reference
-    kernel writes row ``s`` of an output that only has ``num_valid`` rows
-    (kv_ops_triton.py:83-92), which is out of bounds as soon as the mask has a hole; this
-    function implements the documented intent instead: surviving rows are packed in order.
-    Like the reference (kv_ops_triton.py:166) it synchronises to learn ``num_valid``.  The mask
-    is ``[B,S]``; every batch row must keep the same positions (one index vector is shared by
-    all rows, as in the gather kernel), otherwise ``ValueError``.
+    Signature of ``kv_compact_triton`` (src/kernels_t/kv_ops_triton.py:159-181): ``mask`` is ``[B,S]`` and
+    every batch row keeps its own positions.  The reference kernel writes surviving row ``s`` to output
+    row ``s`` of a tensor that only has ``num_valid`` rows (kv_ops_triton.py:83-92), which is out of
+    bounds as soon as the mask has a hole; this function implements the documented intent instead: the
+    survivors of row ``b`` are packed in order into ``out[b, :, :count_b]``, ``num_valid`` is the largest
+    count of any row, and rows with fewer survivors are zero-filled behind them
+    (``return_counts=True`` also returns the int32 counts).  Two launches -- one prefix scan per mask row,
+    one row copy -- and, like the reference (kv_ops_triton.py:166), one host synchronisation to size the
+    output.  ``compat=True`` returns fp32 whatever the cache dtype, as the reference allocates its output
+    without a dtype (kv_ops_triton.py:168).
     """
     _lib.require_cuda(kv_cache, mask)
+    if kv_cache.dim() != 4:
+        raise ValueError("kv_cache must be [batch, heads, seq, head_dim]")
+    if kv_cache.requires_grad:
+        raise RuntimeError("kv_compact is inference-only")
+    lib = _lib.load_library()
+    dev = kv_cache.device
     B, H, S, D = kv_cache.shape
-    m = mask.reshape(B, S) != 0
-    if B > 1 and not bool((m == m[:1]).all()):
-        raise ValueError("kv_compact: every batch row must keep the same positions")
-    keep = torch.nonzero(m[0], as_tuple=False).flatten()
-    return kv_ops(kv_cache, keep, None, "gather", compat=compat)
+    if mask.numel() != B * S:
+        raise ValueError(f"mask must be [{B},{S}]")
+    m = (mask.reshape(B, S) != 0).to(torch.uint8).contiguous()
+    idx = torch.empty(B, S, dtype=torch.int64, device=dev)
+    counts = torch.empty(B, dtype=torch.int32, device=dev)
+    cache = _inner_contiguous(kv_cache)
+    out_dtype = torch.float32 if compat else kv_cache.dtype
+    status = _status_word(dev)
+    with torch.cuda.device(dev):
+        stream = _lib.stream_ptr(dev)
+        _lib.check(lib.ivab_compact_indices(m.data_ptr(), B, S, idx.data_ptr(), counts.data_ptr(), stream))
+        n = int(counts.max().item()) if B else 0            # the host synchronisation
+        out = torch.zeros(B, H, n, D, device=dev, dtype=out_dtype)
+        if n:
+            _lib.check(lib.ivab_kv_gather_rows(
+                cache.data_ptr(), idx.data_ptr(), idx.stride(0), out.data_ptr(), _lib.dtype_code(kv_cache.dtype),
+                _lib.dtype_code(out_dtype), B, H, S, D, n, cache.stride(0), cache.stride(1), cache.stride(2),
+                out.stride(0), out.stride(1), out.stride(2), status.data_ptr(), stream))
+    return (out, counts) if return_counts else out
 
 
 def _pool_strides(pool: torch.Tensor, page_size: int):

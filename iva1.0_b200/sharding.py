@@ -73,6 +73,7 @@ class HeadParallelDecoder:
         self.rank = dist.get_rank(group)
         self.n_q_heads, self.n_kv_heads = n_q_heads, n_kv_heads
         self.q_slice, self.kv_slice = head_slice(n_q_heads, n_kv_heads, self.world, self.rank)
+        self._native = attn_fn is None
         if attn_fn is None:
             from .attention import paged_decode_attention as attn_fn
         self.attn_fn = attn_fn
@@ -81,41 +82,59 @@ class HeadParallelDecoder:
         """This rank's slab of full ``[1,H_kv,S,D]`` pools (a view, no copy)."""
         return k_pool[:, self.kv_slice], v_pool[:, self.kv_slice]
 
+    # One collective carries both results.  Every rank contributes one flat fp32 block: its output rows
+    # ``[B, H_q/world, D]`` followed by its logsumexp ``[B, H_q/world]``.  Both parts are contiguous views of
+    # the block, so the attention kernels store straight into it (fp32 output) -- no packing pass.
+
+    def _block(self, B: int, Hl: int, D: int, device):
+        flat = torch.empty(B * Hl * (D + 1), dtype=torch.float32, device=device)
+        return flat, flat[:B * Hl * D].view(B, Hl, D), flat[B * Hl * D:].view(B, Hl)
+
+    def _local(self, q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view, **kw):
+        if self._native:
+            self.attn_fn(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out=out_view,
+                         lse=lse_view, out_dtype=torch.float32, **kw)
+        else:
+            o, l = self.attn_fn(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, return_lse=True)
+            out_view.copy_(o)
+            lse_view.copy_(l)
+
+    def _unpack(self, gathered: torch.Tensor, B: int, Hl: int, D: int):
+        """``gathered [world, B*Hl*(D+1)]`` -> fp32 ``out [B,H_q,D]`` and ``lse [B,H_q]`` (views when ``B == 1``)."""
+        w = self.world
+        out = gathered[:, :B * Hl * D].view(w, B, Hl, D).permute(1, 0, 2, 3).reshape(B, w * Hl, D)
+        lse = gathered[:, B * Hl * D:].view(w, B, Hl).permute(1, 0, 2).reshape(B, w * Hl)
+        return out, lse
+
     def decode(self, q: torch.Tensor, k_pool_local: torch.Tensor, v_pool_local: torch.Tensor,
                block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
                scale: Optional[float] = None):
         """``q`` is the full ``[B,H_q,D]`` query (replicated) or already this rank's slice.  Returns the
-        full ``out [B,H_q,D]`` and ``lse [B,H_q]`` on every rank."""
+        full ``out [B,H_q,D]`` (in q's dtype) and ``lse [B,H_q]`` on every rank."""
         B = q.shape[0]
         if q.shape[1] == self.n_q_heads and self.world > 1:
             q = q[:, self.q_slice]
-        out_l, lse_l = self.attn_fn(q.contiguous(), k_pool_local, v_pool_local, block_table, ctx_len, page_size,
-                                    scale, return_lse=True)
+        q = q.contiguous()
+        Hl, D = q.shape[1], q.shape[2]
+        flat, out_view, lse_view = self._block(B, Hl, D, q.device)
+        self._local(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view)
         if self.world == 1:
-            return out_l, lse_l
-        Hl, D = out_l.shape[1], out_l.shape[2]
-        # One collective: the logsumexp travels as D+1-th fp32 column of the output rows
-        # (rank r's block lands in rows r*B..(r+1)*B-1 of the gathered tensor).
-        packed = torch.empty(B, Hl, D + 1, dtype=torch.float32, device=out_l.device)
-        packed[:, :, :D] = out_l
-        packed[:, :, D] = lse_l
-        gathered = torch.empty(self.world * B, Hl, D + 1, dtype=torch.float32, device=out_l.device)
-        dist.all_gather_into_tensor(gathered, packed, group=self.group)
-        gathered = gathered.view(self.world, B, Hl, D + 1).permute(1, 0, 2, 3).reshape(B, self.world * Hl, D + 1)
-        out = gathered[:, :, :D].to(out_l.dtype)
-        lse = gathered[:, :, D].contiguous()
-        return out, lse
+            return out_view.to(q.dtype), lse_view
+        gathered = torch.empty(self.world * flat.numel(), dtype=torch.float32, device=q.device)
+        dist.all_gather_into_tensor(gathered, flat, group=self.group)
+        out, lse = self._unpack(gathered.view(self.world, -1), B, Hl, D)
+        return out.to(q.dtype), lse.contiguous()
 
     def capture_local(self, q: torch.Tensor, k_pool_local: torch.Tensor, v_pool_local: torch.Tensor,
                       block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
                       scale: Optional[float] = None):
-        """Record this rank's share of a step -- the attention kernels and the packing of ``out`` and
-        ``lse`` into one fp32 buffer -- in a CUDA graph, and return ``step()``.
+        """Record this rank's share of a step -- the attention kernels, which store their fp32 result
+        straight into the block the collective sends -- in a CUDA graph, and return ``step()``.
 
         At 131072 tokens over 8 GPUs each rank reads 67 MB per step (about 10 microseconds of HBM
         time), so the step is bound by launch latency.  ``step()`` replays the graph and then issues
-        ONE eager ``all_gather_into_tensor``; it returns fp32 views ``(out [B,H_q,D], lse [B,H_q])``
-        of the gathered buffer (no further kernels when ``B == 1``).  The collective is deliberately
+        ONE eager ``all_gather_into_tensor``; it returns fp32 ``(out [B,H_q,D], lse [B,H_q])``
+        (views of the gathered buffer, no further kernels, when ``B == 1``).  The collective is deliberately
         kept outside the capture: recording an NCCL collective of ``torch.distributed`` inside a
         CUDA-graph capture hung on the CUDA 12.9 / NCCL 2.28 stack this was developed on.
         """
@@ -125,21 +144,18 @@ class HeadParallelDecoder:
             q = q[:, self.q_slice]
         q = q.contiguous()
         Hl, D = q.shape[1], q.shape[2]
-        packed = torch.empty(B, Hl, D + 1, dtype=torch.float32, device=dev)
-        gathered = torch.empty(self.world * B, Hl, D + 1, dtype=torch.float32, device=dev)
+        flat, out_view, lse_view = self._block(B, Hl, D, dev)
+        gathered = torch.empty(self.world * flat.numel(), dtype=torch.float32, device=dev)
         # The graph records the scratch pointer: it must be a buffer this object owns, not the shared
         # per-stream one, which a later call on the same stream may replace.
         extra = {}
-        if dev.type == "cuda":
+        if self._native:
             from .attention import decode_workspace_bytes
             n_kv_local = k_pool_local.shape[1]      # both pool layouts keep the KV heads on axis 1
             extra["workspace"] = torch.empty(decode_workspace_bytes(B, Hl, n_kv_local, D), dtype=torch.uint8, device=dev)
 
         def local():
-            out_l, lse_l = self.attn_fn(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale,
-                                        return_lse=True, **extra)
-            packed[:, :, :D] = out_l
-            packed[:, :, D] = lse_l
+            self._local(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view, **extra)
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -149,15 +165,12 @@ class HeadParallelDecoder:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
             local()
-        full = gathered.view(self.world, B, Hl, D + 1).permute(1, 0, 2, 3)
 
         def step(_keep=(side, extra)):           # the capture stream and the scratch live as long as the closure
             graph.replay()
             if self.world > 1:
-                dist.all_gather_into_tensor(gathered, packed, group=self.group)
-                both = full.reshape(B, self.world * Hl, D + 1)
-            else:
-                both = packed
-            return both[:, :, :D], both[:, :, D]
+                dist.all_gather_into_tensor(gathered, flat, group=self.group)
+                return self._unpack(gathered.view(self.world, -1), B, Hl, D)
+            return out_view, lse_view
 
         return step

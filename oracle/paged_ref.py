@@ -49,6 +49,7 @@ __all__ = [
     "kv_gather_ref",
     "kv_scatter_ref",
     "kv_ops_ref",
+    "kv_compact_ref",
     "slots_for_sequence",
     "paged_append_ref",
     "paged_gather_ref",
@@ -99,6 +100,24 @@ def kv_ops_ref(kv_cache, indices, values=None, operation="gather"):
 # --------------------------------------------------------------------------------------------
 # Paging = the reference operators on a flattened slot axis
 # --------------------------------------------------------------------------------------------
+
+def kv_compact_ref(kv_cache: torch.Tensor, mask: torch.Tensor, compat_fp32: bool = True):
+    """The intent of kv_compact_triton (src/kernels_t/kv_ops_triton.py:159-181): per batch row, the
+    positions where ``mask [B,S]`` is non-zero (the test at :82-84), packed in order.  The reference
+    kernel stores survivor ``s`` at output row ``s`` (:86) of an output with ``mask.sum()`` rows (:166-168),
+    which overruns it, so there is no reference output to pin this against; the restatement defines the
+    result as ``out[b, :, :count_b] = kv_cache[b][:, kept_b]`` with ``num_valid = max_b count_b`` and zeros
+    behind shorter rows.  Returns ``(out, counts)``."""
+    B, H, S, D = kv_cache.shape
+    m = mask.reshape(B, S) != 0
+    counts = m.sum(1).to(torch.int32)
+    n = int(counts.max()) if B else 0
+    out = torch.zeros(B, H, n, D, dtype=torch.float32 if compat_fp32 else kv_cache.dtype)
+    for b in range(B):
+        keep = torch.nonzero(m[b]).flatten()
+        out[b, :, :keep.numel()] = kv_cache[b].index_select(1, keep).to(out.dtype)
+    return out, counts
+
 
 def slots_for_sequence(block_row: torch.Tensor, length: int, page_size: int, start: int = 0) -> torch.Tensor:
     """Slot ids of logical positions ``start..length-1``: ``page_id*page_size + offset``."""

@@ -174,6 +174,30 @@ def test_kv_compact_keeps_masked_rows_in_order():
     assert torch.equal(out, cache[:, :, [1, 4, 5, 19]].float())
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_kv_compact_with_independent_rows(dtype):
+    """The reference signature takes a [B,S] mask whose rows differ (kv_ops_triton.py:159-181): every row's
+    survivors are packed in order, shorter rows are zero-filled, the counts come back on request; rows
+    that keep everything, nothing, and a sequence longer than one scan tile are all in the batch."""
+    from oracle import paged_ref as ref
+
+    g = torch.Generator().manual_seed(7)
+    B, H, S, D = 5, 3, 2500, 64
+    cache = torch.randn(B, H, S, D, generator=g).to(dtype)
+    mask = (torch.rand(B, S, generator=g) < 0.3).float()
+    mask[1] = 1
+    mask[2] = 0
+    mask[3, :2000] = 0
+    want, want_counts = ref.kv_compact_ref(cache, mask)
+    got, counts = iva_b200.kv_compact(cache.to(DEV), mask.to(DEV), return_counts=True)
+    assert got.dtype == torch.float32 and torch.equal(counts.cpu(), want_counts)
+    assert torch.equal(got.cpu(), want)
+    same_dtype = iva_b200.kv_compact(cache.to(DEV), mask.to(DEV), compat=False)
+    assert same_dtype.dtype == dtype and torch.equal(same_dtype.cpu().float(), want)
+    empty = iva_b200.kv_compact(cache.to(DEV), torch.zeros(B, S, device=DEV))
+    assert empty.shape == (B, H, 0, D)
+
+
 def test_canary_guards_around_the_pools_stay_intact():
     """Pools, new tokens and outputs are carved out of larger buffers whose surroundings hold a
     sentinel; after append, gather and decode attention every guard byte must be unchanged."""

@@ -130,3 +130,12 @@ def test_padding_masks_match_attention_torch(golden, golden_inputs):
     assert (y - _t(golden["module_padding_out"])).abs().max().item() <= 1e-6
     y, _, _ = ref.attention_module_ref(x, *w, H, ck, cv, attention_mask=m8)
     assert (y - _t(golden["module_padding_cache_out"])).abs().max().item() <= 1e-6
+
+
+def test_compaction_restatement_packs_rows_in_order():
+    cache = torch.arange(2 * 1 * 6 * 2, dtype=torch.float32).view(2, 1, 6, 2)
+    mask = torch.tensor([[0, 1, 0, 1, 1, 0], [1, 0, 0, 0, 0, 0]])
+    out, counts = ref.kv_compact_ref(cache, mask)
+    assert counts.tolist() == [3, 1] and out.shape == (2, 1, 3, 2)
+    assert torch.equal(out[0, 0], cache[0, 0, [1, 3, 4]]) and torch.equal(out[1, 0, 0], cache[1, 0, 0])
+    assert not out[1, 0, 1:].any()
