@@ -307,10 +307,13 @@ _flush_bufs = {}
 
 
 def flusher(dev, nbytes_read=0, always=False):
-    """An L2 flush (two writes of 512 MB, the L2 holds 126 MB) for workloads whose K/V would otherwise
-    stay cached.  ``always``: also for legs whose GPU time per call is shorter than the host's launch
-    cost -- the ~170 us of flush keep the host ahead of the GPU, so the event pair around the call
-    measures the device and not the launch path."""
+    """An L2 flush for workloads whose K/V would otherwise stay cached: 512 MB are written (the L2 holds
+    126 MB) and then read back.  The read pass matters for short kernels: a write-only flush leaves the
+    L2 full of DIRTY lines, and the next kernel pays for writing ~126 MB back to HBM while it runs (about
+    20 us of HBM time -- measured: 10 % on a 100 us kernel); after the read pass the L2 holds clean lines of
+    the flush buffer and nothing of the workload.  ``always``: also for legs whose GPU time per call is
+    shorter than the host's launch cost -- the ~170 us of flush keep the host ahead of the GPU, so the
+    event pair around the call measures the device and not the launch path."""
     if nbytes_read > 4 * 126e6 and not always:
         return None, None
     buf = _flush_bufs.get(dev)
@@ -319,16 +322,31 @@ def flusher(dev, nbytes_read=0, always=False):
 
     def flush():
         buf.fill_(1)
-        buf.fill_(2)
+        buf.view(torch.int64).max()
 
     return buf, flush
+
+
+def graph_of(fn, dev):
+    """``fn`` recorded as a CUDA graph (after one eager run on a side stream, which does the kernels'
+    one-time set-up outside the capture); returns the replay callable."""
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        fn()
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        fn()
+    return graph.replay
 
 
 # ---- decode workloads (c2, c3, c5a) ----------------------------------------------------------------------
 
 def measure_decode(name, wl, ranks, steps, warmup, kv_scales, seqs_total):
-    """Device-resident timing of append + attention on one decode workload.  Returns a dict with the
-    whole step (max over ranks) and the per-kernel legs of this rank."""
+    """Device-resident timing of the decode step (paged_decode_step: append + attention in one call) on one
+    decode workload, plus the attention call and the stand-alone append kernel on their own.  Returns a dict
+    with the whole step (max over ranks) and the per-kernel legs of this rank."""
     dev = ranks.dev
     lib = iva_b200.load_library()
     B = wl.batch
@@ -346,8 +364,9 @@ def measure_decode(name, wl, ranks, steps, warmup, kv_scales, seqs_total):
                                         out=out, lse=lse, **kv_scales)
 
     def step():
-        append()
-        attend()
+        # the decode step as one call: the new token of every sequence is written by the attention launch
+        iva_b200.paged_decode_step(wl.q, wl.k_new, wl.v_new, wl.k_pool, wl.v_pool, wl.block_table, lens, wl.page_size,
+                                   wl.scale, out=out, lse=lse, **kv_scales)
 
     for _ in range(max(warmup, 3)):
         step()
@@ -573,27 +592,41 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True):
         iva_b200.paged_append(k_loc, v_loc, wl.slot_mapping, k_new, v_new, wl.page_size)
 
     if hp is not None:
-        hp_step = hp.capture_local(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale) if use_graph else None
+        hp_attn = hp.capture_local(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale) if use_graph else None
+        # the whole step (append + attention) as one graph replay, followed by the one eager all-gather
+        hp_step = (hp.capture_local(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale,
+                                    new_tokens=(k_new, v_new)) if use_graph else None)
 
         def attend():
-            if hp_step is not None:
-                return hp_step()
+            if hp_attn is not None:
+                return hp_attn()
             return hp.decode(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale)
     else:
         out = torch.empty(1, wl.n_q_heads, wl.head_dim, device=dev, dtype=wl.dtype)
         lse = torch.empty(1, wl.n_q_heads, device=dev, dtype=torch.float32)
+        ws = torch.empty(iva_b200.decode_workspace_bytes(1, wl.n_q_heads, wl.n_kv_heads, wl.head_dim), dtype=torch.uint8,
+                         device=dev)
 
         def attend():
             return iva_b200.paged_decode_attention(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale,
-                                                   out=out, lse=lse)
+                                                   out=out, lse=lse, workspace=ws)
+
+        def both():
+            iva_b200.paged_decode_step(wl.q, k_new, v_new, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale,
+                                       out=out, lse=lse, workspace=ws)
+
+        # one GPU: the same step as one graph replay (a step of ~0.1 ms is launch-bound when issued from Python)
+        hp_step = graph_of(both, dev) if use_graph else None
 
     def local_only():
         iva_b200.paged_decode_attention(wl.q[:, hp.q_slice] if hp is not None else wl.q, k_loc, v_loc, wl.block_table,
                                         lens, wl.page_size, wl.scale, return_lse=True)
 
     def step():
+        if hp_step is not None:
+            return hp_step()
         append()
-        attend()
+        return attend()
 
     for _ in range(max(warmup, 3)):
         step()
@@ -811,17 +844,17 @@ def c1_case(dev):
         step()
     gpu = time_region(step, 50, flush)
     # the same two calls replayed as one CUDA graph (what a serving loop does with a launch-bound step)
-    side = torch.cuda.Stream(device=dev)
-    side.wait_stream(torch.cuda.current_stream(dev))
-    with torch.cuda.stream(side):
-        step()
-    side.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        step()
+    ws = torch.empty(iva_b200.decode_workspace_bytes(wl.batch, wl.n_q_heads, wl.n_kv_heads, wl.head_dim), dtype=torch.uint8,
+                     device=dev)
+
+    def graphed():
+        iva_b200.paged_decode_step(d.q, d.k_new, d.v_new, d.k_pool, d.v_pool, d.block_table, lens, wl.page_size, wl.scale,
+                                   out=out, workspace=ws)
+
+    replay = graph_of(graphed, dev)
     for _ in range(5):
-        graph.replay()
-    gpu_graph = time_region(graph.replay, 50, flush)
+        replay()
+    gpu_graph = time_region(replay, 50, flush)
     nbytes = attention_bytes(wl, wl.ctx_len + 1) + append_bytes(wl)
     return {"config": "batch 4, 16 heads, head_dim 64, fp32, contexts " + str(wl.ctx_len.tolist()),
             "cpu_ms_per_step": statistics.median(cpu) * 1e3, "cpu_cores": torch.get_num_threads(),

@@ -224,6 +224,32 @@ int ivab_paged_decode_attn_fp8(const void* q, int64_t q_stride_b, int64_t q_stri
                                float scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * One decode step in one call: append the newest token of every sequence, then attend over the cache
+ * including it -- ivab_paged_append (one token per sequence) followed by ivab_paged_decode_attn[_fp8],
+ * without the separate copy launch.  It replaces the pair cat-append + attention of
+ * AttentionTorch.forward (src/core/attention.py:61-63 and :77,99,102) for a one-token step.
+ *   k_new, v_new: [batch, kv_heads, head_dim] in `dtype` (strides new_stride_t per sequence, new_stride_h
+ *   per head, in elements).  ctx_len[s] INCLUDES the new token: it is stored at position ctx_len[s] - 1,
+ *   i.e. in page block_table[s][(ctx_len[s]-1) / page_size] -- the block table, not a slot mapping, says
+ *   where (the page must already be in the table).  A sequence with ctx_len 0 appends nothing.
+ *   kv_dtype: `dtype`, or IVAB_F8E4M3 with k_scale / v_scale (then the rows are quantised exactly as
+ *   ivab_paged_append_fp8 does; pool strides in 1-byte elements).
+ * The row is written by the CTA that reads that page (ordinary stores, ordered before its TMA reads), so the
+ * pools end up bit-identical to the two-call sequence and so does the attention result.  Everything
+ * else as for ivab_paged_decode_attn.
+ */
+int ivab_paged_decode_step(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                           const void* k_new, const void* v_new, int64_t new_stride_t, int64_t new_stride_h,
+                           void* k_pool, void* v_pool, int64_t pool_stride_head, int64_t pool_stride_page,
+                           int kv_dtype, float k_scale, float v_scale,
+                           const int32_t* block_table, int64_t block_table_stride,
+                           const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
+                           void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                           int dtype, int out_dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                           int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq,
+                           float scale, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Copies the status word of the last ivab_paged_decode_attn call on `workspace` to the host
  * (synchronises `stream`).  *status_out is a mask of IVAB_STATUS_* bits; returns
  * IVAB_ERR_DEVICE if it is non-zero.

@@ -21,6 +21,7 @@ from .attention import (  # noqa: F401
     decode_workspace_bytes,
     get_attention,
     paged_decode_attention,
+    paged_decode_step,
 )
 from .paged_cache import PagedKVCache  # noqa: F401
 from .decode_step import GraphedDecodeStep  # noqa: F401

@@ -25,8 +25,8 @@ import torch.nn as nn
 from . import _lib
 from .kv_ops import _pool_strides
 
-__all__ = ["paged_decode_attention", "attention", "AttentionB200", "get_attention", "decode_workspace_bytes",
-           "decode_status"]
+__all__ = ["paged_decode_attention", "paged_decode_step", "attention", "AttentionB200", "get_attention",
+           "decode_workspace_bytes", "decode_status"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}   # insertion order = least recently used first
 _MAX_WORKSPACES = 8
@@ -103,10 +103,44 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
                    (float(k_scale), float(v_scale)) if fp8 else None, out_dtype)
 
 
+def paged_decode_step(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_pool: torch.Tensor,
+                      v_pool: torch.Tensor, block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
+                      scale: Optional[float] = None, *, out: Optional[torch.Tensor] = None,
+                      lse: Optional[torch.Tensor] = None, return_lse: bool = False,
+                      workspace: Optional[torch.Tensor] = None, check: bool = False,
+                      ctx_begin: Optional[torch.Tensor] = None, sink_tokens: int = 0,
+                      k_scale: float = 1.0, v_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None):
+    """One decode step in one call: append one new token per sequence (``k_new`` / ``v_new`` ``[B,H_kv,D]`` in q's
+    dtype) and attend over the cache including it -- ``paged_append`` followed by ``paged_decode_attention``
+    without the separate copy launch (the concat-append plus attention of src/core/attention.py:61-63,77,99,102
+    for a one-token step).  ``ctx_len`` INCLUDES the new token, which is stored at position ``ctx_len[s] - 1``
+    through the block table (its page must already be in the table).  The pools end up bit-identical to the
+    two-call sequence, and so does the result.  Other arguments as for ``paged_decode_attention``."""
+    _lib.require_cuda(q, k_new, v_new, k_pool, v_pool, block_table, ctx_len)
+    Hkv, num_pages, sh, sp = _pool_strides(k_pool, page_size)
+    if _pool_strides(v_pool, page_size) != (Hkv, num_pages, sh, sp) or v_pool.dtype != k_pool.dtype:
+        raise ValueError("k_pool and v_pool must have the same shape, strides and dtype")
+    fp8 = k_pool.dtype == torch.float8_e4m3fn
+    if k_pool.shape[-1] != q.shape[-1] or (k_pool.dtype != q.dtype and not fp8):
+        raise ValueError("q and the pools must share dtype and head_dim")
+    if fp8 and q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("8-bit pools need fp16 or bf16 queries")
+    B, D = q.shape[0], q.shape[-1]
+    if k_new.shape != (B, Hkv, D) or v_new.shape != k_new.shape or k_new.dtype != q.dtype or v_new.dtype != q.dtype:
+        raise ValueError("k_new / v_new must be [B, H_kv, D] in q's dtype")
+    if k_new.stride(-1) != 1 or v_new.stride() != k_new.stride():
+        k_new, v_new = k_new.contiguous(), v_new.contiguous()
+    return _decode(q, k_pool, v_pool, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
+                   out, lse, return_lse, workspace, check, ctx_begin, sink_tokens,
+                   (float(k_scale), float(v_scale)) if fp8 else None, out_dtype, new_tokens=(k_new, v_new))
+
+
 def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
-            out, lse, return_lse, workspace, check, ctx_begin=None, sink_tokens=0, fp8_scales=None, out_dtype=None):
+            out, lse, return_lse, workspace, check, ctx_begin=None, sink_tokens=0, fp8_scales=None, out_dtype=None,
+            new_tokens=None):
     """Argument checks and the library call; ``k_base`` / ``v_base`` only supply base pointers, the
-    pool geometry is given by ``Hkv, num_pages, sh, sp`` (element strides of head and page)."""
+    pool geometry is given by ``Hkv, num_pages, sh, sp`` (element strides of head and page).
+    ``new_tokens=(k_new, v_new)`` selects the fused step (append + attention)."""
     if q.requires_grad:
         raise RuntimeError("paged_decode_attention is inference-only")
     lib = _lib.load_library()
@@ -155,7 +189,14 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
                 block_table.shape[1],
                 float(scale), workspace.data_ptr(), workspace.numel(), stream)
         head = (q.data_ptr(), q.stride(0), q.stride(1), k_base.data_ptr(), v_base.data_ptr(), sh, sp)
-        if fp8_scales is None:
+        if new_tokens is not None:
+            kn, vn = new_tokens
+            ks, vs = fp8_scales if fp8_scales is not None else (1.0, 1.0)
+            _lib.check(lib.ivab_paged_decode_step(
+                q.data_ptr(), q.stride(0), q.stride(1), kn.data_ptr(), vn.data_ptr(), kn.stride(0), kn.stride(1),
+                k_base.data_ptr(), v_base.data_ptr(), sh, sp,
+                _lib.F8E4M3 if fp8_scales is not None else _lib.dtype_code(q.dtype), ks, vs, *tail))
+        elif fp8_scales is None:
             _lib.check(lib.ivab_paged_decode_attn(*head, *tail))
         else:
             _lib.check(lib.ivab_paged_decode_attn_fp8(*head, fp8_scales[0], fp8_scales[1], *tail))
@@ -319,7 +360,10 @@ class AttentionB200(nn.Module):
         # rope_state is accepted and ignored, like the reference's _apply_rope (attention.py:112-113)
 
         if getattr(kv_cache, "is_paged", False):
-            prior = kv_cache.append(k, v)                     # [B] lengths before the append (host list)
+            # a plain one-token step writes the new token inside the attention launch (paged_decode_step);
+            # the cache then only does this step's bookkeeping (pages, lengths, table upload)
+            fused = S == 1 and attention_mask is None
+            prior = kv_cache.append(k, v, write=not fused)    # [B] lengths before the append (host list)
             bt, cl = kv_cache.block_table_dev, kv_cache.ctx_len_dev
             if attention_mask is not None:
                 # padding: keys [m_begin, m_end) of each row are real (attention.py:95-97 hides the others)
@@ -334,8 +378,10 @@ class AttentionB200(nn.Module):
                                            kv_cache.page_size, self.scale, ctx_begin=cb)
             elif S == 1:
                 cb = None if sliding_window is None else (cl - int(sliding_window)).clamp_(min=0)
-                o = paged_decode_attention(q.reshape(B, H, D), kv_cache.k_pool, kv_cache.v_pool, bt, cl,
-                                           kv_cache.page_size, self.scale, ctx_begin=cb, sink_tokens=sink)
+                scales = dict(k_scale=kv_cache.k_scale, v_scale=kv_cache.v_scale)
+                o = paged_decode_step(q.reshape(B, H, D), k.reshape(B, H, D), v.reshape(B, H, D), kv_cache.k_pool,
+                                      kv_cache.v_pool, bt, cl, kv_cache.page_size, self.scale, ctx_begin=cb,
+                                      sink_tokens=sink, **scales)
             else:
                 q2 = q.reshape(B * S, H, D)
                 bt2 = bt.repeat_interleave(S, dim=0)

@@ -145,6 +145,19 @@ __device__ __forceinline__ void tma_tile4d_g2s(uint32_t dst_smem, const void* te
         : "memory");
 }
 
+// Orders this thread's earlier generic-proxy accesses (ordinary loads and stores, global memory included)
+// before later accesses of the async proxy (TMA copies) -- needed when a TMA copy must see what ordinary
+// stores of the same CTA have just written to global memory.
+__device__ __forceinline__ void fence_proxy_async_all() {
+    asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// Brings a tensor map (the 128-byte descriptor a tiled TMA copy reads) into the descriptor cache ahead of
+// its first use.
+__device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensor_map)) : "memory");
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -105,6 +105,17 @@ bool use_plan_pdl() {
     return v;
 }
 
+// Order in which work items are handed out: 0 = kv-head-major, 1 = chunk-major, 2 = chunk-major when the plan
+// kernel finds the batch ragged (IVAB_ITEM_ORDER, experiments).
+int item_order() {
+    static int v = [] {
+        const char* e = std::getenv("IVAB_ITEM_ORDER");
+        const int n = e ? std::atoi(e) : kDefaultItemOrder;
+        return n < 0 || n > 2 ? kDefaultItemOrder : n;
+    }();
+    return v;
+}
+
 // Smallest chunk (pages) the plan-free mode cuts; IVAB_DIRECT_MIN_CHUNK overrides it for experiments.
 int direct_min_chunk_pages() {
     static int v = [] {
@@ -123,6 +134,10 @@ size_t carve_workspace(void* base, int64_t B, int64_t Hq, int64_t Hkv, int64_t D
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return p ? p + o : nullptr; };
     int* header = reinterpret_cast<int*>(take(kHdrWords * sizeof(int)));
     int* slots = reinterpret_cast<int*>(take(kStatusSlots * sizeof(int)));   // (ivab_decode_status reads header + slots in one copy)
+#ifdef IVAB_PROFILE
+    unsigned long long* prof_cta = reinterpret_cast<unsigned long long*>(take(kStatusSlots * 4 * sizeof(unsigned long long)));
+    if (ws) ws->prof_cta = prof_cta;
+#endif
     int* prefix = reinterpret_cast<int*>(take((B + 1) * sizeof(int)));
     int* order = reinterpret_cast<int*>(take(B * sizeof(int)));
     int* seq_first = reinterpret_cast<int*>(take(B * sizeof(int)));
@@ -184,6 +199,11 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     // the attention kernel may be scheduled now: its set-up does not depend on the plan, and it
     // waits for this grid to complete before it reads the workspace
     grid_launch_dependents();
+    // This kernel is itself launched as a programmatic dependent of the kernel before it in the stream, so
+    // that its launch latency hides under that kernel (typically the append of the same step).  That kernel
+    // may be the one that wrote ctx_len, and the attention kernel waits for THIS grid only: nothing is read,
+    // and this grid cannot complete, before the predecessor has completed.
+    grid_dependency_wait();
 #ifdef IVAB_PROFILE
     if (tid == 0) {
         PROF_STAMP_SET(ws.header, 0)
@@ -283,6 +303,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         ws.header[kHdrTotalItems] = num_chunks * Hkv;
         ws.header[kHdrNumSplit] = overflow ? 0 : s_split;
         ws.header[kHdrNumBig] = overflow ? 0 : s_big;
+        ws.header[kHdrChunkMajor] = sorted && s_ragged != 0;
 #ifdef IVAB_PROFILE
         for (int i = 16; i < 48; ++i) ws.header[i] = 0;
 #endif
@@ -318,10 +339,6 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     __syncthreads();
     if (tid == 0) PROF_STAMP_SET(ws.header, 1)
 #endif
-    // This kernel may itself have been launched as a programmatic dependent of the kernel before it in
-    // the stream (typically the append of the same step, which it does not depend on).  The attention
-    // kernel waits for THIS grid only, so this grid must not complete before its predecessor has.
-    grid_dependency_wait();
 }
 
 // OR of the header's status word and of the per-CTA slots of the last call, into one device word.
@@ -374,7 +391,8 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
                  int dtype, int out_dtype, int kv_dtype, float k_scale, float v_scale,
                  int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                  int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
-                 void* workspace, size_t workspace_bytes, void* stream) {
+                 void* workspace, size_t workspace_bytes, void* stream,
+                 const void* k_new = nullptr, const void* v_new = nullptr, int64_t new_stride_t = 0, int64_t new_stride_h = 0) {
     const size_t esz = dtype_size(dtype);
     const size_t kv_esz = dtype_size(kv_dtype);
     if (esz == 0 || kv_esz == 0) return set_error(IVAB_ERR_INVALID, "%s: unknown dtype %d / %d", fn, dtype, kv_dtype);
@@ -397,6 +415,9 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     if (batch >= (1LL << 30) || max_pages_per_seq * page_size >= (1LL << 31))
         return set_error(IVAB_ERR_UNSUPPORTED, "%s: batch or context too large", fn);
     if (sink_tokens < 0 || sink_tokens >= (1LL << 31)) return set_error(IVAB_ERR_INVALID, "%s: bad sink_tokens", fn);
+    if ((k_new != nullptr) != (v_new != nullptr)) return set_error(IVAB_ERR_INVALID, "%s: k_new and v_new go together", fn);
+    if (k_new != nullptr && (mis(k_new, 16) || mis(v_new, 16) || (new_stride_t * esz) % 16 || (new_stride_h * esz) % 16))
+        return set_error(IVAB_ERR_INVALID, "%s: new tokens must be 16-byte aligned with 16-byte strides", fn);
 
     const int64_t ratio = q_heads / kv_heads;
     const int kv_div = split_ratio(ratio);
@@ -420,7 +441,7 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     const bool direct = batch <= kDirectMaxBatch && use_direct_mode();
     if (!direct) {
         // a programmatic dependent of whatever kernel precedes it in the stream (the append of the same
-        // step): it reads none of that kernel's output and waits for it before it exits
+        // step): it is placed while that kernel runs and waits for it before it reads anything
         cudaLaunchAttribute pdl{};
         pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
         pdl.val.programmaticStreamSerializationAllowed = 1;
@@ -437,6 +458,7 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     p.direct = direct ? 1 : 0;
     p.batch = (int)batch; p.max_pages = (int)max_pages_per_seq; p.n_virt_heads = (int)virt_heads;
     p.direct_min_chunk = direct_min_chunk_pages();
+    p.chunk_major = item_order();
     p.ctx_len = ctx_len; p.ctx_begin = ctx_begin;
     p.q = q; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
     p.k_pool = static_cast<const char*>(k_pool); p.v_pool = static_cast<const char*>(v_pool);
@@ -451,6 +473,9 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     p.scale_log2 = scale * k_scale * 1.4426950408889634f;   // K = k_scale * stored value
     p.wait_limit_ns = kWaitLimitNs;
     p.ws = ws;
+    p.k_new = static_cast<const char*>(k_new); p.v_new = static_cast<const char*>(v_new);
+    p.new_st_bytes = new_stride_t * (int64_t)esz; p.new_sh_bytes = new_stride_h * (int64_t)esz;
+    p.k_inv_scale = 1.f / k_scale; p.v_inv_scale = 1.f / v_scale;
     const int G = p.group;
     if (kv_dtype == IVAB_F8E4M3) {
         if (dtype == IVAB_F16) return decode_dispatch_fp8_f16((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
@@ -499,6 +524,30 @@ extern "C" int ivab_paged_decode_attn_fp8(const void* q, int64_t q_stride_b, int
                         pool_stride_page, block_table, block_table_stride, ctx_len, ctx_begin, sink_tokens, out,
                         out_stride_b, out_stride_h, lse, dtype, out_dtype, IVAB_F8E4M3, k_scale, v_scale, batch, q_heads, kv_heads,
                         head_dim, page_size, num_pages, max_pages_per_seq, scale, workspace, workspace_bytes, stream);
+}
+
+extern "C" int ivab_paged_decode_step(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                      const void* k_new, const void* v_new, int64_t new_stride_t, int64_t new_stride_h,
+                                      void* k_pool, void* v_pool, int64_t pool_stride_head, int64_t pool_stride_page,
+                                      int kv_dtype, float k_scale, float v_scale,
+                                      const int32_t* block_table, int64_t block_table_stride,
+                                      const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
+                                      void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                                      int dtype, int out_dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                                      int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq,
+                                      float scale, void* workspace, size_t workspace_bytes, void* stream) {
+    const char* fn = "ivab_paged_decode_step";
+    if (batch > 0 && (!k_new || !v_new)) return set_error(IVAB_ERR_INVALID, "%s: null pointer", fn);
+    if (kv_dtype != dtype && kv_dtype != IVAB_F8E4M3)
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: the pools hold the dtype of q, or IVAB_F8E4M3", fn);
+    if (kv_dtype == IVAB_F8E4M3 && (!(k_scale > 0.f) || !(v_scale > 0.f)))
+        return set_error(IVAB_ERR_INVALID, "%s: scales must be positive", fn);
+    if (kv_dtype != IVAB_F8E4M3) k_scale = v_scale = 1.f;
+    return decode_entry(fn, q, q_stride_b, q_stride_h, k_pool, v_pool, pool_stride_head, pool_stride_page, block_table,
+                        block_table_stride, ctx_len, ctx_begin, sink_tokens, out, out_stride_b, out_stride_h, lse, dtype,
+                        out_dtype, kv_dtype, k_scale, v_scale, batch, q_heads, kv_heads, head_dim, page_size, num_pages,
+                        max_pages_per_seq, scale, workspace, workspace_bytes, stream, k_new, v_new, new_stride_t,
+                        new_stride_h);
 }
 
 extern "C" int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream) {

@@ -19,6 +19,8 @@ constexpr int kMaxStages = 32;
 static_assert(kMaxStages % kConsumerWarps == 0, "stage ring must divide among the consumer warps");
 constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
 constexpr int kMinChunkPages = 8;
+constexpr int kRefillParts = 1;       // the producer requests 1/kRefillParts of the stage ring at a time
+constexpr int kDefaultItemOrder = 2;  // 0: kv-head-major, 1: chunk-major, 2: chunk-major for ragged batches only (see split_id)
 // Plan-free ("direct") mode, for batches small enough that one warp holds a sequence per lane:
 constexpr int kDirectMaxBatch = 32;
 constexpr int kDirectItemsPerSlot = 2;       // work items per resident CTA the chunk size aims for
@@ -49,6 +51,7 @@ constexpr int kMaxDevices = 64;      // device ordinals the per-device host cach
 
 // header words at the start of the workspace
 enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrNumSplit = 5, kHdrNumBig = 6,
+       kHdrChunkMajor = 7,   // order in which the items are handed out, chosen by the plan kernel
        kHdrWords = 64 };
 // Status protocol.  header[kHdrStatus] holds the bits of the planning step: written by the plan kernel,
 // or (plan-free mode) by CTA 0 of the attention kernel.  Every CTA of the attention kernel additionally
@@ -75,6 +78,9 @@ struct Workspace {
     float* part_ml;       // [cap*Hkv][G][2]   (running max in log2 units, sum)
     float* part_o;        // [cap*Hkv][G][D]
     int* status_slots;    // [kStatusSlots] per-CTA status words, directly behind the header
+#ifdef IVAB_PROFILE
+    unsigned long long* prof_cta;   // [kStatusSlots][4]: per CTA start, first page, last warp done (ns), items
+#endif
     int cap;
     int target_chunks;
 };
@@ -93,6 +99,7 @@ struct DecodeParams {
     float v_scale;             // 8-bit KV storage: V = v_scale * stored value (1 otherwise); K's scale is folded into scale_log2
     float scale_log2;          // scale * log2(e): scores are kept in base-2 units
     int stages;
+    int refill_pages;        // pages the producer requests at a time (see the producer warp)
     uint64_t wait_limit_ns;
     Workspace ws;
     // Plan-free mode (direct != 0): there is no plan kernel; every CTA derives the chunking from ctx_len
@@ -101,7 +108,13 @@ struct DecodeParams {
     int batch, max_pages, n_virt_heads;        // sequences, block-table width, KV heads the items number
     int direct_target_items, direct_min_chunk; // chunk size = max(min_chunk, ceil(total_pages * heads / target_items))
     int status_slots_per_cta;                  // 2 when the grid is one CTA per SM, else 1
+    int chunk_major;                           // order in which items are handed out: 0, 1, or 2 = as the plan kernel decided
     const int32_t* ctx_len; const int32_t* ctx_begin;
+    // Fused decode step (k_new != nullptr): the newest token of every sequence -- position ctx_len - 1 -- is
+    // written into its page by the CTA that is about to read that page (new tokens [batch, kv_heads, D] in q's
+    // type, strides in bytes; 8-bit pools store fp8(x * inv_scale)).
+    const char* k_new; const char* v_new; int64_t new_st_bytes, new_sh_bytes;
+    float k_inv_scale, v_inv_scale;
 };
 
 namespace {

@@ -23,6 +23,34 @@ namespace {
 // 2. persistent split-K attention
 // ------------------------------------------------------------------------------------------------
 
+// Fused decode step: one warp writes the newest token's K and V rows of one KV head into their slot of the
+// pool (T: type of the new tokens = type of q; TKV: storage type of the pool).  The rows are copied verbatim,
+// or -- 8-bit pools -- quantised exactly as the stand-alone append does (fp8(x * inv_scale), saturating).
+template <typename T, typename TKV, int D>
+__device__ __forceinline__ void append_newest_row(const DecodeParams& p, int seq, int slab, char* krow, char* vrow, int lane) {
+    constexpr int kVecs = D * (int)sizeof(T) / 16;      // 16-byte vectors per source row
+    const char* ks = p.k_new + (int64_t)seq * p.new_st_bytes + (int64_t)slab * p.new_sh_bytes;
+    const char* vs = p.v_new + (int64_t)seq * p.new_st_bytes + (int64_t)slab * p.new_sh_bytes;
+    for (int v = lane; v < 2 * kVecs; v += 32) {
+        const bool is_v = v >= kVecs;
+        const int i = is_v ? v - kVecs : v;
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(is_v ? vs : ks) + i);
+        char* dst = is_v ? vrow : krow;
+        if constexpr (std::is_same<T, TKV>::value) {
+            *reinterpret_cast<uint4*>(dst + i * 16) = u;
+        } else {
+            static_assert(sizeof(T) == 2 && sizeof(TKV) == 1, "quantising append: 16-bit tokens into 8-bit pools");
+            float f[8];
+            Elt<T>::unpack(u, f);
+            const float is = is_v ? p.v_inv_scale : p.k_inv_scale;
+            uint2 q;
+            q.x = (uint32_t)pack_fp8x2(f[0] * is, f[1] * is) | ((uint32_t)pack_fp8x2(f[2] * is, f[3] * is) << 16);
+            q.y = (uint32_t)pack_fp8x2(f[4] * is, f[5] * is) | ((uint32_t)pack_fp8x2(f[6] * is, f[7] * is) << 16);
+            *reinterpret_cast<uint2*>(dst + i * 8) = q;
+        }
+    }
+}
+
 template <typename T, int D, int G, int ENG, typename TKV = T>
 __global__ void __launch_bounds__(kThreads, EngineSelect<ENG, T, TKV, D, G>::type::CTAS_PER_SM)
 decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ TensorMaps tm) {
@@ -50,6 +78,10 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     volatile int* items = reinterpret_cast<volatile int*>(smem + C::OFF_ITEMS);
     unsigned char* stage_base = smem + C::OFF_STAGES;
 
+    if constexpr (Eng::kTiled) {
+        // (the descriptors are kernel parameters, so this needs nothing from the kernels before this one)
+        if (threadIdx.x == kConsumerWarps * 32) { prefetch_tensormap(&tm.k); prefetch_tensormap(&tm.v); }
+    }
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < stages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
@@ -104,6 +136,11 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
 #pragma unroll
         for (int i = 0; i < kConsumerWarps; ++i) cnt[i] = 0;
         const int spw = stages / kConsumerWarps;   // stages per warp
+        // Pages are requested `refill` at a time (a fraction of the ring, a multiple of the consumer-warp
+        // count).  The lanes of a request leave their stage waits together, so a request for the whole
+        // ring would only go out once the ring has drained completely -- one full memory latency without
+        // data per round, which a compute-bound engine (8-bit pools) cannot hide behind other CTAs.
+        const int refill = p.refill_pages;
         int published = 0;  // items published so far
         bool aborted = false;
         // The fetch of an item is three dependent global accesses (work counter -> chunk descriptor ->
@@ -134,17 +171,27 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             return v;
         };
         auto fetch_id = [&]() { return __shfl_sync(0xffffffffu, fetch_id_async(), 0); };
+        // Item id -> (kv head, index in the chunk list).  Head-major order keeps the CTAs that run at the same
+        // time on one or two heads' slabs of the pool; chunk-major order walks the chunk list (longest
+        // sequences first) once for all heads, so the items handed out last are the shortest ones.
+        // A batch of equal lengths is served head-major (measured 0.5-1 % faster: fewer slabs are open at a
+        // time), a ragged one chunk-major (its long items must not be the ones that start last).
+        const bool chunk_major = p.chunk_major == 2 ? (!direct && p.ws.header[kHdrChunkMajor] != 0) : p.chunk_major == 1;
+        auto split_id = [&](int id, int* h_out, int* ci_out) {
+            if (chunk_major) { const int ci = id / p.n_virt_heads; *ci_out = ci; *h_out = id - ci * p.n_virt_heads; }
+            else { const int h = id / num_chunks; *h_out = h; *ci_out = id - h * num_chunks; }
+        };
         auto load_desc = [&](int id, int* h_out) {
             ChunkDesc d{};
             *h_out = 0;
+            int h = 0, ci = 0;
+            if (id < total_items) split_id(id, &h, &ci);
             if (direct) {      // (every lane takes part in the shuffles, whatever the id)
-                const int h = id < total_items ? id / num_chunks : 0;
-                d = direct_desc(dplan, id < total_items ? id - h * num_chunks : 0, p.batch, lane);
+                d = direct_desc(dplan, ci, p.batch, lane);
                 if (id >= total_items) d = ChunkDesc{};
                 *h_out = h;
             } else if (id < total_items) {
-                const int h = id / num_chunks;
-                const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + (id - h * num_chunks));
+                const int4* src = reinterpret_cast<const int4*>(p.ws.chunks + ci);
                 // written by the plan kernel of this call, which may still have been running when this
                 // CTA started: not read-only data, so no ld.global.nc here
                 const int4 a = __ldcg(src), b = __ldcg(src + 1);
@@ -192,7 +239,10 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             if (lane == 0) {
                 volatile int* it = items + slot * kItWords;
                 it[kItSeq] = d.seq; it[kItHead] = h; it[kItPages] = done ? -1 : d.n_pages;
-                it[kItPageBegin] = d.page_begin; it[kItChunks] = d.n_chunks; it[kItIndex] = item;
+                int ci = 0, hh = 0;
+                if (!done) split_id(item, &hh, &ci);
+                // (where this item's partial result is stored: head-major, whatever the processing order)
+                it[kItPageBegin] = d.page_begin; it[kItChunks] = d.n_chunks; it[kItIndex] = hh * num_chunks + ci;
                 it[kItStart] = (d.seq + d.chunk_idx) % kConsumerWarps; it[kItLen] = d.pad0; it[kItBegin] = d.pad1; it[kItSinkPages] = d.pad2;
                 mbar_arrive(bar_item_full(slot));
             }
@@ -202,17 +252,38 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             const int slab = h / p.kv_div;   // the KV head whose pages this item reads
             const char* kbase = p.k_pool + (int64_t)slab * p.pool_sh_bytes;
             const char* vbase = p.v_pool + (int64_t)slab * p.pool_sh_bytes;
+            // Fused decode step: the item that ends a sequence reads the page of its newest token, so this
+            // warp first writes that token's rows (position L - 1) of this KV head into the page, then
+            // orders the stores before its own TMA reads.  No other CTA reads that page -- except, with more
+            // than 8 query heads per KV head, the items of the sibling head groups, which write the same
+            // bytes themselves before they read.
+            if (p.k_new != nullptr && d.chunk_idx == d.n_chunks - 1 && d.pad0 > 0) {
+                const int pos = d.pad0 - 1;
+                const int pid = __ldg(p.block_table + (int64_t)d.seq * p.bt_stride + pos / kPage);
+                if (pid < 0 || pid >= p.num_pages) {
+                    if (lane == 0) atomicOr(cta_status, kStatusBadPage);    // skipped, never written out of range
+                } else {
+                    const int64_t off = (int64_t)slab * p.pool_sh_bytes + (int64_t)pid * p.pool_sp_bytes +
+                                        (int64_t)(pos % kPage) * (D * (int)sizeof(TKV));
+                    append_newest_row<T, TKV, D>(p, d.seq, slab, const_cast<char*>(p.k_pool) + off,
+                                                 const_cast<char*>(p.v_pool) + off, lane);
+                }
+                fence_proxy_async_all();
+                __syncwarp();
+            }
             const int start = (d.seq + d.chunk_idx) % kConsumerWarps;
+            int bt_next = bt0;
             for (int p0 = 0; p0 < d.n_pages && !aborted; p0 += 32) {
-                const int mine = p0 == 0 ? bt0 : load_pages(d, p0);
+                const int mine = bt_next;
+                if (p0 + 32 < d.n_pages) bt_next = load_pages(d, p0 + 32);   // in flight while this batch is issued
                 const int in_batch = min(32, d.n_pages - p0);
                 PROF_MARK(2)   // block-table entries available
                 // Pages are issued a ring's worth at a time, ONE LANE PER PAGE: every lane waits for
                 // its own stage and issues its own copies, so the issue cost of up to `stages` pages
                 // overlaps.  A sub-batch never exceeds the ring (spw pages per consumer warp): a lane
                 // must not wait two phases ahead of a stage's barrier.
-                for (int q0 = 0; q0 < in_batch && !aborted; q0 += stages) {
-                    const int nb = min(stages, in_batch - q0);
+                for (int q0 = 0; q0 < in_batch && !aborted; q0 += refill) {
+                    const int nb = min(refill, in_batch - q0);
                     int pid = __shfl_sync(0xffffffffu, mine, (q0 + lane) & 31);
                     if (lane < nb && (pid < 0 || pid >= p.num_pages)) {
                         atomicOr(cta_status, kStatusBadPage);   // flagged, and page 0 is read instead of faulting
@@ -389,6 +460,8 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     PROF_FLUSH(8)
 #ifdef IVAB_PROFILE
     if (lane == 0) {
+        atomicMax(p.ws.prof_cta + blockIdx.x * 4 + 2, (unsigned long long)globaltimer_ns());
+        if (warp == 0) { p.ws.prof_cta[blockIdx.x * 4 + 0] = prof_cta_start; p.ws.prof_cta[blockIdx.x * 4 + 3] = (unsigned long long)consumed; }
         PROF_STAMP_MAX(p.ws.header, 5, globaltimer_ns())
         atomicMin(reinterpret_cast<unsigned long long*>(p.ws.header + 8), (unsigned long long)globaltimer_ns());   // first warp done
     }
@@ -427,8 +500,8 @@ __device__ __forceinline__ void load_row(const float* src, float (&v)[VPL]) {
 //      holds the (max, sum) pair of chunk j, every lane owns D/32 consecutive dims.  No shared
 //      memory, no barrier -- the common case (a few chunks per sequence) costs one round of loads.
 //   B. a sequence of more chunks (one very long context on an otherwise idle GPU): one CTA per
-//      (sequence, query head, 32-dim slice); warp w folds chunks w, w+8, ... against its own running
-//      maximum, the eight warp results are then combined through shared memory.
+//      (sequence, query head, 32-dim slice); the maximum over all chunks is taken first, then 32 groups of
+//      eight lanes fold chunks g, g+32, ... with 16-byte loads, and the groups are summed in a fixed order.
 template <typename T, int D>
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_constant__ DecodeParams p, int B) {
     const Workspace& ws = p.ws;
@@ -543,7 +616,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     }
     __shared__ float sh_m[kMergeWarps];
     __shared__ float sh_l[kMergeWarps];
-    __shared__ float sh_o[kMergeWarps][32];
+    __shared__ __align__(16) float sh_o[kMergeWarps][32];
     for (int c = blockIdx.x; c < n_big * Hq * VPL; c += gridDim.x) {
         const int unit = c / VPL, slice = c % VPL;
         const int s = direct ? unit / Hq : ws.split_list[B - 1 - unit / Hq], hq = unit % Hq;
@@ -553,32 +626,48 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
         const int h = hq / G, g = hq % G;
         const size_t item0 = (size_t)h * num_chunks + first;
         const float* ml = ws.part_ml + (item0 * G + g) * 2;
-        const float* po = ws.part_o + (item0 * G + g) * D + slice * 32 + lane;
+        // 8 warps x 4 lane groups = 32 chunk groups; the 8 lanes of a group own four dims each of the slice
+        const int grp = warp * 4 + (lane >> 3), dq = lane & 7;
+        const float* po = ws.part_o + (item0 * G + g) * D + slice * 32 + dq * 4;
 
-        float mw = -INFINITY;   // maximum over this warp's chunks
-        for (int j = warp + kMergeWarps * lane; j < n; j += kMergeWarps * 32) mw = fmaxf(mw, ml[(size_t)j * G * 2]);
-        mw = warp_max_f32(mw);
-        float lw = 0.f, acc = 0.f;
+        // the maximum over all chunks first, so that every chunk is weighted once and no partial sum is rescaled
+        float mx = -INFINITY;
+        for (int j = threadIdx.x; j < n; j += kMergeWarps * 32) mx = fmaxf(mx, ml[(size_t)j * G * 2]);
+        mx = warp_max_f32(mx);
+        if (lane == 0) sh_m[warp] = mx;
+        __syncthreads();
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kMergeWarps; ++w) M = fmaxf(M, sh_m[w]);
+
+        // chunk group `grp` folds chunks grp, grp + 32, ...: 16-byte loads, eight of them in flight per thread
+        float lw = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-        for (int j = warp; j < n; j += kMergeWarps) {
+        for (int j = grp; j < n; j += kMergeWarps * 4) {
             const float2 v = *reinterpret_cast<const float2*>(ml + (size_t)j * G * 2);
-            const float fj = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - mw);
+            const float fj = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - M);
+            const float4 o4 = *reinterpret_cast<const float4*>(po + (size_t)j * G * D);
             lw = fmaf(v.y, fj, lw);
-            acc = fmaf(po[(size_t)j * G * D], fj, acc);
+            acc.x = fmaf(o4.x, fj, acc.x); acc.y = fmaf(o4.y, fj, acc.y);
+            acc.z = fmaf(o4.z, fj, acc.z); acc.w = fmaf(o4.w, fj, acc.w);
         }
-        sh_o[warp][lane] = acc;
-        if (lane == 0) { sh_m[warp] = mw; sh_l[warp] = lw; }
+        // the four lane groups of a warp (fixed order: xor 8, then 16), then the eight warps through shared memory
+#pragma unroll
+        for (int off = 8; off <= 16; off <<= 1) {
+            lw += __shfl_xor_sync(0xffffffffu, lw, off);
+            acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off); acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+            acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+        }
+        if (lane < 8) *reinterpret_cast<float4*>(&sh_o[warp][lane * 4]) = acc;
+        if (lane == 0) sh_l[warp] = lw;
         __syncthreads();
         if (warp == 0) {
-            float M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < kMergeWarps; ++w) M = fmaxf(M, sh_m[w]);
             float L = 0.f, O = 0.f;
 #pragma unroll
             for (int w = 0; w < kMergeWarps; ++w) {
-                const float fw = (sh_m[w] == -INFINITY) ? 0.f : fast_exp2(sh_m[w] - M);
-                L = fmaf(sh_l[w], fw, L);
-                O = fmaf(sh_o[w][lane], fw, O);
+                L += sh_l[w];
+                O += sh_o[w][lane];
             }
             const float inv = L > 0.f ? 1.f / L : 0.f;
             const int64_t oi = (int64_t)s * out_sb + (int64_t)hq * out_sh + slice * 32 + lane;
@@ -661,6 +750,16 @@ int direct_items_per_slot() {
     return v;
 }
 
+// The producer requests 1/parts of the stage ring at a time (IVAB_REFILL_PARTS, experiments; read once).
+int refill_parts() {
+    static int v = [] {
+        const char* e = std::getenv("IVAB_REFILL_PARTS");
+        const int n = e ? std::atoi(e) : kRefillParts;
+        return n < 1 ? 1 : (n > 8 ? 8 : n);
+    }();
+    return v;
+}
+
 // Programmatic dependent launch of the attention and merge kernels; IVAB_PDL=0 turns it off.
 bool use_dependent_launch() {
     static bool v = [] {
@@ -695,6 +794,12 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     stages -= stages % kConsumerWarps;
     if (stages < kConsumerWarps) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for the stage ring");
     p.stages = stages;
+    {
+        int parts = refill_parts();
+        int r = stages / parts;
+        r -= r % kConsumerWarps;
+        p.refill_pages = r < kConsumerWarps ? kConsumerWarps : r;
+    }
     const size_t smem = (size_t)C::OFF_STAGES + 1024 + (size_t)stages * Eng::STAGE_BYTES;
     auto kern = decode_kernel<T, D, G, ENG, TKV>;
     // one flag per (kernel instantiation, device); concurrent host threads may both set the attribute, which is harmless

@@ -35,7 +35,7 @@ from typing import List, Optional
 
 import torch
 
-from .attention import decode_workspace_bytes, paged_decode_attention
+from .attention import decode_workspace_bytes, paged_decode_attention, paged_decode_step
 from .kv_ops import _pool_strides, paged_append
 
 __all__ = ["GraphedDecodeStep"]
@@ -55,7 +55,7 @@ class GraphedDecodeStep:
                  use_graph: bool = True, direct_host_output: bool = True,
                  token_dtype: Optional[torch.dtype] = None, k_scale: float = 1.0, v_scale: float = 1.0,
                  n_buffers: int = 2, out_dtype: Optional[torch.dtype] = None,
-                 stream: Optional[torch.cuda.Stream] = None):
+                 stream: Optional[torch.cuda.Stream] = None, fused: bool = True):
         if not k_pool.is_cuda:
             raise RuntimeError("GraphedDecodeStep needs CUDA tensors; there is no CPU implementation")
         if n_buffers < 1:
@@ -126,6 +126,10 @@ class GraphedDecodeStep:
         self.direct_host_output = direct_host_output
         self.stream = stream if stream is not None else torch.cuda.Stream(device=dev)
         self.use_graph = use_graph
+        # fused: the new token is written inside the attention launch (paged_decode_step), at the position the
+        # block table gives for ctx_len - 1; slot_mapping_host is then not used.  fused=False keeps the separate
+        # append through the slot mapping.
+        self.fused = fused
         self._last = 0
 
     @property
@@ -146,13 +150,16 @@ class GraphedDecodeStep:
         b.stage_dev.copy_(b.stage_host, non_blocking=True)
         q, k_new, v_new, slots, lens = b.devs
         scales = dict(k_scale=self.k_scale, v_scale=self.v_scale) if self.fp8 else {}
-        paged_append(self.k_pool, self.v_pool, slots, k_new, v_new, self.page_size, **scales)
-        if self.direct_host_output:
+        out, lse = (b.out_host, b.lse_host) if self.direct_host_output else (b.out_dev, b.lse_dev)
+        if self.fused:
+            paged_decode_step(q, k_new, v_new, self.k_pool, self.v_pool, self.block_table, lens, self.page_size,
+                              self.scale, out=out, lse=lse, workspace=self._ws, **scales)
+        else:
+            paged_append(self.k_pool, self.v_pool, slots, k_new, v_new, self.page_size, **scales)
             paged_decode_attention(q, self.k_pool, self.v_pool, self.block_table, lens, self.page_size, self.scale,
-                                   out=b.out_host, lse=b.lse_host, workspace=self._ws, **scales)
+                                   out=out, lse=lse, workspace=self._ws, **scales)
+        if self.direct_host_output:
             return
-        paged_decode_attention(q, self.k_pool, self.v_pool, self.block_table, lens, self.page_size, self.scale,
-                               out=b.out_dev, lse=b.lse_dev, workspace=self._ws, **scales)
         b.out_host.copy_(b.out_dev, non_blocking=True)
         if b.lse_dev is not None:
             b.lse_host.copy_(b.lse_dev, non_blocking=True)

@@ -121,23 +121,25 @@ class PagedKVCache:
 
     def _reserve(self, new_lens: Sequence[int]) -> None:
         """Grow block tables so that sequence ``s`` can hold ``new_lens[s]`` tokens."""
-        need_total = 0
-        for s, L in enumerate(new_lens):
-            need = (L + self.page_size - 1) // self.page_size
-            if need > self.max_pages_per_seq:
-                raise PoolExhausted(f"sequence {s} needs {need} pages, block table holds {self.max_pages_per_seq}")
-            need_total += max(0, need - len(self._tables[s]))
-        if need_total > len(self._free):
-            raise PoolExhausted(f"need {need_total} pages, {len(self._free)} free")
-        for s, L in enumerate(new_lens):
-            need = (L + self.page_size - 1) // self.page_size
-            while len(self._tables[s]) < need:
-                page = self._free.pop()
-                self._bt_host[s, len(self._tables[s])] = page
-                self._tables[s].append(page)
-                self._bt_dirty = True
-            self._lens[s] = L
-            self._len_host[s] = L
+        ps, tables = self.page_size, self._tables
+        needs = [(L + ps - 1) // ps for L in new_lens]
+        grow = [(s, n) for s, n in enumerate(needs) if n > len(tables[s])]
+        if grow:                                   # (most decode steps stay inside their last page)
+            for s, n in grow:
+                if n > self.max_pages_per_seq:
+                    raise PoolExhausted(f"sequence {s} needs {n} pages, block table holds {self.max_pages_per_seq}")
+            need_total = sum(n - len(tables[s]) for s, n in grow)
+            if need_total > len(self._free):
+                raise PoolExhausted(f"need {need_total} pages, {len(self._free)} free")
+            for s, n in grow:
+                tab = tables[s]
+                while len(tab) < n:
+                    page = self._free.pop()
+                    self._bt_host[s, len(tab)] = page
+                    tab.append(page)
+            self._bt_dirty = True
+        self._lens = [int(L) for L in new_lens]
+        self._len_host.copy_(torch.tensor(self._lens, dtype=torch.int32))
 
     _RING = 4
 
@@ -199,13 +201,14 @@ class PagedKVCache:
 
     # ---- the hot path -----------------------------------------------------------------------
 
-    def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> List[int]:
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor, write: bool = True) -> List[int]:
         """Append ``S`` tokens to every sequence (layer 0; use ``layer(i).append`` for the others).
         ``k_new`` / ``v_new`` are ``[B,S,H,D]`` (projection output order) or ``[B,H,D]`` for one token.
-        Returns the lengths before the append."""
-        return self._append_layer(0, k_new, v_new)
+        ``write=False`` does the bookkeeping only (pages, lengths, table upload) and leaves the rows to the
+        caller, who hands them to ``paged_decode_step``.  Returns the lengths before the append."""
+        return self._append_layer(0, k_new, v_new, write)
 
-    def _append_layer(self, layer: int, k_new: torch.Tensor, v_new: torch.Tensor) -> List[int]:
+    def _append_layer(self, layer: int, k_new: torch.Tensor, v_new: torch.Tensor, write: bool = True) -> List[int]:
         """One layer's share of a step.  The first layer to arrive reserves pages, computes the slot
         mapping and uploads it with the new lengths; the others reuse it.  The step is complete when
         every layer has appended."""
@@ -217,13 +220,18 @@ class PagedKVCache:
         if self._step is None:
             prior = list(self._lens)
             self._reserve([L + S for L in prior])
-            slot_dev = self._sync_device(self._slots_all(prior, S))
+            # the slot mapping is only needed by a layer that writes through the copy kernel; a step whose
+            # layers all use the fused decode step (write=False) never computes or uploads it
+            slot_dev = self._sync_device(self._slots_all(prior, S) if write else None)
             self._step = {"prior": prior, "slots": slot_dev, "S": S, "done": set()}
         st = self._step
         if S != st["S"] or layer in st["done"]:
             raise RuntimeError(f"layer {layer} appended twice, or with a different token count, within one step")
-        paged_append(self._k_pools[layer], self._v_pools[layer], st["slots"], k_new.reshape(B * S, H, D),
-                     v_new.reshape(B * S, H, D), self.page_size, k_scale=self.k_scale, v_scale=self.v_scale)
+        if write:
+            if st["slots"] is None:
+                st["slots"] = self._slots_all(st["prior"], S).to(self.device)
+            paged_append(self._k_pools[layer], self._v_pools[layer], st["slots"], k_new.reshape(B * S, H, D),
+                         v_new.reshape(B * S, H, D), self.page_size, k_scale=self.k_scale, v_scale=self.v_scale)
         st["done"].add(layer)
         if len(st["done"]) == self.n_layers:
             self._step = None
@@ -386,8 +394,8 @@ class _LayerView:
     def __getattr__(self, name):
         return getattr(self._parent, name)
 
-    def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> List[int]:
-        return self._parent._append_layer(self._index, k_new, v_new)
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor, write: bool = True) -> List[int]:
+        return self._parent._append_layer(self._index, k_new, v_new, write)
 
     @property
     def k(self) -> torch.Tensor:

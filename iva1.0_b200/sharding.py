@@ -90,8 +90,13 @@ class HeadParallelDecoder:
         flat = torch.empty(B * Hl * (D + 1), dtype=torch.float32, device=device)
         return flat, flat[:B * Hl * D].view(B, Hl, D), flat[B * Hl * D:].view(B, Hl)
 
-    def _local(self, q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view, **kw):
-        if self._native:
+    def _local(self, q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view,
+               new_tokens=None, **kw):
+        if self._native and new_tokens is not None:
+            from .attention import paged_decode_step
+            paged_decode_step(q, new_tokens[0], new_tokens[1], k_pool_local, v_pool_local, block_table, ctx_len,
+                              page_size, scale, out=out_view, lse=lse_view, out_dtype=torch.float32, **kw)
+        elif self._native:
             self.attn_fn(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out=out_view,
                          lse=lse_view, out_dtype=torch.float32, **kw)
         else:
@@ -127,9 +132,14 @@ class HeadParallelDecoder:
 
     def capture_local(self, q: torch.Tensor, k_pool_local: torch.Tensor, v_pool_local: torch.Tensor,
                       block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
-                      scale: Optional[float] = None):
+                      scale: Optional[float] = None, before: Optional[Callable[[], None]] = None,
+                      new_tokens: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
         """Record this rank's share of a step -- the attention kernels, which store their fp32 result
         straight into the block the collective sends -- in a CUDA graph, and return ``step()``.
+        ``new_tokens=(k_new, v_new)`` (this rank's KV heads, ``[B, H_kv/world, D]``) makes it the fused decode
+        step: the new token of every sequence is appended by the attention launch itself (``ctx_len`` then
+        includes it).  ``before`` (optional) is called first inside the recording, for anything else the step
+        has to do on this stream.
 
         At 131072 tokens over 8 GPUs each rank reads 67 MB per step (about 10 microseconds of HBM
         time), so the step is bound by launch latency.  ``step()`` replays the graph and then issues
@@ -155,7 +165,10 @@ class HeadParallelDecoder:
             extra["workspace"] = torch.empty(decode_workspace_bytes(B, Hl, n_kv_local, D), dtype=torch.uint8, device=dev)
 
         def local():
-            self._local(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view, **extra)
+            if before is not None:
+                before()
+            self._local(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view,
+                        new_tokens=new_tokens, **extra)
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))

@@ -418,3 +418,59 @@ def test_long_and_short_chunk_lists_merge_in_one_call(dtype, D):
     lens = (d.ctx_len + 1).contiguous()
     out2 = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, lens, 16, wl.scale, out=odd, check=True)
     assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("dtype,Hq,Hkv,D,fp8", [
+    (torch.bfloat16, 8, 8, 128, False), (torch.bfloat16, 32, 8, 128, False), (torch.float16, 16, 2, 64, False),
+    (torch.float32, 4, 2, 64, False), (torch.bfloat16, 32, 2, 128, False),        # 16 query heads per KV head: two head groups
+    (torch.bfloat16, 8, 8, 128, True), (torch.bfloat16, 32, 8, 128, True), (torch.float16, 8, 4, 64, True)])
+@pytest.mark.parametrize("batch", [7, 70])
+def test_fused_step_equals_append_then_attention(dtype, Hq, Hkv, D, fp8, batch):
+    """paged_decode_step (the new token written inside the attention launch) against paged_append followed by
+    paged_decode_attention: the pools and the results must agree bit for bit.  New tokens that open a page,
+    close one, sit in the middle; sequences cut into several chunks; an empty sequence; batches below and
+    above the size that goes through the plan kernel."""
+    g = torch.Generator().manual_seed(batch + Hq)
+    base = torch.tensor([0, 15, 16, 31, 100, 2500, 7000])
+    ctx = base if batch == 7 else torch.cat([base, torch.randint(0, 600, (batch - 7,), generator=g)])
+    wl = workloads.make_decode_workload("fused", ctx, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, dtype=dtype,
+                                        seed=batch + D, free_frac=0.1)
+    d = wl.to(DEV)
+    kw = {}
+    if fp8:
+        kw = dict(k_scale=0.02, v_scale=0.03)
+        d.k_pool = ref.quantize_fp8_ref(wl.k_pool, 0.02).to(DEV)
+        d.v_pool = ref.quantize_fp8_ref(wl.v_pool, 0.03).to(DEV)
+    lens = (d.ctx_len + 1).contiguous()
+    k2, v2 = d.k_pool.clone(), d.v_pool.clone()
+    iva_b200.paged_append(k2, v2, d.slot_mapping, d.k_new, d.v_new, 16, check=True, **kw)
+    want, want_lse = iva_b200.paged_decode_attention(d.q, k2, v2, d.block_table, lens, 16, wl.scale, return_lse=True,
+                                                     check=True, **kw)
+    got, got_lse = iva_b200.paged_decode_step(d.q, d.k_new, d.v_new, d.k_pool, d.v_pool, d.block_table, lens, 16, wl.scale,
+                                              return_lse=True, check=True, **kw)
+    raw = (lambda t: t.view(torch.uint8)) if fp8 else (lambda t: t)
+    assert torch.equal(raw(d.k_pool), raw(k2)) and torch.equal(raw(d.v_pool), raw(v2)), "the fused append differs"
+    assert torch.equal(got, want) and torch.equal(got_lse, want_lse)
+    if not fp8:                                             # and both are right: the checker on a few sequences
+        _, _, out_ref, lse_ref = ref.decode_step_ref(wl, seqs=[0, 1, 2, 5])
+        assert_attn_close(got[[0, 1, 2, 5]], out_ref[[0, 1, 2, 5]], dtype, strict=False)
+        assert_lse_close(got_lse[[0, 1, 2, 5]], lse_ref[[0, 1, 2, 5]])
+
+
+def test_fused_step_leaves_an_empty_sequence_alone_and_flags_a_bad_page():
+    """ctx_len 0 appends nothing; a block-table entry out of range for the new token's page is flagged and
+    nothing is written outside the pool."""
+    wl = workloads.make_decode_workload("fz", torch.tensor([20, 0, 33]), n_q_heads=4, n_kv_heads=2, head_dim=128, seed=3)
+    d = wl.to(DEV)
+    lens = torch.tensor([21, 0, 34], dtype=torch.int32, device=DEV)
+    before = d.k_pool.clone()
+    out, lse = iva_b200.paged_decode_step(d.q, d.k_new, d.v_new, d.k_pool, d.v_pool, d.block_table, lens, 16,
+                                          return_lse=True, check=True)
+    changed = (d.k_pool != before).any(-1)[0]               # [H, slots]
+    assert int(changed.any(0).sum()) == 2                   # exactly the two new tokens' slots
+    assert not out[1].any() and torch.isinf(lse[1]).all()
+    bt = d.block_table.clone()
+    bt[0, 1] = 1 << 20
+    ws = torch.empty(decode_workspace_bytes(3, 4, 2, 128), dtype=torch.uint8, device=DEV)
+    iva_b200.paged_decode_step(d.q, d.k_new, d.v_new, d.k_pool, d.v_pool, bt, lens, 16, workspace=ws)
+    assert decode_status(ws) & 2
