@@ -194,6 +194,11 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     __shared__ long long s_total_pages;
     __shared__ int s_bad;
     __shared__ int s_pages[kSortMax];
+    // Batches of up to kSortMax sequences keep the processing order and the chunk prefix in shared memory:
+    // the chunk list is built by a binary search over the prefix per chunk, which through global memory
+    // costs a dependent L2 round trip per step (seven for 128 sequences).
+    __shared__ int s_order[kSortMax];
+    __shared__ int s_prefix[kSortMax + 1];
     __shared__ int s_ragged, s_split, s_big;
     const int tid = threadIdx.x;
     // the attention kernel may be scheduled now: its set-up does not depend on the plan, and it
@@ -226,7 +231,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         if (L_raw < 0 || (long long)L_raw > (long long)max_pages * page_size) s_bad = 1;
         if (ctx_begin != nullptr && (ctx_begin[s] < 0 || ctx_begin[s] > L_raw)) s_bad = 1;
         int L, b, sp;
-        local += seq_range(s, &L, &b, &sp);
+        const int pg = seq_range(s, &L, &b, &sp);
+        if (B <= kSortMax) s_pages[s] = pg;
+        local += pg;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
@@ -246,27 +253,22 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     };
     const bool sorted = B <= kSortMax;
     if (sorted) {
-        for (int s = tid; s < B; s += kPlanThreads) {
-            const int pg = clamped_pages(s);
-            s_pages[s] = pg;
-            if (pg != clamped_pages(0)) s_ragged = 1;
-        }
+        for (int s = tid; s < B; s += kPlanThreads)
+            if (s_pages[s] != s_pages[0]) s_ragged = 1;
         __syncthreads();
         const bool ragged = s_ragged != 0;   // a uniform batch needs no ordering
         for (int s = tid; s < B; s += kPlanThreads) {
-            if (!ragged) { ws.order[s] = s; continue; }
+            if (!ragged) { s_order[s] = s; continue; }
             const int mine = s_pages[s];
             int rank = 0;
             for (int t = 0; t < B; ++t) {
                 const int other = s_pages[t];
                 rank += (other > mine) || (other == mine && t < s);
             }
-            ws.order[rank] = s;
+            s_order[rank] = s;
         }
-    } else {
-        for (int s = tid; s < B; s += kPlanThreads) ws.order[s] = s;
     }
-    __syncthreads();   // order[] written by this block is visible to this block
+    __syncthreads();   // (larger batches keep their natural order: position = sequence)
 
     // chunks per position and their exclusive prefix
     int running = 0;
@@ -274,7 +276,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         const int pos = base + tid;
         int n = 0, s = 0;
         if (pos < B) {
-            s = ws.order[pos];
+            s = sorted ? s_order[pos] : pos;
             const int pages = sorted ? s_pages[s] : clamped_pages(s);
             n = (pages + chunk_pages - 1) / chunk_pages;
             if (n < 1) n = 1;   // an empty sequence still gets one (empty) item, which writes zeros / -inf
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         int tile_total;
         const int incl = block_inclusive_scan(n, warp_sums, &tile_total);
         if (pos < B) {
-            ws.pos_prefix[pos] = running + incl - n;
+            if (sorted) s_prefix[pos] = running + incl - n; else ws.pos_prefix[pos] = running + incl - n;
             ws.seq_first[s] = running + incl - n;
             ws.seq_count[s] = n;
             // order within either end of the list is irrelevant: every entry is merged on its own
@@ -295,7 +297,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     int overflow = 0;
     if (num_chunks > cap) { overflow = 1; num_chunks = 0; }   // cannot happen when cap = B + target_chunks
     if (tid == 0) {
-        ws.pos_prefix[B] = running;
+        if (sorted) s_prefix[B] = running; else ws.pos_prefix[B] = running;
         ws.header[kHdrNumChunks] = num_chunks;
         ws.header[kHdrChunkPages] = chunk_pages;
         ws.header[kHdrCounter] = 0;
@@ -314,11 +316,11 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
         int lo = 0, hi = B - 1;   // largest position with pos_prefix[pos] <= ci
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if (ws.pos_prefix[mid] <= ci) lo = mid; else hi = mid - 1;
+            if ((sorted ? s_prefix[mid] : ws.pos_prefix[mid]) <= ci) lo = mid; else hi = mid - 1;
         }
-        const int s = ws.order[lo];
-        const int first = ws.pos_prefix[lo];
-        const int n = ws.pos_prefix[lo + 1] - first;
+        const int s = sorted ? s_order[lo] : lo;
+        const int first = sorted ? s_prefix[lo] : ws.pos_prefix[lo];
+        const int n = (sorted ? s_prefix[lo + 1] : ws.pos_prefix[lo + 1]) - first;
         const int j = ci - first;
         int L, begin, sink_pages;
         const int pages = seq_range(s, &L, &begin, &sink_pages);

@@ -19,7 +19,6 @@ constexpr int kMaxStages = 32;
 static_assert(kMaxStages % kConsumerWarps == 0, "stage ring must divide among the consumer warps");
 constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
 constexpr int kMinChunkPages = 8;
-constexpr int kRefillParts = 1;       // the producer requests 1/kRefillParts of the stage ring at a time
 constexpr int kDefaultItemOrder = 2;  // 0: kv-head-major, 1: chunk-major, 2: chunk-major for ragged batches only (see split_id)
 // Plan-free ("direct") mode, for batches small enough that one warp holds a sequence per lane:
 constexpr int kDirectMaxBatch = 32;
@@ -99,7 +98,6 @@ struct DecodeParams {
     float v_scale;             // 8-bit KV storage: V = v_scale * stored value (1 otherwise); K's scale is folded into scale_log2
     float scale_log2;          // scale * log2(e): scores are kept in base-2 units
     int stages;
-    int refill_pages;        // pages the producer requests at a time (see the producer warp)
     uint64_t wait_limit_ns;
     Workspace ws;
     // Plan-free mode (direct != 0): there is no plan kernel; every CTA derives the chunking from ctx_len

@@ -1,7 +1,7 @@
 // Page engines of the decode-attention kernel: what a consumer warp does with one staged page of K
 // and V (16 tokens), plus the shared-memory layout of the kernel.  An engine provides
-//   setup(lane), begin_item(params, seq, kv head, lane), page(params, stage, n_valid, hole_lo, hole_hi,
-//   lane, scratch), publish(params, ml, o, lane)
+//   setup(lane), attach(scratch, lane), begin_item(params, seq, kv head, lane), page(params, stage, n_valid,
+//   hole_lo, hole_hi, lane, scratch), publish(params, ml, o, lane)
 // and the constants kTiled, STAGE_BYTES, PAGE_BYTES, SCRATCH_PER_WARP, CTAS_PER_SM (tiled engines also
 // TILES, TILE_COLS, TILE_BYTES).  Included by decode_attn.cu only (internal linkage).
 #pragma once
@@ -114,6 +114,7 @@ struct SimtEngine {
     int r, c, own_tok;
     bool owner;
 
+    __device__ __forceinline__ void attach(unsigned char*, int) {}
     __device__ __forceinline__ void setup(int lane) {
         r = lane / C::LPR;             // which of the RPI rows of a warp-wide load this lane reads
         c = lane % C::LPR;             // which 16-byte vector of the row
@@ -254,13 +255,24 @@ struct MmaCore {
     static constexpr int KSTEPS = D / 16;              // k-steps of Q K^T
     static constexpr int NBLK = D / 8;                 // 8-wide output blocks of P^T V
 
-    uint32_t qa[KSTEPS][2];    // A fragments of Q: head lane/4; rows 8..15 of the tile are zero
+    // With head_dim 256 the accumulators alone take 128 registers; keeping the 32 registers of Q fragments as
+    // well spills (the register file allows 168 per thread at two CTAs of five warps per SM).  There the
+    // fragments live in this warp's scratch instead -- rows of D*2 + 16 bytes, so that the eight heads' rows
+    // start four banks apart and a fragment load is conflict-free -- and are re-read for every k-step.
+    static constexpr bool kQSmem = D >= 256;
+    static constexpr int Q_ROW_WORDS = D / 2 + 4;
+    static constexpr int Q_SCRATCH = kQSmem ? 8 * Q_ROW_WORDS * 4 : 0;
+    uint32_t qa[kQSmem ? 1 : KSTEPS][2];    // A fragments of Q: head lane/4; rows 8..15 of the tile are zero
+    uint32_t* qsm;             // kQSmem: this lane's first fragment word in the warp's scratch
     // Accumulators of P^T V for head lane/4, dims 8j + 2*(lane%4) + {0,1}: [0],[1] collect the 16-bit
     // weights (rows 0..7 of the A tile), [2],[3] the 16-bit corrections (rows 8..15); their sum is O.
     float o[NBLK][4];
     float m_run, l_run;        // running max (raw score units) and this lane's share of the sum
 
     __device__ __forceinline__ void setup(int) {}
+    __device__ __forceinline__ void attach(unsigned char* scratch, int lane) {
+        qsm = reinterpret_cast<uint32_t*>(scratch) + (lane >> 2) * Q_ROW_WORDS + (lane & 3);
+    }
 
     // two consecutive q elements as one register of tile type (bf16 -> fp16 saturates at the fp16 range)
     __device__ __forceinline__ static uint32_t load_q_pair(const TQ* ptr) {
@@ -275,7 +287,16 @@ struct MmaCore {
 
     __device__ __forceinline__ void begin_item(const DecodeParams& p, int seq, int h, int lane) {
         const int g = lane >> 2, c = lane & 3;
-        if (g < p.group) {
+        if constexpr (kQSmem) {
+            __syncwarp();   // every lane is done with the previous item's fragments
+            const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * p.group + g) * p.q_sh;
+#pragma unroll
+            for (int s = 0; s < KSTEPS; ++s) {
+                qsm[8 * s] = g < p.group ? load_q_pair(qrow + 16 * s + 2 * c) : 0u;
+                qsm[8 * s + 4] = g < p.group ? load_q_pair(qrow + 16 * s + 2 * c + 8) : 0u;
+            }
+            __syncwarp();
+        } else if (g < p.group) {
             const TQ* qrow = static_cast<const TQ*>(p.q) + (int64_t)seq * p.q_sb + (int64_t)(h * p.group + g) * p.q_sh;
 #pragma unroll
             for (int s = 0; s < KSTEPS; ++s) {
@@ -316,8 +337,13 @@ struct MmaCore {
             for (int sp = 0; sp < KSTEPS / 2; ++sp) {
                 uint32_t b[4];
                 ldmatrix_x4(kbase + chunk_off(token, 4 * sp + mi), b);     // k-steps 2sp (b0,b1) and 2sp+1 (b2,b3)
-                mma_m16n8k16_top<T>(se, qa[2 * sp][0], qa[2 * sp][1], b[0], b[1]);
-                mma_m16n8k16_top<T>(so, qa[2 * sp + 1][0], qa[2 * sp + 1][1], b[2], b[3]);
+                if constexpr (kQSmem) {
+                    mma_m16n8k16_top<T>(se, qsm[16 * sp], qsm[16 * sp + 4], b[0], b[1]);
+                    mma_m16n8k16_top<T>(so, qsm[16 * sp + 8], qsm[16 * sp + 12], b[2], b[3]);
+                } else {
+                    mma_m16n8k16_top<T>(se, qa[2 * sp][0], qa[2 * sp][1], b[0], b[1]);
+                    mma_m16n8k16_top<T>(so, qa[2 * sp + 1][0], qa[2 * sp + 1][1], b[2], b[3]);
+                }
             }
             s[nb][0] = se[0] + so[0];
             s[nb][1] = se[1] + so[1];
@@ -390,8 +416,12 @@ template <typename T, int D, int G>
 struct MmaEngine : MmaCore<T, T, D, G> {
     using Core = MmaCore<T, T, D, G>;
     static constexpr bool kTiled = true;
-    static constexpr int SCRATCH_PER_WARP = 0;
+    static constexpr int SCRATCH_PER_WARP = Core::Q_SCRATCH;   // the Q fragments, for head_dim 256 only
+#ifdef IVAB_D256_ONE_CTA
+    static constexpr int CTAS_PER_SM = D >= 256 ? 1 : 2;
+#else
     static constexpr int CTAS_PER_SM = 2;
+#endif
     using Core::TILES; using Core::TILE_BYTES; using Core::PAGE_BYTES;
 
     __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int hole_lo,
@@ -502,6 +532,7 @@ struct MmaFp8RegEngine {
     float m_run, l_run;
 
     __device__ __forceinline__ void setup(int) {}
+    __device__ __forceinline__ void attach(unsigned char*, int) {}
 
     __device__ __forceinline__ static uint32_t to_half2(uint32_t raw) {
         if constexpr (std::is_same<TQ, __half>::value) {

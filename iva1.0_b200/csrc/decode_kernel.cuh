@@ -26,22 +26,58 @@ namespace {
 // Fused decode step: one warp writes the newest token's K and V rows of one KV head into their slot of the
 // pool (T: type of the new tokens = type of q; TKV: storage type of the pool).  The rows are copied verbatim,
 // or -- 8-bit pools -- quantised exactly as the stand-alone append does (fp8(x * inv_scale), saturating).
+// The loads (the block-table entry of the token's page and the two source rows, one 16-byte vector per lane
+// and register) are issued one work item ahead; the stores follow when the item starts.
+template <typename T, int D>
+struct NewestRow {
+    static constexpr int kVecs = D * (int)sizeof(T) / 16;      // 16-byte vectors per source row
+    static constexpr int kRegs = (2 * kVecs + 31) / 32;
+    uint4 v[kRegs];
+    int pid;
+    bool on;
+};
+
+template <typename T, int D>
+__device__ __forceinline__ NewestRow<T, D> load_newest_row(const DecodeParams& p, const ChunkDesc& d, int slab, bool valid, int lane) {
+    using R = NewestRow<T, D>;
+    R r{};
+    r.on = valid && p.k_new != nullptr && d.chunk_idx == d.n_chunks - 1 && d.pad0 > 0;
+    if (!r.on) return r;
+    r.pid = __ldg(p.block_table + (int64_t)d.seq * p.bt_stride + (d.pad0 - 1) / kPage);
+    const int64_t row = (int64_t)d.seq * p.new_st_bytes + (int64_t)slab * p.new_sh_bytes;
+#pragma unroll
+    for (int k = 0; k < R::kRegs; ++k) {
+        const int v = lane + 32 * k;
+        if (v < 2 * R::kVecs)
+            r.v[k] = __ldg(reinterpret_cast<const uint4*>((v >= R::kVecs ? p.v_new : p.k_new) + row) + (v >= R::kVecs ? v - R::kVecs : v));
+    }
+    return r;
+}
+
 template <typename T, typename TKV, int D>
-__device__ __forceinline__ void append_newest_row(const DecodeParams& p, int seq, int slab, char* krow, char* vrow, int lane) {
-    constexpr int kVecs = D * (int)sizeof(T) / 16;      // 16-byte vectors per source row
-    const char* ks = p.k_new + (int64_t)seq * p.new_st_bytes + (int64_t)slab * p.new_sh_bytes;
-    const char* vs = p.v_new + (int64_t)seq * p.new_st_bytes + (int64_t)slab * p.new_sh_bytes;
-    for (int v = lane; v < 2 * kVecs; v += 32) {
-        const bool is_v = v >= kVecs;
-        const int i = is_v ? v - kVecs : v;
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(is_v ? vs : ks) + i);
-        char* dst = is_v ? vrow : krow;
+__device__ __forceinline__ void store_newest_row(const DecodeParams& p, const NewestRow<T, D>& r, const ChunkDesc& d, int slab,
+                                                 int* cta_status, int lane) {
+    using R = NewestRow<T, D>;
+    if (r.pid < 0 || r.pid >= p.num_pages) {
+        if (lane == 0) atomicOr(cta_status, kStatusBadPage);    // skipped, never written out of range
+        return;
+    }
+    const int pos = d.pad0 - 1;
+    const int64_t off = (int64_t)slab * p.pool_sh_bytes + (int64_t)r.pid * p.pool_sp_bytes +
+                        (int64_t)(pos % kPage) * (D * (int)sizeof(TKV));
+#pragma unroll
+    for (int k = 0; k < R::kRegs; ++k) {
+        const int v = lane + 32 * k;
+        if (v >= 2 * R::kVecs) continue;
+        const bool is_v = v >= R::kVecs;
+        const int i = is_v ? v - R::kVecs : v;
+        char* dst = const_cast<char*>(is_v ? p.v_pool : p.k_pool) + off;
         if constexpr (std::is_same<T, TKV>::value) {
-            *reinterpret_cast<uint4*>(dst + i * 16) = u;
+            *reinterpret_cast<uint4*>(dst + i * 16) = r.v[k];
         } else {
             static_assert(sizeof(T) == 2 && sizeof(TKV) == 1, "quantising append: 16-bit tokens into 8-bit pools");
             float f[8];
-            Elt<T>::unpack(u, f);
+            Elt<T>::unpack(r.v[k], f);
             const float is = is_v ? p.v_inv_scale : p.k_inv_scale;
             uint2 q;
             q.x = (uint32_t)pack_fp8x2(f[0] * is, f[1] * is) | ((uint32_t)pack_fp8x2(f[2] * is, f[3] * is) << 16);
@@ -136,11 +172,6 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
 #pragma unroll
         for (int i = 0; i < kConsumerWarps; ++i) cnt[i] = 0;
         const int spw = stages / kConsumerWarps;   // stages per warp
-        // Pages are requested `refill` at a time (a fraction of the ring, a multiple of the consumer-warp
-        // count).  The lanes of a request leave their stage waits together, so a request for the whole
-        // ring would only go out once the ring has drained completely -- one full memory latency without
-        // data per round, which a compute-bound engine (8-bit pools) cannot hide behind other CTAs.
-        const int refill = p.refill_pages;
         int published = 0;  // items published so far
         bool aborted = false;
         // The fetch of an item is three dependent global accesses (work counter -> chunk descriptor ->
@@ -218,6 +249,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         ChunkDesc d0 = load_desc(id0, &h0);
         ChunkDesc d1 = load_desc(id1, &h1);
         int bt0 = id0 < total_items ? load_pages(d0, 0) : 0;
+        NewestRow<T, D> nr0 = load_newest_row<T, D>(p, d0, h0 / p.kv_div, id0 < total_items, lane);
         for (;;) {
             const int item = id0, h = h0;
             const ChunkDesc d = d0;
@@ -225,8 +257,12 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             // prefetch for the following items (ids past the end of the list load nothing)
             int bt1 = 0, h2 = 0, id3_raw = 0;
             ChunkDesc d2{};
+            NewestRow<T, D> nr1{};
             if (!done) {
-                if (id1 < total_items) bt1 = load_pages(d1, 0);
+                if (id1 < total_items) {
+                    bt1 = load_pages(d1, 0);
+                    nr1 = load_newest_row<T, D>(p, d1, h1 / p.kv_div, true, lane);
+                }
                 d2 = load_desc(id2, &h2);
                 id3_raw = fetch_id_async();
             }
@@ -253,23 +289,15 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             const char* kbase = p.k_pool + (int64_t)slab * p.pool_sh_bytes;
             const char* vbase = p.v_pool + (int64_t)slab * p.pool_sh_bytes;
             // Fused decode step: the item that ends a sequence reads the page of its newest token, so this
-            // warp first writes that token's rows (position L - 1) of this KV head into the page, then
-            // orders the stores before its own TMA reads.  No other CTA reads that page -- except, with more
-            // than 8 query heads per KV head, the items of the sibling head groups, which write the same
-            // bytes themselves before they read.
-            if (p.k_new != nullptr && d.chunk_idx == d.n_chunks - 1 && d.pad0 > 0) {
-                const int pos = d.pad0 - 1;
-                const int pid = __ldg(p.block_table + (int64_t)d.seq * p.bt_stride + pos / kPage);
-                if (pid < 0 || pid >= p.num_pages) {
-                    if (lane == 0) atomicOr(cta_status, kStatusBadPage);    // skipped, never written out of range
-                } else {
-                    const int64_t off = (int64_t)slab * p.pool_sh_bytes + (int64_t)pid * p.pool_sp_bytes +
-                                        (int64_t)(pos % kPage) * (D * (int)sizeof(TKV));
-                    append_newest_row<T, TKV, D>(p, d.seq, slab, const_cast<char*>(p.k_pool) + off,
-                                                 const_cast<char*>(p.v_pool) + off, lane);
-                }
-                fence_proxy_async_all();
-                __syncwarp();
+            // warp first writes that token's rows (position L - 1) of this KV head into the page -- from
+            // registers, the loads went out one item ago -- and orders the stores before its own TMA reads
+            // when it gets to the item's last request, which is the one that contains that page.  No other
+            // CTA reads that page -- except, with more than 8 query heads per KV head, the items of the sibling
+            // head groups, which write the same bytes themselves before they read.
+            bool need_fence = false;
+            if (nr0.on) {
+                store_newest_row<T, TKV, D>(p, nr0, d, slab, cta_status, lane);
+                need_fence = true;
             }
             const int start = (d.seq + d.chunk_idx) % kConsumerWarps;
             int bt_next = bt0;
@@ -282,8 +310,13 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                 // its own stage and issues its own copies, so the issue cost of up to `stages` pages
                 // overlaps.  A sub-batch never exceeds the ring (spw pages per consumer warp): a lane
                 // must not wait two phases ahead of a stage's barrier.
-                for (int q0 = 0; q0 < in_batch && !aborted; q0 += refill) {
-                    const int nb = min(refill, in_batch - q0);
+                for (int q0 = 0; q0 < in_batch && !aborted; q0 += stages) {
+                    const int nb = min(stages, in_batch - q0);
+                    if (need_fence && p0 + q0 + nb >= d.n_pages) {   // the request that reads the newest token's page
+                        fence_proxy_async_all();
+                        __syncwarp();
+                        need_fence = false;
+                    }
                     int pid = __shfl_sync(0xffffffffu, mine, (q0 + lane) & 31);
                     if (lane < nb && (pid < 0 || pid >= p.num_pages)) {
                         atomicOr(cta_status, kStatusBadPage);   // flagged, and page 0 is read instead of faulting
@@ -332,7 +365,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             }
             PROF_MARK(4)   // TMA issue
             if (aborted) break;
-            id0 = id1; h0 = h1; d0 = d1; bt0 = bt1;
+            id0 = id1; h0 = h1; d0 = d1; bt0 = bt1; nr0 = nr1;
             id1 = id2; h1 = h2; d1 = d2;
             id2 = __shfl_sync(0xffffffffu, id3_raw, 0);
         }
@@ -360,6 +393,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
     T* outg = static_cast<T*>(p.out);
     Eng eng;
     eng.setup(lane);
+    eng.attach(scratch, lane);
 
     const int spw = stages / kConsumerWarps;   // stages of this warp's sub-ring
     int taken = 0;      // pages this warp has consumed so far (position in its sub-ring)
@@ -369,15 +403,15 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         const int slot = consumed % kItemRing;
         if (!mbar_wait_bounded(bar_item_full(slot), (consumed / kItemRing) & 1, abort_flag, limit)) break;
         PROF_MARK(0)   // wait for the next item
+        // The slot stays with this warp until the end of the item: what only the epilogue needs (sequence,
+        // head, chunk count, where the partial goes) is read again there instead of living in registers
+        // through the page loop.
         volatile int* it = items + slot * kItWords;
-        const int seq = it[kItSeq], h = it[kItHead], n_pages = it[kItPages], page_begin = it[kItPageBegin];
-        const int n_chunks = it[kItChunks], item = it[kItIndex], start = it[kItStart], L = it[kItLen];
+        const int n_pages = it[kItPages], page_begin = it[kItPageBegin], start = it[kItStart], L = it[kItLen];
         const int begin = it[kItBegin], sink_pages = it[kItSinkPages];
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_item_empty(slot));
         if (n_pages < 0) break;   // sentinel: the work list is exhausted
 
-        eng.begin_item(p, seq, h, lane);   // query heads of this kv head into registers, state reset
+        eng.begin_item(p, it[kItSeq], it[kItHead], lane);   // query heads of this kv head into registers, state reset
         PROF_MARK(1)   // q load issue
 
         bool ok = true;
@@ -410,6 +444,9 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         // its state only after the previous item's combine has finished.
         if (consumed > 0 && !mbar_wait_bounded(bar_combined, (consumed - 1) & 1, abort_flag, limit)) break;
         PROF_MARK(4)   // wait for the previous combine
+        const int seq = it[kItSeq], h = it[kItHead], n_chunks = it[kItChunks], item = it[kItIndex];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_item_empty(slot));
         eng.publish(p, mrg_ml + (warp * G) * 2, mrg_o + (size_t)(warp * G) * D, lane);
         __threadfence_block();
         __syncwarp();
@@ -750,16 +787,6 @@ int direct_items_per_slot() {
     return v;
 }
 
-// The producer requests 1/parts of the stage ring at a time (IVAB_REFILL_PARTS, experiments; read once).
-int refill_parts() {
-    static int v = [] {
-        const char* e = std::getenv("IVAB_REFILL_PARTS");
-        const int n = e ? std::atoi(e) : kRefillParts;
-        return n < 1 ? 1 : (n > 8 ? 8 : n);
-    }();
-    return v;
-}
-
 // Programmatic dependent launch of the attention and merge kernels; IVAB_PDL=0 turns it off.
 bool use_dependent_launch() {
     static bool v = [] {
@@ -794,12 +821,6 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     stages -= stages % kConsumerWarps;
     if (stages < kConsumerWarps) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: not enough shared memory for the stage ring");
     p.stages = stages;
-    {
-        int parts = refill_parts();
-        int r = stages / parts;
-        r -= r % kConsumerWarps;
-        p.refill_pages = r < kConsumerWarps ? kConsumerWarps : r;
-    }
     const size_t smem = (size_t)C::OFF_STAGES + 1024 + (size_t)stages * Eng::STAGE_BYTES;
     auto kern = decode_kernel<T, D, G, ENG, TKV>;
     // one flag per (kernel instantiation, device); concurrent host threads may both set the attribute, which is harmless
@@ -844,7 +865,8 @@ template <typename T, int D, int G>
 int choose_engine(const DecodeParams& p, int B, int Hkv, cudaStream_t st) {
     TensorMaps tm{};
     if constexpr (sizeof(T) == 2 && D % 64 == 0) {
-        if (G >= tc_min_group(2) && p.scale_log2 > 0.f &&
+        // head_dim 256 with two query heads per KV head is faster on the CUDA-core engine (6.1 against 5.8 TB/s)
+        if (G >= tc_min_group(D >= 256 ? 3 : 2) && p.scale_log2 > 0.f &&
             encode_pool_map(&tm.k, p.k_pool, map_type<T>(), 2, D, p.num_pages, Hkv, p.pool_sp_bytes, p.pool_sh_bytes) &&
             encode_pool_map(&tm.v, p.v_pool, map_type<T>(), 2, D, p.num_pages, Hkv, p.pool_sp_bytes, p.pool_sh_bytes))
             return launch_decode<T, D, G, kEngMma>(p, tm, B, st);
