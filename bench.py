@@ -268,6 +268,8 @@ class Ranks:
         self.dist = None
         if self.world > 1:
             import torch.distributed as dist
+            # whatever NCCL logs (its version banner, for one) goes to stderr: stdout carries the one JSON line
+            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
             dist.init_process_group("nccl", device_id=dev)
             self.dist = dist
 
@@ -570,19 +572,17 @@ def measure_c4(wl, ranks, steps, warmup):
 
 # ---- c5b: head-parallel decode of one long sequence ---------------------------------------------------------
 
-def measure_c5b(wl, ranks, steps, warmup, use_graph=True):
+def measure_c5b(wl, ranks, steps, warmup, use_graph=True, exchange="nccl"):
     from iva_b200.sharding import HeadParallelDecoder
     dev = ranks.dev
     world = ranks.world
     lens = (wl.ctx_len + 1).contiguous()
     nbytes = attention_bytes(wl, lens) // world
     if world > 1:
-        hp = HeadParallelDecoder(wl.n_q_heads, wl.n_kv_heads)
+        hp = HeadParallelDecoder(wl.n_q_heads, wl.n_kv_heads, exchange=exchange)
         k_loc, v_loc = hp.local_pools(wl.k_pool, wl.v_pool)
         k_loc, v_loc = k_loc.contiguous(), v_loc.contiguous()          # each rank keeps only its slab
         k_new, v_new = wl.k_new[:, hp.kv_slice].contiguous(), wl.v_new[:, hp.kv_slice].contiguous()
-        wl.k_pool = wl.v_pool = None
-        torch.cuda.empty_cache()
     else:
         hp = None
         k_loc, v_loc, k_new, v_new = wl.k_pool, wl.v_pool, wl.k_new, wl.v_new
@@ -640,8 +640,11 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True):
     return {"ms_per_step": ms_per_step, "attention_incl_allgather_ms": attn, "attention_kernels_ms": kern,
             "value": 1.0 / (ms_per_step * 1e-3), "unit": "decode tok/s (one sequence)",
             "roofline_local_kernels": roofline_record(nbytes, kern, "this rank's plan + decode + merge kernels"),
-            "kv_heads_per_rank": wl.n_kv_heads // world, "collective": None if world == 1 else
-            "one NCCL all_gather_into_tensor of [1, H_q/N, D+1] fp32 per step (eager; local kernels in a CUDA graph)",
+            "kv_heads_per_rank": wl.n_kv_heads // world, "collective": None if world == 1 else (
+                "one NCCL all_gather_into_tensor of [1, H_q/N, D+1] fp32 per step (eager; local kernels in a CUDA graph)"
+                if exchange == "nccl" else
+                "ivab_peer_allgather: this library's kernel over peer-mapped memory (NVLink stores + arrival counters), "
+                "recorded in the same CUDA graph as the local kernels: one graph replay per step, no NCCL call"),
             "l2": "flushed between timed steps"}
 
 
@@ -741,6 +744,14 @@ def run_gpu(args):
         free_gpu()
         wl = build_workload("c5b", dev, rank, world, args)
         result["c5b"] = measure_c5b(wl, ranks, sub_steps, args.warmup, use_graph=not args.no_graph)
+        if world > 1:
+            # the same step with the outputs reassembled by the library's own kernel over peer memory
+            try:
+                p2p = measure_c5b(wl, ranks, sub_steps, args.warmup, use_graph=not args.no_graph, exchange="p2p")
+                result["c5b"]["peer_memory_exchange"] = {k: p2p[k] for k in ("ms_per_step", "attention_incl_allgather_ms",
+                                                                                 "value", "collective")}
+            except Exception as e:                      # (symmetric memory not available on this system)
+                result["c5b"]["peer_memory_exchange"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         del wl
         free_gpu()
 

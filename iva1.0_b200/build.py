@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libivab.so")
-SOURCES = ["abi.cu", "kv_copy.cu", "decode_attn.cu", "decode_inst_f32.cu", "decode_inst_f16.cu", "decode_inst_bf16.cu",
+SOURCES = ["abi.cu", "kv_copy.cu", "peer_exchange.cu", "decode_attn.cu", "decode_inst_f32.cu", "decode_inst_f16.cu", "decode_inst_bf16.cu",
            "decode_inst_fp8_f16.cu", "decode_inst_fp8_bf16.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

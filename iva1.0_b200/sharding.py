@@ -21,7 +21,7 @@ from typing import Callable, List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_requests", "balance_by_pages", "head_slice", "HeadParallelDecoder"]
+__all__ = ["shard_requests", "balance_by_pages", "head_slice", "HeadParallelDecoder", "PeerExchange"]
 
 
 def shard_requests(n_seq: int, world: int, rank: int) -> range:
@@ -58,6 +58,79 @@ def head_slice(n_q_heads: int, n_kv_heads: int, world: int, rank: int) -> Tuple[
     return slice(rank * per * group, (rank + 1) * per * group), slice(rank * per, (rank + 1) * per)
 
 
+class PeerExchange:
+    """All-gather of one small fp32 block per rank through peer-mapped memory: this library's own kernel
+    (``ivab_peer_allgather``: plain NVLink stores, one arrival counter per source rank, a bounded wait)
+    instead of an NCCL collective.  ``torch.distributed``'s symmetric memory allocates the buffer and maps it
+    into every peer -- plumbing; the data path is the kernel.  All ranks must construct it together and make
+    the same sequence of ``gather`` calls.
+
+    ``gather(block)`` enqueues the exchange on the current stream and returns ``[world, block.numel()]``
+    (a view of this rank's buffer, valid until the call after next); it can be recorded in a CUDA graph.
+    """
+
+    SLOTS = 2
+
+    def __init__(self, numel: int, group: Optional[dist.ProcessGroup] = None, device=None, wait_limit_ns: int = 2_000_000_000):
+        import ctypes
+        import os
+
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        # only plain peer loads and stores are used here: no multicast binding is needed, and none is wanted
+        # (a rank that dies while its memory is bound to a multicast object disturbs its peers' GPUs)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.numel = int(numel)
+        self.block_bytes = (self.numel * 4 + 15) // 16 * 16
+        self.flags_off = self.SLOTS * self.world * self.block_bytes
+        total_words = (self.flags_off + 256) // 4
+        self.buf = symm.empty(total_words, dtype=torch.float32, device=self.device)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm.rendezvous(self.buf, self.group)
+        dist.barrier(self.group)                       # every rank's counters are zero before anyone signals
+        torch.cuda.synchronize(self.device)
+        # the address of every rank's copy of THIS tensor in this process's address space (the tensor may sit at
+        # an offset inside a larger symmetric allocation, so the allocation's base pointers are not enough)
+        self._remote = [self.handle.get_remote_tensor(r, tuple(self.buf.shape), self.buf.dtype) for r in range(self.world)]
+        ptrs = [int(t.data_ptr()) for t in self._remote]
+        if ptrs[self.rank] != self.buf.data_ptr():
+            raise RuntimeError("symmetric memory: this rank's own mapping does not coincide with the local tensor")
+        self._peer_array = (ctypes.c_void_p * self.world)(*ptrs)
+        self._epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._lib, self._check = _lib.load_library(), _lib.check
+        self._stream_ptr = _lib.stream_ptr
+        self.wait_limit_ns = int(wait_limit_ns)
+        self._rows = [self.buf.view(torch.uint8)[s * self.world * self.block_bytes:(s + 1) * self.world * self.block_bytes]
+                      .view(self.world, self.block_bytes).view(torch.float32)[:, :self.numel] for s in range(self.SLOTS)]
+        self._steps = 0
+
+    def enqueue(self, block: torch.Tensor) -> None:
+        """Enqueue one exchange of ``block`` (fp32, ``numel`` elements, 16-byte aligned) on the current stream."""
+        if block.dtype != torch.float32 or block.numel() != self.numel or not block.is_contiguous():
+            raise ValueError("block must be a contiguous fp32 tensor of the size given at construction")
+        with torch.cuda.device(self.device):
+            self._check(self._lib.ivab_peer_allgather(
+                block.data_ptr(), self.block_bytes, self._peer_array, self.world, self.rank, self.SLOTS, self.flags_off,
+                self._epoch.data_ptr(), self.status.data_ptr(), self.wait_limit_ns, self._stream_ptr(self.device)))
+
+    def rows(self, step: int) -> torch.Tensor:
+        """``[world, numel]`` view of the slot that the ``step``-th exchange (counted from 0) fills."""
+        return self._rows[step % self.SLOTS]
+
+    def gather(self, block: torch.Tensor) -> torch.Tensor:
+        self.enqueue(block)
+        out = self.rows(self._steps)
+        self._steps += 1
+        return out
+
+
 class HeadParallelDecoder:
     """Decode attention for a batch whose KV heads are sliced across the ranks of ``group``.
 
@@ -67,7 +140,13 @@ class HeadParallelDecoder:
     """
 
     def __init__(self, n_q_heads: int, n_kv_heads: int, group: Optional[dist.ProcessGroup] = None,
-                 attn_fn: Optional[Callable] = None):
+                 attn_fn: Optional[Callable] = None, exchange: str = "nccl"):
+        """``exchange``: ``"nccl"`` reassembles the outputs with one ``all_gather_into_tensor``; ``"p2p"`` with
+        this library's own kernel over peer-mapped memory (``PeerExchange``; CUDA ranks of one node)."""
+        if exchange not in ("nccl", "p2p"):
+            raise ValueError("exchange must be 'nccl' or 'p2p'")
+        self.exchange = exchange
+        self._peer: Optional[PeerExchange] = None
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -89,6 +168,11 @@ class HeadParallelDecoder:
     def _block(self, B: int, Hl: int, D: int, device):
         flat = torch.empty(B * Hl * (D + 1), dtype=torch.float32, device=device)
         return flat, flat[:B * Hl * D].view(B, Hl, D), flat[B * Hl * D:].view(B, Hl)
+
+    def _peer_exchange(self, numel: int, device) -> PeerExchange:
+        if self._peer is None or self._peer.numel != numel:
+            self._peer = PeerExchange(numel, self.group, device)     # collective: every rank gets here together
+        return self._peer
 
     def _local(self, q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view,
                new_tokens=None, **kw):
@@ -125,6 +209,10 @@ class HeadParallelDecoder:
         self._local(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view)
         if self.world == 1:
             return out_view.to(q.dtype), lse_view
+        if self.exchange == "p2p":
+            rows = self._peer_exchange(flat.numel(), q.device).gather(flat)
+            out, lse = self._unpack(rows, B, Hl, D)
+            return out.to(q.dtype), lse.contiguous()
         gathered = torch.empty(self.world * flat.numel(), dtype=torch.float32, device=q.device)
         dist.all_gather_into_tensor(gathered, flat, group=self.group)
         out, lse = self._unpack(gathered.view(self.world, -1), B, Hl, D)
@@ -142,7 +230,9 @@ class HeadParallelDecoder:
         has to do on this stream.
 
         At 131072 tokens over 8 GPUs each rank reads 67 MB per step (about 10 microseconds of HBM
-        time), so the step is bound by launch latency.  ``step()`` replays the graph and then issues
+        time), so the step is bound by launch latency.  The recording reads the query from ``step.q`` (this
+        rank's heads, copied from ``q`` here; overwrite it in place between steps), the block table, the
+        lengths and the pools in place.  ``step()`` replays the graph and then issues
         ONE eager ``all_gather_into_tensor``; it returns fp32 ``(out [B,H_q,D], lse [B,H_q])``
         (views of the gathered buffer, no further kernels, when ``B == 1``).  The collective is deliberately
         kept outside the capture: recording an NCCL collective of ``torch.distributed`` inside a
@@ -164,11 +254,15 @@ class HeadParallelDecoder:
             n_kv_local = k_pool_local.shape[1]      # both pool layouts keep the KV heads on axis 1
             extra["workspace"] = torch.empty(decode_workspace_bytes(B, Hl, n_kv_local, D), dtype=torch.uint8, device=dev)
 
+        peer = self._peer_exchange(flat.numel(), dev) if (self.exchange == "p2p" and self.world > 1) else None
+
         def local():
             if before is not None:
                 before()
             self._local(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view,
                         new_tokens=new_tokens, **extra)
+            if peer is not None:
+                peer.enqueue(flat)           # the exchange is part of the recording: a step is one graph replay
 
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -179,11 +273,25 @@ class HeadParallelDecoder:
         with torch.cuda.graph(graph, stream=side):
             local()
 
-        def step(_keep=(side, extra)):           # the capture stream and the scratch live as long as the closure
+        if peer is not None:
+            # every rank ran the eager pass and the capture does not execute anything: one exchange so far
+            peer._steps += 1
+            dist.barrier(self.group)
+
+        # Everything the recording points at must outlive it: the local query buffer made above is owned by
+        # nobody else, so the returned function holds it (with the capture stream, the scratch and the block).
+        def step(_keep=(side, extra, q, flat, local)):
             graph.replay()
+            if peer is not None:
+                rows = peer.rows(peer._steps)
+                peer._steps += 1
+                return self._unpack(rows, B, Hl, D)
             if self.world > 1:
                 dist.all_gather_into_tensor(gathered, flat, group=self.group)
                 return self._unpack(gathered.view(self.world, -1), B, Hl, D)
             return out_view, lse_view
 
+        # The graph reads this rank's query heads from ``step.q`` ([B, H_q/world, D]); a decode loop writes the
+        # next step's query there (``step.q.copy_(q_new[:, decoder.q_slice])``) before it calls ``step()``.
+        step.q = q
         return step

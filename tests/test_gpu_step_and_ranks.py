@@ -227,3 +227,60 @@ def test_two_gpus_head_parallel_and_request_sharding():
         ok, err, lerr, err2, covered = ret[r]
         # contexts of 5000, 77 and 300 keys: the plain bf16 bar, no allowance for the output's rounding
         assert ok and covered and err <= OUT_TOL[torch.bfloat16] and lerr <= 1e-3 and err2 <= OUT_TOL[torch.bfloat16], ret[r]
+
+
+def _p2p_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from iva_b200.sharding import HeadParallelDecoder, PeerExchange
+
+        dev = torch.device("cuda", rank)
+        # the exchange alone: five steps, every rank contributes a block that names rank and step
+        xch = PeerExchange(1000, device=dev)
+        ok = True
+        checks = []
+        for t in range(5):
+            block = torch.full((1000,), float(100 * t + rank), device=dev)
+            rows = xch.gather(block)
+            torch.cuda.synchronize()
+            want = torch.tensor([100.0 * t + r for r in range(world)], device=dev).view(world, 1).expand(world, 1000)
+            checks.append((f"rows of step {t}", bool(torch.equal(rows, want))))
+        checks.append(("status", int(xch.status.item()) == 0))
+        # head-parallel decode with the outputs reassembled by that kernel instead of NCCL
+        wl = workloads.make_decode_workload("hp", torch.tensor([5000, 77]), n_q_heads=16, n_kv_heads=4, head_dim=128,
+                                            dtype=torch.bfloat16, seed=11)
+        d = wl.to(dev)
+        single, single_lse = iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16,
+                                                             return_lse=True)
+        dec = HeadParallelDecoder(16, 4, exchange="p2p")
+        kl, vl = dec.local_pools(d.k_pool, d.v_pool)
+        kl, vl = kl.contiguous(), vl.contiguous()
+        out, lse = dec.decode(d.q, kl, vl, d.block_table, d.ctx_len, 16, wl.scale)
+        torch.cuda.synchronize()
+        checks.append(("eager out", bool(torch.equal(out, single))))
+        checks.append(("eager lse", bool(torch.equal(lse, single_lse))))
+        step = dec.capture_local(d.q, kl, vl, d.block_table, d.ctx_len, 16, wl.scale)
+        for i in range(4):                                   # both slots, twice: the whole step is one graph replay
+            g_out, g_lse = step()
+            torch.cuda.synchronize()
+            checks.append((f"graph replay {i} out", bool(torch.equal(g_out.to(single.dtype), single))))
+            checks.append((f"graph replay {i} lse", bool(torch.equal(g_lse, single_lse))))
+        ret[rank] = checks
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_outputs_reassembled_over_peer_memory():
+    """The head-parallel mode with this library's own all-gather kernel (plain peer stores over NVLink, arrival
+    counters, bounded wait) in place of the NCCL collective: same bits as one GPU, eager and as one CUDA-graph
+    replay per step."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_p2p_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    for r in range(2):
+        assert ret.get(r), dict(ret)
+        failed = [name for name, ok in ret[r] if not ok]
+        assert not failed, (r, failed)
