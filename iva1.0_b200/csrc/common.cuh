@@ -152,6 +152,10 @@ __device__ __forceinline__ void fence_proxy_async_all() {
     asm volatile("fence.proxy.async;" ::: "memory");
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // Brings a tensor map (the 128-byte descriptor a tiled TMA copy reads) into the descriptor cache ahead of
 // its first use.
 __device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {

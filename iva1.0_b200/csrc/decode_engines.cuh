@@ -255,11 +255,11 @@ struct MmaCore {
     static constexpr int KSTEPS = D / 16;              // k-steps of Q K^T
     static constexpr int NBLK = D / 8;                 // 8-wide output blocks of P^T V
 
-    // With head_dim 256 the accumulators alone take 128 registers; keeping the 32 registers of Q fragments as
-    // well spills (the register file allows 168 per thread at two CTAs of five warps per SM).  There the
-    // fragments live in this warp's scratch instead -- rows of D*2 + 16 bytes, so that the eight heads' rows
-    // start four banks apart and a fragment load is conflict-free -- and are re-read for every k-step.
-    static constexpr bool kQSmem = D >= 256;
+    // With head_dim 256 the accumulators alone take 128 registers.  The 32 registers of Q fragments then live in
+    // this warp's scratch instead -- rows of D*2 + 16 bytes, so that the eight heads' rows start four banks
+    // apart and a fragment load is conflict-free -- and are re-read for every k-step (measured faster than
+    // keeping them in registers; with eight heads the merge area leaves no room for the scratch).
+    static constexpr bool kQSmem = D >= 256 && G < 8;   // (eight heads x head_dim 256 run one CTA per SM with 255 registers)
     static constexpr int Q_ROW_WORDS = D / 2 + 4;
     static constexpr int Q_SCRATCH = kQSmem ? 8 * Q_ROW_WORDS * 4 : 0;
     uint32_t qa[kQSmem ? 1 : KSTEPS][2];    // A fragments of Q: head lane/4; rows 8..15 of the tile are zero
@@ -417,11 +417,12 @@ struct MmaEngine : MmaCore<T, T, D, G> {
     using Core = MmaCore<T, T, D, G>;
     static constexpr bool kTiled = true;
     static constexpr int SCRATCH_PER_WARP = Core::Q_SCRATCH;   // the Q fragments, for head_dim 256 only
-#ifdef IVAB_D256_ONE_CTA
+    // head_dim 256 runs one CTA per SM: a stage is 16 KB and the merge area up to 32 KB, which at two CTAs per
+    // SM leaves four to six stages (one per consumer warp: no pipelining), and the accumulators alone take 128
+    // of the 168 registers two CTAs allow.  Measured on 64 sequences x 4096 keys (same GPU): four query heads
+    // per KV head 4.50 TB/s at two CTAs with Q in registers, 5.31 with Q in shared memory, 5.61 at one CTA;
+    // eight heads 3.04 -> 3.35 TB/s.
     static constexpr int CTAS_PER_SM = D >= 256 ? 1 : 2;
-#else
-    static constexpr int CTAS_PER_SM = 2;
-#endif
     using Core::TILES; using Core::TILE_BYTES; using Core::PAGE_BYTES;
 
     __device__ __forceinline__ void page(const DecodeParams& p, unsigned char* stage, int n_valid, int hole_lo,

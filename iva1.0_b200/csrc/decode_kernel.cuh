@@ -185,6 +185,8 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         DirectPlan dplan{};
         int static_next = (int)blockIdx.x;
         if (direct) {
+            // the block-table rows are needed right after the lengths: start them towards the L2 now
+            if (lane < p.batch) prefetch_l2(p.block_table + (int64_t)lane * p.bt_stride);
             dplan = direct_plan(p.ctx_len, p.ctx_begin, p.sink_tokens, p.max_pages, p.batch, p.n_virt_heads,
                                 p.direct_target_items, p.direct_min_chunk, lane);
             num_chunks = dplan.num_chunks;
@@ -310,8 +312,11 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                 // its own stage and issues its own copies, so the issue cost of up to `stages` pages
                 // overlaps.  A sub-batch never exceeds the ring (spw pages per consumer warp): a lane
                 // must not wait two phases ahead of a stage's barrier.
-                for (int q0 = 0; q0 < in_batch && !aborted; q0 += stages) {
-                    const int nb = min(stages, in_batch - q0);
+                int nb = 0;
+                for (int q0 = 0; q0 < in_batch && !aborted; q0 += nb) {
+                    nb = min(stages, in_batch - q0);
+                    // the newest token's page goes out on its own, behind the fence: the pages before it need not wait
+                    if (need_fence && p0 + q0 + nb >= d.n_pages && nb > 1) nb -= 1;
                     if (need_fence && p0 + q0 + nb >= d.n_pages) {   // the request that reads the newest token's page
                         fence_proxy_async_all();
                         __syncwarp();
@@ -946,10 +951,20 @@ int dispatch_fp8(int D, int G_real, int Hkv, const DecodeParams& p, int B, cudaS
             }
         }
     }
+    // The CUDA-core engine on 8-bit pools is built for one and two query heads per KV head only (with four
+    // or eight it needs several hundred bytes of spills per thread and was never the faster choice): larger
+    // groups always take a tensor-core engine, which needs a positive softmax scale.
+    if (simt && G > 2) {
+        if (!(p.scale_log2 > 0.f))
+            return set_error(IVAB_ERR_UNSUPPORTED, "8-bit KV decode with more than two query heads per KV head needs scale > 0");
+    }
 #define IVAB_FP8_CASE(DD, GG)                                                                   \
-    if (D == DD && G == GG)                                                                     \
-        return simt ? launch_decode<T, DD, GG, kEngSimt, F8>(p, tm, B, st)                      \
-                    : launch_decode<T, DD, GG, kEngMmaFp8, F8>(p, tm, B, st);
+    if (D == DD && G == GG) {                                                                   \
+        if constexpr (GG <= 2) {                                                                \
+            if (simt) return launch_decode<T, DD, GG, kEngSimt, F8>(p, tm, B, st);              \
+        }                                                                                       \
+        return launch_decode<T, DD, GG, kEngMmaFp8, F8>(p, tm, B, st);                          \
+    }
     IVAB_FP8_CASE(64, 1) IVAB_FP8_CASE(64, 2) IVAB_FP8_CASE(64, 4) IVAB_FP8_CASE(64, 8)
     IVAB_FP8_CASE(128, 1) IVAB_FP8_CASE(128, 2) IVAB_FP8_CASE(128, 4) IVAB_FP8_CASE(128, 8)
 #undef IVAB_FP8_CASE

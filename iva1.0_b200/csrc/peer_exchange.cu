@@ -1,7 +1,7 @@
 // All-gather of one small block per rank over peer-mapped memory (NVLink loads/stores), for the head-parallel
 // decode of one long sequence: every rank ends a step with a few KB of output rows, and every rank needs all
-// of them.  One CTA per destination rank stores this rank's block straight into that rank's buffer, signals
-// it, and waits for the other ranks' signals.  No library collective, no host round trip: the exchange is one
+// of them.  One warp per destination rank stores this rank's block straight into that rank's buffer, signals
+// it, and waits for that rank's signal.  No library collective, no host round trip: the exchange is one
 // more kernel in the step's stream (or CUDA graph), launched as a programmatic dependent of the kernel before it.
 //
 // Buffer of every rank (same layout everywhere, mapped into every peer's address space by the caller):
@@ -25,7 +25,6 @@ extern std::atomic<long long> g_launches;
 namespace {
 
 constexpr int kMaxPeers = 16;
-constexpr int kXchgThreads = 128;
 
 struct PeerParams {
     const char* local;             // this rank's block
@@ -47,38 +46,35 @@ __device__ __forceinline__ void red_release_sys_add(unsigned int* p, unsigned in
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// grid = world CTAs: CTA r serves destination rank r
-__global__ void __launch_bounds__(kXchgThreads) peer_allgather_kernel(const PeerParams pp) {
+// One CTA; warp r serves destination rank r: it stores this rank's block into rank r's buffer, signals it,
+// and waits for rank r's block to arrive here.
+__global__ void __launch_bounds__(kMaxPeers * 32) peer_allgather_kernel(const PeerParams pp) {
     grid_dependency_wait();   // the block is the output of the kernels before this one
-    const int dst = blockIdx.x;
-    const unsigned int epoch = *pp.epoch;             // (every CTA reads it before any CTA can have bumped it: see below)
+    const int dst = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned int epoch = *pp.epoch;
     const int slot = (int)(epoch % (unsigned)pp.slots);
     char* row = pp.peer[dst] + ((int64_t)slot * pp.world + pp.rank) * pp.block_bytes;
-    for (int64_t off = (int64_t)threadIdx.x * 16; off < pp.block_bytes; off += (int64_t)kXchgThreads * 16)
+    for (int64_t off = (int64_t)lane * 16; off < pp.block_bytes; off += 32 * 16)
         *reinterpret_cast<uint4*>(row + off) = *reinterpret_cast<const uint4*>(pp.local + off);
-    __threadfence_system();   // this thread's stores are performed at the destination ...
-    __syncthreads();          // ... for every thread of the CTA, before the one signal below
-    __shared__ int failed;
-    if (threadIdx.x == 0) {
-        failed = 0;
+    __threadfence_system();   // this lane's stores are performed at the destination ...
+    __syncwarp();             // ... for every lane of the warp, before the one signal below
+    if (lane == 0) {
         // one more block from `rank` has landed at `dst`
         red_release_sys_add(reinterpret_cast<unsigned int*>(pp.peer[dst] + pp.flags_off) + pp.rank, 1u);
         // and wait until rank `dst` has delivered ITS block of this step here
         const unsigned int* mine = reinterpret_cast<const unsigned int*>(pp.peer[pp.rank] + pp.flags_off) + dst;
         const uint64_t t0 = globaltimer_ns();
+        bool failed = false;
         // (counters wrap after 2^32 steps; the signed difference keeps the comparison right across the wrap)
         while ((int)(ld_acquire_sys(mine) - (epoch + 1u)) < 0) {
-            if (globaltimer_ns() - t0 > pp.limit_ns) { failed = 1; break; }
+            if (globaltimer_ns() - t0 > pp.limit_ns) { failed = true; break; }
             __nanosleep(100);
         }
         if (failed && pp.status != nullptr) atomicOr(pp.status, kStatusWaitTimeout);
     }
-    __syncthreads();
+    __syncthreads();          // every warp has read the step counter and has seen its peer's block
+    if (threadIdx.x == 0) *pp.epoch = epoch + 1u;
 }
-
-// The step counter is bumped by a separate one-thread kernel behind the exchange: every CTA of the exchange has
-// then read the old value.
-__global__ void bump_epoch_kernel(unsigned int* epoch) { *epoch += 1u; }
 
 }  // namespace
 }  // namespace ivab
@@ -113,11 +109,9 @@ extern "C" int ivab_peer_allgather(const void* local_block, int64_t block_bytes,
     pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl.val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(world); cfg.blockDim = dim3(kXchgThreads); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cfg.gridDim = dim3(1); cfg.blockDim = dim3(world * 32); cfg.dynamicSmemBytes = 0; cfg.stream = st;
     cfg.attrs = &pdl; cfg.numAttrs = 1;
     if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, peer_allgather_kernel, pp), "peer_allgather_kernel launch")) return rc;
     g_launches++;
-    bump_epoch_kernel<<<1, 1, 0, st>>>(epoch);
-    g_launches++;
-    return check_cuda(cudaGetLastError(), "bump_epoch_kernel launch");
+    return IVAB_OK;
 }

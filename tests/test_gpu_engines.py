@@ -19,7 +19,7 @@ from iva_b200 import workloads
 from oracle import paged_ref as ref
 from util import check_decode
 for dtype in (torch.bfloat16, torch.float16):
-    for hq, hkv, D in ((4, 4, 128), (8, 2, 128), (16, 2, 64), (8, 4, 256)):
+    for hq, hkv, D in ((4, 4, 128), (8, 2, 128), (16, 2, 64), (8, 4, 256), (8, 2, 256), (16, 2, 256)):
         ctx = torch.tensor([0, 1, 15, 16, 17, 100, 333, 2500])
         wl = workloads.make_decode_workload("eng", ctx, n_q_heads=hq, n_kv_heads=hkv, head_dim=D, dtype=dtype,
                                             seed=hq + D, free_frac=0.3, poison_unused=True)
