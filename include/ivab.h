@@ -185,7 +185,9 @@ int ivab_decode_workspace_bytes(int64_t batch, int64_t q_heads, int64_t kv_heads
  * IVAB_F32 to receive the kernels' fp32 result without the final rounding to a 16-bit type (the
  * reference computes and returns fp32 for fp32 inputs, and its gather always returns fp32,
  * src/kernels_t/kv_ops_triton.py:112); out strides are in elements of `out_dtype`.
- * Enqueues three kernels (plan, split-K attention, logsumexp merge).  ctx_len[s] == 0
+ * Enqueues up to three kernels: a planning kernel (batches above 32 sequences; smaller batches derive
+ * their chunking inside the attention kernel), the persistent split-K attention kernel, and the logsumexp
+ * merge kernel (not launched when no sequence can be split).  ctx_len[s] == 0
  * (or an empty window)
  * yields zeros and -inf.  `workspace` must be 256-byte aligned and hold
  * ivab_decode_workspace_bytes(); concurrent calls need distinct workspaces.

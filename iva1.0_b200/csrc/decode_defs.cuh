@@ -18,6 +18,8 @@ constexpr int kItemRing = 4;
 constexpr int kMaxStages = 32;
 static_assert(kMaxStages % kConsumerWarps == 0, "stage ring must divide among the consumer warps");
 constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
+constexpr int kDirectSig0 = 0x49564142, kDirectSig1 = 0x5f637472, kDirectSig2 = 0x2e763031;
+constexpr int kDirectBigPages = 256;  // plan-free mode: pages per CTA from which a batch counts as large (finer items, work counter)
 constexpr int kMinChunkPages = 8;
 constexpr int kDefaultItemOrder = 2;  // 0: kv-head-major, 1: chunk-major, 2: chunk-major for ragged batches only (see split_id)
 // Plan-free ("direct") mode, for batches small enough that one warp holds a sequence per lane:
@@ -51,6 +53,12 @@ constexpr int kMaxDevices = 64;      // device ordinals the per-device host cach
 // header words at the start of the workspace
 enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, kHdrTotalItems = 4, kHdrNumSplit = 5, kHdrNumBig = 6,
        kHdrChunkMajor = 7,   // order in which the items are handed out, chosen by the plan kernel
+       // Plan-free mode's work counter and three signature words (one 16-byte unit).  The merge kernel of every
+       // plan-free call leaves {0, signature} behind once the attention kernel is done; an attention kernel that
+       // finds the signature knows the counter is zero and hands the items of a large batch out through it; one
+       // that does not (the first call on a workspace, whose memory is not initialised) assigns them statically,
+       // as every call does for a batch that is not large.
+       kHdrDirectCounter = 8, kHdrDirectSig = 9,
        kHdrWords = 64 };
 // Status protocol.  header[kHdrStatus] holds the bits of the planning step: written by the plan kernel,
 // or (plan-free mode) by CTA 0 of the attention kernel.  Every CTA of the attention kernel additionally
@@ -105,6 +113,9 @@ struct DecodeParams {
     int direct;
     int batch, max_pages, n_virt_heads;        // sequences, block-table width, KV heads the items number
     int direct_target_items, direct_min_chunk; // chunk size = max(min_chunk, ceil(total_pages * heads / target_items))
+    int direct_grid;                           // CTAs of the attention launch
+    int direct_dynamic;                        // 1: a merge kernel follows and re-arms the work counter, so the attention kernel may use it
+    int direct_big_target_items;               // target_items of a large batch (0: same as direct_target_items)
     int status_slots_per_cta;                  // 2 when the grid is one CTA per SM, else 1
     int chunk_major;                           // order in which items are handed out: 0, 1, or 2 = as the plan kernel decided
     const int32_t* ctx_len; const int32_t* ctx_begin;
@@ -155,13 +166,17 @@ struct DirectPlan {
     int L, begin, sink_pages;
     int num_chunks;               // warp-uniform: chunks of the whole batch
     bool bad;                     // warp-uniform: some ctx_len / ctx_begin was out of range
+    bool big;                     // warp-uniform: a large batch (cut with big_target_items)
 };
 
 // Must be called by all 32 lanes.  Deterministic in its inputs, so every CTA of the attention kernel and of
 // the merge kernel arrives at the same plan.  Sequences are split evenly into ceil(pages / c) chunks with
-// c = max(min_chunk, ceil(total_pages * heads / target_items)) pages.
+// c = max(min_chunk, ceil(total_pages * heads / target_items)) pages.  `big_target_items` (0 = none) replaces
+// target_items from kDirectBigPages pages per CTA on: a batch of that size is served through the work counter
+// (when it is armed), where finer items shorten the tail.
 __device__ __forceinline__ DirectPlan direct_plan(const int32_t* ctx_len, const int32_t* ctx_begin, int sink_tokens, int max_pages,
-                                                  int batch, int heads, int target_items, int min_chunk, int lane) {
+                                                  int batch, int heads, int target_items, int min_chunk, int big_target_items,
+                                                  int grid, int lane) {
     DirectPlan d{};
     bool bad = false;
     if (lane < batch) d.pages = seq_page_range(ctx_len, ctx_begin, sink_tokens, max_pages, lane, &d.L, &d.begin, &d.sink_pages, &bad);
@@ -169,6 +184,8 @@ __device__ __forceinline__ DirectPlan direct_plan(const int32_t* ctx_len, const 
     long long total = d.pages;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    d.big = big_target_items > 0 && total * heads >= (long long)grid * kDirectBigPages;
+    if (d.big) target_items = big_target_items;
     long long c64 = (total * heads + target_items - 1) / target_items;
     if (c64 < min_chunk) c64 = min_chunk;
     const int c = (int)(c64 > 0x3fffffff ? 0x3fffffff : c64);

@@ -181,16 +181,25 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         // stream does not pause at item boundaries.
         // Plan-free mode: this warp derives the chunking from ctx_len itself (lane s holds sequence s) and
         // the CTA takes the items blockIdx.x, blockIdx.x + gridDim.x, ...: two dependent global accesses
-        // (ctx_len, block-table entries) before the first page is requested, no work counter.
+        // (ctx_len, block-table entries) before the first page is requested.  Further items come from the
+        // plan-free work counter when the batch is large and the previous call's merge kernel left the counter
+        // armed (signature present), else statically: uninitialised workspace memory is never trusted.
         DirectPlan dplan{};
         int static_next = (int)blockIdx.x;
+        bool dynamic = !direct;
         if (direct) {
+            int4 sig = make_int4(0, 0, 0, 0);   // (in flight while the lengths are loaded and the plan is derived)
+            if (p.direct_dynamic && lane == 0) sig = __ldcg(reinterpret_cast<const int4*>(p.ws.header + kHdrDirectCounter));
             // the block-table rows are needed right after the lengths: start them towards the L2 now
             if (lane < p.batch) prefetch_l2(p.block_table + (int64_t)lane * p.bt_stride);
             dplan = direct_plan(p.ctx_len, p.ctx_begin, p.sink_tokens, p.max_pages, p.batch, p.n_virt_heads,
-                                p.direct_target_items, p.direct_min_chunk, lane);
+                                p.direct_target_items, p.direct_min_chunk, p.direct_big_target_items, p.direct_grid, lane);
             num_chunks = dplan.num_chunks;
             total_items = num_chunks * p.n_virt_heads;
+            if (dplan.big) {   // a large batch: through the work counter, if the previous call left it armed
+                dynamic = __shfl_sync(0xffffffffu, sig.y == kDirectSig0 && sig.z == kDirectSig1 && sig.w == kDirectSig2, 0) != 0;
+                if (dynamic) counter = p.ws.header + kHdrDirectCounter;
+            }
             if (dplan.bad && lane == 0) atomicOr(cta_status, kStatusBadCtxLen);
             if (num_chunks > p.ws.cap) {   // cannot happen while target_items <= kItemsPerSlot x resident CTAs
                 if (lane == 0) atomicOr(cta_status, kStatusOverflow);
@@ -199,7 +208,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         }
         auto fetch_id_async = [&]() {   // lane 0 holds the result; broadcast it only when it is needed
             int v = 0;
-            if (direct) { static_next += (int)gridDim.x; v = static_next; }
+            if (!dynamic) { static_next += (int)gridDim.x; v = static_next; }
             else if (lane == 0) v = (int)gridDim.x + atomicAdd(counter, 1);
             return v;
         };
@@ -246,7 +255,8 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         const uint64_t stream_policy = l2_policy_evict_first();   // K/V pages are read once
         // the first item of a CTA is its own index (no round trip to the work counter before the
         // first page can be requested); the counter hands out the items from gridDim.x on
-        int id0 = (int)blockIdx.x, id1 = fetch_id(), id2 = fetch_id();
+        int id0 = (int)blockIdx.x, id1 = fetch_id_async(), id2 = fetch_id_async();   // (both round trips in flight at once)
+        id1 = __shfl_sync(0xffffffffu, id1, 0); id2 = __shfl_sync(0xffffffffu, id2, 0);
         int h0, h1;
         ChunkDesc d0 = load_desc(id0, &h0);
         ChunkDesc d1 = load_desc(id1, &h1);
@@ -561,8 +571,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     DirectPlan dplan{};
     if (direct)
         dplan = direct_plan(p.ctx_len, p.ctx_begin, p.sink_tokens, p.max_pages, p.batch, p.n_virt_heads,
-                            p.direct_target_items, p.direct_min_chunk, lane);
+                            p.direct_target_items, p.direct_min_chunk, p.direct_big_target_items, p.direct_grid, lane);
     grid_dependency_wait();   // the attention kernel's partial results
+    // the attention kernel is done with the plan-free work counter: leave it zeroed and signed for the next call
+    if (direct && p.direct_dynamic && blockIdx.x == 0 && threadIdx.x == 0)
+        *reinterpret_cast<int4*>(ws.header + kHdrDirectCounter) = make_int4(0, kDirectSig0, kDirectSig1, kDirectSig2);
 #ifdef IVAB_PROFILE
     if (threadIdx.x == 0) PROF_STAMP_MIN(ws.header, 6, globaltimer_ns())
 #endif
@@ -792,6 +805,16 @@ int direct_items_per_slot() {
     return v;
 }
 
+// Plan-free mode: IVAB_DIRECT_DYNAMIC=0 keeps the item ids static (CTA b takes b, b + grid, ...) even where the
+// work counter could be used (experiments).
+bool direct_dynamic_enabled() {
+    static bool v = [] {
+        const char* e = std::getenv("IVAB_DIRECT_DYNAMIC");
+        return !(e && std::atoi(e) == 0);
+    }();
+    return v;
+}
+
 // Programmatic dependent launch of the attention and merge kernels; IVAB_PDL=0 turns it off.
 bool use_dependent_launch() {
     static bool v = [] {
@@ -839,7 +862,14 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     const int grid = sm_count() * kCtas;
     if (2 * sm_count() > kStatusSlots) return set_error(IVAB_ERR_UNSUPPORTED, "decode attention: %d SMs (status slots for %d)", sm_count(), kStatusSlots / 2);
     p.status_slots_per_cta = 2 / kCtas;   // the first 2 x SMs slots are written by every call, whatever the engine
-    if (p.direct) p.direct_target_items = grid * direct_items_per_slot();
+    if (p.direct) {
+        p.direct_target_items = grid * direct_items_per_slot();
+        p.direct_grid = grid;
+        // The work counter is usable when a merge kernel follows (it re-arms the counter for the next call);
+        // a batch that turns out large (the lengths are known only on the device) is cut into finer items.
+        p.direct_dynamic = direct_dynamic_enabled() && p.max_pages > p.direct_min_chunk ? 1 : 0;
+        p.direct_big_target_items = p.direct_dynamic ? grid * kItemsPerSlot : 0;
+    }
     // Both launches below are programmatic dependents of the kernel before them (plan -> attention
     // -> merge): the launch latency and set-up of each overlap the tail of its predecessor.
     cudaLaunchAttribute pdl{};
@@ -857,7 +887,11 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     cfg.gridDim = dim3(merge_grid); cfg.blockDim = dim3(kMergeWarps * 32); cfg.dynamicSmemBytes = 0;
     // plan-free mode with a block table no wider than the smallest chunk: no sequence can be split, nothing to merge
     if (p.direct && p.max_pages <= p.direct_min_chunk) return IVAB_OK;
-    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, p, B), "merge_kernel launch")) return rc;
+    if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, p, B), "merge_kernel launch")) {
+        // (the counter stays as the attention kernel leaves it: drop the signature so that no later call trusts it)
+        if (p.direct_dynamic) cudaMemsetAsync(p.ws.header + kHdrDirectCounter, 0, 4 * sizeof(int), st);
+        return rc;
+    }
     g_launches++;
     return IVAB_OK;
 }

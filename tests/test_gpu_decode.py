@@ -164,6 +164,42 @@ def test_bad_page_id_and_length_are_flagged_not_dereferenced():
     iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16, workspace=ws, check=True)
 
 
+@pytest.mark.parametrize("fill", ["zeros", "ones", "random"])
+def test_workspace_contents_never_matter(fill):
+    """The workspace is scratch the caller does not initialise.  A small batch (cut into work items inside the
+    attention kernel) trusts the work counter in it only after one of its own calls has armed it: whatever the
+    memory holds before the first call, every call gives the same bits -- also after a large batch (planned
+    by the plan kernel) has used the same memory, and after the block of a finished call is scribbled over."""
+    g = torch.Generator().manual_seed(21)
+    ctx = torch.randint(600, 5000, (6,), generator=g)
+    wl = workloads.make_decode_workload("wsfill", ctx, n_q_heads=8, n_kv_heads=2, head_dim=128, seed=22)
+    out_ref, lse_ref = ref.paged_decode_ref(wl.q, wl.k_pool, wl.v_pool, wl.block_table, wl.ctx_len, 16)
+    d = wl.to(DEV)
+    big = workloads.make_decode_workload("wsbig", torch.randint(1, 700, (40,), generator=g), n_q_heads=8, n_kv_heads=2,
+                                         head_dim=128, seed=23)
+    big_ref = ref.paged_decode_ref(big.q, big.k_pool, big.v_pool, big.block_table, big.ctx_len, 16)
+    bd = big.to(DEV)
+    n = max(decode_workspace_bytes(6, 8, 2, 128), decode_workspace_bytes(40, 8, 2, 128))
+    if fill == "random":
+        ws = torch.randint(0, 256, (n,), dtype=torch.uint8, generator=g).to(DEV)
+    else:
+        ws = torch.full((n,), 0 if fill == "zeros" else 255, dtype=torch.uint8, device=DEV)
+    call = lambda: iva_b200.paged_decode_attention(d.q, d.k_pool, d.v_pool, d.block_table, d.ctx_len, 16,
+                                                   return_lse=True, check=True, workspace=ws, out_dtype=torch.float32)
+    first = call()
+    assert_attn_close(first[0], out_ref, wl.dtype, strict=True)
+    assert_lse_close(first[1], lse_ref)
+    for i in range(4):
+        if i == 2:      # a planned batch in between, on the same memory
+            ob, lb = iva_b200.paged_decode_attention(bd.q, bd.k_pool, bd.v_pool, bd.block_table, bd.ctx_len, 16,
+                                                     return_lse=True, check=True, workspace=ws, out_dtype=torch.float32)
+            assert_attn_close(ob, big_ref[0], big.dtype, strict=True)
+        if i == 3:      # somebody else used the memory
+            ws.fill_(0x5A)
+        again = call()
+        assert torch.equal(again[0], first[0]) and torch.equal(again[1], first[1])
+
+
 def test_argument_errors():
     wl = workloads.make_decode_workload("e", torch.tensor([20]), n_q_heads=22, n_kv_heads=2, head_dim=128, seed=2).to(DEV)
     with pytest.raises(ValueError, match="supported: 1 to 8"):      # 11 query heads per KV head: no equal groups of <= 8

@@ -183,6 +183,35 @@ def test_batch_larger_than_the_planner_tiles():
                  out_ref, lse_ref, wl.dtype)
 
 
+@pytest.mark.parametrize("shape", ["uniform", "ragged"])
+def test_large_plan_free_batch(shape):
+    """Batches of at most 32 sequences are cut into work items inside the attention kernel; from 256 pages
+    per CTA on it compares several chunk sizes.  16 x 4096 tokens x 32 heads (uniform) and 24 ragged
+    sequences of up to 12000 tokens reach that search: sampled comparison with the checker, the fused step
+    against append + attention, bit-identical repeats."""
+    if shape == "uniform":
+        wl = workloads.config_c2(device=DEV, batch=16)
+    else:
+        g = torch.Generator().manual_seed(11)
+        ctx = torch.randint(1500, 12000, (24,), generator=g)
+        ctx[3], ctx[17] = 5, 0
+        wl = workloads.make_decode_workload("ragged24", ctx, n_q_heads=32, n_kv_heads=32, head_dim=128,
+                                            dtype=torch.bfloat16, seed=12, device=DEV)
+    lens = (wl.ctx_len + 1).contiguous()
+    out32, lse = iva_b200.paged_decode_step(wl.q, wl.k_new, wl.v_new, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                            return_lse=True, check=True, out_dtype=torch.float32)
+    assert torch.equal(wl.k_pool[0, :, wl.slot_mapping], wl.k_new.permute(1, 0, 2))
+    assert torch.equal(wl.v_pool[0, :, wl.slot_mapping], wl.v_new.permute(1, 0, 2))
+    order = torch.argsort(wl.ctx_len.cpu())
+    seqs = sorted({int(order[0]), int(order[1]), int(order[len(order) // 2]), int(order[-1])})
+    _sampled_oracle(wl, lens, seqs, out32, lse)       # fp32 output: the plain bar, also for the short sequences
+    # the same workspace again (the first call on it assigns items statically, later ones through the work counter)
+    for _ in range(3):
+        out2, lse2 = iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                                     return_lse=True, check=True)
+        assert torch.equal(out2, out32.to(out2.dtype)) and torch.equal(lse2, lse)
+
+
 @pytest.mark.parametrize("config", ["c2", "c3"])
 def test_full_size_on_fp8_pools(config):
     """The MHA and the ragged GQA benchmark configurations on 8-bit pools: quantising append, decode,
