@@ -586,7 +586,19 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True, exchange="nccl"):
     else:
         hp = None
         k_loc, v_loc, k_new, v_new = wl.k_pool, wl.v_pool, wl.k_new, wl.v_new
-    flush_buf, flush = flusher(dev, nbytes, always=True)   # a step is ~0.1 ms or less: see flusher()
+    flush_buf, flush_local = flusher(dev, nbytes, always=True)   # a step is ~0.1 ms or less: see flusher()
+    if world > 1:
+        # The flush takes a different time on every GPU, and a step that ends in a collective would charge
+        # that skew to whichever rank finished its flush first.  A one-word all-reduce behind the flush
+        # (outside the timed region) lets the ranks start each timed step together, as they do in a decode
+        # loop, where the previous step's collective has aligned them.
+        sync_word = torch.zeros(1, device=dev)
+
+        def flush():
+            flush_local()
+            ranks.dist.all_reduce(sync_word)
+    else:
+        flush = flush_local
 
     def append():
         iva_b200.paged_append(k_loc, v_loc, wl.slot_mapping, k_new, v_new, wl.page_size)
@@ -645,7 +657,8 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True, exchange="nccl"):
                 if exchange == "nccl" else
                 "ivab_peer_allgather: this library's kernel over peer-mapped memory (NVLink stores + arrival counters), "
                 "recorded in the same CUDA graph as the local kernels: one graph replay per step, no NCCL call"),
-            "l2": "flushed between timed steps"}
+            "l2": "flushed between timed steps" + ("; ranks aligned by a one-word all-reduce behind each flush, "
+                                                    "outside the timed region" if world > 1 else "")}
 
 
 # ---- the GPU arm --------------------------------------------------------------------------------------
