@@ -19,7 +19,7 @@ constexpr int kMaxStages = 32;
 static_assert(kMaxStages % kConsumerWarps == 0, "stage ring must divide among the consumer warps");
 constexpr int kItemsPerSlot = 8;     // target work items per resident CTA
 constexpr int kDirectSig0 = 0x49564142, kDirectSig1 = 0x5f637472, kDirectSig2 = 0x2e763031;
-constexpr int kDirectBigPages = 256;  // plan-free mode: pages per CTA from which a batch counts as large (finer items, work counter)
+constexpr int kDirectBigKB = 768;     // plan-free mode: KB of K/V per CTA from which a batch counts as large (finer items, work counter)
 constexpr int kMinChunkPages = 8;
 constexpr int kDefaultItemOrder = 2;  // 0: kv-head-major, 1: chunk-major, 2: chunk-major for ragged batches only (see split_id)
 // Plan-free ("direct") mode, for batches small enough that one warp holds a sequence per lane:
@@ -116,6 +116,7 @@ struct DecodeParams {
     int direct_grid;                           // CTAs of the attention launch
     int direct_dynamic;                        // 1: a merge kernel follows and re-arms the work counter, so the attention kernel may use it
     int direct_big_target_items;               // target_items of a large batch (0: same as direct_target_items)
+    int direct_big_pages;                      // pages per CTA from which a batch counts as large
     int status_slots_per_cta;                  // 2 when the grid is one CTA per SM, else 1
     int chunk_major;                           // order in which items are handed out: 0, 1, or 2 = as the plan kernel decided
     const int32_t* ctx_len; const int32_t* ctx_begin;
@@ -172,11 +173,11 @@ struct DirectPlan {
 // Must be called by all 32 lanes.  Deterministic in its inputs, so every CTA of the attention kernel and of
 // the merge kernel arrives at the same plan.  Sequences are split evenly into ceil(pages / c) chunks with
 // c = max(min_chunk, ceil(total_pages * heads / target_items)) pages.  `big_target_items` (0 = none) replaces
-// target_items from kDirectBigPages pages per CTA on: a batch of that size is served through the work counter
+// target_items from big_pages pages per CTA on: a batch of that size is served through the work counter
 // (when it is armed), where finer items shorten the tail.
 __device__ __forceinline__ DirectPlan direct_plan(const int32_t* ctx_len, const int32_t* ctx_begin, int sink_tokens, int max_pages,
                                                   int batch, int heads, int target_items, int min_chunk, int big_target_items,
-                                                  int grid, int lane) {
+                                                  int big_pages, int grid, int lane) {
     DirectPlan d{};
     bool bad = false;
     if (lane < batch) d.pages = seq_page_range(ctx_len, ctx_begin, sink_tokens, max_pages, lane, &d.L, &d.begin, &d.sink_pages, &bad);
@@ -184,7 +185,8 @@ __device__ __forceinline__ DirectPlan direct_plan(const int32_t* ctx_len, const 
     long long total = d.pages;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
-    d.big = big_target_items > 0 && total * heads >= (long long)grid * kDirectBigPages;
+    // (one sequence alone is split evenly by construction: finer items would only add partial results to merge)
+    d.big = big_target_items > 0 && batch > 1 && total * heads >= (long long)grid * big_pages;
     if (d.big) target_items = big_target_items;
     long long c64 = (total * heads + target_items - 1) / target_items;
     if (c64 < min_chunk) c64 = min_chunk;

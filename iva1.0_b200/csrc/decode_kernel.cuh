@@ -193,7 +193,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             // the block-table rows are needed right after the lengths: start them towards the L2 now
             if (lane < p.batch) prefetch_l2(p.block_table + (int64_t)lane * p.bt_stride);
             dplan = direct_plan(p.ctx_len, p.ctx_begin, p.sink_tokens, p.max_pages, p.batch, p.n_virt_heads,
-                                p.direct_target_items, p.direct_min_chunk, p.direct_big_target_items, p.direct_grid, lane);
+                                p.direct_target_items, p.direct_min_chunk, p.direct_big_target_items, p.direct_big_pages, p.direct_grid, lane);
             num_chunks = dplan.num_chunks;
             total_items = num_chunks * p.n_virt_heads;
             if (dplan.big) {   // a large batch: through the work counter, if the previous call left it armed
@@ -209,6 +209,14 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         auto fetch_id_async = [&]() {   // lane 0 holds the result; broadcast it only when it is needed
             int v = 0;
             if (!dynamic) { static_next += (int)gridDim.x; v = static_next; }
+            else if (direct) {
+                // Plan-free: a CTA's first two items are static; the counter hands out what lies beyond two
+                // rounds over the grid.  Ids are claimed up to three items ahead, so claiming everything from
+                // the counter would let the CTAs that ask first take most of a short list.
+                if (static_next < (int)gridDim.x) { static_next += (int)gridDim.x; v = static_next; }
+                else if (total_items <= 2 * (int)gridDim.x) v = total_items;
+                else if (lane == 0) v = 2 * (int)gridDim.x + atomicAdd(counter, 1);
+            }
             else if (lane == 0) v = (int)gridDim.x + atomicAdd(counter, 1);
             return v;
         };
@@ -571,7 +579,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     DirectPlan dplan{};
     if (direct)
         dplan = direct_plan(p.ctx_len, p.ctx_begin, p.sink_tokens, p.max_pages, p.batch, p.n_virt_heads,
-                            p.direct_target_items, p.direct_min_chunk, p.direct_big_target_items, p.direct_grid, lane);
+                            p.direct_target_items, p.direct_min_chunk, p.direct_big_target_items, p.direct_big_pages, p.direct_grid, lane);
     grid_dependency_wait();   // the attention kernel's partial results
     // the attention kernel is done with the plan-free work counter: leave it zeroed and signed for the next call
     if (direct && p.direct_dynamic && blockIdx.x == 0 && threadIdx.x == 0)
@@ -805,6 +813,13 @@ int direct_items_per_slot() {
     return v;
 }
 
+int env_int(const char* name, int dflt, int lo, int hi) {
+    const char* e = std::getenv(name);
+    if (!e) return dflt;
+    const int n = std::atoi(e);
+    return n < lo ? lo : (n > hi ? hi : n);
+}
+
 // Plan-free mode: IVAB_DIRECT_DYNAMIC=0 keeps the item ids static (CTA b takes b, b + grid, ...) even where the
 // work counter could be used (experiments).
 bool direct_dynamic_enabled() {
@@ -868,7 +883,13 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
         // The work counter is usable when a merge kernel follows (it re-arms the counter for the next call);
         // a batch that turns out large (the lengths are known only on the device) is cut into finer items.
         p.direct_dynamic = direct_dynamic_enabled() && p.max_pages > p.direct_min_chunk ? 1 : 0;
-        p.direct_big_target_items = p.direct_dynamic ? grid * kItemsPerSlot : 0;
+        // (8-bit pools stream a page in half the time, so the fixed work per item weighs more: fewer, longer items
+        //  and a threshold in bytes, not pages -- IVAB_DIRECT_BIG_IPS / IVAB_DIRECT_BIG_KB override both for experiments)
+        const int big_ips = env_int("IVAB_DIRECT_BIG_IPS", sizeof(TKV) == 1 ? kItemsPerSlot * 3 / 4 : kItemsPerSlot, 1, kItemsPerSlot);
+        p.direct_big_target_items = p.direct_dynamic ? grid * big_ips : 0;
+        const long long page_bytes = 2LL * kPage * D * (long long)sizeof(TKV);   // K and V
+        const long long big_pages = (long long)env_int("IVAB_DIRECT_BIG_KB", kDirectBigKB, 1, 1 << 20) * 1024 / page_bytes;
+        p.direct_big_pages = (int)(big_pages < 1 ? 1 : big_pages);
     }
     // Both launches below are programmatic dependents of the kernel before them (plan -> attention
     // -> merge): the launch latency and set-up of each overlap the tail of its predecessor.
