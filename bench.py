@@ -590,13 +590,14 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True, exchange="nccl"):
     if world > 1:
         # The flush takes a different time on every GPU, and a step that ends in a collective would charge
         # that skew to whichever rank finished its flush first.  A one-word all-reduce behind the flush
-        # (outside the timed region) lets the ranks start each timed step together, as they do in a decode
+        # (outside the timed region; issued twice) lets the ranks start each timed step together, as they do in a decode
         # loop, where the previous step's collective has aligned them.
         sync_word = torch.zeros(1, device=dev)
 
         def flush():
             flush_local()
-            ranks.dist.all_reduce(sync_word)
+            ranks.dist.all_reduce(sync_word)   # absorbs the skew of the flush ...
+            ranks.dist.all_reduce(sync_word)   # ... and this one starts, and so ends, nearly together on all ranks
     else:
         flush = flush_local
 

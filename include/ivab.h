@@ -298,16 +298,18 @@ int ivab_paged_decode_attn_noalloc(const void* q, int64_t q_stride_b, int64_t q_
  * has no parallel decode path; its collectives go through torch.distributed, src/utils/distributed.py:29-34).
  *   peer_bufs[r]  (host array of `world` device pointers) base of rank r's exchange buffer as mapped into THIS
  *                 process; peer_bufs[rank] is this rank's own buffer.  Every buffer has the layout
- *                 [slots][world][block_bytes] data rows, then at `flags_offset` `world` uint32 arrival counters,
+ *                 [slots][world][block_bytes] result rows, then at `staging_offset` a staging area of
+ *                 [slots][world][2 * block_bytes] bytes that the peers write ({payload, step tag} 64-bit words),
  *                 and must be zero before its first use (all ranks, before any rank's first call).
  *   epoch         device uint32 of this rank, zero before the first call: steps exchanged so far.
- * After the call's kernels have run, row r of slot (epoch_before % slots) of this rank's buffer holds rank
- * r's block.  Every rank must make the same sequence of calls.  Plain peer stores and loads only; the wait
- * for the peers is bounded by wait_limit_ns and sets IVAB_STATUS_WAIT_TIMEOUT in *status (device int32, may be
+ * After the call's kernel has run, result row r of slot (epoch_before % slots) of this rank's buffer holds rank
+ * r's block.  Every rank must make the same sequence of calls.  Plain peer stores and local loads only, no
+ * fence and no separate arrival flag (a word that carries the step's tag carries its payload); the wait for
+ * the peers is bounded by wait_limit_ns and sets IVAB_STATUS_WAIT_TIMEOUT in *status (device int32, may be
  * NULL) when it expires.  world <= 16, slots >= 2, block_bytes a multiple of 16.
  */
 int ivab_peer_allgather(const void* local_block, int64_t block_bytes, void* const* peer_bufs, int world, int rank,
-                        int slots, int64_t flags_offset, uint32_t* epoch, int32_t* status, int64_t wait_limit_ns,
+                        int slots, int64_t staging_offset, uint32_t* epoch, int32_t* status, int64_t wait_limit_ns,
                         void* stream);
 
 /*

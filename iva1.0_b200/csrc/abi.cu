@@ -52,7 +52,7 @@ extern "C" {
 
 const char* ivab_last_error(void) { return ivab::g_err; }
 
-int ivab_version(void) { return 110; }   // 110: decode entry points take out_dtype
+int ivab_version(void) { return 111; }   // 111: peer exchange buffers carry a staging area instead of arrival counters
 
 int64_t ivab_launch_count(void) { return ivab::g_launches.load(); }
 

@@ -60,7 +60,7 @@ def head_slice(n_q_heads: int, n_kv_heads: int, world: int, rank: int) -> Tuple[
 
 class PeerExchange:
     """All-gather of one small fp32 block per rank through peer-mapped memory: this library's own kernel
-    (``ivab_peer_allgather``: plain NVLink stores, one arrival counter per source rank, a bounded wait)
+    (``ivab_peer_allgather``: plain NVLink stores of {payload, step tag} words, a bounded wait per word)
     instead of an NCCL collective.  ``torch.distributed``'s symmetric memory allocates the buffer and maps it
     into every peer -- plumbing; the data path is the kernel.  All ranks must construct it together and make
     the same sequence of ``gather`` calls.
@@ -88,12 +88,13 @@ class PeerExchange:
         self.numel = int(numel)
         self.block_bytes = (self.numel * 4 + 15) // 16 * 16
         self.flags_off = self.SLOTS * self.world * self.block_bytes
-        total_words = (self.flags_off + 256) // 4
+        # result rows, then the staging area the peers write: every payload word as a {payload, step tag} pair
+        total_words = (self.flags_off + self.SLOTS * self.world * 2 * self.block_bytes) // 4
         self.buf = symm.empty(total_words, dtype=torch.float32, device=self.device)
         self.buf.zero_()
         torch.cuda.synchronize(self.device)
         self.handle = symm.rendezvous(self.buf, self.group)
-        dist.barrier(self.group)                       # every rank's counters are zero before anyone signals
+        dist.barrier(self.group)                       # every rank's staging area is zero before anyone sends
         torch.cuda.synchronize(self.device)
         # the address of every rank's copy of THIS tensor in this process's address space (the tensor may sit at
         # an offset inside a larger symmetric allocation, so the allocation's base pointers are not enough)
@@ -103,7 +104,8 @@ class PeerExchange:
             raise RuntimeError("symmetric memory: this rank's own mapping does not coincide with the local tensor")
         self._peer_array = (ctypes.c_void_p * self.world)(*ptrs)
         self._epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._status_block = torch.zeros(128, dtype=torch.int32, device=self.device)   # (debug builds write time stamps behind word 0)
+        self.status = self._status_block[:1]
         self._lib, self._check = _lib.load_library(), _lib.check
         self._stream_ptr = _lib.stream_ptr
         self.wait_limit_ns = int(wait_limit_ns)
