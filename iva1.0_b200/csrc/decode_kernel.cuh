@@ -581,6 +581,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
         dplan = direct_plan(p.ctx_len, p.ctx_begin, p.sink_tokens, p.max_pages, p.batch, p.n_virt_heads,
                             p.direct_target_items, p.direct_min_chunk, p.direct_big_target_items, p.direct_big_pages, p.direct_grid, lane);
     grid_dependency_wait();   // the attention kernel's partial results
+    // Whatever follows as a programmatic dependent (the next step's plan or attention kernel, the peer exchange)
+    // may be placed now: it waits for this grid to finish before it reads anything this kernel writes.
+    grid_launch_dependents();
     // the attention kernel is done with the plan-free work counter: leave it zeroed and signed for the next call
     if (direct && p.direct_dynamic && blockIdx.x == 0 && threadIdx.x == 0)
         *reinterpret_cast<int4*>(ws.header + kHdrDirectCounter) = make_int4(0, kDirectSig0, kDirectSig1, kDirectSig2);
