@@ -313,6 +313,30 @@ int ivab_peer_allgather(const void* local_block, int64_t block_bytes, void* cons
                         void* stream);
 
 /*
+ * Head-parallel decode step with the all-gather folded into it: ivab_paged_decode_step (k_new / v_new may both
+ * be NULL: attention only) whose fp32 output rows and logsumexp are written into `local_block` and exchanged
+ * as ivab_peer_allgather would -- by the merge kernel's last CTA, so that no exchange kernel is launched
+ * behind the step (a step whose block table is too narrow for any split has no merge kernel; the
+ * stand-alone exchange kernel is launched then).  `out` (fp32, strides in elements) and `lse` must lie
+ * inside [local_block, local_block + block_bytes); the exchange arguments are those of ivab_peer_allgather.
+ * Every rank must make the same sequence of calls; batch must be positive.
+ * No counterpart in the reference (it has no parallel decode path).
+ */
+int ivab_paged_decode_step_allgather(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                     const void* k_new, const void* v_new, int64_t new_stride_t, int64_t new_stride_h,
+                                     void* k_pool, void* v_pool, int64_t pool_stride_head, int64_t pool_stride_page,
+                                     int kv_dtype, float k_scale, float v_scale,
+                                     const int32_t* block_table, int64_t block_table_stride,
+                                     const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
+                                     void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                                     int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                                     int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq,
+                                     float scale, void* workspace, size_t workspace_bytes,
+                                     const void* local_block, int64_t block_bytes, void* const* peer_bufs, int world,
+                                     int rank, int slots, int64_t staging_offset, uint32_t* epoch,
+                                     int32_t* exchange_status, int64_t wait_limit_ns, void* stream);
+
+/*
  * Number of kernels of this library launched by the calling process since load
  * (for benchmark bookkeeping).
  */

@@ -50,6 +50,12 @@ SIGNATURES = {
                                        c_int64, c_int64, c_int, c_float, c_float, c_void_p, c_int64, c_void_p, c_void_p,
                                        c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int, c_int] + [c_int64] * 7 +
                                [c_float, c_void_p, c_size_t, c_void_p]),
+    "ivab_paged_decode_step_allgather": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                                                 c_int64, c_int64, c_int, c_float, c_float, c_void_p, c_int64, c_void_p, c_void_p,
+                                                 c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int] + [c_int64] * 7 +
+                                         [c_float, c_void_p, c_size_t,
+                                          c_void_p, c_int64, POINTER(c_void_p), c_int, c_int, c_int, c_int64, c_void_p, c_void_p,
+                                          c_int64, c_void_p]),
     "ivab_peer_allgather": (c_int, [c_void_p, c_int64, POINTER(c_void_p), c_int, c_int, c_int, c_int64, c_void_p, c_void_p,
                                     c_int64, c_void_p]),
     "ivab_decode_status": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),

@@ -73,7 +73,8 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
                            lse: Optional[torch.Tensor] = None, return_lse: bool = False,
                            workspace: Optional[torch.Tensor] = None, check: bool = False,
                            ctx_begin: Optional[torch.Tensor] = None, sink_tokens: int = 0,
-                           k_scale: float = 1.0, v_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None):
+                           k_scale: float = 1.0, v_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None,
+                           exchange=None):
     """``out[s,h] = softmax(q[s,h] . K_s^T * scale) . V_s`` over the ``ctx_len[s]`` cached tokens of
     sequence ``s``, K/V read in place from the page pool through ``block_table``.
 
@@ -100,7 +101,7 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         raise ValueError("8-bit pools need fp16 or bf16 queries")
     return _decode(q, k_pool, v_pool, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
                    out, lse, return_lse, workspace, check, ctx_begin, sink_tokens,
-                   (float(k_scale), float(v_scale)) if fp8 else None, out_dtype)
+                   (float(k_scale), float(v_scale)) if fp8 else None, out_dtype, exchange=exchange)
 
 
 def paged_decode_step(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_pool: torch.Tensor,
@@ -109,7 +110,8 @@ def paged_decode_step(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
                       lse: Optional[torch.Tensor] = None, return_lse: bool = False,
                       workspace: Optional[torch.Tensor] = None, check: bool = False,
                       ctx_begin: Optional[torch.Tensor] = None, sink_tokens: int = 0,
-                      k_scale: float = 1.0, v_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None):
+                      k_scale: float = 1.0, v_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None,
+                      exchange=None):
     """One decode step in one call: append one new token per sequence (``k_new`` / ``v_new`` ``[B,H_kv,D]`` in q's
     dtype) and attend over the cache including it -- ``paged_append`` followed by ``paged_decode_attention``
     without the separate copy launch (the concat-append plus attention of src/core/attention.py:61-63,77,99,102
@@ -132,12 +134,12 @@ def paged_decode_step(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
         k_new, v_new = k_new.contiguous(), v_new.contiguous()
     return _decode(q, k_pool, v_pool, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
                    out, lse, return_lse, workspace, check, ctx_begin, sink_tokens,
-                   (float(k_scale), float(v_scale)) if fp8 else None, out_dtype, new_tokens=(k_new, v_new))
+                   (float(k_scale), float(v_scale)) if fp8 else None, out_dtype, new_tokens=(k_new, v_new), exchange=exchange)
 
 
 def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, page_size, scale,
             out, lse, return_lse, workspace, check, ctx_begin=None, sink_tokens=0, fp8_scales=None, out_dtype=None,
-            new_tokens=None):
+            new_tokens=None, exchange=None):
     """Argument checks and the library call; ``k_base`` / ``v_base`` only supply base pointers, the
     pool geometry is given by ``Hkv, num_pages, sh, sp`` (element strides of head and page).
     ``new_tokens=(k_new, v_new)`` selects the fused step (append + attention)."""
@@ -189,7 +191,25 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
                 block_table.shape[1],
                 float(scale), workspace.data_ptr(), workspace.numel(), stream)
         head = (q.data_ptr(), q.stride(0), q.stride(1), k_base.data_ptr(), v_base.data_ptr(), sh, sp)
-        if new_tokens is not None:
+        if exchange is not None:
+            # head-parallel step: ``exchange = (PeerExchange, block)``; out / lse are fp32 views into ``block``, which the
+            # merge kernel's last CTA sends to the peers (sharding.HeadParallelDecoder sets this up)
+            px, block = exchange
+            if out_dtype != torch.float32 or lse is None:
+                raise ValueError("a step with an exchange writes fp32 rows and the logsumexp into the exchanged block")
+            kn, vn = new_tokens if new_tokens is not None else (None, None)
+            ks, vs = fp8_scales if fp8_scales is not None else (1.0, 1.0)
+            _lib.check(lib.ivab_paged_decode_step_allgather(
+                q.data_ptr(), q.stride(0), q.stride(1), kn.data_ptr() if kn is not None else None,
+                vn.data_ptr() if vn is not None else None, kn.stride(0) if kn is not None else 0,
+                kn.stride(1) if kn is not None else 0, k_base.data_ptr(), v_base.data_ptr(), sh, sp,
+                _lib.F8E4M3 if fp8_scales is not None else _lib.dtype_code(q.dtype), ks, vs,
+                block_table.data_ptr(), block_table.stride(0), ctx_len.data_ptr(),
+                ctx_begin.data_ptr() if ctx_begin is not None else None, int(sink_tokens),
+                out.data_ptr(), out.stride(0), out.stride(1), lse.data_ptr(), _lib.dtype_code(q.dtype),
+                B, Hq, Hkv, D, page_size, num_pages, block_table.shape[1], float(scale), workspace.data_ptr(), workspace.numel(),
+                *px.exchange_args(block), stream))
+        elif new_tokens is not None:
             kn, vn = new_tokens
             ks, vs = fp8_scales if fp8_scales is not None else (1.0, 1.0)
             _lib.check(lib.ivab_paged_decode_step(

@@ -394,7 +394,8 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
                  int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                  int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq, float scale,
                  void* workspace, size_t workspace_bytes, void* stream,
-                 const void* k_new = nullptr, const void* v_new = nullptr, int64_t new_stride_t = 0, int64_t new_stride_h = 0) {
+                 const void* k_new = nullptr, const void* v_new = nullptr, int64_t new_stride_t = 0, int64_t new_stride_h = 0,
+                 const PeerParams* xchg = nullptr) {
     const size_t esz = dtype_size(dtype);
     const size_t kv_esz = dtype_size(kv_dtype);
     if (esz == 0 || kv_esz == 0) return set_error(IVAB_ERR_INVALID, "%s: unknown dtype %d / %d", fn, dtype, kv_dtype);
@@ -478,6 +479,7 @@ int decode_entry(const char* fn, const void* q, int64_t q_stride_b, int64_t q_st
     p.k_new = static_cast<const char*>(k_new); p.v_new = static_cast<const char*>(v_new);
     p.new_st_bytes = new_stride_t * (int64_t)esz; p.new_sh_bytes = new_stride_h * (int64_t)esz;
     p.k_inv_scale = 1.f / k_scale; p.v_inv_scale = 1.f / v_scale;
+    if (xchg != nullptr) { p.xchg_on = 1; p.xchg = *xchg; }
     const int G = p.group;
     if (kv_dtype == IVAB_F8E4M3) {
         if (dtype == IVAB_F16) return decode_dispatch_fp8_f16((int)head_dim, G, (int)kv_heads, p, (int)batch, st);
@@ -550,6 +552,43 @@ extern "C" int ivab_paged_decode_step(const void* q, int64_t q_stride_b, int64_t
                         out_dtype, kv_dtype, k_scale, v_scale, batch, q_heads, kv_heads, head_dim, page_size, num_pages,
                         max_pages_per_seq, scale, workspace, workspace_bytes, stream, k_new, v_new, new_stride_t,
                         new_stride_h);
+}
+
+extern "C" int ivab_paged_decode_step_allgather(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                                const void* k_new, const void* v_new, int64_t new_stride_t, int64_t new_stride_h,
+                                                void* k_pool, void* v_pool, int64_t pool_stride_head, int64_t pool_stride_page,
+                                                int kv_dtype, float k_scale, float v_scale,
+                                                const int32_t* block_table, int64_t block_table_stride,
+                                                const int32_t* ctx_len, const int32_t* ctx_begin, int64_t sink_tokens,
+                                                void* out, int64_t out_stride_b, int64_t out_stride_h, float* lse,
+                                                int dtype, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                                                int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages_per_seq,
+                                                float scale, void* workspace, size_t workspace_bytes,
+                                                const void* local_block, int64_t block_bytes, void* const* peer_bufs, int world,
+                                                int rank, int slots, int64_t staging_offset, uint32_t* epoch,
+                                                int32_t* exchange_status, int64_t wait_limit_ns, void* stream) {
+    const char* fn = "ivab_paged_decode_step_allgather";
+    if ((k_new != nullptr) != (v_new != nullptr)) return set_error(IVAB_ERR_INVALID, "%s: k_new and v_new go together", fn);
+    if (kv_dtype != dtype && kv_dtype != IVAB_F8E4M3)
+        return set_error(IVAB_ERR_UNSUPPORTED, "%s: the pools hold the dtype of q, or IVAB_F8E4M3", fn);
+    if (kv_dtype == IVAB_F8E4M3 && (!(k_scale > 0.f) || !(v_scale > 0.f)))
+        return set_error(IVAB_ERR_INVALID, "%s: scales must be positive", fn);
+    if (kv_dtype != IVAB_F8E4M3) k_scale = v_scale = 1.f;
+    if (batch <= 0) return set_error(IVAB_ERR_INVALID, "%s: every rank must take part in the exchange: batch must be positive", fn);
+    PeerParams pp{};
+    if (int rc = make_peer_params(fn, local_block, block_bytes, peer_bufs, world, rank, slots, staging_offset, epoch,
+                                  exchange_status, wait_limit_ns, &pp)) return rc;
+    // the rows this call writes are the block that is sent: fp32, inside [local_block, local_block + block_bytes)
+    const char* lo = static_cast<const char*>(local_block);
+    const char* o = static_cast<const char*>(out);
+    if (!out || o < lo || o >= lo + block_bytes || (lse && (reinterpret_cast<const char*>(lse) < lo ||
+                                                            reinterpret_cast<const char*>(lse) >= lo + block_bytes)))
+        return set_error(IVAB_ERR_INVALID, "%s: out (and lse) must lie inside the block that is exchanged", fn);
+    return decode_entry(fn, q, q_stride_b, q_stride_h, k_pool, v_pool, pool_stride_head, pool_stride_page, block_table,
+                        block_table_stride, ctx_len, ctx_begin, sink_tokens, out, out_stride_b, out_stride_h, lse, dtype,
+                        IVAB_F32, kv_dtype, k_scale, v_scale, batch, q_heads, kv_heads, head_dim, page_size, num_pages,
+                        max_pages_per_seq, scale, workspace, workspace_bytes, stream, k_new, v_new, new_stride_t,
+                        new_stride_h, &pp);
 }
 
 extern "C" int ivab_decode_status(const void* workspace, int32_t* status_out, void* stream) {

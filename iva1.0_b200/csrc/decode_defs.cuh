@@ -7,6 +7,7 @@
 #include <cstdint>
 
 #include "common.cuh"
+#include "peer_exchange.cuh"
 
 namespace ivab {
 namespace {
@@ -59,6 +60,7 @@ enum { kHdrNumChunks = 0, kHdrChunkPages = 1, kHdrCounter = 2, kHdrStatus = 3, k
        // that does not (the first call on a workspace, whose memory is not initialised) assigns them statically,
        // as every call does for a batch that is not large.
        kHdrDirectCounter = 8, kHdrDirectSig = 9,
+       kHdrMergeDone = 12,   // merge CTAs that have finished (zeroed by attention CTA 0 of the same call); the last one runs the peer exchange
        kHdrWords = 64 };
 // Status protocol.  header[kHdrStatus] holds the bits of the planning step: written by the plan kernel,
 // or (plan-free mode) by CTA 0 of the attention kernel.  Every CTA of the attention kernel additionally
@@ -117,6 +119,8 @@ struct DecodeParams {
     int direct_dynamic;                        // 1: a merge kernel follows and re-arms the work counter, so the attention kernel may use it
     int direct_big_target_items;               // target_items of a large batch (0: same as direct_target_items)
     int direct_big_pages;                      // pages per CTA from which a batch counts as large
+    int xchg_on;                               // head-parallel decode: the last merge CTA also runs the all-gather over peer memory
+    PeerParams xchg;
     int status_slots_per_cta;                  // 2 when the grid is one CTA per SM, else 1
     int chunk_major;                           // order in which items are handed out: 0, 1, or 2 = as the plan kernel decided
     const int32_t* ctx_len; const int32_t* ctx_begin;

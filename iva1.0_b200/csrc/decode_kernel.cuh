@@ -158,6 +158,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
                 const int st = *reinterpret_cast<volatile int*>(cta_status) | (*abort_flag ? kStatusWaitTimeout : 0);
                 for (int k = 0; k < p.status_slots_per_cta; ++k) p.ws.status_slots[blockIdx.x + k * gridDim.x] = st;
                 if (direct && blockIdx.x == 0) p.ws.header[kHdrStatus] = 0;
+                if (p.xchg_on && blockIdx.x == 0) p.ws.header[kHdrMergeDone] = 0;   // counted up by the merge CTAs of this call
             }
         }
     };
@@ -591,11 +592,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     if (threadIdx.x == 0) PROF_STAMP_MIN(ws.header, 6, globaltimer_ns())
 #endif
     const int num_chunks = direct ? dplan.num_chunks : ws.header[kHdrNumChunks];
-    if (direct && num_chunks > ws.cap) return;   // flagged by the attention kernel; nothing was computed
+    const bool skip = direct && num_chunks > ws.cap;   // flagged by the attention kernel; nothing was computed
     // units of pass A / B: the plan kernel's lists of split sequences, or (plan-free) every sequence, of
     // which those with a fitting chunk count are taken
-    const int n_small = direct ? B : ws.header[kHdrNumSplit];   // single-chunk sequences were written by the attention kernel
-    const int n_big = direct ? (__any_sync(0xffffffffu, dplan.n > kMergeWarpMax) ? B : 0) : ws.header[kHdrNumBig];
+    const int n_small = skip ? 0 : (direct ? B : ws.header[kHdrNumSplit]);   // single-chunk sequences were written by the attention kernel
+    const int n_big = skip ? 0 : (direct ? (__any_sync(0xffffffffu, dplan.n > kMergeWarpMax) ? B : 0) : ws.header[kHdrNumBig]);
     // a lane's VPL outputs go out as one store when every output row is aligned for it
     constexpr int kVecBytes = VPL * (int)sizeof(T);
     const bool vec_out = !out_f32 && VPL >= 2 && (sizeof(T) == 2 || VPL % 4 == 0) &&
@@ -674,12 +675,6 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     }
 
     // ---- pass B
-    if (n_big == 0) {
-#ifdef IVAB_PROFILE
-        if (threadIdx.x == 0) PROF_STAMP_MAX(ws.header, 7, globaltimer_ns())
-#endif
-        return;
-    }
     __shared__ float sh_m[kMergeWarps];
     __shared__ float sh_l[kMergeWarps];
     __shared__ __align__(16) float sh_o[kMergeWarps][32];
@@ -747,6 +742,25 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
 #ifdef IVAB_PROFILE
     if (threadIdx.x == 0) PROF_STAMP_MAX(ws.header, 7, globaltimer_ns())
 #endif
+    // ---- head-parallel decode: the CTA that finishes last sends this rank's rows to the peers and collects theirs,
+    // so the step needs no exchange launch behind this kernel.  (The rows also hold what the attention kernel
+    // wrote for unsplit sequences: that grid finished before any CTA here passed its dependency wait.)
+    if (p.xchg_on) {
+        __shared__ int s_last;
+        __syncthreads();   // this CTA's rows are written
+        if (threadIdx.x == 0) {
+            __threadfence();
+            s_last = atomicAdd(ws.header + kHdrMergeDone, 1) == (int)gridDim.x - 1;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();   // the other CTAs' rows, published before their increments
+            const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(p.xchg.epoch);
+            peer_exchange_step(p.xchg, epoch, warp, kMergeWarps, lane);
+            __syncthreads();
+            if (threadIdx.x == 0) *p.xchg.epoch = epoch + 1u;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -910,7 +924,7 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
     const int merge_grid = (int)(units < (long long)sm_count() * 4 ? units : (long long)sm_count() * 4);
     cfg.gridDim = dim3(merge_grid); cfg.blockDim = dim3(kMergeWarps * 32); cfg.dynamicSmemBytes = 0;
     // plan-free mode with a block table no wider than the smallest chunk: no sequence can be split, nothing to merge
-    if (p.direct && p.max_pages <= p.direct_min_chunk) return IVAB_OK;
+    if (p.direct && p.max_pages <= p.direct_min_chunk) return p.xchg_on ? launch_peer_allgather(p.xchg, st) : IVAB_OK;
     if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, merge_kernel<T, D>, p, B), "merge_kernel launch")) {
         // (the counter stays as the attention kernel leaves it: drop the signature so that no later call trusts it)
         if (p.direct_dynamic) cudaMemsetAsync(p.ws.header + kHdrDirectCounter, 0, 4 * sizeof(int), st);

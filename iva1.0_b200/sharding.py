@@ -113,14 +113,18 @@ class PeerExchange:
                       .view(self.world, self.block_bytes).view(torch.float32)[:, :self.numel] for s in range(self.SLOTS)]
         self._steps = 0
 
-    def enqueue(self, block: torch.Tensor) -> None:
-        """Enqueue one exchange of ``block`` (fp32, ``numel`` elements, 16-byte aligned) on the current stream."""
+    def exchange_args(self, block: torch.Tensor) -> tuple:
+        """The exchange arguments of ``ivab_peer_allgather`` / ``ivab_paged_decode_step_allgather`` for ``block``
+        (everything between the block pointer and the stream)."""
         if block.dtype != torch.float32 or block.numel() != self.numel or not block.is_contiguous():
             raise ValueError("block must be a contiguous fp32 tensor of the size given at construction")
+        return (block.data_ptr(), self.block_bytes, self._peer_array, self.world, self.rank, self.SLOTS, self.flags_off,
+                self._epoch.data_ptr(), self.status.data_ptr(), self.wait_limit_ns)
+
+    def enqueue(self, block: torch.Tensor) -> None:
+        """Enqueue one exchange of ``block`` (fp32, ``numel`` elements, 16-byte aligned) on the current stream."""
         with torch.cuda.device(self.device):
-            self._check(self._lib.ivab_peer_allgather(
-                block.data_ptr(), self.block_bytes, self._peer_array, self.world, self.rank, self.SLOTS, self.flags_off,
-                self._epoch.data_ptr(), self.status.data_ptr(), self.wait_limit_ns, self._stream_ptr(self.device)))
+            self._check(self._lib.ivab_peer_allgather(*self.exchange_args(block), self._stream_ptr(self.device)))
 
     def rows(self, step: int) -> torch.Tensor:
         """``[world, numel]`` view of the slot that the ``step``-th exchange (counted from 0) fills."""
@@ -183,6 +187,8 @@ class HeadParallelDecoder:
             paged_decode_step(q, new_tokens[0], new_tokens[1], k_pool_local, v_pool_local, block_table, ctx_len,
                               page_size, scale, out=out_view, lse=lse_view, out_dtype=torch.float32, **kw)
         elif self._native:
+            # (``exchange`` in kw: the library's own attention entry point takes it; the step then ends with the
+            #  all-gather, run by the merge kernel's last CTA)
             self.attn_fn(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out=out_view,
                          lse=lse_view, out_dtype=torch.float32, **kw)
         else:
@@ -258,12 +264,16 @@ class HeadParallelDecoder:
 
         peer = self._peer_exchange(flat.numel(), dev) if (self.exchange == "p2p" and self.world > 1) else None
 
+        fused_exchange = peer is not None and self._native
+        if fused_exchange:
+            extra["exchange"] = (peer, flat)   # the merge kernel's last CTA sends the block and collects the peers'
+
         def local():
             if before is not None:
                 before()
             self._local(q, k_pool_local, v_pool_local, block_table, ctx_len, page_size, scale, out_view, lse_view,
                         new_tokens=new_tokens, **extra)
-            if peer is not None:
+            if peer is not None and not fused_exchange:
                 peer.enqueue(flat)           # the exchange is part of the recording: a step is one graph replay
 
         side = torch.cuda.Stream(device=dev)

@@ -156,6 +156,59 @@ def test_step_buffers_keep_two_steps_apart():
     assert step.graph is not None and step.inputs(1).graph is not None
 
 
+class _SelfExchange:
+    """The exchange buffers of a one-rank "group": the library's all-gather with this GPU as its only peer,
+    which exercises the kernels (send, poll, slots, step counter) without a second GPU."""
+
+    SLOTS = 2
+
+    def __init__(self, numel):
+        import ctypes
+        self.numel = numel
+        self.block_bytes = (numel * 4 + 15) // 16 * 16
+        self.staging_off = self.SLOTS * self.block_bytes
+        self.buf = torch.zeros((self.staging_off + self.SLOTS * 2 * self.block_bytes) // 4, dtype=torch.float32, device=DEV)
+        self.peers = (ctypes.c_void_p * 1)(self.buf.data_ptr())
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=DEV)
+        self.status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def exchange_args(self, block):
+        return (block.data_ptr(), self.block_bytes, self.peers, 1, 0, self.SLOTS, self.staging_off,
+                self.epoch.data_ptr(), self.status.data_ptr(), 1_000_000_000)
+
+    def row(self, step):
+        return self.buf.view(torch.uint8)[(step % 2) * self.block_bytes:(step % 2 + 1) * self.block_bytes].view(torch.float32)[:self.numel]
+
+
+@pytest.mark.parametrize("ctx", [[3000, 70, 1500], [20, 5, 31], [40000]])
+def test_step_that_ends_in_the_all_gather(ctx):
+    """``ivab_paged_decode_step_allgather``: the rows of a step are written into one block and exchanged by the
+    merge kernel's last CTA (or, when no sequence can be split, by the stand-alone exchange kernel).  One rank:
+    the result row must be the block, the block must be the plain fp32 result, over four steps (both slots)."""
+    wl = workloads.make_decode_workload("xchg", torch.tensor(ctx), n_q_heads=8, n_kv_heads=2, head_dim=128, seed=31).to(DEV)
+    B, Hq, D = wl.q.shape
+    flat = torch.zeros(B * Hq * (D + 1), dtype=torch.float32, device=DEV)
+    out_view, lse_view = flat[:B * Hq * D].view(B, Hq, D), flat[B * Hq * D:].view(B, Hq)
+    xch = _SelfExchange(flat.numel())
+    lens = (wl.ctx_len + 1).contiguous()
+    ref_pools = (wl.k_pool.clone(), wl.v_pool.clone())
+    o_ref, l_ref = iva_b200.paged_decode_step(wl.q, wl.k_new, wl.v_new, ref_pools[0], ref_pools[1], wl.block_table, lens, 16,
+                                              return_lse=True, out_dtype=torch.float32, check=True)
+    for step in range(4):
+        flat.zero_()
+        if step % 2 == 0:
+            iva_b200.paged_decode_step(wl.q, wl.k_new, wl.v_new, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                       out=out_view, lse=lse_view, out_dtype=torch.float32, check=True, exchange=(xch, flat))
+        else:       # attention only (the token is in the pool already)
+            iva_b200.paged_decode_attention(wl.q, wl.k_pool, wl.v_pool, wl.block_table, lens, 16,
+                                            out=out_view, lse=lse_view, out_dtype=torch.float32, check=True, exchange=(xch, flat))
+        torch.cuda.synchronize()
+        assert int(xch.status.item()) == 0 and int(xch.epoch.item()) == step + 1
+        assert torch.equal(out_view, o_ref) and torch.equal(lse_view, l_ref)
+        assert torch.equal(xch.row(step), flat)
+    assert torch.equal(wl.k_pool, ref_pools[0]) and torch.equal(wl.v_pool, ref_pools[1])
+
+
 def test_fp8_cache_object():
     cache = iva_b200.PagedKVCache(batch_size=2, n_heads=2, head_dim=128, device=DEV, dtype=torch.float8_e4m3fn,
                                   max_seq_len=64, k_scale=0.02, v_scale=0.02)
