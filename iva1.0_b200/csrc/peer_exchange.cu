@@ -1,7 +1,7 @@
 // All-gather of one small block per rank over peer-mapped memory (NVLink stores), for the head-parallel
 // decode of one long sequence: every rank ends a step with a few KB of output rows, and every rank needs all
-// of them.  One warp per peer: it stores this rank's block into that peer's staging area and collects that
-// peer's block from its own.  No library collective, no host round trip: the exchange is one more kernel in
+// of them.  The warps of one CTA share the (peer, unit of the block) pairs: each stores its units of this
+// rank's block into the peers' staging areas and collects the same units of the peers' blocks from its own.  No library collective, no host round trip: the exchange is one more kernel in
 // the step's stream (or CUDA graph), launched as a programmatic dependent of the kernel before it.
 //
 // Flag-in-data protocol: every 32-bit payload word travels as one 64-bit store {payload, tag} with
@@ -30,8 +30,9 @@ extern std::atomic<long long> g_launches;
 
 namespace {
 
-// One CTA; warp r serves peer r: it sends this rank's block to rank r and collects rank r's block here.
-__global__ void __launch_bounds__(kMaxPeers * 32) peer_allgather_kernel(const PeerParams pp) {
+// One CTA of kExchangeWarps warps that share the (peer, unit of the block) pairs.
+constexpr int kExchangeWarps = 16;
+__global__ void __launch_bounds__(kExchangeWarps * 32) peer_allgather_kernel(const PeerParams pp) {
     grid_dependency_wait();   // the block is the output of the kernels before this one
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned int epoch = *pp.epoch;
@@ -74,7 +75,7 @@ int launch_peer_allgather(const PeerParams& pp, cudaStream_t st) {
     pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl.val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(1); cfg.blockDim = dim3(pp.world * 32); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cfg.gridDim = dim3(1); cfg.blockDim = dim3(kExchangeWarps * 32); cfg.dynamicSmemBytes = 0; cfg.stream = st;
     cfg.attrs = &pdl; cfg.numAttrs = 1;
     if (int rc = check_cuda(cudaLaunchKernelEx(&cfg, peer_allgather_kernel, pp), "peer_allgather_kernel launch")) return rc;
     g_launches++;
