@@ -656,8 +656,9 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True, exchange="nccl"):
             "kv_heads_per_rank": wl.n_kv_heads // world, "collective": None if world == 1 else (
                 "one NCCL all_gather_into_tensor of [1, H_q/N, D+1] fp32 per step (eager; local kernels in a CUDA graph)"
                 if exchange == "nccl" else
-                "ivab_peer_allgather: this library's kernel over peer-mapped memory (NVLink stores of {payload, step tag} words, no fence), "
-                "recorded in the same CUDA graph as the local kernels: one graph replay per step, no NCCL call"),
+                "ivab_paged_decode_step_allgather: the merge kernel's last CTA sends this rank's rows to the peers over NVLink "
+                "({payload, step tag} words into peer-mapped memory, no fence) and collects theirs; one graph replay per step, "
+                "no exchange launch, no NCCL call"),
             "l2": "flushed between timed steps" + ("; ranks aligned by a one-word all-reduce behind each flush, "
                                                     "outside the timed region" if world > 1 else "")}
 
