@@ -52,10 +52,10 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch from an ncu capture,
 # as a multiple of the algorithmic bytes of that launch (see profiles/); None until captured.
-# c2: 8-sequence case, 539.11 MB read + 4.42 MB written (mean of two launches) for 537.14 MB algorithmic;
-# c3: 32-sequence case, 350.44 MB + 3.65 MB for 349.93 MB.  Traffic grows with the tokens read, so the
+# c2: 8-sequence case, 539.11 MB read + 4.06 MB written (mean of two launches) for 537.14 MB algorithmic;
+# c3: 32-sequence case, 350.44 MB + 4.98 MB for 349.93 MB.  Traffic grows with the tokens read, so the
 # ratio carries over to the full-size launch.
-NCU_TRAFFIC_RATIO = {"c2": (539.11 + 4.42) / 537.14, "c3": (350.44 + 3.65) / 349.93, "c5a": (350.44 + 3.65) / 349.93}
+NCU_TRAFFIC_RATIO = {"c2": (539.11 + 4.06) / 537.14, "c3": (350.44 + 4.98) / 349.93, "c5a": (350.44 + 4.98) / 349.93}
 
 
 def measured_peak():
