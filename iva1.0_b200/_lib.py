@@ -137,6 +137,17 @@ def require_cuda(*tensors) -> None:
             )
 
 
+def require_device_readable(*tensors) -> None:
+    """CUDA tensors, or pinned host tensors (page-locked memory is mapped into the device's address space under
+    unified addressing, so a kernel can read it in place over the bus)."""
+    for t in tensors:
+        if t is not None and not t.is_cuda and not t.is_pinned():
+            raise RuntimeError(
+                "iva_b200 operators read CUDA tensors or pinned host tensors only (got pageable memory on "
+                f"{t.device}); there is no CPU implementation in this package"
+            )
+
+
 def status_message(status: int) -> str:
     names = []
     for bit, name in ((1, "a bounded in-kernel wait timed out"), (2, "block-table entry out of range"),

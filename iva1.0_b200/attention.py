@@ -118,7 +118,10 @@ def paged_decode_step(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
     for a one-token step).  ``ctx_len`` INCLUDES the new token, which is stored at position ``ctx_len[s] - 1``
     through the block table (its page must already be in the table).  The pools end up bit-identical to the
     two-call sequence, and so does the result.  Other arguments as for ``paged_decode_attention``."""
-    _lib.require_cuda(q, k_new, v_new, k_pool, v_pool, block_table, ctx_len)
+    # q, the new tokens and the lengths may also be pinned host tensors, read in place by the kernels (the pools and
+    # the block table, which are read many times, have to be in device memory)
+    _lib.require_cuda(k_pool, v_pool, block_table)
+    _lib.require_device_readable(q, k_new, v_new, ctx_len)
     Hkv, num_pages, sh, sp = _pool_strides(k_pool, page_size)
     if _pool_strides(v_pool, page_size) != (Hkv, num_pages, sh, sp) or v_pool.dtype != k_pool.dtype:
         raise ValueError("k_pool and v_pool must have the same shape, strides and dtype")
@@ -146,7 +149,7 @@ def _decode(q, k_base, v_base, Hkv, num_pages, sh, sp, block_table, ctx_len, pag
     if q.requires_grad:
         raise RuntimeError("paged_decode_attention is inference-only")
     lib = _lib.load_library()
-    dev = q.device
+    dev = k_base.device
     if q.dim() != 3:
         raise ValueError("q must be [batch, q_heads, head_dim]")
     B, Hq, D = q.shape

@@ -19,6 +19,10 @@ other buffer and read step k's result from the buffer it ran from: ``inputs(b)``
 views, ``run(b)`` enqueues it, ``result(b)`` waits for it.  ``run()`` / ``result()`` without an
 argument and the ``*_host`` attributes address buffer 0, for a host that takes one step at a time.
 
+``zero_copy_inputs=True`` drops the upload: the kernels read the query, the new tokens and the lengths from the
+pinned staging block in place (page-locked host memory is addressable from the device), so those bytes cross the
+bus while the attention kernel streams the pools instead of in front of it.
+
 What may overlap is the caller's business: inside one sequence, step k+1's query (and its K/V)
 depend on step k's output, so that host has to read ``result()`` before it can fill the next inputs,
 and nothing overlaps.  A server that keeps two independent batches in flight (each with its own
@@ -55,7 +59,7 @@ class GraphedDecodeStep:
                  use_graph: bool = True, direct_host_output: bool = True,
                  token_dtype: Optional[torch.dtype] = None, k_scale: float = 1.0, v_scale: float = 1.0,
                  n_buffers: int = 2, out_dtype: Optional[torch.dtype] = None,
-                 stream: Optional[torch.cuda.Stream] = None, fused: bool = True):
+                 stream: Optional[torch.cuda.Stream] = None, fused: bool = True, zero_copy_inputs: bool = False):
         if not k_pool.is_cuda:
             raise RuntimeError("GraphedDecodeStep needs CUDA tensors; there is no CPU implementation")
         if n_buffers < 1:
@@ -130,6 +134,12 @@ class GraphedDecodeStep:
         # block table gives for ctx_len - 1; slot_mapping_host is then not used.  fused=False keeps the separate
         # append through the slot mapping.
         self.fused = fused
+        # zero_copy_inputs (fused steps only): no upload at all -- the kernels read q, the new tokens and the lengths
+        # from the pinned staging block in place, while they stream the pools, instead of waiting for a
+        # host->device copy in front of the step.
+        if zero_copy_inputs and not fused:
+            raise ValueError("zero_copy_inputs needs the fused step")
+        self.zero_copy_inputs = zero_copy_inputs
         self._last = 0
 
     @property
@@ -147,8 +157,11 @@ class GraphedDecodeStep:
         return self._bufs[buf]
 
     def _enqueue(self, b: SimpleNamespace) -> None:
-        b.stage_dev.copy_(b.stage_host, non_blocking=True)
-        q, k_new, v_new, slots, lens = b.devs
+        if self.zero_copy_inputs:
+            q, k_new, v_new, slots, lens = b.q_host, b.k_new_host, b.v_new_host, b.slot_mapping_host, b.ctx_len_host
+        else:
+            b.stage_dev.copy_(b.stage_host, non_blocking=True)
+            q, k_new, v_new, slots, lens = b.devs
         scales = dict(k_scale=self.k_scale, v_scale=self.v_scale) if self.fp8 else {}
         out, lse = (b.out_host, b.lse_host) if self.direct_host_output else (b.out_dev, b.lse_dev)
         if self.fused:

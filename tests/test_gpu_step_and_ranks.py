@@ -18,8 +18,9 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.mark.parametrize("use_graph,direct", [(False, False), (True, False), (True, True)])
-def test_graphed_decode_steps_follow_the_dense_reference(use_graph, direct):
+@pytest.mark.parametrize("use_graph,direct,zero_copy", [(False, False, False), (True, False, False), (True, True, False),
+                                                        (True, True, True), (False, True, True)])
+def test_graphed_decode_steps_follow_the_dense_reference(use_graph, direct, zero_copy):
     """Six consecutive decode steps from pinned host buffers; every step is checked against the
     CPU checker on the pool it should have produced."""
     cache = iva_b200.PagedKVCache(batch_size=3, n_heads=2, head_dim=128, device=DEV, dtype=torch.bfloat16,
@@ -29,7 +30,8 @@ def test_graphed_decode_steps_follow_the_dense_reference(use_graph, direct):
     prompt_v = torch.randn(3, 40, 2, 128, generator=g).to(torch.bfloat16)
     cache.append(prompt_k.to(DEV), prompt_v.to(DEV))
     step = iva_b200.GraphedDecodeStep(cache.k_pool, cache.v_pool, cache.block_table_dev, n_q_heads=8,
-                                      return_lse=True, use_graph=use_graph, direct_host_output=direct)
+                                      return_lse=True, use_graph=use_graph, direct_host_output=direct,
+                                      zero_copy_inputs=zero_copy)
     k_ref, v_ref = cache.k_pool.cpu(), cache.v_pool.cpu()
     for t in range(6):
         L = 40 + t
