@@ -104,8 +104,7 @@ class PeerExchange:
             raise RuntimeError("symmetric memory: this rank's own mapping does not coincide with the local tensor")
         self._peer_array = (ctypes.c_void_p * self.world)(*ptrs)
         self._epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._status_block = torch.zeros(128, dtype=torch.int32, device=self.device)   # (debug builds write time stamps behind word 0)
-        self.status = self._status_block[:1]
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._lib, self._check = _lib.load_library(), _lib.check
         self._stream_ptr = _lib.stream_ptr
         self.wait_limit_ns = int(wait_limit_ns)

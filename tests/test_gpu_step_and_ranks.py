@@ -211,6 +211,28 @@ def test_step_that_ends_in_the_all_gather(ctx):
     assert torch.equal(wl.k_pool, ref_pools[0]) and torch.equal(wl.v_pool, ref_pools[1])
 
 
+def test_step_that_ends_in_the_all_gather_on_8bit_pools():
+    """The same entry point on e4m3 pools (quantising fused append, 8-bit engine), one rank as its own peer."""
+    wl = workloads.make_decode_workload("xchg8", torch.tensor([2500, 90]), n_q_heads=8, n_kv_heads=2, head_dim=128, seed=33).to(DEV)
+    ks, vs = 0.03, 0.04
+    k8, v8 = ref.quantize_fp8_ref(wl.k_pool, ks), ref.quantize_fp8_ref(wl.v_pool, vs)
+    k8r, v8r = k8.clone(), v8.clone()
+    B, Hq, D = wl.q.shape
+    flat = torch.zeros(B * Hq * (D + 1), dtype=torch.float32, device=DEV)
+    out_view, lse_view = flat[:B * Hq * D].view(B, Hq, D), flat[B * Hq * D:].view(B, Hq)
+    xch = _SelfExchange(flat.numel())
+    lens = (wl.ctx_len + 1).contiguous()
+    o_ref, l_ref = iva_b200.paged_decode_step(wl.q, wl.k_new, wl.v_new, k8r, v8r, wl.block_table, lens, 16, return_lse=True,
+                                              out_dtype=torch.float32, check=True, k_scale=ks, v_scale=vs)
+    for step in range(2):
+        iva_b200.paged_decode_step(wl.q, wl.k_new, wl.v_new, k8, v8, wl.block_table, lens, 16, out=out_view, lse=lse_view,
+                                   out_dtype=torch.float32, check=True, k_scale=ks, v_scale=vs, exchange=(xch, flat))
+        torch.cuda.synchronize()
+        assert int(xch.status.item()) == 0 and int(xch.epoch.item()) == step + 1
+        assert torch.equal(out_view, o_ref) and torch.equal(lse_view, l_ref) and torch.equal(xch.row(step), flat)
+    assert torch.equal(k8.view(torch.uint8), k8r.view(torch.uint8)) and torch.equal(v8.view(torch.uint8), v8r.view(torch.uint8))
+
+
 def test_fp8_cache_object():
     cache = iva_b200.PagedKVCache(batch_size=2, n_heads=2, head_dim=128, device=DEV, dtype=torch.float8_e4m3fn,
                                   max_seq_len=64, k_scale=0.02, v_scale=0.02)
