@@ -237,8 +237,10 @@ int ivab_paged_decode_attn_fp8(const void* q, int64_t q_stride_b, int64_t q_stri
  *   kv_dtype: `dtype`, or IVAB_F8E4M3 with k_scale / v_scale (then the rows are quantised exactly as
  *   ivab_paged_append_fp8 does; pool strides in 1-byte elements).
  * The row is written by the CTA that reads that page (ordinary stores, ordered before its TMA reads), so the
- * pools end up bit-identical to the two-call sequence and so does the attention result.  Everything
- * else as for ivab_paged_decode_attn.
+ * pools end up bit-identical to the two-call sequence and so does the attention result.  q, k_new, v_new and
+ * ctx_len may point into page-locked host memory that is addressable from the device: the kernels then read
+ * the step's inputs in place, over the bus, with no upload in front of the step (the pools, the block table
+ * and the workspace must be device memory).  Everything else as for ivab_paged_decode_attn.
  */
 int ivab_paged_decode_step(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                            const void* k_new, const void* v_new, int64_t new_stride_t, int64_t new_stride_h,
