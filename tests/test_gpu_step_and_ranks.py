@@ -182,7 +182,8 @@ class _SelfExchange:
         return self.buf.view(torch.uint8)[(step % 2) * self.block_bytes:(step % 2 + 1) * self.block_bytes].view(torch.float32)[:self.numel]
 
 
-@pytest.mark.parametrize("ctx", [[3000, 70, 1500], [20, 5, 31], [40000]])
+@pytest.mark.parametrize("ctx", [[3000, 70, 1500], [20, 5, 31], [40000], [37 * (i % 9) + 11 * i + 1 for i in range(40)]],
+                         ids=["split", "unsplit", "one_long", "planned_batch_of_40"])
 def test_step_that_ends_in_the_all_gather(ctx):
     """``ivab_paged_decode_step_allgather``: the rows of a step are written into one block and exchanged by the
     merge kernel's last CTA (or, when no sequence can be split, by the stand-alone exchange kernel).  One rank:
