@@ -670,6 +670,15 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True, exchange="nccl"):
     kern_ms = time_region(local_only, steps, flush)      # this rank's attention kernels only
     ms_per_step = ranks.max(sum(per_step)) / steps
     attn, kern = ranks.max(statistics.mean(attn_ms), statistics.mean(kern_ms))
+    eager_ms = None
+    if hp is not None and exchange == "p2p":
+        # the same step launched eagerly (one library call; this measurement's flush keeps the host ahead of the GPU)
+        eager_step = hp.capture_local(wl.q, k_loc, v_loc, wl.block_table, lens, wl.page_size, wl.scale,
+                                      new_tokens=(k_new, v_new), graph=False)
+        for _ in range(3):
+            eager_step()
+        ranks.barrier()
+        eager_ms = ranks.max(sum(time_region(eager_step, steps, flush))) / steps
     # what the step returned (all ranks' rows on this rank): both exchange methods must give the same bits
     res = step()
     if not isinstance(res, tuple):      # one GPU: the graph replay wrote into out / lse
@@ -677,7 +686,7 @@ def measure_c5b(wl, ranks, steps, warmup, use_graph=True, exchange="nccl"):
     torch.cuda.synchronize()
     import hashlib
     digest = hashlib.sha1(b"".join(t.detach().float().cpu().contiguous().numpy().tobytes() for t in res)).hexdigest()[:16]
-    return {"ms_per_step": ms_per_step, "result_digest": digest, "attention_incl_allgather_ms": attn, "attention_kernels_ms": kern,
+    return {"ms_per_step": ms_per_step, "result_digest": digest, "ms_per_step_eager_launch": eager_ms, "attention_incl_allgather_ms": attn, "attention_kernels_ms": kern,
             "value": 1.0 / (ms_per_step * 1e-3), "unit": "decode tok/s (one sequence)",
             "roofline_local_kernels": roofline_record(nbytes, kern, "this rank's plan + decode + merge kernels"),
             "kv_heads_per_rank": wl.n_kv_heads // world, "collective": None if world == 1 else (
@@ -791,7 +800,7 @@ def run_gpu(args):
             try:
                 p2p = measure_c5b(wl, ranks, sub_steps, args.warmup, use_graph=not args.no_graph, exchange="p2p")
                 result["c5b"]["peer_memory_exchange"] = {"same_bits_as_nccl": p2p["result_digest"] == result["c5b"]["result_digest"]}
-                result["c5b"]["peer_memory_exchange"].update({k: p2p[k] for k in ("ms_per_step", "attention_incl_allgather_ms",
+                result["c5b"]["peer_memory_exchange"].update({k: p2p[k] for k in ("ms_per_step", "ms_per_step_eager_launch", "attention_incl_allgather_ms",
                                                                                  "value", "collective")})
             except Exception as e:                      # (symmetric memory not available on this system)
                 result["c5b"]["peer_memory_exchange"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}

@@ -228,13 +228,18 @@ class HeadParallelDecoder:
     def capture_local(self, q: torch.Tensor, k_pool_local: torch.Tensor, v_pool_local: torch.Tensor,
                       block_table: torch.Tensor, ctx_len: torch.Tensor, page_size: int = 16,
                       scale: Optional[float] = None, before: Optional[Callable[[], None]] = None,
-                      new_tokens: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+                      new_tokens: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, graph: bool = True):
         """Record this rank's share of a step -- the attention kernels, which store their fp32 result
         straight into the block the collective sends -- in a CUDA graph, and return ``step()``.
         ``new_tokens=(k_new, v_new)`` (this rank's KV heads, ``[B, H_kv/world, D]``) makes it the fused decode
         step: the new token of every sequence is appended by the attention launch itself (``ctx_len`` then
         includes it).  ``before`` (optional) is called first inside the recording, for anything else the step
         has to do on this stream.
+
+        ``graph=False`` prepares the same step without recording it: ``step()`` then launches the kernels eagerly
+        on the current stream (with ``exchange="p2p"`` that is one library call per step).  Programmatic dependent
+        launches then overlap the step's start with whatever runs before it in the stream, which a graph launch
+        does not; the price is the host time of the call.
 
         At 131072 tokens over 8 GPUs each rank reads 67 MB per step (about 10 microseconds of HBM
         time), so the step is bound by launch latency.  The recording reads the query from ``step.q`` (this
@@ -280,9 +285,11 @@ class HeadParallelDecoder:
         with torch.cuda.stream(side):
             local()                      # one-time set-up of the kernels happens outside the capture
         side.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            local()
+        recorded = None
+        if graph:
+            recorded = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(recorded, stream=side):
+                local()
 
         if peer is not None:
             # every rank ran the eager pass and the capture does not execute anything: one exchange so far
@@ -292,7 +299,10 @@ class HeadParallelDecoder:
         # Everything the recording points at must outlive it: the local query buffer made above is owned by
         # nobody else, so the returned function holds it (with the capture stream, the scratch and the block).
         def step(_keep=(side, extra, q, flat, local)):
-            graph.replay()
+            if recorded is not None:
+                recorded.replay()
+            else:
+                local()
             if peer is not None:
                 rows = peer.rows(peer._steps)
                 peer._steps += 1

@@ -345,6 +345,13 @@ def _p2p_worker(rank, world, port, ret):
             torch.cuda.synchronize()
             checks.append((f"graph replay {i} out", bool(torch.equal(g_out.to(single.dtype), single))))
             checks.append((f"graph replay {i} lse", bool(torch.equal(g_lse, single_lse))))
+        prepared = dec.capture_local(d.q, kl, vl, d.block_table, d.ctx_len, 16, wl.scale, graph=False)
+        for i in range(3):                                   # the same step launched eagerly (one library call)
+            e_out, e_lse = prepared()
+            torch.cuda.synchronize()
+            checks.append((f"eager step {i} out", bool(torch.equal(e_out.to(single.dtype), single))))
+            checks.append((f"eager step {i} lse", bool(torch.equal(e_lse, single_lse))))
+        checks.append(("status at the end", int(dec._peer.status.item()) == 0))
         ret[rank] = checks
     finally:
         dist.destroy_process_group()
