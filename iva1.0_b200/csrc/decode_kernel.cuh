@@ -860,8 +860,8 @@ template <typename T, int D, int G, int ENG, typename TKV = T>
 int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStream_t st) {
     using Eng = typename EngineSelect<ENG, T, TKV, D, G>::type;
     using C = SmemLayout<Eng::SCRATCH_PER_WARP, D, G>;
-    constexpr int kCtas = Eng::CTAS_PER_SM;
     DecodeParams p = p0;
+    constexpr int kCtas = Eng::CTAS_PER_SM;
     int dev = 0;
     if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
     int max_optin = 0;
@@ -902,10 +902,11 @@ int launch_decode(const DecodeParams& p0, const TensorMaps& tm, int B, cudaStrea
         p.direct_dynamic = direct_dynamic_enabled() && p.max_pages > p.direct_min_chunk ? 1 : 0;
         // (8-bit pools stream a page in half the time, so the fixed work per item weighs more: fewer, longer items
         //  and a threshold in bytes, not pages -- IVAB_DIRECT_BIG_IPS / IVAB_DIRECT_BIG_KB override both for experiments)
-        const int big_ips = env_int("IVAB_DIRECT_BIG_IPS", sizeof(TKV) == 1 ? kItemsPerSlot * 3 / 4 : kItemsPerSlot, 1, kItemsPerSlot);
+        static const int big_ips = env_int("IVAB_DIRECT_BIG_IPS", sizeof(TKV) == 1 ? kItemsPerSlot * 3 / 4 : kItemsPerSlot, 1, kItemsPerSlot);
         p.direct_big_target_items = p.direct_dynamic ? grid * big_ips : 0;
         const long long page_bytes = 2LL * kPage * D * (long long)sizeof(TKV);   // K and V
-        const long long big_pages = (long long)env_int("IVAB_DIRECT_BIG_KB", kDirectBigKB, 1, 1 << 20) * 1024 / page_bytes;
+        static const int big_kb = env_int("IVAB_DIRECT_BIG_KB", kDirectBigKB, 1, 1 << 20);
+        const long long big_pages = (long long)big_kb * 1024 / page_bytes;
         p.direct_big_pages = (int)(big_pages < 1 ? 1 : big_pages);
     }
     // Both launches below are programmatic dependents of the kernel before them (plan -> attention
