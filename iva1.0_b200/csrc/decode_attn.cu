@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const int32_t* __res
     if (tid == 0) {
         PROF_STAMP_SET(ws.header, 0)
         for (int i = 2; i < 8; ++i) PROF_STAMP_PTR(ws.header)[i] = (i == 5 || i == 7) ? 0ull : ~0ull;
-        *reinterpret_cast<unsigned long long*>(ws.header + 8) = ~0ull;
+        *reinterpret_cast<unsigned long long*>(ws.header + 14) = ~0ull;   // (words 8..12 belong to the plan-free counter and the merge count)
     }
 #endif
     if (tid == 0) { s_total_pages = 0; s_bad = 0; s_ragged = 0; s_split = 0; s_big = 0; }

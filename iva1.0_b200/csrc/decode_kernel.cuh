@@ -524,7 +524,7 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
         atomicMax(p.ws.prof_cta + blockIdx.x * 4 + 2, (unsigned long long)globaltimer_ns());
         if (warp == 0) { p.ws.prof_cta[blockIdx.x * 4 + 0] = prof_cta_start; p.ws.prof_cta[blockIdx.x * 4 + 3] = (unsigned long long)consumed; }
         PROF_STAMP_MAX(p.ws.header, 5, globaltimer_ns())
-        atomicMin(reinterpret_cast<unsigned long long*>(p.ws.header + 8), (unsigned long long)globaltimer_ns());   // first warp done
+        atomicMin(reinterpret_cast<unsigned long long*>(p.ws.header + 14), (unsigned long long)globaltimer_ns());   // first warp done
     }
 #endif
     leave();
