@@ -445,7 +445,10 @@ decode_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ Te
             if (!mbar_wait_bounded(bar_full(stage), (taken / spw) & 1, abort_flag, limit)) { ok = false; break; }
             PROF_MARK(2)   // wait for page data
 #ifdef IVAB_PROFILE
-            if (taken == 0 && lane == 0) PROF_STAMP_MIN(p.ws.header, 4, globaltimer_ns())
+            if (taken == 0 && lane == 0) {
+                PROF_STAMP_MIN(p.ws.header, 4, globaltimer_ns())
+                atomicCAS(p.ws.prof_cta + blockIdx.x * 4 + 1, 0ull, (unsigned long long)globaltimer_ns());   // this CTA's first page
+            }
 #endif
             // Token t of this page is key 16*pg + t.  It counts if it lies below L and outside the
             // hole [sink, begin) between the sink keys and the window; only the last page of the
