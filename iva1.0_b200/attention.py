@@ -273,6 +273,30 @@ def _dense_as_pool(k: torch.Tensor, v: torch.Tensor):
     return k, v, bt.contiguous(), n_pages, Lp * D, _PAGE * D
 
 
+def _pack_queries(q: torch.Tensor, Hkv: int):
+    """Queries of one batch row that see the same keys can share one pass over them: ``q [B,S,H_q,D]`` becomes
+    ``[B*ceil(S/Sc), H_kv*Sc*G, D]`` -- pseudo-sequences of ``Sc = 8 // G`` queries whose ``Sc*G`` rows per KV head
+    the kernels treat as one query-head group (K/V pages are read once per group).  Returns the packed tensor,
+    ``Sc`` and the number of pseudo-sequences per row; ``Sc == 1`` means nothing is gained."""
+    B, S, Hq, D = q.shape
+    G = Hq // Hkv
+    Sc = max(1, min(8 // G if G <= 8 else 1, S))
+    nS = (S + Sc - 1) // Sc
+    if Sc == 1:
+        return q.reshape(B * S, Hq, D), 1, S
+    if nS * Sc != S:
+        q = torch.cat([q, q.new_zeros(B, nS * Sc - S, Hq, D)], dim=1)      # padding rows, dropped again by _unpack_rows
+    q2 = q.view(B, nS, Sc, Hkv, G, D).permute(0, 1, 3, 2, 4, 5).reshape(B * nS, Hkv * Sc * G, D)
+    return q2, Sc, nS
+
+
+def _unpack_rows(o2: torch.Tensor, B: int, S: int, Hkv: int, G: int, Sc: int, nS: int) -> torch.Tensor:
+    """Inverse of ``_pack_queries`` for results ``[B*nS, H_kv*Sc*G, ...]`` -> ``[B, S, H_q, ...]``."""
+    tail = o2.shape[2:]
+    o = o2.view(B, nS, Hkv, Sc, G, *tail).transpose(2, 3).reshape(B, nS * Sc, Hkv * G, *tail)
+    return o[:, :S]
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, dropout_prob: float = 0.0,
               training: bool = True, *, ctx_len: Optional[torch.Tensor] = None,
               ctx_begin: Optional[torch.Tensor] = None, return_lse: bool = False,
@@ -299,6 +323,22 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, d
     if Bk != B or Dk != D or Hq % Hkv:
         raise ValueError("q and k/v shapes do not match")
     kd, vd, bt, n_pages, sh, sp = _dense_as_pool(k.to(q.dtype), v.to(q.dtype))
+    shared = S > 1 and (ctx_len is None or ctx_len.numel() == B) and (ctx_begin is None or ctx_begin.numel() == B)
+    if shared:
+        # every query of a row sees the same keys: up to eight (query, head) rows per KV head share one pass over them
+        q2, Sc, nS = _pack_queries(q.permute(0, 2, 1, 3), Hkv)
+        if Sc > 1:
+            cl = (torch.full((B,), L, dtype=torch.int32, device=q.device) if ctx_len is None
+                  else ctx_len.to(device=q.device, dtype=torch.int32).reshape(B)).repeat_interleave(nS).contiguous()
+            cb = None if ctx_begin is None else ctx_begin.to(device=q.device, dtype=torch.int32).reshape(B).repeat_interleave(nS).contiguous()
+            res = _decode(q2.contiguous(), kd, vd, Hkv, n_pages, sh, sp, bt.repeat_interleave(nS, dim=0), cl, _PAGE, scale,
+                          None, None, return_lse, None, False, cb, out_dtype=out_dtype)
+            o2, lse = res if return_lse else (res, None)
+            G = Hq // Hkv
+            o = _unpack_rows(o2, B, S, Hkv, G, Sc, nS).permute(0, 2, 1, 3)
+            if return_lse:
+                return o, _unpack_rows(lse, B, S, Hkv, G, Sc, nS).permute(0, 2, 1)
+            return o
     # one pseudo-sequence per (batch row, query position), all sharing the row's block table
     q2 = q.permute(0, 2, 1, 3).reshape(B * S, Hq, D)
     bt2 = bt.repeat_interleave(S, dim=0) if S > 1 else bt
@@ -405,6 +445,14 @@ class AttentionB200(nn.Module):
                 o = paged_decode_step(q.reshape(B, H, D), k.reshape(B, H, D), v.reshape(B, H, D), kv_cache.k_pool,
                                       kv_cache.v_pool, bt, cl, kv_cache.page_size, self.scale, ctx_begin=cb,
                                       sink_tokens=sink, **scales)
+            elif not self.causal and sliding_window is None and 8 // max(1, H // kv_cache.n_heads) > 1:
+                # every query of the chunk sees the whole cache (the reference's working configuration): up to eight
+                # (query, head) rows per KV head share one pass over the pages
+                q2, Sc, nS = _pack_queries(q, kv_cache.n_heads)
+                o2 = paged_decode_attention(q2.contiguous(), kv_cache.k_pool, kv_cache.v_pool, bt.repeat_interleave(nS, dim=0),
+                                            cl.repeat_interleave(nS).contiguous(), kv_cache.page_size, self.scale,
+                                            k_scale=kv_cache.k_scale, v_scale=kv_cache.v_scale)
+                o = _unpack_rows(o2, B, S, kv_cache.n_heads, H // kv_cache.n_heads, Sc, nS)
             else:
                 q2 = q.reshape(B * S, H, D)
                 bt2 = bt.repeat_interleave(S, dim=0)
@@ -420,7 +468,8 @@ class AttentionB200(nn.Module):
                     cb2 = (pos + 1 - int(sliding_window)).clamp_(min=0).reshape(-1).contiguous()
                     cl2 = torch.minimum(cl2.view(B, S), pos + 1).reshape(-1) if not self.causal else cl2
                 o = paged_decode_attention(q2, kv_cache.k_pool, kv_cache.v_pool, bt2, cl2.contiguous(),
-                                           kv_cache.page_size, self.scale, ctx_begin=cb2)
+                                           kv_cache.page_size, self.scale, ctx_begin=cb2,
+                                           k_scale=kv_cache.k_scale, v_scale=kv_cache.v_scale)
             new_cache = kv_cache
             o = o.reshape(B, S, dm)
         else:

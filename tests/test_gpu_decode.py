@@ -258,6 +258,33 @@ def test_attention_operator_multi_query_and_errors():
         iva_b200.attention(q.to(DEV).requires_grad_(), k.to(DEV), v.to(DEV), 0.125)
 
 
+@pytest.mark.parametrize("dtype,Hq,Hkv,S", [(torch.bfloat16, 8, 8, 8), (torch.bfloat16, 8, 8, 19), (torch.bfloat16, 8, 4, 7),
+                                            (torch.float16, 8, 2, 5), (torch.float32, 4, 4, 3), (torch.bfloat16, 12, 4, 6),
+                                            (torch.bfloat16, 16, 2, 4)])
+def test_queries_that_share_their_keys_are_packed(dtype, Hq, Hkv, S):
+    """Several query positions per row that all see the same keys (the reference module's chunk with
+    causal=False): up to eight (query, head) rows per KV head go through the kernels as one head group, so the
+    keys are read once per group instead of once per query.  Same results as the checker, with and without a
+    per-row key limit; the last case (eight heads per KV head) has nothing to pack and takes the old route."""
+    g = torch.Generator().manual_seed(100 * S + Hq)
+    B, D, L = 3, 128 if dtype != torch.float32 else 64, 333
+    q = torch.randn(B, Hq, S, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, L, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, L, D, generator=g).to(dtype)
+    scale = 1 / math.sqrt(D)
+    rep = Hq // Hkv
+    kx, vx = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+    want, lse_want = ref.attention_math_ref(q, kx, vx, scale)
+    check_decode(lambda od: iva_b200.attention(q.to(DEV), k.to(DEV), v.to(DEV), scale, 0.0, False, return_lse=True,
+                                               out_dtype=od), want, lse_want, dtype)
+    lim = torch.tensor([L, 17, 200], dtype=torch.int32)
+    for b in range(B):
+        w_b, l_b = ref.attention_math_ref(q[b:b + 1], kx[b:b + 1, :, :int(lim[b])], vx[b:b + 1, :, :int(lim[b])], scale)
+        want[b], lse_want[b] = w_b[0], l_b[0]
+    check_decode(lambda od: iva_b200.attention(q.to(DEV), k.to(DEV), v.to(DEV), scale, 0.0, False, return_lse=True,
+                                               out_dtype=od, ctx_len=lim.to(DEV)), want, lse_want, dtype)
+
+
 def test_module_matches_attention_torch_golden(golden, golden_inputs):
     """AttentionB200 with the reference module's weights and a dense reference-style cache."""
     B, H, hd, L, w, x, ck, cv = golden_inputs.module_inputs()
